@@ -1,0 +1,158 @@
+/*
+ * svdq_b200 - C ABI of the B200 (sm_100a) SVDQuant W4A4 linear hot path.
+ *
+ * Plain C: raw device pointers, sizes and flags; no C++ or torch types.  Every
+ * entry point returns 0 on success or a negative SVDQ_ERR_* code, never throws,
+ * aborts or traps; svdq_last_error_string() gives the reason (thread local).
+ * Launches are asynchronous on the given stream (a cudaStream_t passed as
+ * void*), on the current CUDA device.  Nothing is allocated by the library: all
+ * buffers, including scratch, are caller owned.
+ *
+ * The two compute entry points replace the reference's
+ *   nunchaku::ops::quantize_w4a4_act_fuse_lora   (nunchaku/csrc/ops.h:82-110,
+ *       src/kernels/zgemm/zgemm.h:36-43, gemm_w4a4.cu:113-125) and
+ *   nunchaku::ops::gemm_w4a4                     (nunchaku/csrc/ops.h:10-80,
+ *       src/kernels/zgemm/zgemm.h:8-34, gemm_w4a4.cu:34-105).
+ */
+#ifndef SVDQ_B200_H
+#define SVDQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SVDQ_OK 0
+#define SVDQ_ERR_INVALID_ARGUMENT (-1) /* null / misaligned pointer, bad shape          */
+#define SVDQ_ERR_UNSUPPORTED (-2)      /* valid in the reference, not built here (yet)   */
+#define SVDQ_ERR_UNSUPPORTED_ARCH (-3) /* current device is not compute capability 10.x  */
+#define SVDQ_ERR_CUDA (-4)             /* a CUDA runtime / driver call failed            */
+#define SVDQ_ERR_TIMEOUT (-5)          /* a bounded device-side wait ran out (see status) */
+
+/* Memory order of the activation-side tensors (codes, scales, low-rank activations). */
+#define SVDQ_LAYOUT_NATIVE 0    /* row-major codes, 512-byte scale atoms, row-major fp32 low-rank */
+#define SVDQ_LAYOUT_REFERENCE 1 /* the reference's mma.sync fragment order (gemm_base.cuh:265-340) */
+
+#define SVDQ_ACT_NONE 0
+#define SVDQ_ACT_SILU 1 /* fuse_silu  (gemm_w4a4_launch_impl.cuh:407-420) */
+#define SVDQ_ACT_GELU 2 /* GELU before next-layer requantisation (launch_impl.cuh:282-309) */
+
+/*
+ * Activation quantiser fused with the LoRA down projection.
+ * Replaces kernels::quantize_w4a4_act_fuse_lora (zgemm.h:36-43;
+ * GEMM_W4A4_Launch::quantize_w4a4_act_fuse_lora, gemm_w4a4_launch_impl.cuh:451-521).
+ * `smooth` and `lora_down` are taken in the reference's packed order, exactly as
+ * stored in SVDQW4A4Linear.smooth_factor / .proj_down (nunchaku/models/linear.py:56-64).
+ */
+typedef struct svdq_quantize_args {
+    const void* input;     /* bf16 [M, K] row-major ([M, 2K] when fuse_glu)                   */
+    void* codes;           /* uint8 [M_pad, K/2]                                              */
+    void* scales;          /* NVFP4: e4m3 bytes [K/16, M_pad]; INT4: bf16 [K/64, M_pad]      */
+    float* lora_act;       /* fp32 [M_pad, R]; fully written, no zero-fill needed             */
+    const void* smooth;    /* bf16 [K], reference-packed                                      */
+    const void* lora_down; /* bf16 [K, R], reference-packed                                   */
+    int32_t M;             /* valid rows                                                      */
+    int32_t M_pad;         /* multiple of 256 (nunchaku/ops/quantize.py:40)                   */
+    int32_t K;             /* multiple of 128                                                 */
+    int32_t R;             /* multiple of 16, 16..128                                         */
+    int32_t fp4;           /* 1: NVFP4 group 16, 0: INT4 group 64                             */
+    int32_t fuse_glu;      /* 1: input holds (value, gate) pairs, quantise value*silu(gate)   */
+    int32_t layout;        /* SVDQ_LAYOUT_* of codes / scales / lora_act                      */
+} svdq_quantize_args;
+
+int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* stream);
+
+/*
+ * One-time re-tiling of a layer's weights from the reference's packed order
+ * (NunchakuWeightPacker, nunchaku/lora/flux/packer.py:187-398) into the order
+ * the sm_100a GEMM streams with TMA.  Replaces nothing in the reference (its
+ * kernels read the packed order directly); it is what lets the checkpoint
+ * format stay byte-identical.  Output buffers are caller allocated with the
+ * sizes svdq_w4a4_prepared_bytes() reports.
+ */
+typedef struct svdq_prepared_weights {
+    void* wgt;        /* uint8 [N, K/2] row-major codes                                    */
+    void* wscales;    /* NVFP4: 512-byte e4m3 atoms [N/128][K/64]; INT4: fp32 [K/64, N]    */
+    float* lora_up;   /* fp32 [N, R32] (R32 = R rounded up to 32), pre-divided by col_scale */
+    float* col_scale; /* fp32 [N] = alpha * wcscales                                       */
+    float* col_bias;  /* fp32 [N]                                                          */
+} svdq_prepared_weights;
+
+typedef struct svdq_weights_args {
+    const void* qweight;  /* int8 [N, K/2], reference-packed (SVDQW4A4Linear.qweight)       */
+    const void* wscales;  /* reference-packed: e4m3 [K/16, N] or bf16 [K/64, N]             */
+    const void* lora_up;  /* bf16 [N, R] reference-packed, may be NULL when R == 0          */
+    const void* bias;     /* bf16 [N] reference-packed, may be NULL                         */
+    const void* wcscales; /* bf16 [N] reference-packed, may be NULL (NVFP4 only)            */
+    const float* lora_scales; /* host array, one per 16 ranks, may be NULL (all 1.0)        */
+    float alpha;          /* NVFP4 per-tensor weight scale (wtscale); must be 1 for INT4    */
+    int32_t N, K, R, fp4;
+} svdq_weights_args;
+
+/* bytes[0..4] = sizes of wgt, wscales, lora_up, col_scale, col_bias */
+int svdq_w4a4_prepared_bytes(int32_t N, int32_t K, int32_t R, int32_t fp4, size_t bytes[5]);
+int svdq_w4a4_prepare_weights(const svdq_weights_args* args, const svdq_prepared_weights* out, void* stream);
+
+/*
+ * 4-bit GEMM with the fused epilogue
+ *   acc*alpha*wcscale + bias -> + lora_act_in @ lora_up^T -> [SiLU|GELU] ->
+ *   { store bf16 `out` } and/or { next layer: LoRA-down, (+shift)/smooth, group-quantise }.
+ * Replaces kernels::gemm_w4a4 (zgemm.h:8-34; GEMM_W4A4_Launch::gemm_w4a4,
+ * gemm_w4a4_launch_impl.cuh:7-424).
+ */
+typedef struct svdq_gemm_args {
+    const void* act;          /* uint8 [M_pad, K/2]                                          */
+    const void* ascales;      /* e4m3 [K/16, M_pad] or bf16 [K/64, M_pad]                    */
+    const float* lora_act_in; /* fp32 [M_pad, R] or NULL                                     */
+    svdq_prepared_weights w;  /* from svdq_w4a4_prepare_weights                              */
+    void* out;                /* bf16 [M, N] or NULL                                         */
+    /* next-layer requantisation (all NULL when unused) */
+    void* qout;               /* uint8 [M_pad, N/2]                                          */
+    void* oscales;            /* e4m3 [N/16, M_pad] or bf16 [N/64, M_pad]                    */
+    float* lora_act_out;      /* fp32 [M_pad, R_next]                                        */
+    const void* next_smooth;    /* bf16 [N] reference-packed                                 */
+    const void* next_lora_down; /* bf16 [N, R_next] reference-packed                         */
+    void* workspace;          /* scratch, svdq_gemm_w4a4_workspace_bytes() bytes, 256-aligned */
+    size_t workspace_bytes;
+    int32_t M, M_pad, N, K, R, R_next;
+    int32_t fp4;              /* precision of act / weights                                  */
+    int32_t act_unsigned;     /* INT4 only: activations are u4 codes                         */
+    int32_t activation;       /* SVDQ_ACT_*                                                  */
+    int32_t act_layout;       /* layout of act / ascales / lora_act_in                       */
+    int32_t out_layout;       /* layout of qout / oscales / lora_act_out                     */
+    int32_t next_fp4;         /* precision of the requantised output                         */
+} svdq_gemm_args;
+
+int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes);
+int svdq_gemm_w4a4(const svdq_gemm_args* args, void* stream);
+
+/*
+ * Activation-side layout conversion (codes, scales, low-rank activations) between
+ * SVDQ_LAYOUT_REFERENCE and SVDQ_LAYOUT_NATIVE; no counterpart in the reference,
+ * where only one order exists.  NULL pairs are skipped.
+ */
+typedef struct svdq_relayout_args {
+    const void* codes_in;  void* codes_out;   /* uint8 [M_pad, K/2]   */
+    const void* scales_in; void* scales_out;  /* see svdq_quantize_args */
+    const float* lora_in;  float* lora_out;   /* fp32 [M_pad, R]      */
+    int32_t M_pad, K, R, fp4;
+    int32_t from_layout, to_layout;
+} svdq_relayout_args;
+int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream);
+
+/*
+ * Device-side status word of the current device: 0, or the SVDQ_ERR_TIMEOUT code a
+ * kernel recorded when one of its bounded waits ran out.  Synchronises the device.
+ * `detail` (may be NULL) receives a kernel-specific location code.  Reading clears it.
+ */
+int svdq_device_status(int32_t* status, int32_t* detail);
+
+const char* svdq_last_error_string(void);
+int svdq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVDQ_B200_H */

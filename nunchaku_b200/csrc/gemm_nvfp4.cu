@@ -1,0 +1,342 @@
+// NVFP4 W4A4 GEMM with the fused SVDQuant epilogue, sm_100a.
+//
+// What it computes (reference: gemm_w4a4_fp4_kernel, src/kernels/zgemm/gemm_w4a4.cuh:273-405,
+// epilogue chain gemm_w4a4_launch_impl.cuh:172-420):
+//   D[m, n]   = sum_k a[m,k]*sa[m,k/16] * w[n,k]*sw[n,k/16]           E2M1 codes, UE4M3 group-16 scales
+//             + sum_r lora_act[m,r] * Wu'[n,r]                          low-rank branch, same accumulator
+//   out[m, n] = act( D[m,n] * col_scale[n] + col_bias[n] )             col_scale = alpha * wcscale
+// (Wu' is the LoRA-up weight pre-divided by col_scale, so both branches share one fp32 accumulator.)
+//
+// How it maps to a B200 SM.  One persistent CTA per SM walks 128 x 192 output tiles.
+//   warp 0      producer: TMA loads of 128B-swizzled operand tiles (128 rows x 256 codes of A, 192 x 256 of
+//               B per stage) and bulk copies of the 512-byte scale-factor atoms, 4-stage mbarrier ring
+//   warp 1      MMA issuer: tcgen05.cp moves the scale atoms into TMEM, then 4 x
+//               tcgen05.mma.kind::mxf4nvf4.block_scale (M128 N192 K64) per stage; the low-rank branch is
+//               fed through the same ring as fp32 tiles and issued as kind::tf32 into the same TMEM
+//               accumulator; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 stores
+// TMEM: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
+// plus 16 + 32 columns of scale factors = 432 of 512 columns.
+#include <cuda_bf16.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace svdq {
+
+constexpr int G_BM = 128;
+constexpr int G_BN = 192;
+constexpr int G_BK = 256;                       // codes per stage = 128 bytes per row
+constexpr int G_STAGES = 4;
+constexpr int G_A_BYTES = G_BM * 128;           // 16 KB
+constexpr int G_B_BYTES = G_BN * 128;           // 24 KB
+constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
+constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
+constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 47104 = 46 * 1024
+constexpr int G_THREADS = 6 * 32;
+constexpr int G_TMEM_COLS = 512;
+constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
+constexpr int G_TM_SFA = 2 * G_BN;              // 384
+constexpr int G_TM_SFB = G_TM_SFA + 16;         // 400
+constexpr size_t G_SMEM_BYTES = 1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + 256;
+
+struct GemmParams {
+    const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
+    const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
+    __nv_bfloat16* out;       // [M, N]
+    const float* col_scale;   // [N]
+    const float* col_bias;    // [N]
+    int* status;
+    int M, M_pad, N, K;
+    int lora_chunks;          // number of 32-rank chunks of the low-rank branch (0 = none)
+    int tiles_m, tiles_n;
+    int activation;
+};
+
+struct GemmShared {
+    uint64_t full[G_STAGES];
+    uint64_t empty[G_STAGES];
+    uint64_t tfull[2];
+    uint64_t tempty[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (sh->abort_flag) return false;
+        if (globaltimer_ns() - t0 > 2000000000ull) {
+            sh->abort_flag = 1;
+            atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+            atomicExch(&status[1], where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ float apply_act(float v, int activation) {
+    if (activation == SVDQ_ACT_SILU) {
+        return v / (1.0f + __expf(-v));
+    } else if (activation == SVDQ_ACT_GELU) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.79788456f * (v + 0.044715f * v * v * v)));
+        return v * (0.5f + 0.5f * t);
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
+                  const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    GemmShared* sh = reinterpret_cast<GemmShared*>(smem + G_STAGES * G_STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int KB = p.K / 64;                         // 64-code blocks along K
+    const int kstages = (KB + 3) / 4;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int NB = p.N / 128;                        // weight scale atoms along N
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < G_STAGES; ++s) {
+            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sh->tfull[i], 1);
+            mbar_init(&sh->tempty[i], 4);
+        }
+        mbar_init(&sh->drain, 1);
+        sh->abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+        if (p.lora_chunks) {
+            prefetch_tmap(&tm_la);
+            prefetch_tmap(&tm_lu);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(&sh->tmem_base, G_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * G_BM;
+                const int n0 = (tile / p.tiles_m) * G_BN;
+                const int atom0 = n0 >> 7;
+                for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+                    const int s = it % G_STAGES;
+                    if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = smem + s * G_STAGE_BYTES;
+                    if (ks < kstages) {
+                        const int nkb = min(4, KB - ks * 4);
+                        const int natoms = min(2, NB - atom0);
+                        mbar_arrive_expect_tx(&sh->full[s], G_A_BYTES + G_B_BYTES + nkb * 512 * (1 + natoms));
+                        tma_load_2d(st, &tm_a, &sh->full[s], ks * 128, m0);
+                        tma_load_2d(st + G_A_BYTES, &tm_b, &sh->full[s], ks * 128, n0);
+                        bulk_load(st + G_A_BYTES + G_B_BYTES, p.sfa + (static_cast<size_t>(m0 >> 7) * KB + ks * 4) * 512,
+                                  nkb * 512, &sh->full[s]);
+                        for (int a = 0; a < natoms; ++a)
+                            bulk_load(st + G_A_BYTES + G_B_BYTES + G_SFA_BYTES + a * 2048,
+                                      p.sfb + (static_cast<size_t>(atom0 + a) * KB + ks * 4) * 512, nkb * 512, &sh->full[s]);
+                    } else {
+                        const int c = ks - kstages;
+                        mbar_arrive_expect_tx(&sh->full[s], G_A_BYTES + G_B_BYTES);
+                        tma_load_2d(st, &tm_la, &sh->full[s], c * 32, m0);
+                        tma_load_2d(st + G_A_BYTES, &tm_lu, &sh->full[s], c * 32, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
+            constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
+                const int n0 = (tile / p.tiles_m) * G_BN;
+                const uint32_t as = lt & 1;
+                if (!wait_or_abort(&sh->tempty[as], ((lt >> 1) & 1) ^ 1, sh, p.status, 20)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem + as * G_TM_ACC1;
+                const uint32_t sfb_off = (n0 & 127) ? 2u : 0u;   // tile starts in the middle of a 128-row atom
+                uint32_t accumulate = 0;
+                for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+                    const int s = it % G_STAGES;
+                    if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
+                    if (ks < kstages) {
+                        const int nkb = min(4, KB - ks * 4);
+                        const uint32_t sfa_s = sa + G_A_BYTES + G_B_BYTES;
+                        const uint32_t sfb_s = sfa_s + G_SFA_BYTES;
+                        for (int j = 0; j < nkb; ++j) {
+                            tc_cp_32x128b_warpx4(tmem + G_TM_SFA + 4 * j, smem_desc_sf(sfa_s + j * 512));
+                            tc_cp_32x128b_warpx4(tmem + G_TM_SFB + 8 * j, smem_desc_sf(sfb_s + j * 512));
+                            tc_cp_32x128b_warpx4(tmem + G_TM_SFB + 8 * j + 4, smem_desc_sf(sfb_s + 2048 + j * 512));
+                        }
+                        for (int j = 0; j < nkb; ++j) {
+                            tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, tmem + G_TM_SFA + 4 * j,
+                                         tmem + G_TM_SFB + 8 * j + sfb_off, accumulate);
+                            accumulate = 1;
+                        }
+                    } else {
+                        for (int j = 0; j < 4; ++j) {
+                            tc_mma_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, accumulate);
+                            accumulate = 1;
+                        }
+                    }
+                    tc_commit(&sh->empty[s]);   // stage is free once these MMAs have read it
+                }
+                if (ok) tc_commit(&sh->tfull[as]);  // accumulator complete
+            }
+            if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
+                tc_commit(&sh->drain);
+                mbar_wait(&sh->drain, 0, 200000000ull);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lane quadrant this warp may read
+        uint32_t lt = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
+            const int m0 = (tile % p.tiles_m) * G_BM;
+            const int n0 = (tile / p.tiles_m) * G_BN;
+            const uint32_t as = lt & 1;
+            if (!wait_or_abort(&sh->tfull[as], (lt >> 1) & 1, sh, p.status, 30)) break;
+            tc_fence_after_sync();
+            const int m = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
+            __nv_bfloat16* orow = p.out + static_cast<size_t>(m) * p.N + n0;
+#pragma unroll 1
+            for (int c = 0; c < G_BN / 32; ++c) {
+                const int n = n0 + c * 32;
+                if (n >= p.N) break;
+                uint32_t r[32];
+                tc_ld_32x32b_x32(taddr + c * 32, r);
+                tc_wait_ld();
+                const float4* cs = reinterpret_cast<const float4*>(p.col_scale + n);
+                const float4* cb = reinterpret_cast<const float4*>(p.col_bias + n);
+                uint32_t o[16];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 s4 = __ldg(cs + i);
+                    const float4 b4 = __ldg(cb + i);
+                    const float v0 = apply_act(fmaf(__uint_as_float(r[4 * i + 0]), s4.x, b4.x), p.activation);
+                    const float v1 = apply_act(fmaf(__uint_as_float(r[4 * i + 1]), s4.y, b4.y), p.activation);
+                    const float v2 = apply_act(fmaf(__uint_as_float(r[4 * i + 2]), s4.z, b4.z), p.activation);
+                    const float v3 = apply_act(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w), p.activation);
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
+                    __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
+                    o[2 * i] = *reinterpret_cast<uint32_t*>(&p0);
+                    o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+                }
+                if (m < p.M) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->tempty[as]);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, G_TMEM_COLS);
+    }
+}
+
+int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
+    SVDQ_CHECK_ARG(a->out != nullptr, "gemm(nvfp4): `out` is required (next-layer requantisation is not built yet)");
+    if (a->qout || a->oscales || a->lora_act_out)
+        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): fused next-layer requantisation is not built yet");
+    SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): activations must be in SVDQ_LAYOUT_NATIVE "
+                                                         "(convert with svdq_w4a4_relayout_act)");
+    SVDQ_CHECK_ARG(!a->act_unsigned, "gemm(nvfp4): act_unsigned is INT4 only (gemm_w4a4_launch_impl.cuh:127)");
+    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
+
+    int dev = 0, sms = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+    GemmParams p = {};
+    p.sfa = static_cast<const uint8_t*>(a->ascales);
+    p.sfb = static_cast<const uint8_t*>(a->w.wscales);
+    p.out = static_cast<__nv_bfloat16*>(a->out);
+    p.col_scale = a->w.col_scale;
+    p.col_bias = a->w.col_bias;
+    p.M = a->M;
+    p.M_pad = a->M_pad;
+    p.N = a->N;
+    p.K = a->K;
+    p.lora_chunks = (a->R + 31) / 32;
+    p.tiles_m = (a->M + G_BM - 1) / G_BM;
+    p.tiles_n = (a->N + G_BN - 1) / G_BN;
+    p.activation = a->activation;
+    if (int rc = status_words(&p.status)) return rc;
+
+    CUtensorMap tm_a, tm_b, tm_la, tm_lu;
+    if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 128, G_BM)) return rc;
+    if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->N, a->K / 2, 128, G_BN)) return rc;
+    if (a->R > 0) {
+        const int R32 = (a->R + 31) / 32 * 32;
+        if (int rc = make_tmap_2d(&tm_la, a->lora_act_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
+                                  static_cast<uint64_t>(a->R) * 4, 32, G_BM))
+            return rc;
+        if (int rc = make_tmap_2d(&tm_lu, a->w.lora_up, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, R32, a->N,
+                                  static_cast<uint64_t>(R32) * 4, 32, G_BN))
+            return rc;
+    } else {
+        tm_la = tm_a;
+        tm_lu = tm_b;
+    }
+    static bool attr_done[64] = {};
+    if (dev < 64 && !attr_done[dev]) {
+        SVDQ_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(G_SMEM_BYTES)));
+        attr_done[dev] = true;
+    }
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    gemm_nvfp4_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, p);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+}  // namespace svdq

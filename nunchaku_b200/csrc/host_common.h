@@ -1,0 +1,54 @@
+// Host-side helpers shared by the translation units of libsvdq_b200: error
+// reporting, argument checks and TMA tensor-map construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/svdq_b200.h"
+
+namespace svdq {
+
+// Thread-local text of the last error returned by an entry point.
+std::string& last_error();
+
+inline int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error() = buf;
+    return code;
+}
+
+#define SVDQ_CHECK_ARG(cond, ...)                                             \
+    do {                                                                      \
+        if (!(cond)) return ::svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+#define SVDQ_CUDA(call)                                                                     \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess)                                                              \
+            return ::svdq::fail(SVDQ_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Checks that the current device is compute capability 10.x (B200 / GB200).
+int check_arch();
+
+// Device pointer to the library's status words {code, detail} on the current device.
+int status_words(int** ptr);
+
+// 2-D tiled tensor map: inner dimension contiguous, `row_bytes` between rows.
+// `elem` is a CUtensorMapDataType, box_inner*elem_size must be <= 128 with 128B swizzle.
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem /*CUtensorMapDataType*/, uint64_t inner,
+                 uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows);
+
+}  // namespace svdq

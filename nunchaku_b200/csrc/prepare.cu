@@ -1,0 +1,280 @@
+// Layout conversion kernels: reference fragment order <-> the order the sm_100a
+// kernels stream.  All of them are word-granular permutations (HBM bound, run once
+// per layer for weights), one thread per 32-bit word, fully coalesced on the
+// reading side.
+#include <cuda_bf16.h>
+
+#include "host_common.h"
+
+namespace svdq {
+
+__device__ __forceinline__ int packed_vec_pos128(int n) {
+    return (n & ~15) | (((n >> 1) & 3) << 2) | (((n >> 3) & 1) << 1) | (n & 1);
+}
+
+// 4-bit weight codes.  Reference (packer.py:187-239): [N/128][K/64][ntile 8][g 8][t 4][half 2][kh 2] words,
+// word = 8 consecutive k of row bn*128 + nt*16 + half*8 + g starting at k = bk*64 + kh*32 + t*8.
+// Native: row-major [N][K/2] bytes.
+__global__ void retile_wgt_codes_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N, int K) {
+    const size_t total = static_cast<size_t>(N) * K / 8;
+    const int KB = K / 64;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t r = i;
+        const int kh = r & 1; r >>= 1;
+        const int half = r & 1; r >>= 1;
+        const int t = r & 3; r >>= 2;
+        const int g = r & 7; r >>= 3;
+        const int nt = r & 7; r >>= 3;
+        const int bk = r % KB;
+        const int bn = r / KB;
+        const int n = bn * 128 + nt * 16 + half * 8 + g;
+        const int k = bk * 64 + kh * 32 + t * 8;
+        dst[(static_cast<size_t>(n) * K + k) / 8] = src[i];
+    }
+}
+
+// NVFP4 weight micro-scales.  Reference (packer.py:303-360): [N/128][K/64][d 8][c 4][s 4] words, word = the 4
+// k-group bytes of row bn*128 + s*32 + c*8 + d.  Native: 512-byte atoms [N/128][K/64][r0 32][r1 4] words with
+// row = r1*32 + r0.
+__global__ void retile_wgt_mscales_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int N, int K) {
+    const size_t total = static_cast<size_t>(N) * K / 64;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int s = i & 3, c = (i >> 2) & 3, d = (i >> 4) & 7;
+        const size_t atom = i >> 7;
+        const int r0 = c * 8 + d;
+        dst[atom * 128 + r0 * 4 + s] = src[i];
+    }
+}
+
+// INT4 weight scales.  Reference (packer.py:241-301): [N/128][K/64][a 8][c 4][b 2][d 2] bf16,
+// n = a*16 + b*8 + c*2 + d.  Native: fp32 [K/64][N].
+__global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int N, int K) {
+    const int KB = K / 64;
+    const size_t total = static_cast<size_t>(N) * KB;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int pos = i & 127;
+        const size_t blk = i >> 7;
+        const int bk = blk % KB;
+        const int bn = blk / KB;
+        const int a = pos >> 4, c = (pos >> 2) & 3, b = (pos >> 1) & 1, d = pos & 1;
+        const int n = bn * 128 + a * 16 + b * 8 + c * 2 + d;
+        dst[static_cast<size_t>(bk) * N + n] = __bfloat162float(src[i]);
+    }
+}
+
+// Per-column epilogue constants and the LoRA-up weight.
+//   col_scale[n] = alpha * wcscales[n], col_bias[n] = bias[n]
+//   lora_up[n][r] = tf32_rn( Wu[n][r] * lora_scale[r/16] / col_scale[n] ), zero padded to R32 columns
+// Reference order of Wu (packer.py:362-398): [N/16][R/16][g 8][t 4][nh 2][kh 2][e 2],
+// n = cp*16 + nh*8 + g, r = rp*16 + kh*8 + 2t + e.
+struct LoraScales {
+    float v[8];
+};
+
+__global__ void prepare_columns_kernel(const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ wcscales,
+                                       const __nv_bfloat16* __restrict__ lora_up, float* __restrict__ col_scale,
+                                       float* __restrict__ col_bias, float* __restrict__ lora_out, float alpha, int N,
+                                       int R, int R32, LoraScales ls) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    const int pos = (n & ~127) + packed_vec_pos128(n & 127);
+    const float wc = wcscales ? __bfloat162float(wcscales[pos]) : 1.0f;
+    const float cs = alpha * wc;
+    col_scale[n] = cs;
+    col_bias[n] = bias ? __bfloat162float(bias[pos]) : 0.0f;
+    if (lora_out == nullptr) return;
+    const float inv = cs != 0.0f ? 1.0f / cs : 0.0f;
+    const int cp = n >> 4, nh = (n >> 3) & 1, g = n & 7;
+    for (int r = 0; r < R32; ++r) {
+        float v = 0.0f;
+        if (r < R) {
+            const int rp = r >> 4, kh = (r >> 3) & 1, t = (r >> 1) & 3, e = r & 1;
+            const size_t idx = ((((static_cast<size_t>(cp) * (R / 16) + rp) * 8 + g) * 4 + t) * 2 + nh) * 4 + kh * 2 + e;
+            v = __bfloat162float(lora_up[idx]) * ls.v[rp] * inv;
+            uint32_t u;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+            v = __uint_as_float(u);
+        }
+        lora_out[static_cast<size_t>(n) * R32 + r] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Activation-side conversions (reference order -> native order and back)
+// ---------------------------------------------------------------------------
+// codes: reference [M/256][K/64][warp 8][mtile 2][g 8][t 4][kh 2][half 2] words (gemm_w4a4.cuh:163-187)
+template <bool TO_NATIVE>
+__global__ void relayout_act_codes_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int M, int K) {
+    const size_t total = static_cast<size_t>(M) * K / 8;
+    const int KB = K / 64;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t r = i;
+        const int half = r & 1; r >>= 1;
+        const int kh = r & 1; r >>= 1;
+        const int t = r & 3; r >>= 2;
+        const int g = r & 7; r >>= 3;
+        const int mt = r & 1; r >>= 1;
+        const int w = r & 7; r >>= 3;
+        const int bk = r % KB;
+        const int bm = r / KB;
+        const int m = bm * 256 + w * 32 + mt * 16 + half * 8 + g;
+        const int k = bk * 64 + kh * 32 + t * 8;
+        const size_t j = (static_cast<size_t>(m) * K + k) / 8;
+        if (TO_NATIVE) dst[j] = src[i]; else dst[i] = src[j];
+    }
+}
+
+// NVFP4 activation scales: reference [M/256][K/64][warp 8][lane 32] words, row in warp =
+// ((l%4)/2)*16 + (l%2)*8 + l/4 (gemm_w4a4.cuh:144-155); native 512-byte atoms [M/128][K/64][r0 32][r1 4].
+template <bool TO_NATIVE>
+__global__ void relayout_act_mscales_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst, int M, int K) {
+    const size_t total = static_cast<size_t>(M) * K / 64;
+    const int KB = K / 64;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int l = i & 31, w = (i >> 5) & 7;
+        const size_t blk = i >> 8;
+        const int bk = blk % KB;
+        const int bm = blk / KB;
+        const int m = bm * 256 + w * 32 + ((l & 3) >> 1) * 16 + (l & 1) * 8 + (l >> 2);
+        const size_t j = (static_cast<size_t>(m >> 7) * KB + bk) * 128 + (m & 31) * 4 + ((m >> 5) & 3);
+        if (TO_NATIVE) dst[j] = src[i]; else dst[i] = src[j];
+    }
+}
+
+// INT4 activation scales: reference [M/256][K/64][warp 8][q 2][g 8][e 2] bf16 (gemm_base.cuh:452-468);
+// native bf16 [K/64][M].
+template <bool TO_NATIVE>
+__global__ void relayout_act_scales_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int M, int K) {
+    const int KB = K / 64;
+    const size_t total = static_cast<size_t>(M) * KB;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int e = i & 1, g = (i >> 1) & 7, q = (i >> 4) & 1, w = (i >> 5) & 7;
+        const size_t blk = i >> 8;
+        const int bk = blk % KB;
+        const int bm = blk / KB;
+        const int m = bm * 256 + w * 32 + q * 16 + e * 8 + g;
+        const size_t j = static_cast<size_t>(bk) * M + m;
+        if (TO_NATIVE) dst[j] = src[i]; else dst[i] = src[j];
+    }
+}
+
+// low-rank activations: reference [M/256][R/16][warp 8][mtile 2][nh 2][half 2][e 2][g 8][t 4] fp32
+// (lora.cuh:61-94); native fp32 [M][R].
+template <bool TO_NATIVE>
+__global__ void relayout_lora_act_kernel(const float* __restrict__ src, float* __restrict__ dst, int M, int R) {
+    const size_t total = static_cast<size_t>(M) * R;
+    const int RT = R / 16;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t r = i;
+        const int t = r & 3; r >>= 2;
+        const int g = r & 7; r >>= 3;
+        const int e = r & 1; r >>= 1;
+        const int half = r & 1; r >>= 1;
+        const int nh = r & 1; r >>= 1;
+        const int mt = r & 1; r >>= 1;
+        const int w = r & 7; r >>= 3;
+        const int rt = r % RT;
+        const int bm = r / RT;
+        const int m = bm * 256 + w * 32 + mt * 16 + half * 8 + g;
+        const int rank = rt * 16 + nh * 8 + 2 * t + e;
+        const size_t j = static_cast<size_t>(m) * R + rank;
+        if (TO_NATIVE) dst[j] = src[i]; else dst[i] = src[j];
+    }
+}
+
+static inline int grid_for(size_t total) {
+    size_t b = (total + 255) / 256;
+    return static_cast<int>(b > 148 * 16 ? 148 * 16 : (b == 0 ? 1 : b));
+}
+
+int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]) {
+    SVDQ_CHECK_ARG(N > 0 && N % 128 == 0 && K > 0 && K % 128 == 0 && R >= 0 && R % 16 == 0,
+                   "prepared_bytes: need N%%128==0, K%%128==0, R%%16==0 (N=%d K=%d R=%d)", N, K, R);
+    const size_t R32 = (static_cast<size_t>(R) + 31) / 32 * 32;
+    bytes[0] = static_cast<size_t>(N) * K / 2;
+    bytes[1] = fp4 ? static_cast<size_t>(N) * K / 16 : static_cast<size_t>(N) * (K / 64) * 4;
+    bytes[2] = static_cast<size_t>(N) * R32 * 4;
+    bytes[3] = static_cast<size_t>(N) * 4;
+    bytes[4] = static_cast<size_t>(N) * 4;
+    return SVDQ_OK;
+}
+
+int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights* o, cudaStream_t stream) {
+    SVDQ_CHECK_ARG(a && o, "prepare_weights: null args");
+    SVDQ_CHECK_ARG(a->qweight && a->wscales && o->wgt && o->wscales && o->col_scale && o->col_bias,
+                   "prepare_weights: null tensor pointer");
+    SVDQ_CHECK_ARG(a->N > 0 && a->N % 128 == 0 && a->K > 0 && a->K % 128 == 0, "prepare_weights: need N%%128==0 and K%%128==0");
+    SVDQ_CHECK_ARG(a->R >= 0 && a->R % 16 == 0 && a->R <= 128, "prepare_weights: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R == 0 || (a->lora_up && o->lora_up), "prepare_weights: lora_up missing");
+    SVDQ_CHECK_ARG(a->fp4 || a->alpha == 1.0f, "prepare_weights: alpha must be 1 for INT4 (gemm_w4a4_launch_impl.cuh:107)");
+    SVDQ_CHECK_ARG(aligned(a->qweight, 16) && aligned(a->wscales, 16) && aligned(o->wgt, 16) && aligned(o->wscales, 16),
+                   "prepare_weights: tensors must be 16-byte aligned");
+    if (int rc = check_arch()) return rc;
+    const size_t words = static_cast<size_t>(a->N) * a->K / 8;
+    retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                static_cast<uint32_t*>(o->wgt), a->N, a->K);
+    if (a->fp4) {
+        const size_t sw = static_cast<size_t>(a->N) * a->K / 64;
+        retile_wgt_mscales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint32_t*>(a->wscales),
+                                                                   static_cast<uint32_t*>(o->wscales), a->N, a->K);
+    } else {
+        const size_t sw = static_cast<size_t>(a->N) * (a->K / 64);
+        retile_wgt_scales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a->wscales),
+                                                                  static_cast<float*>(o->wscales), a->N, a->K);
+    }
+    LoraScales ls;
+    for (int i = 0; i < 8; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
+    const int R32 = (a->R + 31) / 32 * 32;
+    prepare_columns_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(a->bias), static_cast<const __nv_bfloat16*>(a->wcscales),
+        static_cast<const __nv_bfloat16*>(a->lora_up), o->col_scale, o->col_bias, a->R ? o->lora_up : nullptr, a->alpha,
+        a->N, a->R, R32, ls);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+template <bool TO_NATIVE>
+static int relayout_dir(const svdq_relayout_args* a, cudaStream_t stream) {
+    if (a->codes_in && a->codes_out) {
+        const size_t words = static_cast<size_t>(a->M_pad) * a->K / 8;
+        relayout_act_codes_kernel<TO_NATIVE><<<grid_for(words), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(a->codes_in), static_cast<uint32_t*>(a->codes_out), a->M_pad, a->K);
+    }
+    if (a->scales_in && a->scales_out) {
+        if (a->fp4) {
+            const size_t words = static_cast<size_t>(a->M_pad) * a->K / 64;
+            relayout_act_mscales_kernel<TO_NATIVE><<<grid_for(words), 256, 0, stream>>>(
+                static_cast<const uint32_t*>(a->scales_in), static_cast<uint32_t*>(a->scales_out), a->M_pad, a->K);
+        } else {
+            const size_t n = static_cast<size_t>(a->M_pad) * (a->K / 64);
+            relayout_act_scales_kernel<TO_NATIVE><<<grid_for(n), 256, 0, stream>>>(
+                static_cast<const uint16_t*>(a->scales_in), static_cast<uint16_t*>(a->scales_out), a->M_pad, a->K);
+        }
+    }
+    if (a->lora_in && a->lora_out && a->R > 0) {
+        const size_t n = static_cast<size_t>(a->M_pad) * a->R;
+        relayout_lora_act_kernel<TO_NATIVE><<<grid_for(n), 256, 0, stream>>>(a->lora_in, a->lora_out, a->M_pad, a->R);
+    }
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+int relayout_impl(const svdq_relayout_args* a, cudaStream_t stream) {
+    SVDQ_CHECK_ARG(a != nullptr, "relayout: null args");
+    SVDQ_CHECK_ARG(a->M_pad > 0 && a->M_pad % 256 == 0 && a->K % 128 == 0 && a->R % 16 == 0,
+                   "relayout: need M_pad%%256==0, K%%128==0, R%%16==0");
+    SVDQ_CHECK_ARG(a->from_layout != a->to_layout, "relayout: from_layout == to_layout");
+    SVDQ_CHECK_ARG(a->codes_in != a->codes_out || !a->codes_in, "relayout: in-place conversion is not supported");
+    if (int rc = check_arch()) return rc;
+    if (a->to_layout == SVDQ_LAYOUT_NATIVE) return relayout_dir<true>(a, stream);
+    return relayout_dir<false>(a, stream);
+}
+
+}  // namespace svdq

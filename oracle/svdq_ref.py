@@ -1,0 +1,312 @@
+"""CPU restatement of the SVDQuant W4A4 linear arithmetic (test infrastructure, never shipped).
+
+All tensors here are *logical* (unpacked, row-major); ``oracle.layouts`` turns
+them into reference or native memory order.  Functions cite the reference code
+they follow by file:line (paths inside the nunchaku tree).
+
+Rounding model.  Every ``half_t`` operation of the reference is a bf16
+round-to-nearest-even of the exact result.  ``__fdividef`` and
+``rcp.approx.ftz`` (gemm_utils.cuh:258-262,329-344) are modelled as correctly
+rounded fp32 division / reciprocal.  A group whose absolute maximum is zero has
+``scale = 0``; the reference then multiplies by ``rcp(0) = inf`` and converts a
+NaN, here (and in the CUDA kernels of this repository) the reciprocal of a zero
+scale is defined as 0 so that such a group gets all-zero codes.  The dequantised
+value (0) is the same either way.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+from . import fmt
+
+F32 = torch.float32
+BF16 = torch.bfloat16
+
+# fp32 compile-time constants of the reference (gemm_w4a4.cuh:91-93,435-441)
+RCP6 = torch.tensor(1.0, dtype=F32) / torch.tensor(6.0, dtype=F32)
+RCP7 = torch.tensor(1.0, dtype=F32) / torch.tensor(7.0, dtype=F32)
+RCP15 = torch.tensor(1.0, dtype=F32) / torch.tensor(15.0, dtype=F32)
+INT4_UNSIGNED_SHIFT = 0.171875  # gemm_w4a4_launch_impl.cuh:286-294
+
+
+def ceil_to(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+@dataclasses.dataclass
+class QuantOut:
+    codes: torch.Tensor      # uint8 [M_pad, K], one nibble value per element
+    scales: torch.Tensor     # NVFP4: uint8 e4m3 bytes [K/16, M_pad]; INT4: bf16 [K/64, M_pad]
+    lora_act: torch.Tensor   # fp32 [M_pad, R]
+    fp4: bool
+    unsigned: bool = False
+
+
+def _silu_bf16(y: torch.Tensor) -> torch.Tensor:
+    """gemm_utils.cuh:321-327: (T)(float(x) * sigmoid(float(x)))."""
+    yf = y.to(F32)
+    return (yf * torch.sigmoid(yf)).to(BF16)
+
+
+def gelu_f32(x: torch.Tensor) -> torch.Tensor:
+    """gemm_utils.cuh:305-319: x * (0.5 + 0.5 * tanh(0.79788456 * (x + 0.044715 x^3)))."""
+    x = x.to(F32)
+    return x * (0.5 + 0.5 * torch.tanh(0.79788456 * (x + 0.044715 * x * x * x)))
+
+
+def group_quantize(v: torch.Tensor, *, fp4: bool, unsigned: bool = False):
+    """Group-quantise an already smoothed bf16 tensor ``v`` [rows, K].
+
+    Follows quantize_w4a4_fp4_from_fpsum_warp (gemm_w4a4.cuh:85-187) and
+    quantize_w4a4_from_fpsum_warp (gemm_w4a4.cuh:429-523).
+    Returns (codes uint8 [rows, K], scales [K/G, rows]).
+    """
+    assert v.dtype == BF16
+    rows, K = v.shape
+    G = 16 if fp4 else 64
+    vf = v.to(F32).reshape(rows, K // G, G)
+    amax = vf.abs().amax(dim=2)  # exact in bf16
+    if fp4:
+        scale = torch.minimum(amax * RCP6, torch.tensor(448.0))
+        stored = fmt.e4m3_encode(scale)
+    else:
+        scale = amax * (RCP15 if unsigned else RCP7)
+        stored = scale.to(BF16)
+    rscale = torch.where(scale == 0, torch.zeros_like(scale), 1.0 / scale)
+    q = vf * rscale.unsqueeze(2)
+    codes = fmt.e2m1_encode(q) if fp4 else fmt.int4_encode(q, unsigned)
+    return codes.reshape(rows, K), stored.t().contiguous()
+
+
+def ref_quantize(
+    x: torch.Tensor,
+    smooth: torch.Tensor,
+    lora_down: torch.Tensor | None,
+    *,
+    fp4: bool,
+    fuse_glu: bool = False,
+    pad_size: int = 256,
+) -> QuantOut:
+    """quantize_w4a4_fuse_lora_kernel (gemm_w4a4.cuh:1097-1184).
+
+    x         bf16 [M, K]  ([M, 2K] interleaved (value, gate) pairs when fuse_glu)
+    smooth    bf16 [K]     logical order
+    lora_down bf16 [R, K]  logical order (the unpacked ``proj_down``)
+    """
+    assert x.dtype == BF16 and smooth.dtype == BF16
+    M = x.shape[0]
+    if fuse_glu:  # gemm_base.cuh:612-623: pack[j] = raw[j].x * silu(raw[j].y), both in bf16
+        v = (x[:, 0::2].to(F32) * _silu_bf16(x[:, 1::2]).to(F32)).to(BF16)
+    else:
+        v = x
+    K = v.shape[1]
+    M_pad = ceil_to(M, pad_size)
+    vp = torch.zeros(M_pad, K, dtype=BF16)
+    vp[:M] = v
+    # LoRA down on the un-smoothed tile (lora.cuh:243-353), fp32 accumulation
+    if lora_down is not None:
+        lora_act = (vp.to(torch.float64) @ lora_down.to(torch.float64).t()).to(F32)
+    else:
+        lora_act = torch.zeros(M_pad, 0, dtype=F32)
+    # EpilogueQuantize (gemm_w4a4.cuh:930-1043) with shift_value = 0: bf16 add of +0, then h2div
+    vs = (vp.to(F32) + 0.0).to(BF16)
+    vs = (vs.to(F32) / smooth.to(F32).unsqueeze(0)).to(BF16)
+    codes, scales = group_quantize(vs, fp4=fp4, unsigned=False)
+    return QuantOut(codes, scales, lora_act, fp4)
+
+
+def dequant_act(q: QuantOut) -> torch.Tensor:
+    rows, K = q.codes.shape
+    if q.fp4:
+        val = fmt.e2m1_decode(q.codes)
+        s = fmt.e4m3_decode(q.scales).t()  # [rows, K/16]
+        return (val.reshape(rows, K // 16, 16) * s.unsqueeze(2)).reshape(rows, K)
+    val = fmt.int4_decode(q.codes, q.unsigned)
+    s = q.scales.to(F32).t()
+    return (val.reshape(rows, K // 64, 64) * s.unsqueeze(2)).reshape(rows, K)
+
+
+@dataclasses.dataclass
+class Linear:
+    """One SVDQuant W4A4 linear with logical (unpacked) parameters."""
+
+    K: int
+    N: int
+    R: int
+    fp4: bool
+    wcodes: torch.Tensor          # uint8 [N, K] nibble values
+    wscales: torch.Tensor         # NVFP4: uint8 e4m3 [K/16, N]; INT4: bf16 [K/64, N]
+    smooth: torch.Tensor          # bf16 [K]
+    lora_down: torch.Tensor       # bf16 [R, K]
+    lora_up: torch.Tensor         # bf16 [N, R]
+    bias: torch.Tensor | None     # bf16 [N]
+    wtscale: float = 1.0          # NVFP4 per-tensor weight scale ("alpha")
+    wcscales: torch.Tensor | None = None  # NVFP4 per-channel scale, bf16 [N]
+
+    def dequant_weight(self) -> torch.Tensor:
+        """fp32 [N, K]; includes ``wtscale`` but not ``wcscales``."""
+        if self.fp4:
+            val = fmt.e2m1_decode(self.wcodes)
+            s = fmt.e4m3_decode(self.wscales).t()
+            w = (val.reshape(self.N, self.K // 16, 16) * s.unsqueeze(2)).reshape(self.N, self.K)
+            return w * self.wtscale
+        val = fmt.int4_decode(self.wcodes, False)
+        s = self.wscales.to(F32).t()
+        return (val.reshape(self.N, self.K // 64, 64) * s.unsqueeze(2)).reshape(self.N, self.K)
+
+
+def ref_gemm(
+    q: QuantOut,
+    lin: Linear,
+    *,
+    M: int | None = None,
+    act: str | None = None,
+    lora_scales: list[float] | None = None,
+    use_lora: bool = True,
+) -> torch.Tensor:
+    """The "math" oracle of gemm_w4a4: dequantise, fp32 matmul, epilogue in fp32.
+
+    Order of the fused epilogue (gemm_w4a4_launch_impl.cuh:172-420):
+    acc*alpha -> *wcscale + bias (gemm_base.cuh:710-781) -> + LoRA-up
+    (lora.cuh:110-241) -> GELU | SiLU.  Returns fp32 [M, N] (not rounded to bf16).
+    """
+    M = q.codes.shape[0] if M is None else M
+    a = dequant_act(q)[:M]
+    y = a @ lin.dequant_weight().t()
+    if lin.wcscales is not None:
+        y = y * lin.wcscales.to(F32).unsqueeze(0)
+    if lin.bias is not None:
+        y = y + lin.bias.to(F32).unsqueeze(0)
+    if use_lora and lin.R > 0:
+        la = q.lora_act[:M]
+        if lora_scales is not None:
+            sc = torch.tensor(lora_scales, dtype=F32).repeat_interleave(16)[: lin.R]
+            la = la * sc.unsqueeze(0)
+        y = y + la @ lin.lora_up.to(F32).t()
+    if act == "gelu":
+        y = gelu_f32(y)
+    elif act == "silu":
+        y = y * torch.sigmoid(y)
+    return y
+
+
+def ref_requantize(
+    y: torch.Tensor,
+    nxt: Linear,
+    *,
+    M_pad: int,
+    unsigned: bool,
+) -> QuantOut:
+    """Next-layer requantisation fused into the GEMM epilogue
+    (gemm_w4a4_launch_impl.cuh:282-309, gemm_w4a4.cuh:930-1043, lora.cuh:243-353):
+    LoRA-down on the activated value, then (+shift) / smooth_next, group-quantise.
+    ``y`` is the activated GEMM output in fp32 [M, N]; it is rounded to bf16 first,
+    as the reference's accumulator tile is bf16 at that point."""
+    M, N = y.shape
+    yb = torch.zeros(M_pad, N, dtype=BF16)
+    yb[:M] = y.to(BF16)
+    lora_act = (yb.to(torch.float64) @ nxt.lora_down.to(torch.float64).t()).to(F32)
+    shift = INT4_UNSIGNED_SHIFT if unsigned else 0.0
+    v = (yb.to(F32) + shift).to(BF16)
+    v = (v.to(F32) / nxt.smooth.to(F32).unsqueeze(0)).to(BF16)
+    codes, scales = group_quantize(v, fp4=nxt.fp4, unsigned=unsigned)
+    return QuantOut(codes, scales, lora_act, nxt.fp4, unsigned)
+
+
+# ---------------------------------------------------------------------------
+# Synthetic SVDQuant problems (the reference has no quantiser; its checkpoints
+# come from the external DeepCompressor project).
+# ---------------------------------------------------------------------------
+def make_activations(M: int, K: int, seed: int = 0, outlier_frac: float = 0.01, outlier_mul: float = 20.0):
+    """bf16 [M, K] ~ N(0,1) with a fraction of channels scaled up (outliers)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g, dtype=F32)
+    n_out = max(1, math.ceil(outlier_frac * K))
+    cols = torch.randperm(K, generator=g)[:n_out]
+    x[:, cols] *= outlier_mul
+    return x.to(BF16)
+
+
+def quantize_weight(res: torch.Tensor, fp4: bool):
+    """Residual fp32 [N, K] -> (codes uint8 [N,K], scales [K/G, N], wtscale)."""
+    N, K = res.shape
+    if fp4:
+        amax_t = res.abs().max().item()
+        wtscale = float(torch.tensor(max(amax_t / (6.0 * 448.0), 1e-12), dtype=BF16).item())  # module stores bf16
+        g = res.reshape(N, K // 16, 16)
+        s = g.abs().amax(dim=2) / (6.0 * wtscale)
+        sb = fmt.e4m3_encode(s)
+        sd = fmt.e4m3_decode(sb) * wtscale
+        q = g / torch.where(sd == 0, torch.ones_like(sd), sd).unsqueeze(2)
+        codes = fmt.e2m1_encode(q).reshape(N, K)
+        return codes, sb.t().contiguous(), wtscale
+    g = res.reshape(N, K // 64, 64)
+    s = (g.abs().amax(dim=2) / 7.0).to(BF16)
+    sf = s.to(F32)
+    q = g / torch.where(sf == 0, torch.ones_like(sf), sf).unsqueeze(2)
+    codes = fmt.int4_encode(q, False).reshape(N, K)
+    return codes, s.t().contiguous(), 1.0
+
+
+def make_linear(
+    K: int,
+    N: int,
+    R: int,
+    *,
+    fp4: bool,
+    x_absmax: torch.Tensor | None = None,
+    seed: int = 0,
+    mode: str = "literal",
+    bias: bool = True,
+    w_std: float = 0.02,
+    wcscales: bool = False,
+) -> Linear:
+    """Random-init SVDQuant linear.
+
+    ``mode='literal'``: weights ~N(0, w_std) with their rank-R SVD component
+    removed, low-rank factors drawn independently ~N(0, 0.02).
+    ``mode='svd'``: low-rank factors are the removed SVD component, so the layer
+    approximates ``x @ W.T + b`` of the bf16 master weight (returned as ``.master``).
+    """
+    g = torch.Generator().manual_seed(seed + 1000003)
+    W = torch.randn(N, K, generator=g, dtype=F32) * w_std
+    if x_absmax is None:
+        x_absmax = torch.ones(K)
+    w_absmax = W.abs().amax(dim=0).clamp(min=1e-8)
+    smooth = torch.sqrt(x_absmax.to(F32).clamp(min=1e-8) / w_absmax).clamp(min=1e-4).to(BF16)
+    What = W * smooth.to(F32).unsqueeze(0)
+    if R > 0:
+        if min(N, K) <= 1024:
+            U, S, Vh = torch.linalg.svd(What, full_matrices=False)
+            U, S, V = U[:, :R], S[:R], Vh[:R].t()
+        else:
+            torch.manual_seed(seed)
+            U, S, V = torch.svd_lowrank(What, q=R + 8, niter=2)
+            U, S, V = U[:, :R], S[:R], V[:, :R]
+        low = (U * S) @ V.t()
+    else:
+        low = torch.zeros_like(What)
+    res = What - low
+    wcodes, wscales, wtscale = quantize_weight(res, fp4)
+    if mode == "literal":
+        lora_down = (torch.randn(R, K, generator=g) * 0.02).to(BF16)
+        lora_up = (torch.randn(N, R, generator=g) * 0.02).to(BF16)
+    else:
+        lora_up = (U * S).to(BF16)
+        lora_down = (V.t() / smooth.to(F32).unsqueeze(0)).to(BF16)
+    b = (torch.randn(N, generator=g) * 0.02).to(BF16) if bias else None
+    wc = None
+    if fp4:
+        wc = (1.0 + 0.25 * torch.rand(N, generator=g)).to(BF16) if wcscales else torch.ones(N, dtype=BF16)
+    lin = Linear(K, N, R, fp4, wcodes, wscales, smooth, lora_down, lora_up, b, wtscale, wc)
+    lin.master = W  # type: ignore[attr-defined]
+    return lin
+
+
+def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    a = a.to(torch.float64)
+    b = b.to(torch.float64)
+    return float((a - b).norm() / b.norm().clamp(min=1e-30))
