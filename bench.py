@@ -189,7 +189,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shape", default=None, help="M,K,N override: a smaller case of the same path for profiler captures "
+                    "(the default is the benchmark workload)")
     args = ap.parse_args()
+    if args.shape:
+        global M, K, N, FLOP_GEMM, FLOP_STEP, QUANT_BYTES
+        M, K, N = (int(v) for v in args.shape.split(","))
+        FLOP_GEMM = 2.0 * M * N * K + 2.0 * M * N * R
+        FLOP_STEP = FLOP_GEMM
+        QUANT_BYTES = 2 * M * K + M * K // 2 + M * K // 16 + 4 * M * R + 2 * K * R + 2 * K
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     from nunchaku_b200 import distributed as D

@@ -10,7 +10,7 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsvdq_b200.so")
+LIB_PATH = os.environ.get("SVDQ_B200_LIB") or os.path.join(_HERE, "libsvdq_b200.so")
 
 SVDQ_OK = 0
 SVDQ_ERR_INVALID_ARGUMENT = -1

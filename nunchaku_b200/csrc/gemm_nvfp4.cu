@@ -10,14 +10,17 @@
 // How it maps to a B200 SM.  One persistent CTA per SM walks 128 x 192 output tiles.
 //   warp 0      producer: TMA loads of 128B-swizzled operand tiles (128 rows x 256 codes of A, 192 x 256 of
 //               B per stage) and bulk copies of the 512-byte scale-factor atoms, 4-stage mbarrier ring
-//   warp 1      MMA issuer: tcgen05.cp moves the scale atoms into TMEM, then 4 x
-//               tcgen05.mma.kind::mxf4nvf4.block_scale (M128 N192 K64) per stage; the low-rank branch is
-//               fed through the same ring as fp32 tiles and issued as kind::tf32 into the same TMEM
-//               accumulator; tcgen05.commit releases the stage / publishes the accumulator
-//   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 stores
+//   warp 1      MMA issuer: 4 x tcgen05.mma.kind::mxf4nvf4.block_scale (M128 N192 K64) per stage; the
+//               low-rank branch is fed through the same ring as fp32 tiles and issued as kind::tf32 into
+//               the same TMEM accumulator; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 6..9  scale-factor loaders: shared memory -> registers -> TMEM (tcgen05.st), one lane quadrant each
+//   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
+//               staging buffer, TMA store (coalesced, clipped at M and N by the hardware)
 // TMEM: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
-// plus 16 + 32 columns of scale factors = 432 of 512 columns.
+// plus three 40-column scale-factor buffers (16 for A, 24 for B) = 504 of 512 columns.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 #include "host_common.h"
 #include "ptx.cuh"
@@ -26,19 +29,23 @@ namespace svdq {
 
 constexpr int G_BM = 128;
 constexpr int G_BN = 192;
-constexpr int G_BK = 256;                       // codes per stage = 128 bytes per row
 constexpr int G_STAGES = 4;
 constexpr int G_A_BYTES = G_BM * 128;           // 16 KB
 constexpr int G_B_BYTES = G_BN * 128;           // 24 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
 constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 47104 = 46 * 1024
-constexpr int G_THREADS = 6 * 32;
+constexpr int G_THREADS = 10 * 32;
+constexpr int G_SF_BUFS = 3;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
-constexpr int G_TM_SFA = 2 * G_BN;              // 384
-constexpr int G_TM_SFB = G_TM_SFA + 16;         // 400
-constexpr size_t G_SMEM_BYTES = 1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + 256;
+constexpr int G_TM_SF = 2 * G_BN;               // 384: scale-factor buffers of 40 columns each
+constexpr int G_TM_SF_STRIDE = 40;              // per buffer: 4 x 4 columns for A, 4 x 6 for B (one per 32 rows)
+constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
+constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
+constexpr int G_COLV_BYTES = 4 * 2 * G_BN * 4;              // per epilogue warp: {scale, bias} of the tile's columns
+constexpr size_t G_SMEM_BYTES =
+    1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + G_EPI_BYTES + G_COLV_BYTES + 256;
 
 struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
@@ -51,28 +58,46 @@ struct GemmParams {
     int lora_chunks;          // number of 32-rank chunks of the low-rank branch (0 = none)
     int tiles_m, tiles_n;
     int activation;
+#ifdef SVDQ_PROF
+    long long* prof;
+    int dbg;
+#endif
 };
+
+#ifdef SVDQ_PROF
+__device__ long long g_gemm_prof[148 * 8];
+#define PROF_T0() const long long pt0_ = clock64()
+#define PROF_ADD(i) p.prof[blockIdx.x * 8 + (i)] += clock64() - pt0_
+#else
+#define PROF_T0()
+#define PROF_ADD(i)
+#endif
 
 struct GemmShared {
     uint64_t full[G_STAGES];
     uint64_t empty[G_STAGES];
     uint64_t tfull[2];
     uint64_t tempty[2];
+    uint64_t sf_full[G_SF_BUFS];    // scale factors of a stage are in TMEM (4 loader warps arrive)
+    uint64_t sf_empty[G_SF_BUFS];   // the MMAs that read a scale-factor buffer are done (tcgen05.commit)
     uint64_t drain;
     uint32_t tmem_base;
     volatile int abort_flag;
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    for (int i = 0; i < 512; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 256; ++i) {
+        for (int i = 0; i < 128; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
         }
         if (sh->abort_flag) return false;
-        if (globaltimer_ns() - t0 > 2000000000ull) {
+        if (clock64() - t0 > 4000000000ll) {  // about 2 s
             sh->abort_flag = 1;
             atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
             atomicExch(&status[1], where);
@@ -95,10 +120,12 @@ __device__ __forceinline__ float apply_act(float v, int activation) {
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
-                  const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    GemmShared* sh = reinterpret_cast<GemmShared*>(smem + G_STAGES * G_STAGE_BYTES);
+    uint8_t* epi_smem = smem + G_STAGES * G_STAGE_BYTES;
+    float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
+    GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + G_COLV_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -116,11 +143,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             mbar_init(&sh->tfull[i], 1);
             mbar_init(&sh->tempty[i], 4);
         }
+        for (int i = 0; i < G_SF_BUFS; ++i) {
+            mbar_init(&sh->sf_full[i], 4);
+            mbar_init(&sh->sf_empty[i], 1);
+        }
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
+        prefetch_tmap(&tm_out);
         if (p.lora_chunks) {
             prefetch_tmap(&tm_la);
             prefetch_tmap(&tm_lu);
@@ -134,6 +166,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
+#ifdef SVDQ_PROF
+    const long long kt0 = clock64();
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
@@ -146,9 +181,13 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const int atom0 = n0 >> 7;
                 for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
                     const int s = it % G_STAGES;
-                    if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
-                        ok = false;
-                        break;
+                    {
+                        PROF_T0();
+                        if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
+                            ok = false;
+                            break;
+                        }
+                        PROF_ADD(0);
                     }
                     uint8_t* st = smem + s * G_STAGE_BYTES;
                     if (ks < kstages) {
@@ -176,41 +215,62 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (lane == 0) {
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
-            uint32_t it = 0, lt = 0;
+            uint32_t it = 0, lt = 0, sq = 0;  // ring position, local tile count, scale-factor stage count
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
-                const int n0 = (tile / p.tiles_m) * G_BN;
                 const uint32_t as = lt & 1;
-                if (!wait_or_abort(&sh->tempty[as], ((lt >> 1) & 1) ^ 1, sh, p.status, 20)) break;
+                {
+                    PROF_T0();
+                    if (!wait_or_abort(&sh->tempty[as], ((lt >> 1) & 1) ^ 1, sh, p.status, 20)) break;
+                    PROF_ADD(2);
+                }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem + as * G_TM_ACC1;
-                const uint32_t sfb_off = (n0 & 127) ? 2u : 0u;   // tile starts in the middle of a 128-row atom
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
                     const int s = it % G_STAGES;
-                    if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
-                        ok = false;
-                        break;
+                    {
+                        PROF_T0();
+                        if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
+                            ok = false;
+                            break;
+                        }
+                        PROF_ADD(1);
                     }
-                    tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
                     const uint64_t adesc = smem_desc_sw128(sa);
                     const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
                     if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
-                        const uint32_t sfa_s = sa + G_A_BYTES + G_B_BYTES;
-                        const uint32_t sfb_s = sfa_s + G_SFA_BYTES;
-                        for (int j = 0; j < nkb; ++j) {
-                            tc_cp_32x128b_warpx4(tmem + G_TM_SFA + 4 * j, smem_desc_sf(sfa_s + j * 512));
-                            tc_cp_32x128b_warpx4(tmem + G_TM_SFB + 8 * j, smem_desc_sf(sfb_s + j * 512));
-                            tc_cp_32x128b_warpx4(tmem + G_TM_SFB + 8 * j + 4, smem_desc_sf(sfb_s + 2048 + j * 512));
+                        const uint32_t b = sq % G_SF_BUFS;
+#ifdef SVDQ_PROF
+                        if (!(p.dbg & 16))
+#endif
+                        {
+                            PROF_T0();
+                            if (!wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22)) {
+                                ok = false;
+                                break;
+                            }
+                            PROF_ADD(6);
                         }
+                        tc_fence_after_sync();
+                        const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
+                        const uint32_t t_sfb = t_sfa + 16;
+#ifdef SVDQ_PROF
+                        if (!(p.dbg & 4))
+#endif
                         for (int j = 0; j < nkb; ++j) {
-                            tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, tmem + G_TM_SFA + 4 * j,
-                                         tmem + G_TM_SFB + 8 * j + sfb_off, accumulate);
+                            tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j, accumulate);
                             accumulate = 1;
                         }
+#ifdef SVDQ_PROF
+                        if (!(p.dbg & 16))
+#endif
+                        tc_commit(&sh->sf_empty[b]);
+                        ++sq;
                     } else {
+                        tc_fence_after_sync();
                         for (int j = 0; j < 4; ++j) {
                             tc_mma_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, accumulate);
                             accumulate = 1;
@@ -222,64 +282,176 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
                 tc_commit(&sh->drain);
-                mbar_wait(&sh->drain, 0, 200000000ull);
+                mbar_wait(&sh->drain, 0, 400000000ll);
+            }
+        }
+    } else if (warp >= 6) {
+        // ------------------------------------------------------------------ scale-factor loaders (warps 6..9)
+        // tcgen05.cp would put the scale factors into TMEM through the tensor pipe, where each copy costs
+        // about 60 cycles that no MMA can overlap (12 copies per stage against 4 MMAs of ~100 cycles).
+        // Instead each of these four warps reads the stage's 512-byte atoms from shared memory (row r0 =
+        // lane, 16 bytes = the 4 row groups x 4 scale bytes) and writes them to its own TMEM lane quadrant
+        // with tcgen05.st: 16 columns for A, 24 for B per stage.
+        const int q = warp & 3;
+        uint32_t it = 0, sq = 0;
+        bool ok = true;
+#ifdef SVDQ_PROF
+        if (p.dbg & 16) ok = false;
+#endif
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const bool mid_atom = (((tile / p.tiles_m) * G_BN) & 127) != 0;  // tile starts 64 rows into an atom
+            for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+                if (ks >= kstages) continue;  // low-rank stages carry no scale factors
+                const int s = it % G_STAGES;
+                const uint32_t b = sq % G_SF_BUFS;
+                if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 40) ||
+                    !wait_or_abort(&sh->sf_empty[b], ((sq / G_SF_BUFS) & 1) ^ 1, sh, p.status, 41)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint8_t* sf = smem + s * G_STAGE_BYTES + G_A_BYTES + G_B_BYTES + lane * 16;
+                // registers 0..15: A (k-block j, row group c -> 4j + c); 16..39: B (6j + c), where the tile's
+                // 192 weight rows are row groups off..off+5 of the two 128-row atoms in shared memory
+                uint32_t r32[32], r8[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(sf + j * 512);
+                    const uint4 b0 = *reinterpret_cast<const uint4*>(sf + G_SFA_BYTES + j * 512);
+                    const uint4 b1 = *reinterpret_cast<const uint4*>(sf + G_SFA_BYTES + 2048 + j * 512);
+                    r32[4 * j] = a.x; r32[4 * j + 1] = a.y; r32[4 * j + 2] = a.z; r32[4 * j + 3] = a.w;
+                    uint32_t w[6];
+                    if (mid_atom) { w[0] = b0.z; w[1] = b0.w; w[2] = b1.x; w[3] = b1.y; w[4] = b1.z; w[5] = b1.w; }
+                    else          { w[0] = b0.x; w[1] = b0.y; w[2] = b0.z; w[3] = b0.w; w[4] = b1.x; w[5] = b1.y; }
+#pragma unroll
+                    for (int c = 0; c < 6; ++c) {
+                        const int idx = 16 + 6 * j + c;   // compile-time after unrolling
+                        if (idx < 32) r32[idx] = w[c]; else r8[idx - 32] = w[c];
+                    }
+                }
+                const uint32_t t_sf = tmem + (static_cast<uint32_t>(q * 32) << 16) + G_TM_SF + b * G_TM_SF_STRIDE;
+#ifdef SVDQ_PROF
+                if (!(p.dbg & 8))
+#endif
+                {
+                    tc_st_32x32b_x32(t_sf, r32);
+                    tc_st_32x32b_x8(t_sf + 32, r8);
+                    tc_wait_st();
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->sf_full[b]);
+                ++sq;
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
+        // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
+        // hardware clips rows >= M and columns >= N).  Two staging buffers per warp keep a store in flight.
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
-        uint32_t lt = 0;
+        uint8_t* my_buf = epi_smem + q * 2 * G_EPI_BUF_BYTES;
+        uint32_t lt = 0, nstore = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
             const int m0 = (tile % p.tiles_m) * G_BM;
             const int n0 = (tile / p.tiles_m) * G_BN;
             const uint32_t as = lt & 1;
-            if (!wait_or_abort(&sh->tfull[as], (lt >> 1) & 1, sh, p.status, 30)) break;
+            // per-column constants of this tile -> this warp's shared-memory copy (issued before the
+            // accumulator is needed, so the latency hides behind the wait)
+            float* cvs = colv + q * 2 * G_BN;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) {
+                const int e = lane + 32 * i;            // 0..95: 48 float4 of scale, then 48 of bias
+                const int which = e / 48, c4 = (e % 48) * 4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (n0 + c4 < p.N) v = __ldg(reinterpret_cast<const float4*>((which ? p.col_bias : p.col_scale) + n0 + c4));
+                *reinterpret_cast<float4*>(cvs + which * G_BN + c4) = v;
+            }
+            __syncwarp();
+            {
+                PROF_T0();
+                if (!wait_or_abort(&sh->tfull[as], (lt >> 1) & 1, sh, p.status, 30)) break;
+#ifdef SVDQ_PROF
+                if (threadIdx.x == 64) PROF_ADD(3);
+#endif
+            }
+            PROF_T0();
             tc_fence_after_sync();
-            const int m = m0 + q * 32 + lane;
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
-            __nv_bfloat16* orow = p.out + static_cast<size_t>(m) * p.N + n0;
 #pragma unroll 1
-            for (int c = 0; c < G_BN / 32; ++c) {
-                const int n = n0 + c * 32;
-                if (n >= p.N) break;
-                uint32_t r[32];
-                tc_ld_32x32b_x32(taddr + c * 32, r);
+            for (int h = 0; h < G_BN / 64; ++h) {
+                if (n0 + h * 64 >= p.N) break;
+#ifdef SVDQ_PROF
+                if (p.dbg & 1) break;
+#endif
+                uint32_t r0[32], r1[32];
+                tc_ld_32x32b_x32(taddr + h * 64, r0);
+                tc_ld_32x32b_x32(taddr + h * 64 + 32, r1);
+                uint8_t* buf = my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
+                if (lane == 0) bulk_wait_group_read<1>();  // the store that used this buffer two chunks ago
+                __syncwarp();
                 tc_wait_ld();
-                const float4* cs = reinterpret_cast<const float4*>(p.col_scale + n);
-                const float4* cb = reinterpret_cast<const float4*>(p.col_bias + n);
-                uint32_t o[16];
+                const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
+                const float4* cb = reinterpret_cast<const float4*>(cvs + G_BN + h * 64);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float4 s4 = __ldg(cs + i);
-                    const float4 b4 = __ldg(cb + i);
-                    const float v0 = apply_act(fmaf(__uint_as_float(r[4 * i + 0]), s4.x, b4.x), p.activation);
-                    const float v1 = apply_act(fmaf(__uint_as_float(r[4 * i + 1]), s4.y, b4.y), p.activation);
-                    const float v2 = apply_act(fmaf(__uint_as_float(r[4 * i + 2]), s4.z, b4.z), p.activation);
-                    const float v3 = apply_act(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w), p.activation);
-                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
-                    __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
-                    o[2 * i] = *reinterpret_cast<uint32_t*>(&p0);
-                    o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
-                }
-                if (m < p.M) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                for (int j = 0; j < 8; ++j) {   // 16-byte chunk j = columns 8j .. 8j+7 of this 64-column block
+                    const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
+                    uint32_t o[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    for (int i = 0; i < 2; ++i) {
+                        const float4 s4 = cs[2 * j + i];
+                        const float4 b4 = cb[2 * j + i];
+                        const float v0 = apply_act(fmaf(__uint_as_float(r[4 * i + 0]), s4.x, b4.x), p.activation);
+                        const float v1 = apply_act(fmaf(__uint_as_float(r[4 * i + 1]), s4.y, b4.y), p.activation);
+                        const float v2 = apply_act(fmaf(__uint_as_float(r[4 * i + 2]), s4.z, b4.z), p.activation);
+                        const float v3 = apply_act(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w), p.activation);
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
+                        o[2 * i] = *reinterpret_cast<uint32_t*>(&p0);
+                        o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+                    }
+                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, n0 + h * 64, m0 + q * 32);
+                    bulk_commit_group();
+                }
+                ++nstore;
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tempty[as]);
+#ifdef SVDQ_PROF
+            if (threadIdx.x == 64) { PROF_ADD(4); p.prof[blockIdx.x * 8 + 7] += 1; }
+#endif
         }
+        if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
     }
 
     tc_fence_before_sync();
     __syncthreads();
+#ifdef SVDQ_PROF
+    if (threadIdx.x == 0) p.prof[blockIdx.x * 8 + 5] += clock64() - kt0;
+#endif
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, G_TMEM_COLS);
     }
 }
+
+#ifdef SVDQ_PROF
+extern "C" int svdq_debug_gemm_prof(long long* host, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(host, g_gemm_prof, sizeof(long long) * 148 * 8);
+    if (reset) {
+        static long long zeros[148 * 8] = {};
+        cudaMemcpyToSymbol(g_gemm_prof, zeros, sizeof(zeros));
+    }
+    return 0;
+}
+#endif
 
 int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     SVDQ_CHECK_ARG(a->out != nullptr, "gemm(nvfp4): `out` is required (next-layer requantisation is not built yet)");
@@ -310,6 +482,15 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.tiles_n = (a->N + G_BN - 1) / G_BN;
     p.activation = a->activation;
     if (int rc = status_words(&p.status)) return rc;
+#ifdef SVDQ_PROF
+    {
+        void* pp = nullptr;
+        SVDQ_CUDA(cudaGetSymbolAddress(&pp, g_gemm_prof));
+        p.prof = static_cast<long long*>(pp);
+        const char* e = getenv("SVDQ_DBG");
+        p.dbg = e ? atoi(e) : 0;
+    }
+#endif
 
     CUtensorMap tm_a, tm_b, tm_la, tm_lu;
     if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 128, G_BM)) return rc;
@@ -326,6 +507,9 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_la = tm_a;
         tm_lu = tm_b;
     }
+    CUtensorMap tm_out;
+    if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+        return rc;
     static bool attr_done[64] = {};
     if (dev < 64 && !attr_done[dev]) {
         SVDQ_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -334,7 +518,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     }
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int grid = num_tiles < sms ? num_tiles : sms;
-    gemm_nvfp4_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, p);
+    gemm_nvfp4_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, tm_out, p);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }

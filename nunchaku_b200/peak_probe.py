@@ -1,0 +1,56 @@
+"""Measure the tensor-pipe rate of tcgen05.mma on this GPU with operands resident in shared memory /
+TMEM (no loads): the measured dense peak that a GEMM's tensor-pipe fraction is judged against.
+
+    python -m nunchaku_b200.peak_probe
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+
+import torch
+
+from . import _lib
+
+KINDS = {"mxf4nvf4": (0, 64), "tf32": (1, 8), "i8": (2, 32)}
+
+
+def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_buffers: int = 1, grid: int | None = None):
+    lib = _lib.load()
+    lib.svdq_probe_mma_rate.restype = ctypes.c_int32
+    lib.svdq_probe_mma_rate.argtypes = [ctypes.c_int32] * 6 + [ctypes.c_void_p, ctypes.c_void_p]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    grid = grid or sms
+    cyc = torch.zeros(grid * 2, dtype=torch.int64, device=dev)
+    code, k = KINDS[kind]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(2):
+        e0.record()
+        _lib.check(lib.svdq_probe_mma_rate(code, n, iters, cps_per_group, sf_buffers, grid, cyc.data_ptr(),
+                                           torch.cuda.current_stream(dev).cuda_stream))
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    c = cyc.view(grid, 2).double().mean(0)
+    flops = 2.0 * 128 * n * k * 4 * iters * grid
+    return {
+        "kind": kind, "n": n, "cps_per_group": cps_per_group, "sf_buffers": sf_buffers,
+        "cycles_per_mma_issue": c[0].item() / (4 * iters), "cycles_per_mma": c[1].item() / (4 * iters),
+        "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms,
+    }
+
+
+def main():
+    out = []
+    for kind, n in [("mxf4nvf4", 256), ("mxf4nvf4", 192), ("mxf4nvf4", 128), ("i8", 256), ("i8", 128), ("tf32", 192)]:
+        out.append(mma_rate(kind, n))
+    for cps, bufs in [(4, 1), (12, 1), (12, 2)]:
+        out.append(mma_rate("mxf4nvf4", 192, cps_per_group=cps, sf_buffers=bufs))
+    for r in out:
+        print(json.dumps(r))
+    assert _lib.device_status() == (0, 0)
+
+
+if __name__ == "__main__":
+    main()
