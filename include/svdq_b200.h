@@ -73,7 +73,7 @@ int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* strea
  * sizes svdq_w4a4_prepared_bytes() reports.
  */
 typedef struct svdq_prepared_weights {
-    void* wgt;        /* uint8 [N, K/2] row-major codes                                    */
+    void* wgt;        /* NVFP4: uint8 [N, K/2] row-major codes; INT4: int8 [N, K], one code per byte */
     void* wscales;    /* NVFP4: 512-byte e4m3 atoms [N/128][K/64]; INT4: fp32 [K/64, N]    */
     float* lora_up;   /* fp32 [N, R32] (R32 = R rounded up to 32), pre-divided by col_scale */
     float* col_scale; /* fp32 [N] = alpha * wcscales                                       */

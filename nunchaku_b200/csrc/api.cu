@@ -55,7 +55,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, uint64_t rows, uint64_t row_bytes,
-                 uint32_t box_inner, uint32_t box_rows) {
+                 uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     SVDQ_CHECK_ARG(aligned(base, 16) && row_bytes % 16 == 0, "tensor map: base and row pitch must be 16-byte aligned");
@@ -64,7 +64,8 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, u
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, static_cast<CUtensorMapDataType>(elem), 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
     return SVDQ_OK;

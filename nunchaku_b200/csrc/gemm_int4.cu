@@ -1,12 +1,432 @@
-// INT4 (group 64) W4A4 GEMM, sm_100a -- placeholder until the kind::i8 kernel lands.
+// INT4 (group 64) W4A4 GEMM with the fused SVDQuant epilogue, sm_100a.
+//
+// What it computes (reference: gemm_w4a4_kernel, src/kernels/zgemm/gemm_w4a4.cuh:832-928,1046-1095;
+// scale application gemm_base.cuh:367-409; epilogue chain gemm_w4a4_launch_impl.cuh:172-420):
+//   acc[m, n] = sum_g ascale[m, g] * wscale[n, g] * ( sum_{k in group g} a[m, k] * w[n, k] )     s4|u4 x s4 -> s32
+//             + sum_r lora_act[m, r] * Wu[n, r]
+//   out[m, n] = act( acc[m, n] + bias[n] )
+// The reference accumulates the per-group terms in bf16; here they are accumulated in fp32.
+//
+// sm_100 has no 4-bit integer MMA kind, so the codes run through tcgen05.mma kind::i8:
+//   * weights are expanded to one signed byte per code once, at weight-preparation time (they are static);
+//   * activation codes stay packed in HBM (the public tensor) and are unpacked nibble -> byte in shared
+//     memory by four converter warps, straight into the 128B-swizzled K-major tile the MMA reads;
+//   * a group of 64 k is two K=32 MMAs into its own 128-column int32 TMEM buffer (4 buffers), and eight
+//     epilogue warps drain each group: int32 -> fp32 (magic-number add, no I2F), times ascale[m,g] *
+//     wscale[n,g], accumulated in registers.  The low-rank branch is one more "group": a kind::tf32 MMA of
+//     the fp32 lora_act and LoRA-up tiles whose fp32 result is added as is.
+// One persistent CTA per SM, 128 x 128 output tiles, K in steps of 128 (two groups per stage).
+//   warp 0       TMA producer      warp 1       MMA issuer       warps 2..5   nibble -> s8 converters
+//   warps 6..13  epilogue (lane quadrant = warp % 4, column half = (warp - 6) / 4)
+// The rescale work (M*N*K/64 fused multiply-adds on the SIMT pipes) is what bounds this kernel, not the
+// tensor pipe: that is the price of group-64 integer scales on a machine whose block-scaled MMA kinds only
+// exist for FP4/FP8 with power-of-two or E4M3 scales.
+#include <cuda_bf16.h>
+
 #include "host_common.h"
+#include "ptx.cuh"
 
 namespace svdq {
 
+constexpr int I_BM = 128;
+constexpr int I_BN = 128;
+constexpr int I_PK_STAGES = 4;                      // packed activation staging ring
+constexpr int I_PK_BYTES = I_BM * 64;               // 128 rows x 128 codes packed = 8 KB
+constexpr int I_U_STAGES = 3;                       // unpacked operand ring
+constexpr int I_A_BYTES = I_BM * 128;               // 16 KB (s8, 128 k per row)
+constexpr int I_B_BYTES = I_BN * 128;               // 16 KB
+constexpr int I_U_BYTES = I_A_BYTES + I_B_BYTES;
+constexpr int I_EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
+constexpr int I_EPI_BYTES = 8 * I_EPI_BUF_BYTES;
+constexpr int I_THREADS = 14 * 32;
+constexpr int I_TBUFS = 4;                          // TMEM group buffers of 128 columns
+constexpr size_t I_SMEM_BYTES =
+    1024 + static_cast<size_t>(I_U_STAGES) * I_U_BYTES + I_PK_STAGES * I_PK_BYTES + I_EPI_BYTES + 512;
+
+struct Int4Params {
+    const __nv_bfloat16* ascales;   // [K/64][M_pad]
+    const float* wscales;           // [K/64][N]
+    const float* col_bias;          // [N]
+    int* status;
+    int M, M_pad, N, K;
+    int lora_chunks;
+    int tiles_m, tiles_n;
+    int activation;
+    int act_unsigned;
+};
+
+struct Int4Shared {
+    uint64_t pk_full[I_PK_STAGES];
+    uint64_t pk_empty[I_PK_STAGES];
+    uint64_t b_full[I_U_STAGES];    // weights (or both low-rank tiles) of the stage have landed
+    uint64_t a_full[I_U_STAGES];    // converters have written the stage's activation tile
+    uint64_t u_empty[I_U_STAGES];   // MMAs that read the stage are done
+    uint64_t t_full[I_TBUFS];
+    uint64_t t_empty[I_TBUFS];
+    uint64_t drain;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+
+__device__ __forceinline__ bool i4_wait(uint64_t* bar, uint32_t parity, Int4Shared* sh, int* status, int where) {
+#pragma unroll 1
+    for (int i = 0; i < 512; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 128; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (sh->abort_flag) return false;
+        if (clock64() - t0 > 4000000000ll) {
+            sh->abort_flag = 1;
+            atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+            atomicExch(&status[1], where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ float i4_act(float v, int activation) {
+    if (activation == SVDQ_ACT_SILU) return v / (1.0f + __expf(-v));
+    if (activation == SVDQ_ACT_GELU) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.79788456f * (v + 0.044715f * v * v * v)));
+        return v * (0.5f + 0.5f * t);
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(I_THREADS, 1)
+gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
+                 const __grid_constant__ CUtensorMap tm_out, const Int4Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ubuf = smem;                                           // [I_U_STAGES][A 16K | B 16K]
+    uint8_t* epi_smem = ubuf + I_U_STAGES * I_U_BYTES;              // 8 x 4 KB, 1024-aligned
+    uint8_t* pkbuf = epi_smem + I_EPI_BYTES;                        // [I_PK_STAGES][8K]
+    Int4Shared* sh = reinterpret_cast<Int4Shared*>(pkbuf + I_PK_STAGES * I_PK_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kstages = p.K / 128;
+    const int per_tile = kstages + p.lora_chunks;       // stages per tile
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < I_PK_STAGES; ++s) {
+            mbar_init(&sh->pk_full[s], 1);
+            mbar_init(&sh->pk_empty[s], 4);
+        }
+        for (int s = 0; s < I_U_STAGES; ++s) {
+            mbar_init(&sh->b_full[s], 1);
+            mbar_init(&sh->a_full[s], 4);
+            mbar_init(&sh->u_empty[s], 1);
+        }
+        for (int i = 0; i < I_TBUFS; ++i) {
+            mbar_init(&sh->t_full[i], 1);
+            mbar_init(&sh->t_empty[i], 8);
+        }
+        mbar_init(&sh->drain, 1);
+        sh->abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+        prefetch_tmap(&tm_out);
+    }
+    if (warp == 1) {
+        tmem_alloc(&sh->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t it = 0, pk = 0;   // unpacked-ring position, packed-ring position
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * I_BM;
+                const int n0 = (tile / p.tiles_m) * I_BN;
+                for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                    const int u = it % I_U_STAGES;
+                    uint8_t* ub = ubuf + u * I_U_BYTES;
+                    if (ks < kstages) {
+                        // packed activations -> staging ring (independent of the unpacked ring's progress)
+                        const int s = pk % I_PK_STAGES;
+                        if (!i4_wait(&sh->pk_empty[s], ((pk / I_PK_STAGES) & 1) ^ 1, sh, p.status, 10)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&sh->pk_full[s], I_PK_BYTES);
+                        tma_load_2d(pkbuf + s * I_PK_BYTES, &tm_a, &sh->pk_full[s], ks * 64, m0);
+                        ++pk;
+                        if (!i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 11)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&sh->b_full[u], I_B_BYTES);
+                        tma_load_2d(ub + I_A_BYTES, &tm_b, &sh->b_full[u], ks * 128, n0);
+                    } else {
+                        const int c = ks - kstages;
+                        if (!i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 12)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&sh->b_full[u], I_A_BYTES + I_B_BYTES);
+                        tma_load_2d(ub, &tm_la, &sh->b_full[u], c * 32, m0);
+                        tma_load_2d(ub + I_A_BYTES, &tm_lu, &sh->b_full[u], c * 32, n0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_int8 = idesc_i8(I_BM, I_BN, !p.act_unsigned);
+            constexpr uint32_t IDESC_TF32 = idesc_tf32(I_BM, I_BN);
+            uint32_t it = 0, gq = 0;   // stage count, group (TMEM buffer) count
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (int ks = 0; ks < per_tile && ok; ++ks, ++it) {
+                    const int u = it % I_U_STAGES;
+                    if (!i4_wait(&sh->b_full[u], (it / I_U_STAGES) & 1, sh, p.status, 20) ||
+                        !i4_wait(&sh->a_full[u], (it / I_U_STAGES) & 1, sh, p.status, 21)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(ubuf + u * I_U_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + I_A_BYTES);
+                    const int ngroups = ks < kstages ? 2 : 1;
+                    for (int g = 0; g < ngroups; ++g, ++gq) {
+                        const uint32_t tb = gq % I_TBUFS;
+                        if (!i4_wait(&sh->t_empty[tb], ((gq / I_TBUFS) & 1) ^ 1, sh, p.status, 22)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t d = tmem + tb * 128;
+                        if (ks < kstages) {
+                            tc_mma_i8(d, adesc + 4 * g, bdesc + 4 * g, idesc_int8, 0);
+                            tc_mma_i8(d, adesc + 4 * g + 2, bdesc + 4 * g + 2, idesc_int8, 1);
+                        } else {
+                            for (int j = 0; j < 4; ++j) tc_mma_tf32(d, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j ? 1u : 0u);
+                        }
+                        tc_commit(&sh->t_full[tb]);
+                    }
+                    if (ok) tc_commit(&sh->u_empty[u]);
+                }
+            }
+            if (sh->abort_flag) {
+                tc_commit(&sh->drain);
+                mbar_wait(&sh->drain, 0, 400000000ll);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ converters (warps 2..5)
+        // 128 rows x 64 packed bytes -> 128 rows x 128 s8 bytes in the 128B-swizzled K-major layout.
+        // Task = one 16-byte chunk (32 codes); consecutive lanes take consecutive chunks of the staging tile.
+        const int ct = threadIdx.x - 64;   // 0..127
+        const bool is_signed = !p.act_unsigned;
+        uint32_t it = 0, pk = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                const int u = it % I_U_STAGES;
+                if (ks < kstages) {
+                    const int s = pk % I_PK_STAGES;
+                    if (!i4_wait(&sh->pk_full[s], (pk / I_PK_STAGES) & 1, sh, p.status, 30) ||
+                        !i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 31)) { ok = false; break; }
+                    const uint8_t* src = pkbuf + s * I_PK_BYTES;
+                    uint8_t* dst = ubuf + u * I_U_BYTES;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int idx = i * 128 + ct;
+                        const int row = idx >> 2, c = idx & 3;
+                        const uint4 w = *reinterpret_cast<const uint4*>(src + idx * 16);
+                        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+                        uint32_t o[8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t lo = ws[j] & 0x0F0F0F0Fu, hi = (ws[j] >> 4) & 0x0F0F0F0Fu;
+                            if (is_signed) {
+                                lo |= (lo & 0x08080808u) * 0x1Eu;
+                                hi |= (hi & 0x08080808u) * 0x1Eu;
+                            }
+                            o[2 * j] = __byte_perm(lo, hi, 0x5140);
+                            o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                        }
+                        uint8_t* drow = dst + row * 128;
+                        *reinterpret_cast<uint4*>(drow + (((2 * c) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(drow + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core (async proxy)
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&sh->pk_empty[s]);
+                        mbar_arrive(&sh->a_full[u]);
+                    }
+                    ++pk;
+                } else {
+                    // low-rank stage: both tiles come by TMA; still wait for the buffer's previous use so that
+                    // this barrier never runs a phase ahead of the MMA issuer
+                    if (!i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 32)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive(&sh->a_full[u]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 6..13)
+        const int q = warp & 3;            // TMEM lane quadrant
+        const int h = (warp - 6) >> 2;     // column half (64 columns)
+        uint8_t* buf = epi_smem + (warp - 6) * I_EPI_BUF_BYTES;
+        const int KB = p.K / 64;
+        uint32_t gq = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % p.tiles_m) * I_BM;
+            const int n0 = (tile / p.tiles_m) * I_BN;
+            const int m = m0 + q * 32 + lane;               // < M_pad always
+            const int nb = n0 + h * 64;
+            float acc[64];
+#pragma unroll
+            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+            const __nv_bfloat16* asp = p.ascales + m;
+            float as_next = __bfloat162float(asp[0]);
+            const int groups = KB + p.lora_chunks;
+            for (int g = 0; g < groups; ++g, ++gq) {
+                const uint32_t tb = gq % I_TBUFS;
+                const float as_g = as_next;
+                if (g + 1 < KB) as_next = __bfloat162float(asp[static_cast<size_t>(g + 1) * p.M_pad]);
+                if (!i4_wait(&sh->t_full[tb], (gq / I_TBUFS) & 1, sh, p.status, 40)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + tb * 128 + h * 64;
+                if (g < KB) {
+                    const float4* wsp = reinterpret_cast<const float4*>(p.wscales + static_cast<size_t>(g) * p.N + nb);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t r[32];
+                        tc_ld_32x32b_x32(taddr + half * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 w4 = __ldg(wsp + half * 8 + i);
+                            // int32 -> fp32 without I2F: |partial| <= 64*15*8 < 2^22, so 1.5*2^23 + p is exact
+                            const float x0 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 0])) - 12582912.0f;
+                            const float x1 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 1])) - 12582912.0f;
+                            const float x2 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 2])) - 12582912.0f;
+                            const float x3 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 3])) - 12582912.0f;
+                            acc[half * 32 + 4 * i + 0] = fmaf(x0, as_g * w4.x, acc[half * 32 + 4 * i + 0]);
+                            acc[half * 32 + 4 * i + 1] = fmaf(x1, as_g * w4.y, acc[half * 32 + 4 * i + 1]);
+                            acc[half * 32 + 4 * i + 2] = fmaf(x2, as_g * w4.z, acc[half * 32 + 4 * i + 2]);
+                            acc[half * 32 + 4 * i + 3] = fmaf(x3, as_g * w4.w, acc[half * 32 + 4 * i + 3]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t r[32];
+                        tc_ld_32x32b_x32(taddr + half * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[half * 32 + i] += __uint_as_float(r[i]);
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->t_empty[tb]);
+            }
+            if (!ok) break;
+            // bias + activation -> bf16 -> swizzled staging -> TMA store of this warp's 32 x 64 box
+            if (lane == 0) bulk_wait_group_read<0>();
+            __syncwarp();
+            if (nb < p.N) {
+                const float4* cb = reinterpret_cast<const float4*>(p.col_bias + nb);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float4 b4 = __ldg(cb + 2 * j + i);
+                        const float v0 = i4_act(acc[8 * j + 4 * i + 0] + b4.x, p.activation);
+                        const float v1 = i4_act(acc[8 * j + 4 * i + 1] + b4.y, p.activation);
+                        const float v2 = i4_act(acc[8 * j + 4 * i + 2] + b4.z, p.activation);
+                        const float v3 = i4_act(acc[8 * j + 4 * i + 3] + b4.w, p.activation);
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
+                        __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
+                        o[2 * i] = *reinterpret_cast<uint32_t*>(&p0);
+                        o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+                    }
+                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, nb, m0 + q * 32);
+                    bulk_commit_group();
+                }
+            }
+        }
+        if (lane == 0) bulk_wait_group<0>();
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
 int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
-    (void)a;
-    (void)stream;
-    return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): the INT4 tcgen05 kernel is not built yet");
+    SVDQ_CHECK_ARG(a->out != nullptr, "gemm(int4): `out` is required (next-layer requantisation is not built yet)");
+    if (a->qout || a->oscales || a->lora_act_out)
+        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): fused next-layer requantisation is not built yet");
+    SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): activations must be in SVDQ_LAYOUT_NATIVE "
+                                                        "(convert with svdq_w4a4_relayout_act)");
+    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
+
+    int dev = 0, sms = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+    Int4Params p = {};
+    p.ascales = static_cast<const __nv_bfloat16*>(a->ascales);
+    p.wscales = static_cast<const float*>(a->w.wscales);
+    p.col_bias = a->w.col_bias;
+    p.M = a->M;
+    p.M_pad = a->M_pad;
+    p.N = a->N;
+    p.K = a->K;
+    p.lora_chunks = (a->R + 31) / 32;
+    p.tiles_m = (a->M + I_BM - 1) / I_BM;
+    p.tiles_n = (a->N + I_BN - 1) / I_BN;
+    p.activation = a->activation;
+    p.act_unsigned = a->act_unsigned;
+    if (int rc = status_words(&p.status)) return rc;
+
+    CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
+    if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 64, I_BM, false)) return rc;
+    if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K, a->N, a->K, 128, I_BN)) return rc;
+    if (a->R > 0) {
+        const int R32 = (a->R + 31) / 32 * 32;
+        if (int rc = make_tmap_2d(&tm_la, a->lora_act_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
+                                  static_cast<uint64_t>(a->R) * 4, 32, I_BM))
+            return rc;
+        if (int rc = make_tmap_2d(&tm_lu, a->w.lora_up, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, R32, a->N,
+                                  static_cast<uint64_t>(R32) * 4, 32, I_BN))
+            return rc;
+    } else {
+        tm_la = tm_b;
+        tm_lu = tm_b;
+    }
+    if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+        return rc;
+    static bool attr_done[64] = {};
+    if (dev < 64 && !attr_done[dev]) {
+        SVDQ_CUDA(cudaFuncSetAttribute(gemm_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(I_SMEM_BYTES)));
+        attr_done[dev] = true;
+    }
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    gemm_int4_kernel<<<grid, I_THREADS, I_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
 }
 
 }  // namespace svdq

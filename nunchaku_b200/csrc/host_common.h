@@ -49,6 +49,6 @@ int status_words(int** ptr);
 // 2-D tiled tensor map: inner dimension contiguous, `row_bytes` between rows.
 // `elem` is a CUtensorMapDataType, box_inner*elem_size must be <= 128 with 128B swizzle.
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem /*CUtensorMapDataType*/, uint64_t inner,
-                 uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows);
+                 uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128 = true);
 
 }  // namespace svdq

@@ -34,6 +34,32 @@ __global__ void retile_wgt_codes_kernel(const uint32_t* __restrict__ src, uint32
     }
 }
 
+// INT4 weights: same source order, but expanded to one signed byte per code, row-major [N][K], so that
+// the kind::i8 GEMM streams them with TMA without a per-tile unpack (weights are static; activations are
+// unpacked in shared memory by the GEMM).
+__global__ void retile_wgt_codes_s8_kernel(const uint32_t* __restrict__ src, uint2* __restrict__ dst, int N, int K) {
+    const size_t total = static_cast<size_t>(N) * K / 8;
+    const int KB = K / 64;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t r = i;
+        const int kh = r & 1; r >>= 1;
+        const int half = r & 1; r >>= 1;
+        const int t = r & 3; r >>= 2;
+        const int g = r & 7; r >>= 3;
+        const int nt = r & 7; r >>= 3;
+        const int bk = r % KB;
+        const int bn = r / KB;
+        const int n = bn * 128 + nt * 16 + half * 8 + g;
+        const int k = bk * 64 + kh * 32 + t * 8;
+        const uint32_t w = src[i];
+        uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+        lo |= (lo & 0x08080808u) * 0x1Eu;   // sign-extend each nibble to a byte
+        hi |= (hi & 0x08080808u) * 0x1Eu;
+        dst[(static_cast<size_t>(n) * K + k) / 8] = make_uint2(__byte_perm(lo, hi, 0x5140), __byte_perm(lo, hi, 0x7362));
+    }
+}
+
 // NVFP4 weight micro-scales.  Reference (packer.py:303-360): [N/128][K/64][d 8][c 4][s 4] words, word = the 4
 // k-group bytes of row bn*128 + s*32 + c*8 + d.  Native: 512-byte atoms [N/128][K/64][r0 32][r1 4] words with
 // row = r1*32 + r0.
@@ -198,7 +224,7 @@ int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]) {
     SVDQ_CHECK_ARG(N > 0 && N % 128 == 0 && K > 0 && K % 128 == 0 && R >= 0 && R % 16 == 0,
                    "prepared_bytes: need N%%128==0, K%%128==0, R%%16==0 (N=%d K=%d R=%d)", N, K, R);
     const size_t R32 = (static_cast<size_t>(R) + 31) / 32 * 32;
-    bytes[0] = static_cast<size_t>(N) * K / 2;
+    bytes[0] = fp4 ? static_cast<size_t>(N) * K / 2 : static_cast<size_t>(N) * K;
     bytes[1] = fp4 ? static_cast<size_t>(N) * K / 16 : static_cast<size_t>(N) * (K / 64) * 4;
     bytes[2] = static_cast<size_t>(N) * R32 * 4;
     bytes[3] = static_cast<size_t>(N) * 4;
@@ -218,8 +244,12 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
                    "prepare_weights: tensors must be 16-byte aligned");
     if (int rc = check_arch()) return rc;
     const size_t words = static_cast<size_t>(a->N) * a->K / 8;
-    retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
-                                                                static_cast<uint32_t*>(o->wgt), a->N, a->K);
+    if (a->fp4)
+        retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                    static_cast<uint32_t*>(o->wgt), a->N, a->K);
+    else
+        retile_wgt_codes_s8_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                       static_cast<uint2*>(o->wgt), a->N, a->K);
     if (a->fp4) {
         const size_t sw = static_cast<size_t>(a->N) * a->K / 64;
         retile_wgt_mscales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint32_t*>(a->wscales),

@@ -135,3 +135,69 @@ def test_linear_module_end_to_end():
     q = R.ref_quantize(x, lin.smooth, lin.lora_down, fp4=True)
     assert R.rel_l2(y, R.ref_gemm(q, lin, M=M)) <= REL_L2_TIGHT
     assert R.rel_l2(y, x.float() @ lin.master.t() + lin.bias.float()) <= 0.12  # 4-bit quantisation error
+
+
+# ----------------------------------------------------------------------------- INT4 (group 64)
+@pytest.mark.parametrize("M,K,N,Rk,use_lora", [
+    (256, 128, 128, 32, False),
+    (256, 256, 384, 32, True),
+    (300, 512, 640, 16, True),
+    (1, 128, 256, 32, True),
+    (512, 640, 1280, 64, True),
+])
+def test_int4_gemm_matches_oracle(M, K, N, Rk, use_lora):
+    x, lin, q = problem(M, K, N, Rk, False, seed=M + N)
+    exp = R.ref_gemm(q, lin, M=M, use_lora=use_lora)
+    got = gemm(q, lin, M, use_lora=use_lora)
+    assert not torch.isnan(got).any()
+    assert R.rel_l2(got, exp) <= REL_L2_TIGHT
+
+
+def test_int4_exact_small_integers():
+    """All codes +-1..7 with unit scales: the int32 group sums and their fp32 total are exact."""
+    M, K, N = 256, 256, 256
+    g = torch.Generator().manual_seed(3)
+    acodes = torch.randint(0, 16, (M, K), generator=g, dtype=torch.uint8)
+    wcodes = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+    ones_a = torch.ones(K // 64, M, dtype=torch.bfloat16)
+    ones_w = torch.ones(K // 64, N, dtype=torch.bfloat16)
+    q = R.QuantOut(acodes, ones_a, torch.zeros(M, 32), False)
+    lin = R.Linear(K, N, 32, False, wcodes, ones_w, torch.ones(K, dtype=torch.bfloat16), torch.zeros(32, K, dtype=torch.bfloat16),
+                   torch.zeros(N, 32, dtype=torch.bfloat16), None)
+    exp = R.ref_gemm(q, lin, M=M, use_lora=False)          # |sum| <= 256*64 = 16384: needs 15 bits, bf16 has 8
+    got = gemm(q, lin, M, use_lora=False)
+    assert torch.equal(got, exp.to(torch.bfloat16).float())
+
+
+def test_int4_gemm_unsigned_activations_and_silu():
+    """u4 activation codes (the post-GELU shifted path of the reference, act_unsigned=True)."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops.gemm import svdq_gemm_w4a4_cuda
+
+    M, K, N = 300, 256, 384
+    lin = R.make_linear(K, N, 32, fp4=False, seed=8)
+    y = torch.rand(M, K) * 2.0          # non-negative "activated" values
+    q = R.ref_requantize(y, lin, M_pad=512, unsigned=True)
+    exp = R.ref_gemm(q, lin, M=M, act="silu")
+    sd = {k: v.cuda() for k, v in H.packed_params(lin).items()}
+    codes, scales, lora = [t.cuda() for t in H.pack_quant_out(q, "native")]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    svdq_gemm_w4a4_cuda(act=codes, wgt=sd["qweight"], out=out, ascales=scales, wscales=sd["wscales"], lora_act_in=lora,
+                        lora_up=sd["proj_up"], bias=sd["bias"], fp4=False, act_unsigned=True, fuse_silu=True,
+                        act_layout=_lib.LAYOUT_NATIVE)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert R.rel_l2(out.float().cpu(), exp) <= REL_L2_TIGHT
+
+
+def test_int4_headline_config0():
+    """BASELINE config 0: M=4096, K=3072, N=3072, rank 32, INT4 group 64, through the module."""
+    M, K, N = 4096, 3072, 3072
+    x = R.make_activations(M, K, seed=0)
+    lin = R.make_linear(K, N, 32, fp4=False, x_absmax=x.float().abs().amax(0), seed=0, mode="literal")
+    m = H.to_module(lin)
+    y = m(x.cuda().view(1, M, K)).float().cpu().view(M, N)
+    q = R.ref_quantize(x, lin.smooth, lin.lora_down, fp4=False)
+    rows = torch.arange(0, M, 8)
+    q_rows = R.QuantOut(q.codes[rows], q.scales[:, rows].contiguous(), q.lora_act[rows], False)
+    assert R.rel_l2(y[rows], R.ref_gemm(q_rows, lin)) <= REL_L2_TIGHT
