@@ -4,8 +4,11 @@
 // epilogue chain gemm_w4a4_launch_impl.cuh:172-420):
 //   D[m, n]   = sum_k a[m,k]*sa[m,k/16] * w[n,k]*sw[n,k/16]           E2M1 codes, UE4M3 group-16 scales
 //             + sum_r lora_act[m,r] * Wu'[n,r]                          low-rank branch, same accumulator
-//   out[m, n] = act( D[m,n] * col_scale[n] + col_bias[n] )             col_scale = alpha * wcscale
+//   y[m, n]   = act( D[m,n] * col_scale[n] + col_bias[n] )             col_scale = alpha * wcscale
 // (Wu' is the LoRA-up weight pre-divided by col_scale, so both branches share one fp32 accumulator.)
+// Plain epilogue: out = bf16(y).  Requantising epilogue (GELU + next layer, launch_impl.cuh:282-309,
+// gemm_w4a4.cuh:930-1043, lora.cuh:243-353): yb = bf16(y);  lora_act_out = yb @ Wd_next^T (fp32);
+// codes/scales = NVFP4 group quantisation of bf16(yb / smooth_next);  out (optional) = yb.
 //
 // How it maps to a B200 SM.  One persistent CTA per SM walks 128 x 192 output tiles.
 //   warp 0      producer: TMA loads of 128B-swizzled operand tiles (128 rows x 256 codes of A, 192 x 256 of
@@ -15,15 +18,21 @@
 //               the same TMEM accumulator; tcgen05.commit releases the stage / publishes the accumulator
 //   warps 6..9  scale-factor loaders: shared memory -> registers -> TMEM (tcgen05.st), one lane quadrant each
 //   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
-//               staging buffer, TMA store (coalesced, clipped at M and N by the hardware)
+//               staging buffer, TMA store (coalesced, clipped at M and N by the hardware); when requantising,
+//               the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix + mma.sync) and the
+//               thread's own row chunk is group-quantised in registers
 // TMEM: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
 // plus three 40-column scale-factor buffers (16 for A, 24 for B) = 504 of 512 columns.
+//
+// The next layer's LoRA-down is a sum over all N, i.e. over tiles of different CTAs.  It is kept
+// deterministic: in requantising mode every CTA owns a contiguous run of tiles in n-fastest order, adds up
+// its tiles of one 128-row block in registers, writes one partial per row block it touches to caller
+// scratch, and a second small kernel adds the partials in CTA order.
 #include <cuda_bf16.h>
-
-#include <cstdlib>
 
 #include "host_common.h"
 #include "ptx.cuh"
+#include "quant_common.cuh"
 
 namespace svdq {
 
@@ -43,14 +52,14 @@ constexpr int G_TM_SF = 2 * G_BN;               // 384: scale-factor buffers of 
 constexpr int G_TM_SF_STRIDE = 40;              // per buffer: 4 x 4 columns for A, 4 x 6 for B (one per 32 rows)
 constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
-constexpr int G_COLV_BYTES = 4 * 2 * G_BN * 4;              // per epilogue warp: {scale, bias} of the tile's columns
+constexpr int G_COLV_FLOATS = 3 * G_BN;                     // per epilogue warp: scale, bias, 1/smooth_next
+constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;
 constexpr size_t G_SMEM_BYTES =
     1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + G_EPI_BYTES + G_COLV_BYTES + 256;
 
 struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
     const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
-    __nv_bfloat16* out;       // [M, N]
     const float* col_scale;   // [N]
     const float* col_bias;    // [N]
     int* status;
@@ -58,20 +67,18 @@ struct GemmParams {
     int lora_chunks;          // number of 32-rank chunks of the low-rank branch (0 = none)
     int tiles_m, tiles_n;
     int activation;
-#ifdef SVDQ_PROF
-    long long* prof;
-    int dbg;
-#endif
+    int store_out;            // bf16 `out` is wanted
+    // tile schedule: 0: m-fastest, strided by gridDim; 1: n-fastest, each CTA a contiguous run of `run` tiles
+    int contiguous;
+    int run;
+    // requantising epilogue
+    uint8_t* qout;                      // [M_pad][N/2]
+    uint8_t* oscales;                   // scale atoms [M_pad/128][N/64][512]
+    const __nv_bfloat16* next_smooth;   // [N] reference-packed
+    const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
+    float* lora_partial;                // scratch [grid][slots][128][Rn]
+    int slots;
 };
-
-#ifdef SVDQ_PROF
-__device__ long long g_gemm_prof[148 * 8];
-#define PROF_T0() const long long pt0_ = clock64()
-#define PROF_ADD(i) p.prof[blockIdx.x * 8 + (i)] += clock64() - pt0_
-#else
-#define PROF_T0()
-#define PROF_ADD(i)
-#endif
 
 struct GemmShared {
     uint64_t full[G_STAGES];
@@ -84,6 +91,34 @@ struct GemmShared {
     uint32_t tmem_base;
     volatile int abort_flag;
 };
+
+struct TileRun {
+    int first, stride, count;
+};
+
+__device__ __forceinline__ TileRun tile_run(const GemmParams& p) {
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    TileRun r;
+    if (p.contiguous) {
+        r.first = blockIdx.x * p.run;
+        r.stride = 1;
+        r.count = max(0, min(p.run, num_tiles - r.first));
+    } else {
+        r.first = blockIdx.x;
+        r.stride = gridDim.x;
+        r.count = num_tiles > r.first ? (num_tiles - r.first + r.stride - 1) / r.stride : 0;
+    }
+    return r;
+}
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m0, int& n0) {
+    if (p.contiguous) {
+        m0 = (tile / p.tiles_n) * G_BM;
+        n0 = (tile % p.tiles_n) * G_BN;
+    } else {
+        m0 = (tile % p.tiles_m) * G_BM;
+        n0 = (tile / p.tiles_m) * G_BN;
+    }
+}
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
 #pragma unroll 1
@@ -117,6 +152,8 @@ __device__ __forceinline__ float apply_act(float v, int activation) {
     return v;
 }
 
+// RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
+template <int RTN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
@@ -131,8 +168,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int lane = threadIdx.x & 31;
     const int KB = p.K / 64;                         // 64-code blocks along K
     const int kstages = (KB + 3) / 4;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int per_tile = kstages + p.lora_chunks;
     const int NB = p.N / 128;                        // weight scale atoms along N
+    const TileRun tr = tile_run(p);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
@@ -166,28 +204,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
-#ifdef SVDQ_PROF
-    const long long kt0 = clock64();
-#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * G_BM;
-                const int n0 = (tile / p.tiles_m) * G_BN;
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
+                int m0, n0;
+                tile_coords(p, tr.first + ti * tr.stride, m0, n0);
                 const int atom0 = n0 >> 7;
-                for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+                for (int ks = 0; ks < per_tile; ++ks, ++it) {
                     const int s = it % G_STAGES;
-                    {
-                        PROF_T0();
-                        if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
-                            ok = false;
-                            break;
-                        }
-                        PROF_ADD(0);
+                    if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
+                        ok = false;
+                        break;
                     }
                     uint8_t* st = smem + s * G_STAGE_BYTES;
                     if (ks < kstages) {
@@ -215,27 +246,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (lane == 0) {
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
-            uint32_t it = 0, lt = 0, sq = 0;  // ring position, local tile count, scale-factor stage count
+            uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++lt) {
-                const uint32_t as = lt & 1;
-                {
-                    PROF_T0();
-                    if (!wait_or_abort(&sh->tempty[as], ((lt >> 1) & 1) ^ 1, sh, p.status, 20)) break;
-                    PROF_ADD(2);
-                }
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
+                const uint32_t as = ti & 1;
+                if (!wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem + as * G_TM_ACC1;
                 uint32_t accumulate = 0;
-                for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+                for (int ks = 0; ks < per_tile; ++ks, ++it) {
                     const int s = it % G_STAGES;
-                    {
-                        PROF_T0();
-                        if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
-                            ok = false;
-                            break;
-                        }
-                        PROF_ADD(1);
+                    if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
+                        ok = false;
+                        break;
                     }
                     const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
                     const uint64_t adesc = smem_desc_sw128(sa);
@@ -243,30 +266,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
                         const uint32_t b = sq % G_SF_BUFS;
-#ifdef SVDQ_PROF
-                        if (!(p.dbg & 16))
-#endif
-                        {
-                            PROF_T0();
-                            if (!wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22)) {
-                                ok = false;
-                                break;
-                            }
-                            PROF_ADD(6);
+                        if (!wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22)) {
+                            ok = false;
+                            break;
                         }
                         tc_fence_after_sync();
                         const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
                         const uint32_t t_sfb = t_sfa + 16;
-#ifdef SVDQ_PROF
-                        if (!(p.dbg & 4))
-#endif
                         for (int j = 0; j < nkb; ++j) {
                             tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j, accumulate);
                             accumulate = 1;
                         }
-#ifdef SVDQ_PROF
-                        if (!(p.dbg & 16))
-#endif
                         tc_commit(&sh->sf_empty[b]);
                         ++sq;
                     } else {
@@ -295,12 +305,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int q = warp & 3;
         uint32_t it = 0, sq = 0;
         bool ok = true;
-#ifdef SVDQ_PROF
-        if (p.dbg & 16) ok = false;
-#endif
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const bool mid_atom = (((tile / p.tiles_m) * G_BN) & 127) != 0;  // tile starts 64 rows into an atom
-            for (int ks = 0; ks < kstages + p.lora_chunks; ++ks, ++it) {
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            int m0, n0;
+            tile_coords(p, tr.first + ti * tr.stride, m0, n0);
+            const bool mid_atom = (n0 & 127) != 0;  // tile starts 64 rows into a 128-row atom
+            for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 if (ks >= kstages) continue;  // low-rank stages carry no scale factors
                 const int s = it % G_STAGES;
                 const uint32_t b = sq % G_SF_BUFS;
@@ -330,14 +339,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                 }
                 const uint32_t t_sf = tmem + (static_cast<uint32_t>(q * 32) << 16) + G_TM_SF + b * G_TM_SF_STRIDE;
-#ifdef SVDQ_PROF
-                if (!(p.dbg & 8))
-#endif
-                {
-                    tc_st_32x32b_x32(t_sf, r32);
-                    tc_st_32x32b_x8(t_sf + 32, r8);
-                    tc_wait_st();
-                }
+                tc_st_32x32b_x32(t_sf, r32);
+                tc_st_32x32b_x8(t_sf + 32, r8);
+                tc_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->sf_full[b]);
@@ -351,14 +355,58 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // hardware clips rows >= M and columns >= N).  Two staging buffers per warp keep a store in flight.
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         uint8_t* my_buf = epi_smem + q * 2 * G_EPI_BUF_BYTES;
-        uint32_t lt = 0, nstore = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++lt) {
-            const int m0 = (tile % p.tiles_m) * G_BM;
-            const int n0 = (tile / p.tiles_m) * G_BN;
-            const uint32_t as = lt & 1;
+        float* cvs = colv + q * G_COLV_FLOATS;
+        uint32_t nstore = 0;
+        // next layer's LoRA-down partial of this warp's 32 rows: [m-tile 2][rank tile][8]
+        constexpr int RTA = RTN > 0 ? RTN : 1;
+        float lacc[2][RTA][8];
+        int cur_m0 = -1, slot = 0;
+        auto lacc_zero = [&]() {
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int b = 0; b < RTA; ++b)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) lacc[a][b][c] = 0.f;
+        };
+        auto lacc_flush = [&]() {   // partial of row block cur_m0 -> scratch[blockIdx][slot][128][Rn]
+            if constexpr (RTN > 0) {
+                constexpr int RN = RTN * 16;
+                float* dst = p.lora_partial + (static_cast<size_t>(blockIdx.x) * p.slots + slot) * (G_BM * RN);
+                const int gq = lane >> 2, t = lane & 3;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int rt = 0; rt < RTN; ++rt)
+#pragma unroll
+                        for (int nh = 0; nh < 2; ++nh)
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                const int row = q * 32 + mt * 16 + gq + half * 8;
+                                const int rank = rt * 16 + nh * 8 + 2 * t;
+                                *reinterpret_cast<float2*>(dst + row * RN + rank) =
+                                    make_float2(lacc[mt][rt][nh * 4 + half * 2], lacc[mt][rt][nh * 4 + half * 2 + 1]);
+                            }
+                ++slot;
+            }
+        };
+        lacc_zero();
+
+        for (int ti = 0; ti < tr.count; ++ti) {
+            int m0, n0;
+            tile_coords(p, tr.first + ti * tr.stride, m0, n0);
+            const uint32_t as = ti & 1;
+            if constexpr (RTN > 0) {
+                if (m0 != cur_m0) {
+                    if (cur_m0 >= 0) {
+                        lacc_flush();
+                        lacc_zero();
+                    }
+                    cur_m0 = m0;
+                }
+            }
             // per-column constants of this tile -> this warp's shared-memory copy (issued before the
             // accumulator is needed, so the latency hides behind the wait)
-            float* cvs = colv + q * 2 * G_BN;
 #pragma unroll
             for (int i = 0; i < 3; ++i) {
                 const int e = lane + 32 * i;            // 0..95: 48 float4 of scale, then 48 of bias
@@ -367,23 +415,23 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 if (n0 + c4 < p.N) v = __ldg(reinterpret_cast<const float4*>((which ? p.col_bias : p.col_scale) + n0 + c4));
                 *reinterpret_cast<float4*>(cvs + which * G_BN + c4) = v;
             }
-            __syncwarp();
-            {
-                PROF_T0();
-                if (!wait_or_abort(&sh->tfull[as], (lt >> 1) & 1, sh, p.status, 30)) break;
-#ifdef SVDQ_PROF
-                if (threadIdx.x == 64) PROF_ADD(3);
-#endif
+            if constexpr (RTN > 0) {
+#pragma unroll
+                for (int i = 0; i < G_BN / 32; ++i) {
+                    const int n = n0 + lane + 32 * i;
+                    float r = 0.f;
+                    if (n < p.N) r = __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)]));
+                    cvs[2 * G_BN + lane + 32 * i] = r;
+                }
             }
-            PROF_T0();
+            __syncwarp();
+            if (!wait_or_abort(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
+            const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
 #pragma unroll 1
             for (int h = 0; h < G_BN / 64; ++h) {
                 if (n0 + h * 64 >= p.N) break;
-#ifdef SVDQ_PROF
-                if (p.dbg & 1) break;
-#endif
                 uint32_t r0[32], r1[32];
                 tc_ld_32x32b_x32(taddr + h * 64, r0);
                 tc_ld_32x32b_x32(taddr + h * 64 + 32, r1);
@@ -393,10 +441,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tc_wait_ld();
                 const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
                 const float4* cb = reinterpret_cast<const float4*>(cvs + G_BN + h * 64);
+                uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {   // 16-byte chunk j = columns 8j .. 8j+7 of this 64-column block
                     const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
-                    uint32_t o[4];
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const float4 s4 = cs[2 * j + i];
@@ -407,70 +455,175 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         const float v3 = apply_act(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w), p.activation);
                         __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
                         __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
-                        o[2 * i] = *reinterpret_cast<uint32_t*>(&p0);
-                        o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+                        ow[4 * j + 2 * i] = *reinterpret_cast<uint32_t*>(&p0);
+                        ow[4 * j + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
                     }
-                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                        make_uint4(ow[4 * j], ow[4 * j + 1], ow[4 * j + 2], ow[4 * j + 3]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    if (m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, n0 + h * 64, m0 + q * 32);
+                    if (p.store_out && m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, n0 + h * 64, m0 + q * 32);
                     bulk_commit_group();
                 }
                 ++nstore;
+
+                if constexpr (RTN > 0) {
+                    // ---- next layer's LoRA-down on the staged bf16 tile: [32 x 64] x Wd_next[64 x Rn]
+                    const int ch_tile0 = (n0 + h * 64) >> 4;           // 16-channel tile index of the chunk
+                    const uint32_t bufa = smem_u32(buf);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        uint4 bfrag[RTA];
+#pragma unroll
+                        for (int rt = 0; rt < RTN; ++rt)
+                            bfrag[rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * RTN + rt) * 32 + lane);
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            const int arow = mt * 16 + (lane & 15);
+                            uint32_t a[4];
+                            ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
+#pragma unroll
+                            for (int rt = 0; rt < RTN; ++rt) {
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[rt].x, bfrag[rt].y);
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[rt].z, bfrag[rt].w);
+                            }
+                        }
+                    }
+                    // ---- NVFP4 group quantisation of this thread's 64 values (4 groups of 16)
+                    const float4* rcn = reinterpret_cast<const float4*>(cvs + 2 * G_BN + h * 64);
+                    uint32_t codes[8];
+                    uint32_t sw = 0;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint32_t xw[8] = {ow[8 * g], ow[8 * g + 1], ow[8 * g + 2], ow[8 * g + 3],
+                                                ow[8 * g + 4], ow[8 * g + 5], ow[8 * g + 6], ow[8 * g + 7]};
+                        __nv_bfloat162 qv[8];
+                        const float amax = smooth16(xw, rcn + 4 * g, qv);
+                        uint32_t cw[2];
+                        sw |= nvfp4_encode16(qv, amax, cw) << (8 * g);
+                        codes[2 * g] = cw[0];
+                        codes[2 * g + 1] = cw[1];
+                    }
+                    uint4* qdst = reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(grow) * (p.N >> 1) + ((n0 + h * 64) >> 1));
+                    qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                    qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                    const size_t soff = (static_cast<size_t>(grow >> 7) * (p.N >> 6) + ((n0 + h * 64) >> 6)) * 512 +
+                                        (grow & 31) * 16 + ((grow >> 5) & 3) * 4;
+                    *reinterpret_cast<uint32_t*>(p.oscales + soff) = sw;
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tempty[as]);
-#ifdef SVDQ_PROF
-            if (threadIdx.x == 64) { PROF_ADD(4); p.prof[blockIdx.x * 8 + 7] += 1; }
-#endif
+        }
+        if constexpr (RTN > 0) {
+            if (cur_m0 >= 0) lacc_flush();
         }
         if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
     }
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef SVDQ_PROF
-    if (threadIdx.x == 0) p.prof[blockIdx.x * 8 + 5] += clock64() - kt0;
-#endif
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, G_TMEM_COLS);
     }
 }
 
-#ifdef SVDQ_PROF
-extern "C" int svdq_debug_gemm_prof(long long* host, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(host, g_gemm_prof, sizeof(long long) * 148 * 8);
-    if (reset) {
-        static long long zeros[148 * 8] = {};
-        cudaMemcpyToSymbol(g_gemm_prof, zeros, sizeof(zeros));
+// lora_act_out[row][r] = sum over the CTAs that touched the row's 128-row block, in CTA order, of their partial.
+// Row block mb holds tiles [mb*tiles_n, (mb+1)*tiles_n); CTA c owns tiles [c*run, (c+1)*run).
+__global__ void lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n,
+                                           int run, int slots, int grid_ctas) {
+    const int mb = blockIdx.x;
+    const int c_lo = (mb * tiles_n) / run;
+    const int c_hi = min(grid_ctas - 1, ((mb + 1) * tiles_n - 1) / run);
+    for (int i = threadIdx.x; i < G_BM * rn; i += blockDim.x) {
+        float s = 0.f;
+        for (int c = c_lo; c <= c_hi; ++c) {
+            const int first_mb = (c * run) / tiles_n;
+            s += partial[(static_cast<size_t>(c) * slots + (mb - first_mb)) * (G_BM * rn) + i];
+        }
+        out[static_cast<size_t>(mb) * G_BM * rn + i] = s;
     }
-    return 0;
 }
-#endif
+
+struct NvfpPlan {
+    int requant, tiles_m, tiles_n, grid, run, slots, rn;
+    size_t workspace;
+};
+
+static void plan_nvfp4(const svdq_gemm_args* a, int sms, NvfpPlan* pl) {
+    pl->requant = a->qout != nullptr;
+    pl->tiles_n = (a->N + G_BN - 1) / G_BN;
+    pl->tiles_m = pl->requant ? a->M_pad / G_BM : (a->M + G_BM - 1) / G_BM;
+    const int num_tiles = pl->tiles_m * pl->tiles_n;
+    pl->grid = num_tiles < sms ? num_tiles : sms;
+    pl->run = (num_tiles + pl->grid - 1) / pl->grid;
+    if (pl->requant) pl->grid = (num_tiles + pl->run - 1) / pl->run;
+    pl->slots = (pl->run + pl->tiles_n - 2) / pl->tiles_n + 1;
+    pl->rn = a->R_next;
+    pl->workspace = pl->requant ? static_cast<size_t>(pl->grid) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
+}
+
+int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
+    int dev = 0, sms = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    NvfpPlan pl;
+    plan_nvfp4(a, sms, &pl);
+    *bytes = pl.workspace;
+    return SVDQ_OK;
+}
+
+template <int RTN>
+static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
+                        const CUtensorMap& lu, const CUtensorMap& o, const GemmParams& p) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_done[dev]) {
+        SVDQ_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel<RTN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(G_SMEM_BYTES)));
+        attr_done[dev] = true;
+    }
+    gemm_nvfp4_kernel<RTN><<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(a, b, la, lu, o, p);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
 
 int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
-    SVDQ_CHECK_ARG(a->out != nullptr, "gemm(nvfp4): `out` is required (next-layer requantisation is not built yet)");
-    if (a->qout || a->oscales || a->lora_act_out)
-        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): fused next-layer requantisation is not built yet");
+    const bool requant = a->qout != nullptr;
+    SVDQ_CHECK_ARG(a->out != nullptr || requant, "gemm(nvfp4): neither `out` nor `qout` given");
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                          "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(!a->act_unsigned, "gemm(nvfp4): act_unsigned is INT4 only (gemm_w4a4_launch_impl.cuh:127)");
     SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
+    if (requant) {
+        SVDQ_CHECK_ARG(a->oscales && a->lora_act_out && a->next_smooth && a->next_lora_down,
+                       "gemm(nvfp4): requantisation needs oscales, lora_act_out, next_smooth and next_lora_down");
+        SVDQ_CHECK_ARG(a->next_fp4, "gemm(nvfp4): the requantised output must be NVFP4 as well");
+        SVDQ_CHECK_ARG(a->out_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): requantised output is written in SVDQ_LAYOUT_NATIVE");
+        SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
+                           aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
+                       "gemm(nvfp4): requantisation tensors must be 16-byte aligned (workspace: 256)");
+        if (a->R_next != 16 && a->R_next != 32 && a->R_next != 64)
+            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
+    }
 
     int dev = 0, sms = 0;
     SVDQ_CUDA(cudaGetDevice(&dev));
     SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    NvfpPlan pl;
+    plan_nvfp4(a, sms, &pl);
+    SVDQ_CHECK_ARG(!requant || (a->workspace && a->workspace_bytes >= pl.workspace),
+                   "gemm(nvfp4): workspace of %zu bytes required (svdq_gemm_w4a4_workspace_bytes)", pl.workspace);
 
     GemmParams p = {};
     p.sfa = static_cast<const uint8_t*>(a->ascales);
     p.sfb = static_cast<const uint8_t*>(a->w.wscales);
-    p.out = static_cast<__nv_bfloat16*>(a->out);
     p.col_scale = a->w.col_scale;
     p.col_bias = a->w.col_bias;
     p.M = a->M;
@@ -478,21 +631,21 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.N = a->N;
     p.K = a->K;
     p.lora_chunks = (a->R + 31) / 32;
-    p.tiles_m = (a->M + G_BM - 1) / G_BM;
-    p.tiles_n = (a->N + G_BN - 1) / G_BN;
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
     p.activation = a->activation;
+    p.store_out = a->out != nullptr;
+    p.contiguous = requant;
+    p.run = pl.run;
+    p.qout = static_cast<uint8_t*>(a->qout);
+    p.oscales = static_cast<uint8_t*>(a->oscales);
+    p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
+    p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
+    p.lora_partial = static_cast<float*>(a->workspace);
+    p.slots = pl.slots;
     if (int rc = status_words(&p.status)) return rc;
-#ifdef SVDQ_PROF
-    {
-        void* pp = nullptr;
-        SVDQ_CUDA(cudaGetSymbolAddress(&pp, g_gemm_prof));
-        p.prof = static_cast<long long*>(pp);
-        const char* e = getenv("SVDQ_DBG");
-        p.dbg = e ? atoi(e) : 0;
-    }
-#endif
 
-    CUtensorMap tm_a, tm_b, tm_la, tm_lu;
+    CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
     if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 128, G_BM)) return rc;
     if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->N, a->K / 2, 128, G_BN)) return rc;
     if (a->R > 0) {
@@ -507,19 +660,23 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_la = tm_a;
         tm_lu = tm_b;
     }
-    CUtensorMap tm_out;
-    if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
-        return rc;
-    static bool attr_done[64] = {};
-    if (dev < 64 && !attr_done[dev]) {
-        SVDQ_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(G_SMEM_BYTES)));
-        attr_done[dev] = true;
+    if (a->out) {
+        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+            return rc;
+    } else {
+        tm_out = tm_a;
     }
-    const int num_tiles = p.tiles_m * p.tiles_n;
-    const int grid = num_tiles < sms ? num_tiles : sms;
-    gemm_nvfp4_kernel<<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    SVDQ_CUDA(cudaGetLastError());
+    int rc;
+    if (!requant) rc = launch_nvfp4<0>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 16) rc = launch_nvfp4<1>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 32) rc = launch_nvfp4<2>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else rc = launch_nvfp4<4>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    if (rc) return rc;
+    if (requant) {
+        lora_partial_reduce_kernel<<<pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
+                                                                  pl.slots, pl.grid);
+        SVDQ_CUDA(cudaGetLastError());
+    }
     return SVDQ_OK;
 }
 
