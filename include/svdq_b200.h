@@ -129,6 +129,23 @@ int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes);
 int svdq_gemm_w4a4(const svdq_gemm_args* args, void* stream);
 
 /*
+ * The same GEMM for callers that cannot supply `workspace`: a host that divided up its device memory at
+ * start-up and has no allocator to call per request, or one that may not make allocation calls once it is
+ * serving.  The scratch the requantising epilogue needs (per-CTA partial sums of the next layer's LoRA-down)
+ * then comes from an array inside the library: SVDQ_STATIC_SCRATCH_BYTES (8 MiB) of device memory on every GPU
+ * that loads the library, kept until the process ends.  args->workspace / workspace_bytes are ignored; inputs
+ * and outputs are still the caller's.  No counterpart in the reference, which allocates nothing in this op
+ * because its LoRA-down uses atomics.
+ *   - Limit: problems that need more than SVDQ_STATIC_SCRATCH_BYTES (see svdq_gemm_w4a4_workspace_bytes) are
+ *     refused with SVDQ_ERR_INVALID_ARGUMENT; NVFP4 only.
+ *   - The first call on each device looks up the array's device address; make that call before starting any
+ *     stream capture.
+ *   - All calls share the array: do not let two of them run on the same GPU at the same time.
+ */
+#define SVDQ_STATIC_SCRATCH_BYTES (8u << 20)
+int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* stream);
+
+/*
  * Activation-side layout conversion (codes, scales, low-rank activations) between
  * SVDQ_LAYOUT_REFERENCE and SVDQ_LAYOUT_NATIVE; no counterpart in the reference,
  * where only one order exists.  NULL pairs are skipped.

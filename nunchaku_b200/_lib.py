@@ -124,6 +124,7 @@ EXPORTS = {
     "svdq_w4a4_prepare_weights": (c_int32, [POINTER(WeightsArgs), POINTER(PreparedWeights), c_void_p]),
     "svdq_gemm_w4a4_workspace_bytes": (c_int32, [POINTER(GemmArgs), POINTER(c_size_t)]),
     "svdq_gemm_w4a4": (c_int32, [POINTER(GemmArgs), c_void_p]),
+    "svdq_gemm_w4a4_static_scratch": (c_int32, [POINTER(GemmArgs), c_void_p]),
     "svdq_w4a4_relayout_act": (c_int32, [POINTER(RelayoutArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),

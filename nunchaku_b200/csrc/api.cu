@@ -72,7 +72,7 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, u
     return SVDQ_OK;
 }
 
-static int check_gemm_common(const svdq_gemm_args* a) {
+int check_gemm_common(const svdq_gemm_args* a) {
     SVDQ_CHECK_ARG(a != nullptr, "gemm: null args");
     SVDQ_CHECK_ARG(a->act && a->ascales && a->w.wgt && a->w.wscales && a->w.col_scale && a->w.col_bias,
                    "gemm: null tensor pointer");

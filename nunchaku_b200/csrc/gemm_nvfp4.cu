@@ -30,6 +30,8 @@
 // scratch, and a second small kernel adds the partials in CTA order.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "host_common.h"
 #include "ptx.cuh"
 #include "quant_common.cuh"
@@ -681,3 +683,66 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 }
 
 }  // namespace svdq
+
+// ---------------------------------------------------------------------------------------------------
+// svdq_gemm_w4a4_static_scratch: the requantising NVFP4 GEMM for hosts that have no way to hand over a
+// workspace.  Think of a C or C++ serving loop that carved up its device memory once at start-up and has no
+// allocator to ask per call, of a host whose policy forbids allocation calls after initialisation (they can
+// synchronise the device), or of an op layer that is only ever given the operator's tensors.  For them the
+// per-CTA LoRA-down partials live in a library-owned array in device memory instead of args->workspace.
+//
+// The array is a file-scope __device__ symbol: SVDQ_STATIC_SCRATCH_BYTES of device memory on every GPU that
+// loads this library, held until the process exits.  On the host its name is only a handle, not an address,
+// so the device address is looked up with cudaGetSymbolAddress - once per device, on the first call made with
+// that device current.  That first call per device should therefore happen before any stream capture begins.
+// Nothing is allocated or freed, here or in anything this calls.
+//
+// All calls share the one array.  Every partial a launch reads was written earlier by the same launch, so
+// nothing has to be cleared between calls; but two launches that are in flight on the same GPU at the same
+// time (different streams) would overwrite each other's partials: callers must not overlap them.
+// Problems whose partials do not fit are refused with SVDQ_ERR_INVALID_ARGUMENT.
+// ---------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[SVDQ_STATIC_SCRATCH_BYTES];
+
+namespace svdq {
+
+static int static_scratch_ptr(void** out) {
+    static std::mutex mu;
+    static void* ptrs[64] = {};
+    int dev = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(SVDQ_ERR_UNSUPPORTED, "static scratch: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        SVDQ_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));   // device address of the symbol on the current device
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return SVDQ_OK;
+}
+
+}  // namespace svdq
+
+extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* stream) {
+    using namespace svdq;
+    if (int rc = check_gemm_common(args)) return rc;
+    if (!args->fp4)
+        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(static scratch): only the NVFP4 GEMM has a variant with library-owned scratch");
+    size_t need = 0;
+    if (args->qout) {
+        if (int rc = gemm_nvfp4_workspace_bytes(args, &need)) return rc;
+    }
+    if (need > SVDQ_STATIC_SCRATCH_BYTES)
+        return fail(SVDQ_ERR_INVALID_ARGUMENT,
+                    "gemm(static scratch): this problem needs %zu bytes of scratch, the built-in array holds %u; "
+                    "use svdq_gemm_w4a4 with a caller workspace",
+                    need, SVDQ_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int rc = static_scratch_ptr(&scratch)) return rc;
+    svdq_gemm_args local = *args;
+    local.workspace = scratch;
+    local.workspace_bytes = SVDQ_STATIC_SCRATCH_BYTES;
+    return gemm_nvfp4_impl(&local, static_cast<cudaStream_t>(stream));
+}
+

@@ -51,4 +51,7 @@ int status_words(int** ptr);
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem /*CUtensorMapDataType*/, uint64_t inner,
                  uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128 = true);
 
+// Pointer / shape / alignment / architecture checks shared by the GEMM entry points.
+int check_gemm_common(const svdq_gemm_args* a);
+
 }  // namespace svdq
