@@ -345,6 +345,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tc_st_32x32b_x8(t_sf + 32, r8);
                 tc_wait_st();
                 tc_fence_before_sync();
+                fence_proxy_async_smem();   // generic reads of the stage above, TMA refill below the MMA's commit
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->sf_full[b]);
                 ++sq;
@@ -501,7 +502,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     for (int g = 0; g < 4; ++g) {
                         const uint32_t xw[8] = {ow[8 * g], ow[8 * g + 1], ow[8 * g + 2], ow[8 * g + 3],
                                                 ow[8 * g + 4], ow[8 * g + 5], ow[8 * g + 6], ow[8 * g + 7]};
-                        __nv_bfloat162 qv[8];
+                        uint32_t qv[8];
                         const float amax = smooth16(xw, rcn + 4 * g, qv);
                         uint32_t cw[2];
                         sw |= nvfp4_encode16(qv, amax, cw) << (8 * g);

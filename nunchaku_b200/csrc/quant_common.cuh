@@ -37,47 +37,75 @@ __device__ __forceinline__ int packed_vec_pos(int n) {
     return (n & ~15) | (((n >> 1) & 3) << 2) | (((n >> 3) & 1) << 1) | (n & 1);
 }
 
+// Eight fp32 values -> eight E2M1 nibbles in one word (lowest nibble = first value).
+__device__ __forceinline__ uint32_t e2m1x8(float2 a, float2 b, float2 c, float2 d) {
+    uint32_t r;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+        : "=r"(r)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y), "f"(d.x), "f"(d.y));
+    return r;
+}
+
+// |result| = max(|a|, |b|) per bf16 lane (the sign of the result is meaningless): one instruction per
+// pair instead of two abs and a max.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
 // 16 bf16 values (8 packed words, low half = lower column) times their 16 reciprocal smoothing factors
 // (fp32, 16-byte aligned), rounded to bf16: q[] and the group's absolute maximum.
 // "x * rcp + 0.0f" as one FMA: the reference adds a bf16 zero shift before dividing, which turns -0 into +0.
-__device__ __forceinline__ float smooth16(const uint32_t (&xw)[8], const float4* rc, __nv_bfloat162 (&q)[8]) {
-    __nv_bfloat162 mx = __floats2bfloat162_rn(0.f, 0.f);
+// Packed fp32x2 arithmetic (two IEEE operations per instruction on sm_100).
+__device__ __forceinline__ float smooth16(const uint32_t (&xw)[8], const float4* rc, uint32_t (&q)[8]) {
+    uint32_t mx = 0u;
+    const float2 zero = make_float2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float4 r4 = rc[i];
-        const float a0 = fmaf(__uint_as_float(xw[2 * i] << 16), r4.x, 0.0f);
-        const float a1 = fmaf(__uint_as_float(xw[2 * i] & 0xffff0000u), r4.y, 0.0f);
-        const float a2 = fmaf(__uint_as_float(xw[2 * i + 1] << 16), r4.z, 0.0f);
-        const float a3 = fmaf(__uint_as_float(xw[2 * i + 1] & 0xffff0000u), r4.w, 0.0f);
-        q[2 * i] = __floats2bfloat162_rn(a0, a1);
-        q[2 * i + 1] = __floats2bfloat162_rn(a2, a3);
-        mx = __hmax2(mx, __hmax2(__habs2(q[2 * i]), __habs2(q[2 * i + 1])));
+        const float2 a = __ffma2_rn(bf16x2_to_float2(xw[2 * i]), make_float2(r4.x, r4.y), zero);
+        const float2 b = __ffma2_rn(bf16x2_to_float2(xw[2 * i + 1]), make_float2(r4.z, r4.w), zero);
+        __nv_bfloat162 qa = __float22bfloat162_rn(a), qb = __float22bfloat162_rn(b);
+        q[2 * i] = *reinterpret_cast<uint32_t*>(&qa);
+        q[2 * i + 1] = *reinterpret_cast<uint32_t*>(&qb);
+        mx = absmax_bf16x2(mx, q[2 * i]);
+        mx = absmax_bf16x2(mx, q[2 * i + 1]);
     }
-    return fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+    const float2 m = bf16x2_to_float2(mx);
+    return fmaxf(fabsf(m.x), fabsf(m.y));
 }
 
 // NVFP4 group of 16: E4M3 scale byte and two words of E2M1 codes (lowest nibble = lowest column).
-__device__ __forceinline__ uint32_t nvfp4_encode16(const __nv_bfloat162 (&q)[8], float amax, uint32_t (&cw)[2]) {
+__device__ __forceinline__ uint32_t nvfp4_encode16(const uint32_t (&q)[8], float amax, uint32_t (&cw)[2]) {
     const float scale = fminf(amax * (1.0f / 6.0f), 448.0f);
     const float rs = scale == 0.f ? 0.f : __frcp_rn(scale);
-    cw[0] = cw[1] = 0u;
+    const float2 rs2 = make_float2(rs, rs);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float2 f = __bfloat1622float2(q[i]);
-        cw[i >> 2] |= e2m1x2(f.x * rs, f.y * rs) << ((i & 3) * 8);
-    }
+    for (int w = 0; w < 2; ++w)
+        cw[w] = e2m1x8(__fmul2_rn(bf16x2_to_float2(q[4 * w]), rs2), __fmul2_rn(bf16x2_to_float2(q[4 * w + 1]), rs2),
+                       __fmul2_rn(bf16x2_to_float2(q[4 * w + 2]), rs2), __fmul2_rn(bf16x2_to_float2(q[4 * w + 3]), rs2));
     return static_cast<uint32_t>(__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3));
 }
 
 // INT4 codes of 16 values given the group's (64-wide) absolute maximum; returns the fp32 scale.
 template <bool UNSIGNED>
-__device__ __forceinline__ float int4_encode16(const __nv_bfloat162 (&q)[8], float amax, uint32_t (&cw)[2]) {
+__device__ __forceinline__ float int4_encode16(const uint32_t (&q)[8], float amax, uint32_t (&cw)[2]) {
     const float scale = amax * (UNSIGNED ? (1.0f / 15.0f) : (1.0f / 7.0f));
     const float rs = scale == 0.f ? 0.f : __frcp_rn(scale);
     cw[0] = cw[1] = 0u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float2 f = __bfloat1622float2(q[i]);
+        const float2 f = bf16x2_to_float2(q[i]);
         int c0 = __float2int_rn(f.x * rs), c1 = __float2int_rn(f.y * rs);
         if (UNSIGNED) {
             c0 = max(0, min(15, c0));

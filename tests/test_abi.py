@@ -97,11 +97,11 @@ def test_quantiser_launch_plan(lib):
         assert rc == 0
         return ks.value, nst.value, smem.value
 
-    k, n, s = plan(4608, 3072, 32)       # 36 row blocks x 4 = 144 CTAs on 148 SMs
-    assert k == 4 and n >= 4 and s <= 227 * 1024
-    k, n, s = plan(36864, 3072, 32)      # batch 8: 288 row blocks already fill two waves
+    k, n, s = plan(4608, 3072, 32)       # 72 row blocks x cluster of 2 = 144 CTAs on 148 SMs, one wave
+    assert k == 2 and n >= 4 and s <= 227 * 1024
+    k, n, s = plan(36864, 3072, 32)      # batch 8: 576 row blocks already fill four waves
     assert k == 1 and s <= 227 * 1024
-    k, n, s = plan(256, 128, 32)         # tiny problem: K has only 2 blocks
-    assert k in (1, 2) and n >= 1
+    k, n, s = plan(256, 128, 32)         # tiny problem: K is a single 128-column chunk
+    assert k == 1 and n >= 1
     k, n, s = plan(4608, 12288, 128)
-    assert s <= 227 * 1024 and n * 16384 >= 128 * 128 * 4 or k == 1
+    assert s <= 227 * 1024 and n * 16384 >= 64 * 128 * 4

@@ -31,7 +31,8 @@ def run_case(M, K, Rk, fp4, layout, x=None, seed=0):
     assert torch.equal(codes.cpu(), ec), "packed 4-bit codes differ from the oracle"
     assert torch.equal(scales.cpu().view(view), es.view(view)), "scale bytes differ from the oracle"
     err = (lora.cpu() - el).abs().max().item()
-    assert err <= LORA_RTOL * max(el.abs().max().item(), 1.0) + 1e-6
+    tol = LORA_RTOL * max(el.abs().max().item(), 1.0) + 1e-6
+    assert err <= tol, f"lora_act M={M} K={K} R={Rk} fp4={fp4} {layout}: max err {err:.3e} > {tol:.3e} ({int(((lora.cpu() - el).abs() > tol).sum())} elements)"
     return q
 
 
