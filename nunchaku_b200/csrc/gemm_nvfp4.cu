@@ -245,57 +245,73 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
-            constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
-            uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
-            bool ok = true;
-            for (int ti = 0; ti < tr.count && ok; ++ti) {
-                const uint32_t as = ti & 1;
-                if (!wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20)) break;
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem + as * G_TM_ACC1;
-                uint32_t accumulate = 0;
-                for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int s = it % G_STAGES;
-                    if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
-                    const uint64_t adesc = smem_desc_sw128(sa);
-                    const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
-                    if (ks < kstages) {
-                        const int nkb = min(4, KB - ks * 4);
-                        const uint32_t b = sq % G_SF_BUFS;
-                        if (!wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
-                        const uint32_t t_sfb = t_sfa + 16;
-                        for (int j = 0; j < nkb; ++j) {
-                            tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j, accumulate);
-                            accumulate = 1;
+        // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and barrier
+        // addresses then stay warp-uniform.  (With the loop inside `if (lane == 0)` every operand is a
+        // per-thread value and the issue rate, not the tensor pipe, bounds the kernel.)
+        constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
+        constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
+        uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
+        bool ok = true;
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            const uint32_t as = ti & 1;
+            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
+            if (!ok) break;
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem + as * G_TM_ACC1;
+            uint32_t accumulate = 0;
+            for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                const int s = it % G_STAGES;
+                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
+                if (!ok) break;
+                const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(sa);
+                const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
+                if (ks < kstages) {
+                    const int nkb = min(4, KB - ks * 4);
+                    const uint32_t b = sq % G_SF_BUFS;
+                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22));
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
+                    const uint32_t t_sfb = t_sfa + 16;
+                    if (elect_one()) {
+                        if (nkb == 4) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
+                                             j == 0 ? accumulate : 1u);
+                        } else {
+                            for (int j = 0; j < nkb; ++j)
+                                tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
+                                             j == 0 ? accumulate : 1u);
                         }
                         tc_commit(&sh->sf_empty[b]);
-                        ++sq;
-                    } else {
-                        tc_fence_after_sync();
-                        for (int j = 0; j < 4; ++j) {
-                            tc_mma_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, accumulate);
-                            accumulate = 1;
-                        }
+                        tc_commit(&sh->empty[s]);   // stage is free once these MMAs have read it
                     }
-                    tc_commit(&sh->empty[s]);   // stage is free once these MMAs have read it
+                    ++sq;
+                } else {
+                    tc_fence_after_sync();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_mma_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j == 0 ? accumulate : 1u);
+                        tc_commit(&sh->empty[s]);
+                    }
                 }
-                if (ok) tc_commit(&sh->tfull[as]);  // accumulator complete
+                accumulate = 1;
+                __syncwarp();
             }
-            if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
+            if (ok) {
+                if (elect_one()) tc_commit(&sh->tfull[as]);  // accumulator complete
+                __syncwarp();
+            }
+        }
+        if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
+            if (lane == 0) {
                 tc_commit(&sh->drain);
                 mbar_wait(&sh->drain, 0, 400000000ll);
             }
+            __syncwarp();
         }
     } else if (warp >= 6) {
         // ------------------------------------------------------------------ scale-factor loaders (warps 6..9)

@@ -10,12 +10,19 @@ namespace svdq {
 
 struct ProbeShared {
     uint64_t done;
+    uint64_t scratch;
+    uint64_t never;
     uint32_t tmem_base;
+    volatile int finished;
 };
 
 // kind: 0 = mxf4nvf4 block-scaled (K=64 per MMA), 1 = tf32 (K=8), 2 = i8 (K=32)
-__global__ void __launch_bounds__(64, 1)
-mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, long long* cycles, int* status) {
+// sfb_step: TMEM column distance between the B scale factors of consecutive K blocks; commit_every: a
+// tcgen05.commit to a scratch barrier after every group of 4 MMAs; blockDim beyond 64 threads = extra warps
+// that poll an mbarrier until the loop is over (what waiting epilogue / loader warps do in a real kernel).
+__global__ void __launch_bounds__(512, 1)
+mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, int sfb_step, int commit_every,
+                long long* cycles, int* status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int STAGE = 48 * 1024;
@@ -23,6 +30,9 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, l
     for (int i = threadIdx.x; i < 4 * STAGE / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x == 0) {
         mbar_init(&sh->done, 1);
+        mbar_init(&sh->scratch, 1);
+        mbar_init(&sh->never, 1);
+        sh->finished = 0;
         fence_mbar_init();
     }
     if (threadIdx.x < 32) {
@@ -34,7 +44,8 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, l
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        // the whole warp runs the loop; one elected lane issues
         const uint32_t idesc = kind == 0 ? idesc_nvfp4(128, n) : kind == 1 ? idesc_tf32(128, n) : idesc_i8(128, n, true);
         const long long t0 = clock64();
         for (int it = 0; it < iters; ++it) {
@@ -42,23 +53,39 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, l
             const uint64_t adesc = smem_desc_sw128(sa);
             const uint64_t bdesc = smem_desc_sw128(sa + 16384);
             const uint32_t t_sf = tmem + 384 + (sf_buffers > 1 ? (it % sf_buffers) * 48 : 0);
-            for (int j = 0; j < cps_per_group; ++j)
-                tc_cp_32x128b_warpx4(t_sf + 4 * j, smem_desc_sf(sa + 40960 + j * 512));
-            for (int j = 0; j < 4; ++j) {
-                if (kind == 0)
-                    tc_mma_nvfp4(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + 4 * j, t_sf + 16 + 8 * j, 1);
-                else if (kind == 1)
-                    tc_mma_tf32(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
-                else
-                    tc_mma_i8(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
+            if (elect_one()) {
+                for (int j = 0; j < cps_per_group; ++j)
+                    tc_cp_32x128b_warpx4(t_sf + 4 * j, smem_desc_sf(sa + 40960 + j * 512));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (kind == 0)
+                        tc_mma_nvfp4(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + 4 * j, t_sf + 16 + sfb_step * j, 1);
+                    else if (kind == 1)
+                        tc_mma_tf32(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
+                    else
+                        tc_mma_i8(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
+                }
+                if (commit_every & 1) tc_commit(&sh->scratch);
             }
+            __syncwarp();
         }
         const long long t1 = clock64();
-        tc_commit(&sh->done);
-        if (!mbar_wait(&sh->done, 0)) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+        bool ok = true;
+        if (elect_one()) tc_commit(&sh->done);
+        __syncwarp();
+        ok = mbar_wait(&sh->done, 0);
         const long long t2 = clock64();
-        cycles[blockIdx.x * 2] = t1 - t0;      // issue time
-        cycles[blockIdx.x * 2 + 1] = t2 - t0;  // until the last MMA completed
+        if (threadIdx.x == 0) {
+            if (!ok) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+            cycles[blockIdx.x * 2] = t1 - t0;      // issue time
+            cycles[blockIdx.x * 2 + 1] = t2 - t0;  // until the last MMA completed
+            sh->finished = 1;
+        }
+    } else if (threadIdx.x >= 64) {
+        while (!sh->finished) {
+            for (int i = 0; i < 64; ++i)
+                if (mbar_try_wait(&sh->never, 0)) break;
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -68,21 +95,76 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, l
     }
 }
 
+// L2 -> shared-memory ingest probe: one thread per CTA keeps `depth` bulk copies of `chunk` bytes in
+// flight from a buffer that fits in L2, and reports the cycles for `iters` chunks.  Run with few and
+// with all SMs it tells a per-SM port limit from an aggregate L2 limit.
+__global__ void __launch_bounds__(256, 1)
+ingest_rate_kernel(const uint8_t* src, size_t src_bytes, int chunk, int depth, int iters, long long* cycles, int* status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // every warp is an independent issuer with its own ring of `depth` stages
+    const int issuers = blockDim.x / 32, w = threadIdx.x / 32;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(issuers) * depth * chunk) + w * depth;
+    smem += static_cast<size_t>(w) * depth * chunk;
+    if ((threadIdx.x & 31) == 0) {
+        for (int s = 0; s < depth; ++s) mbar_init(&full[s], 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) {
+        const size_t nchunks = src_bytes / chunk;
+        size_t pos = (static_cast<size_t>(blockIdx.x * issuers + w) * 7919) % nchunks;
+        const long long t0 = clock64();
+        bool ok = true;
+        for (int it = 0; it < iters + depth && ok; ++it) {
+            const int s = it % depth;
+            if (it >= depth) ok = mbar_wait(&full[s], ((it / depth) - 1) & 1);
+            if (it < iters && ok) {
+                mbar_arrive_expect_tx(&full[s], chunk);
+                bulk_load(smem + static_cast<size_t>(s) * chunk, src + pos * chunk, chunk, &full[s]);
+                pos = pos + 1 == nchunks ? 0 : pos + 1;
+            }
+        }
+        if (!ok) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+        if (w == 0) cycles[blockIdx.x] = clock64() - t0;
+    }
+}
+
 }  // namespace svdq
+
+extern "C" int svdq_probe_ingest_rate(const void* src, size_t src_bytes, int chunk, int depth, int iters, int grid,
+                                      int issuers, long long* cycles, void* stream) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(src && cycles && grid > 0 && grid <= 1024 && iters > 0 && chunk >= 1024 && chunk % 1024 == 0 &&
+                       depth >= 1 && issuers >= 1 && issuers <= 8 &&
+                       static_cast<size_t>(issuers) * depth * chunk <= 200 * 1024 && src_bytes >= static_cast<size_t>(chunk),
+                   "ingest probe: bad argument");
+    if (int rc = check_arch()) return rc;
+    int* status = nullptr;
+    if (int rc = status_words(&status)) return rc;
+    const size_t smem = 1024 + static_cast<size_t>(issuers) * depth * (chunk + 8) + 64;
+    SVDQ_CUDA(cudaFuncSetAttribute(ingest_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    ingest_rate_kernel<<<grid, 32 * issuers, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(src), src_bytes, chunk,
+                                                                           depth, iters, cycles, status);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
 
 // cycles: device buffer of 2 * grid int64 {issue, complete} per CTA.  No counterpart in the reference.
 extern "C" int svdq_probe_mma_rate(int kind, int n, int iters, int cps_per_group, int sf_buffers, int grid,
-                                   long long* cycles, void* stream) {
+                                   long long* cycles, void* stream, int sfb_step, int commit_every, int poll_warps) {
     using namespace svdq;
     SVDQ_CHECK_ARG(cycles && grid > 0 && grid <= 1024 && iters > 0 && n >= 16 && n <= 256 && n % 16 == 0 &&
-                       cps_per_group >= 0 && cps_per_group <= 12 && sf_buffers >= 1 && sf_buffers <= 2 && kind >= 0 && kind <= 2,
+                       cps_per_group >= 0 && cps_per_group <= 12 && sf_buffers >= 1 && sf_buffers <= 2 && kind >= 0 && kind <= 2 &&
+                       sfb_step >= 4 && sfb_step <= 8 && poll_warps >= 0 && poll_warps <= 14,
                    "probe: bad argument");
     if (int rc = check_arch()) return rc;
     int* status = nullptr;
     if (int rc = status_words(&status)) return rc;
     const size_t smem = 1024 + 4 * 48 * 1024 + 64;
     SVDQ_CUDA(cudaFuncSetAttribute(mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    mma_rate_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(kind, n, iters, cps_per_group, sf_buffers, cycles, status);
+    mma_rate_kernel<<<grid, 64 + 32 * poll_warps, smem, static_cast<cudaStream_t>(stream)>>>(kind, n, iters, cps_per_group, sf_buffers,
+                                                                                     sfb_step, commit_every, cycles, status);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }

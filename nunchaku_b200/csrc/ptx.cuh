@@ -13,6 +13,21 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp.  tcgen05 and TMA instructions take their operands from uniform registers:
+// a loop that the whole warp runs, with only the instruction itself behind this predicate, lets the
+// compiler keep descriptors and coordinates there.  Wrapping the whole loop in `if (lane == 0)` instead
+// makes every operand a per-thread value that has to be moved over for each instruction, and the issue
+// rate (not the tensor pipe) then bounds the kernel.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -70,7 +70,7 @@ def prepare_weights(
 
 
 _cache: dict[tuple, tuple[PreparedWeights, list]] = {}
-_alpha_cache: dict[tuple, float] = {}
+_alpha_cache: dict[tuple, tuple[float, weakref.ref]] = {}
 
 
 def _ident(t: torch.Tensor | None):
@@ -84,10 +84,18 @@ def _alpha_value(alpha) -> float:
     if alpha is None:
         return 1.0
     if isinstance(alpha, torch.Tensor):
+        # keyed by address + version, and only valid while that very tensor object is alive: the allocator
+        # hands the address of a freed one-element tensor to the next one
         key = _ident(alpha)
-        if key not in _alpha_cache:
-            _alpha_cache[key] = float(alpha.detach().float().reshape(-1)[0].item())
-        return _alpha_cache[key]
+        hit = _alpha_cache.get(key)
+        if hit is not None and hit[1]() is alpha:
+            return hit[0]
+        value = float(alpha.detach().float().reshape(-1)[0].item())
+        if len(_alpha_cache) > 4096:
+            for k in [k for k, v in _alpha_cache.items() if v[1]() is None]:
+                del _alpha_cache[k]
+        _alpha_cache[key] = (value, weakref.ref(alpha))
+        return value
     return float(alpha)
 
 
@@ -96,12 +104,13 @@ def cached_prepared_weights(wgt, wscales, lora_up, bias, wcscales, alpha, lora_s
     key = (_ident(wgt), _ident(wscales), _ident(lora_up), _ident(bias), _ident(wcscales), a,
            None if lora_scales is None else tuple(lora_scales), bool(fp4))
     hit = _cache.get(key)
-    if hit is not None and all(r() is not None for r in hit[1]):
+    live = [t for t in (wgt, wscales, lora_up, bias, wcscales) if t is not None]
+    if hit is not None and len(hit[1]) == len(live) and all(r() is t for r, t in zip(hit[1], live)):
         return hit[0]
     if lora_scales is not None and all(s == 1.0 for s in lora_scales):
         lora_scales = None
     prepared = prepare_weights(wgt, wscales, lora_up, bias, wcscales, a, lora_scales, fp4)
-    refs = [weakref.ref(t) for t in (wgt, wscales, lora_up, bias, wcscales) if t is not None]
+    refs = [weakref.ref(t) for t in live]
     _cache[key] = (prepared, refs)
     if len(_cache) > 4096:  # drop entries whose parameters are gone
         for k in [k for k, v in _cache.items() if any(r() is None for r in v[1])]:

@@ -15,10 +15,11 @@ from . import _lib
 KINDS = {"mxf4nvf4": (0, 64), "tf32": (1, 8), "i8": (2, 32)}
 
 
-def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_buffers: int = 1, grid: int | None = None):
+def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_buffers: int = 1, grid: int | None = None,
+             sfb_step: int = 8, commit_every: bool = False, poll_warps: int = 0):
     lib = _lib.load()
     lib.svdq_probe_mma_rate.restype = ctypes.c_int32
-    lib.svdq_probe_mma_rate.argtypes = [ctypes.c_int32] * 6 + [ctypes.c_void_p, ctypes.c_void_p]
+    lib.svdq_probe_mma_rate.argtypes = [ctypes.c_int32] * 6 + [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int32] * 3
     dev = torch.device("cuda", torch.cuda.current_device())
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     grid = grid or sms
@@ -28,17 +29,35 @@ def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_bu
     for rep in range(2):
         e0.record()
         _lib.check(lib.svdq_probe_mma_rate(code, n, iters, cps_per_group, sf_buffers, grid, cyc.data_ptr(),
-                                           torch.cuda.current_stream(dev).cuda_stream))
+                                           torch.cuda.current_stream(dev).cuda_stream, sfb_step, int(commit_every), poll_warps))
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     c = cyc.view(grid, 2).double().mean(0)
     flops = 2.0 * 128 * n * k * 4 * iters * grid
     return {
-        "kind": kind, "n": n, "cps_per_group": cps_per_group, "sf_buffers": sf_buffers,
+        "kind": kind, "n": n, "cps_per_group": cps_per_group, "sf_buffers": sf_buffers, "sfb_step": sfb_step,
+        "commit_every": commit_every, "poll_warps": poll_warps,
         "cycles_per_mma_issue": c[0].item() / (4 * iters), "cycles_per_mma": c[1].item() / (4 * iters),
         "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms,
     }
+
+
+def ingest_rate(grid: int, chunk: int = 16384, depth: int = 4, iters: int = 4000, src_mb: int = 32, issuers: int = 2):
+    """Bytes per clock per SM that bulk copies from an L2-resident buffer deliver to shared memory."""
+    lib = _lib.load()
+    lib.svdq_probe_ingest_rate.restype = ctypes.c_int32
+    lib.svdq_probe_ingest_rate.argtypes = [ctypes.c_void_p, ctypes.c_size_t] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    src = torch.zeros(src_mb << 20, dtype=torch.uint8, device=dev)
+    cyc = torch.zeros(grid, dtype=torch.int64, device=dev)
+    for rep in range(2):
+        _lib.check(lib.svdq_probe_ingest_rate(src.data_ptr(), src.numel(), chunk, depth, iters, grid, issuers, cyc.data_ptr(),
+                                              torch.cuda.current_stream(dev).cuda_stream))
+        torch.cuda.synchronize()
+    c = cyc.double()
+    return {"grid": grid, "chunk": chunk, "depth": depth, "issuers": issuers, "src_mb": src_mb,
+            "bytes_per_clk_per_sm": issuers * chunk * iters / c.mean().item(), "min": issuers * chunk * iters / c.max().item()}
 
 
 def main():
