@@ -331,15 +331,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 if (ks >= kstages) continue;  // low-rank stages carry no scale factors
                 const int s = it % G_STAGES;
                 const uint32_t b = sq % G_SF_BUFS;
-                if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 40) ||
-                    !wait_or_abort(&sh->sf_empty[b], ((sq / G_SF_BUFS) & 1) ^ 1, sh, p.status, 41)) {
+                if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 40)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after_sync();
                 const uint8_t* sf = smem + s * G_STAGE_BYTES + G_A_BYTES + G_B_BYTES + lane * 16;
                 // registers 0..15: A (k-block j, row group c -> 4j + c); 16..39: B (6j + c), where the tile's
-                // 192 weight rows are row groups off..off+5 of the two 128-row atoms in shared memory
+                // 192 weight rows are row groups off..off+5 of the two 128-row atoms in shared memory.
+                // The shared-memory reads happen before the wait for the TMEM buffer: only the TMEM store is on
+                // the path between "the MMAs that used this buffer are done" and "the next MMAs may start".
                 uint32_t r32[32], r8[8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -356,12 +356,17 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         if (idx < 32) r32[idx] = w[c]; else r8[idx - 32] = w[c];
                     }
                 }
+                fence_proxy_async_smem();   // generic reads of the stage above, TMA refill below the MMA's commit
+                if (!wait_or_abort(&sh->sf_empty[b], ((sq / G_SF_BUFS) & 1) ^ 1, sh, p.status, 41)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
                 const uint32_t t_sf = tmem + (static_cast<uint32_t>(q * 32) << 16) + G_TM_SF + b * G_TM_SF_STRIDE;
                 tc_st_32x32b_x32(t_sf, r32);
                 tc_st_32x32b_x8(t_sf + 32, r8);
                 tc_wait_st();
                 tc_fence_before_sync();
-                fence_proxy_async_smem();   // generic reads of the stage above, TMA refill below the MMA's commit
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sh->sf_full[b]);
                 ++sq;
