@@ -10,24 +10,33 @@
 // gemm_w4a4.cuh:930-1043, lora.cuh:243-353): yb = bf16(y);  lora_act_out = yb @ Wd_next^T (fp32);
 // codes/scales = NVFP4 group quantisation of bf16(yb / smooth_next);  out (optional) = yb.
 //
-// How it maps to a B200 SM.  One persistent CTA per SM walks 128 x 192 output tiles.
-//   warp 0      producer: TMA loads of 128B-swizzled operand tiles (128 rows x 256 codes of A, 192 x 256 of
-//               B per stage) and bulk copies of the 512-byte scale-factor atoms, 4-stage mbarrier ring
-//   warp 1      MMA issuer: 4 x tcgen05.mma.kind::mxf4nvf4.block_scale (M128 N192 K64) per stage; the
-//               low-rank branch is fed through the same ring as fp32 tiles and issued as kind::tf32 into
-//               the same TMEM accumulator; tcgen05.commit releases the stage / publishes the accumulator
+// How it maps to a B200.  The two SMs of a CTA pair (cluster of 2) walk 256 x 192 output tiles together with
+// tcgen05 cta_group::2: each CTA holds 128 rows of A, 128 rows of the accumulator (its own TMEM) and 96 of the
+// tile's 192 weight rows; the even CTA ("leader") issues one 256-row MMA for both.  Per byte loaded the pair
+// does 1.4x the math of two independent 128 x 192 CTAs, so a five-stage ring covers the load latency that a
+// four-stage ring of full tiles could not.  In each CTA:
+//   warp 0      producer: TMA loads of its 128B-swizzled operand tiles (128 rows x 256 codes of A, 96 x 256 of B
+//               per stage; completion counted on the leader's barrier) and bulk copies of the 512-byte
+//               scale-factor atoms (its own 128 rows of A, all 192 rows of B; counted on a local barrier)
+//   warp 1      leader only: MMA issuer, 4 x tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N192 K64)
+//               per stage; the low-rank branch is fed through the same ring as fp32 tiles and issued as
+//               kind::tf32 into the same accumulator; one multicast tcgen05.commit per stage releases the stage
+//               and its scale-factor buffer in both CTAs, one per tile publishes the accumulator
 //   warps 6..9  scale-factor loaders: shared memory -> registers -> TMEM (tcgen05.st), one lane quadrant each
 //   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
 //               staging buffer, TMA store (coalesced, clipped at M and N by the hardware); when requantising,
 //               the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix + mma.sync) and the
 //               thread's own row chunk is group-quantised in registers
-// TMEM: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
+// TMEM per CTA: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
 // plus three 40-column scale-factor buffers (16 for A, 24 for B) = 504 of 512 columns.
+// Every loop that issues tcgen05 / TMA instructions is run by a whole warp with one elected lane issuing, so
+// that descriptors and coordinates stay warp-uniform.  Every wait is bounded; a wait that runs out raises the
+// abort flag of both CTAs, all roles leave their loops, and the status words tell the host.
 //
-// The next layer's LoRA-down is a sum over all N, i.e. over tiles of different CTAs.  It is kept
-// deterministic: in requantising mode every CTA owns a contiguous run of tiles in n-fastest order, adds up
-// its tiles of one 128-row block in registers, writes one partial per row block it touches to caller
-// scratch, and a second small kernel adds the partials in CTA order.
+// The next layer's LoRA-down is a sum over all N, i.e. over tiles of different pairs.  It is kept
+// deterministic: in requantising mode every pair owns a contiguous run of tiles in n-fastest order, each CTA
+// adds up its tiles of one 128-row block in registers, writes one partial per row block it touches to caller
+// scratch, and a second small kernel adds the partials in pair order.
 #include <cuda_bf16.h>
 
 #include <mutex>
@@ -40,12 +49,13 @@ namespace svdq {
 
 constexpr int G_BM = 128;
 constexpr int G_BN = 192;
-constexpr int G_STAGES = 4;
+constexpr int G_BNH = G_BN / 2;                 // weight rows each CTA of a pair loads
+constexpr int G_STAGES = 5;
 constexpr int G_A_BYTES = G_BM * 128;           // 16 KB
-constexpr int G_B_BYTES = G_BN * 128;           // 24 KB
+constexpr int G_B_BYTES = G_BNH * 128;          // 12 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
-constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 47104 = 46 * 1024
+constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 34816 = 34 * 1024
 constexpr int G_THREADS = 10 * 32;
 constexpr int G_SF_BUFS = 3;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
@@ -67,7 +77,7 @@ struct GemmParams {
     int* status;
     int M, M_pad, N, K;
     int lora_chunks;          // number of 32-rank chunks of the low-rank branch (0 = none)
-    int tiles_m, tiles_n;
+    int tiles_m, tiles_n;     // in 256 x 192 pair tiles
     int activation;
     int store_out;            // bf16 `out` is wanted
     // tile schedule: 0: m-fastest, strided by gridDim; 1: n-fastest, each CTA a contiguous run of `run` tiles
@@ -78,17 +88,17 @@ struct GemmParams {
     uint8_t* oscales;                   // scale atoms [M_pad/128][N/64][512]
     const __nv_bfloat16* next_smooth;   // [N] reference-packed
     const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
-    float* lora_partial;                // scratch [grid][slots][128][Rn]
+    float* lora_partial;                // scratch [CTA][slots][128][Rn]
     int slots;
 };
 
 struct GemmShared {
-    uint64_t full[G_STAGES];
-    uint64_t empty[G_STAGES];
-    uint64_t tfull[2];
-    uint64_t tempty[2];
-    uint64_t sf_full[G_SF_BUFS];    // scale factors of a stage are in TMEM (4 loader warps arrive)
-    uint64_t sf_empty[G_SF_BUFS];   // the MMAs that read a scale-factor buffer are done (tcgen05.commit)
+    uint64_t full[G_STAGES];        // leader: operand tiles of both CTAs have landed (2 arrivals + bytes)
+    uint64_t sffull[G_STAGES];      // each CTA: its scale-factor atoms have landed
+    uint64_t empty[G_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
+    uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
+    uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
+    uint64_t sf_full[G_SF_BUFS];    // leader: scale factors of a stage are in TMEM (4 loader warps x 2 CTAs)
     uint64_t drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -101,25 +111,33 @@ struct TileRun {
 __device__ __forceinline__ TileRun tile_run(const GemmParams& p) {
     const int num_tiles = p.tiles_m * p.tiles_n;
     TileRun r;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     if (p.contiguous) {
-        r.first = blockIdx.x * p.run;
+        r.first = pair * p.run;
         r.stride = 1;
         r.count = max(0, min(p.run, num_tiles - r.first));
     } else {
-        r.first = blockIdx.x;
-        r.stride = gridDim.x;
+        r.first = pair;
+        r.stride = npairs;
         r.count = num_tiles > r.first ? (num_tiles - r.first + r.stride - 1) / r.stride : 0;
     }
     return r;
 }
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m0, int& n0) {
+// first row of THIS CTA's half of the pair tile, first column of the tile
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, uint32_t rank, int& m0, int& n0) {
     if (p.contiguous) {
-        m0 = (tile / p.tiles_n) * G_BM;
+        m0 = (tile / p.tiles_n) * (2 * G_BM);
         n0 = (tile % p.tiles_n) * G_BN;
     } else {
-        m0 = (tile % p.tiles_m) * G_BM;
+        m0 = (tile % p.tiles_m) * (2 * G_BM);
         n0 = (tile / p.tiles_m) * G_BN;
     }
+    m0 += rank * G_BM;
+}
+
+__device__ __forceinline__ void raise_abort(GemmShared* sh) {
+    sh->abort_flag = 1;
+    st_shared_cluster_u32(mapa_shared(smem_u32(const_cast<int*>(&sh->abort_flag)), cluster_ctarank() ^ 1u), 1u);
 }
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
@@ -135,7 +153,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ge
         }
         if (sh->abort_flag) return false;
         if (clock64() - t0 > 4000000000ll) {  // about 2 s
-            sh->abort_flag = 1;
+            raise_abort(sh);
             atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
             atomicExch(&status[1], where);
             return false;
@@ -174,19 +192,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int NB = p.N / 128;                        // weight scale atoms along N
     const TileRun tr = tile_run(p);
 
+    const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&sh->full[s], 1);
+            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->sffull[s], 1);
             mbar_init(&sh->empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->tfull[i], 1);
-            mbar_init(&sh->tempty[i], 4);
+            mbar_init(&sh->tempty[i], 8);
         }
-        for (int i = 0; i < G_SF_BUFS; ++i) {
-            mbar_init(&sh->sf_full[i], 4);
-            mbar_init(&sh->sf_empty[i], 1);
-        }
+        for (int i = 0; i < G_SF_BUFS; ++i) mbar_init(&sh->sf_full[i], 8);
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         fence_mbar_init();
@@ -199,119 +216,124 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
     }
     if (warp == 1) {
-        tmem_alloc(&sh->tmem_base, G_TMEM_COLS);
-        tmem_relinquish();
+        tmem_alloc_pair(&sh->tmem_base, G_TMEM_COLS);
+        tmem_relinquish_pair();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    cluster_sync_all();   // barriers of both CTAs are initialised before anything remote touches them
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
-            bool ok = true;
-            for (int ti = 0; ti < tr.count && ok; ++ti) {
-                int m0, n0;
-                tile_coords(p, tr.first + ti * tr.stride, m0, n0);
-                const int atom0 = n0 >> 7;
-                for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int s = it % G_STAGES;
-                    if (!wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10)) {
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* st = smem + s * G_STAGE_BYTES;
+        // ------------------------------------------------------------------ producer (whole warp, elected lane issues)
+        uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
+        bool ok = true;
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            int m0, n0;
+            tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+            const int atom0 = n0 >> 7;
+            const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
+            for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                const int s = it % G_STAGES;
+                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10));
+                if (!ok) break;
+                uint8_t* st = smem + s * G_STAGE_BYTES;
+                const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
+                if (elect_one()) {
                     if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
                         const int natoms = min(2, NB - atom0);
-                        mbar_arrive_expect_tx(&sh->full[s], G_A_BYTES + G_B_BYTES + nkb * 512 * (1 + natoms));
-                        tma_load_2d(st, &tm_a, &sh->full[s], ks * 128, m0);
-                        tma_load_2d(st + G_A_BYTES, &tm_b, &sh->full[s], ks * 128, n0);
+                        mbar_arrive_expect_tx(&sh->sffull[s], nkb * 512 * (1 + natoms));
                         bulk_load(st + G_A_BYTES + G_B_BYTES, p.sfa + (static_cast<size_t>(m0 >> 7) * KB + ks * 4) * 512,
-                                  nkb * 512, &sh->full[s]);
+                                  nkb * 512, &sh->sffull[s]);
                         for (int a = 0; a < natoms; ++a)
                             bulk_load(st + G_A_BYTES + G_B_BYTES + G_SFA_BYTES + a * 2048,
-                                      p.sfb + (static_cast<size_t>(atom0 + a) * KB + ks * 4) * 512, nkb * 512, &sh->full[s]);
+                                      p.sfb + (static_cast<size_t>(atom0 + a) * KB + ks * 4) * 512, nkb * 512, &sh->sffull[s]);
+                        mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES + G_B_BYTES);
+                        tma_load_2d_pair(st, &tm_a, lfull, ks * 128, m0);
+                        tma_load_2d_pair(st + G_A_BYTES, &tm_b, lfull, ks * 128, nb0);
                     } else {
                         const int c = ks - kstages;
-                        mbar_arrive_expect_tx(&sh->full[s], G_A_BYTES + G_B_BYTES);
-                        tma_load_2d(st, &tm_la, &sh->full[s], c * 32, m0);
-                        tma_load_2d(st + G_A_BYTES, &tm_lu, &sh->full[s], c * 32, n0);
+                        mbar_arrive(&sh->sffull[s]);   // no scale factors in this stage: keep the barrier's phase in step with the ring
+                        mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES + G_B_BYTES);
+                        tma_load_2d_pair(st, &tm_la, lfull, c * 32, m0);
+                        tma_load_2d_pair(st + G_A_BYTES, &tm_lu, lfull, c * 32, nb0);
                     }
                 }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and barrier
         // addresses then stay warp-uniform.  (With the loop inside `if (lane == 0)` every operand is a
         // per-thread value and the issue rate, not the tensor pipe, bounds the kernel.)
-        constexpr uint32_t IDESC_FP4 = idesc_nvfp4(G_BM, G_BN);
-        constexpr uint32_t IDESC_TF32 = idesc_tf32(G_BM, G_BN);
-        uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
-        bool ok = true;
-        for (int ti = 0; ti < tr.count && ok; ++ti) {
-            const uint32_t as = ti & 1;
-            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
-            if (!ok) break;
-            tc_fence_after_sync();
-            const uint32_t d_tmem = tmem + as * G_TM_ACC1;
-            uint32_t accumulate = 0;
-            for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                const int s = it % G_STAGES;
-                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
+        if (rank == 0) {
+            constexpr uint32_t IDESC_FP4 = idesc_nvfp4(2 * G_BM, G_BN);
+            constexpr uint32_t IDESC_TF32 = idesc_tf32(2 * G_BM, G_BN);
+            uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
+            bool ok = true;
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
+                const uint32_t as = ti & 1;
+                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
                 if (!ok) break;
-                const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
-                const uint64_t adesc = smem_desc_sw128(sa);
-                const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
-                if (ks < kstages) {
-                    const int nkb = min(4, KB - ks * 4);
-                    const uint32_t b = sq % G_SF_BUFS;
-                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22));
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem + as * G_TM_ACC1;
+                uint32_t accumulate = 0;
+                for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                    const int s = it % G_STAGES;
+                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
                     if (!ok) break;
-                    tc_fence_after_sync();
-                    const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
-                    const uint32_t t_sfb = t_sfa + 16;
-                    if (elect_one()) {
-                        if (nkb == 4) {
+                    const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
+                    if (ks < kstages) {
+                        const int nkb = min(4, KB - ks * 4);
+                        const uint32_t b = sq % G_SF_BUFS;
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22));
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
+                        const uint32_t t_sfb = t_sfa + 16;
+                        if (elect_one()) {
+                            if (nkb == 4) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
+                                                      j == 0 ? accumulate : 1u);
+                            } else {
+                                for (int j = 0; j < nkb; ++j)
+                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
+                                                      j == 0 ? accumulate : 1u);
+                            }
+                            // one commit frees the stage and its scale-factor buffer, in both CTAs
+                            tc_commit_pair(&sh->empty[s], 3);
+                        }
+                        ++sq;
+                    } else {
+                        tc_fence_after_sync();
+                        if (elect_one()) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
-                                             j == 0 ? accumulate : 1u);
-                        } else {
-                            for (int j = 0; j < nkb; ++j)
-                                tc_mma_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
-                                             j == 0 ? accumulate : 1u);
+                                tc_mma_pair_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j == 0 ? accumulate : 1u);
+                            tc_commit_pair(&sh->empty[s], 3);
                         }
-                        tc_commit(&sh->sf_empty[b]);
-                        tc_commit(&sh->empty[s]);   // stage is free once these MMAs have read it
                     }
-                    ++sq;
-                } else {
-                    tc_fence_after_sync();
-                    if (elect_one()) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            tc_mma_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j == 0 ? accumulate : 1u);
-                        tc_commit(&sh->empty[s]);
-                    }
+                    accumulate = 1;
+                    __syncwarp();
                 }
-                accumulate = 1;
+                if (ok) {
+                    if (elect_one()) tc_commit_pair(&sh->tfull[as], 3);  // accumulator complete, both CTAs
+                    __syncwarp();
+                }
+            }
+            if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
+                if (lane == 0) {
+                    tc_commit_pair(&sh->drain, 1);
+                    mbar_wait(&sh->drain, 0, 400000000ll);
+                }
                 __syncwarp();
             }
-            if (ok) {
-                if (elect_one()) tc_commit(&sh->tfull[as]);  // accumulator complete
-                __syncwarp();
-            }
-        }
-        if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
-            if (lane == 0) {
-                tc_commit(&sh->drain);
-                mbar_wait(&sh->drain, 0, 400000000ll);
-            }
-            __syncwarp();
         }
     } else if (warp >= 6) {
         // ------------------------------------------------------------------ scale-factor loaders (warps 6..9)
@@ -320,18 +342,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         // Instead each of these four warps reads the stage's 512-byte atoms from shared memory (row r0 =
         // lane, 16 bytes = the 4 row groups x 4 scale bytes) and writes them to its own TMEM lane quadrant
         // with tcgen05.st: 16 columns for A, 24 for B per stage.
+        // A TMEM buffer is free again when the MMAs of the stage that used it (three scale-factor stages
+        // earlier) are done, which is what that stage's `empty` barrier says: `used_by` remembers its ring
+        // position.  G_STAGES > G_SF_BUFS, so that barrier cannot complete another phase before this wait.
         const int q = warp & 3;
         uint32_t it = 0, sq = 0;
+        uint32_t used_by[G_SF_BUFS] = {};
         bool ok = true;
         for (int ti = 0; ti < tr.count && ok; ++ti) {
             int m0, n0;
-            tile_coords(p, tr.first + ti * tr.stride, m0, n0);
+            tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
             const bool mid_atom = (n0 & 127) != 0;  // tile starts 64 rows into a 128-row atom
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 if (ks >= kstages) continue;  // low-rank stages carry no scale factors
                 const int s = it % G_STAGES;
                 const uint32_t b = sq % G_SF_BUFS;
-                if (!wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 40)) {
+                if (!wait_or_abort(&sh->sffull[s], (it / G_STAGES) & 1, sh, p.status, 40)) {
                     ok = false;
                     break;
                 }
@@ -357,10 +383,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     }
                 }
                 fence_proxy_async_smem();   // generic reads of the stage above, TMA refill below the MMA's commit
-                if (!wait_or_abort(&sh->sf_empty[b], ((sq / G_SF_BUFS) & 1) ^ 1, sh, p.status, 41)) {
-                    ok = false;
-                    break;
+                if (sq >= G_SF_BUFS) {
+                    const uint32_t pit = used_by[b];
+                    if (!wait_or_abort(&sh->empty[pit % G_STAGES], (pit / G_STAGES) & 1, sh, p.status, 41)) {
+                        ok = false;
+                        break;
+                    }
                 }
+                used_by[b] = it;
                 tc_fence_after_sync();
                 const uint32_t t_sf = tmem + (static_cast<uint32_t>(q * 32) << 16) + G_TM_SF + b * G_TM_SF_STRIDE;
                 tc_st_32x32b_x32(t_sf, r32);
@@ -368,7 +398,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tc_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->sf_full[b]);
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sf_full[b]), 0));
                 ++sq;
             }
         }
@@ -418,7 +448,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
         for (int ti = 0; ti < tr.count; ++ti) {
             int m0, n0;
-            tile_coords(p, tr.first + ti * tr.stride, m0, n0);
+            tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
             const uint32_t as = ti & 1;
             if constexpr (RTN > 0) {
                 if (m0 != cur_m0) {
@@ -540,7 +570,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tempty[as]);
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tempty[as]), 0));
         }
         if constexpr (RTN > 0) {
             if (cur_m0 >= 0) lacc_flush();
@@ -548,47 +578,53 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
     }
 
+    // Neither CTA may leave (or give up its TMEM) while the other can still signal its barriers or the
+    // leader's MMAs can still read its shared memory: both have passed all their tiles here.
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem, G_TMEM_COLS);
+        tmem_dealloc_pair(tmem, G_TMEM_COLS);
     }
 }
 
-// lora_act_out[row][r] = sum over the CTAs that touched the row's 128-row block, in CTA order, of their partial.
-// Row block mb holds tiles [mb*tiles_n, (mb+1)*tiles_n); CTA c owns tiles [c*run, (c+1)*run).
+// lora_act_out[row][r] = sum over the pairs that touched the row's 256-row block, in pair order, of the partial
+// of the CTA that owns the row's half.  Row block mb2 (256 rows) holds pair tiles [mb2*tiles_n, (mb2+1)*tiles_n);
+// pair c owns tiles [c*run, (c+1)*run); CTA 2c + h of the pair owns rows h*128.. of each tile.
 __global__ void lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n,
-                                           int run, int slots, int grid_ctas) {
-    const int mb = blockIdx.x;
-    const int c_lo = (mb * tiles_n) / run;
-    const int c_hi = min(grid_ctas - 1, ((mb + 1) * tiles_n - 1) / run);
+                                           int run, int slots, int npairs) {
+    const int mb = blockIdx.x;   // 128-row block
+    const int mb2 = mb >> 1, h = mb & 1;
+    const int c_lo = (mb2 * tiles_n) / run;
+    const int c_hi = min(npairs - 1, ((mb2 + 1) * tiles_n - 1) / run);
     for (int i = threadIdx.x; i < G_BM * rn; i += blockDim.x) {
         float s = 0.f;
         for (int c = c_lo; c <= c_hi; ++c) {
-            const int first_mb = (c * run) / tiles_n;
-            s += partial[(static_cast<size_t>(c) * slots + (mb - first_mb)) * (G_BM * rn) + i];
+            const int first_mb2 = (c * run) / tiles_n;
+            s += partial[(static_cast<size_t>(2 * c + h) * slots + (mb2 - first_mb2)) * (G_BM * rn) + i];
         }
         out[static_cast<size_t>(mb) * G_BM * rn + i] = s;
     }
 }
 
 struct NvfpPlan {
-    int requant, tiles_m, tiles_n, grid, run, slots, rn;
+    int requant, tiles_m, tiles_n, npairs, run, slots, rn;   // tiles are 256 x 192 pair tiles
     size_t workspace;
 };
 
 static void plan_nvfp4(const svdq_gemm_args* a, int sms, NvfpPlan* pl) {
     pl->requant = a->qout != nullptr;
     pl->tiles_n = (a->N + G_BN - 1) / G_BN;
-    pl->tiles_m = pl->requant ? a->M_pad / G_BM : (a->M + G_BM - 1) / G_BM;
+    pl->tiles_m = pl->requant ? a->M_pad / (2 * G_BM) : (a->M + 2 * G_BM - 1) / (2 * G_BM);   // M_pad is a multiple of 256
     const int num_tiles = pl->tiles_m * pl->tiles_n;
-    pl->grid = num_tiles < sms ? num_tiles : sms;
-    pl->run = (num_tiles + pl->grid - 1) / pl->grid;
-    if (pl->requant) pl->grid = (num_tiles + pl->run - 1) / pl->run;
+    const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;
+    pl->npairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+    pl->run = (num_tiles + pl->npairs - 1) / pl->npairs;
+    if (pl->requant) pl->npairs = (num_tiles + pl->run - 1) / pl->run;
     pl->slots = (pl->run + pl->tiles_n - 2) / pl->tiles_n + 1;
     pl->rn = a->R_next;
-    pl->workspace = pl->requant ? static_cast<size_t>(pl->grid) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
+    pl->workspace = pl->requant ? static_cast<size_t>(2 * pl->npairs) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
 }
 
 int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
@@ -612,8 +648,19 @@ static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, con
                                        static_cast<int>(G_SMEM_BYTES)));
         attr_done[dev] = true;
     }
-    gemm_nvfp4_kernel<RTN><<<grid, G_THREADS, G_SMEM_BYTES, stream>>>(a, b, la, lu, o, p);
-    SVDQ_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);   // 2 CTAs per pair
+    cfg.blockDim = dim3(G_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = G_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<RTN>, a, b, la, lu, o, p));
     return SVDQ_OK;
 }
 
@@ -671,14 +718,14 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 
     CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
     if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 128, G_BM)) return rc;
-    if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->N, a->K / 2, 128, G_BN)) return rc;
+    if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->N, a->K / 2, 128, G_BNH)) return rc;
     if (a->R > 0) {
         const int R32 = (a->R + 31) / 32 * 32;
         if (int rc = make_tmap_2d(&tm_la, a->lora_act_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
                                   static_cast<uint64_t>(a->R) * 4, 32, G_BM))
             return rc;
         if (int rc = make_tmap_2d(&tm_lu, a->w.lora_up, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, R32, a->N,
-                                  static_cast<uint64_t>(R32) * 4, 32, G_BN))
+                                  static_cast<uint64_t>(R32) * 4, 32, G_BNH))
             return rc;
     } else {
         tm_la = tm_a;
@@ -691,14 +738,14 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_out = tm_a;
     }
     int rc;
-    if (!requant) rc = launch_nvfp4<0>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else if (a->R_next == 16) rc = launch_nvfp4<1>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else if (a->R_next == 32) rc = launch_nvfp4<2>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else rc = launch_nvfp4<4>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    if (!requant) rc = launch_nvfp4<0>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 16) rc = launch_nvfp4<1>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 32) rc = launch_nvfp4<2>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else rc = launch_nvfp4<4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
     if (rc) return rc;
     if (requant) {
-        lora_partial_reduce_kernel<<<pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
-                                                                  pl.slots, pl.grid);
+        lora_partial_reduce_kernel<<<2 * pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
+                                                                      pl.slots, pl.npairs);
         SVDQ_CUDA(cudaGetLastError());
     }
     return SVDQ_OK;
@@ -767,4 +814,5 @@ extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* s
     local.workspace_bytes = SVDQ_STATIC_SCRATCH_BYTES;
     return gemm_nvfp4_impl(&local, static_cast<cudaStream_t>(stream));
 }
+
 

@@ -95,6 +95,81 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, i
     }
 }
 
+// The same loop on a CTA pair: cluster of 2, TMEM allocated with cta_group::2 by both CTAs, the even CTA
+// issues 256-row MMAs (each CTA's tensor core does 128 x n), the completion is multicast to both.
+__global__ void __launch_bounds__(64, 1)
+mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int STAGE = 48 * 1024;
+    ProbeShared* sh = reinterpret_cast<ProbeShared*>(smem + 4 * STAGE);
+    for (int i = threadIdx.x; i < 4 * STAGE / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+    const uint32_t rank = cluster_ctarank();
+    if (threadIdx.x == 0) {
+        mbar_init(&sh->done, 1);
+        fence_mbar_init();
+    }
+    if (threadIdx.x < 32) {
+        tmem_alloc_pair(&sh->tmem_base, 512);
+        tmem_relinquish_pair();
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+    if (threadIdx.x < 32) {
+        const uint32_t idesc = kind == 0 ? idesc_nvfp4(256, n) : idesc_tf32(256, n);
+        const long long t0 = clock64();
+        if (rank == 0) {
+            for (int it = 0; it < iters; ++it) {
+                const uint32_t sa = smem_u32(smem + (it & 3) * STAGE);
+                const uint64_t adesc = smem_desc_sw128(sa);
+                const uint64_t bdesc = smem_desc_sw128(sa + 16384);
+                const uint32_t t_sf = tmem + 384;
+                if (elect_one()) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (kind == 0)
+                            tc_mma_pair_nvfp4(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + 4 * j, t_sf + 16 + 8 * j, 1);
+                        else
+                            tc_mma_pair_tf32(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        const long long t1 = clock64();
+        if (rank == 0) {
+            if (elect_one()) tc_commit_pair(&sh->done, 3);
+            __syncwarp();
+        }
+        bool ok = true;
+        for (int i = 0; i < 64 && ok; ++i) {   // bounded, cluster-scope acquire
+            const long long w0 = clock64();
+            ok = false;
+            while (clock64() - w0 < 60000000ll) {
+                if (mbar_try_wait_cluster(&sh->done, 0)) { ok = true; break; }
+            }
+            if (ok) break;
+            ok = i < 63;
+        }
+        const bool completed = mbar_try_wait_cluster(&sh->done, 0);
+        const long long t2 = clock64();
+        if (threadIdx.x == 0) {
+            if (!completed) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+            cycles[blockIdx.x * 2] = t1 - t0;
+            cycles[blockIdx.x * 2 + 1] = t2 - t0;
+        }
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (threadIdx.x < 32) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem, 512);
+    }
+}
+
 // L2 -> shared-memory ingest probe: one thread per CTA keeps `depth` bulk copies of `chunk` bytes in
 // flight from a buffer that fits in L2, and reports the cycles for `iters` chunks.  Run with few and
 // with all SMs it tells a per-SM port limit from an aggregate L2 limit.
@@ -147,6 +222,33 @@ extern "C" int svdq_probe_ingest_rate(const void* src, size_t src_bytes, int chu
     ingest_rate_kernel<<<grid, 32 * issuers, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(src), src_bytes, chunk,
                                                                            depth, iters, cycles, status);
     SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+// kind 0 = mxf4nvf4, 1 = tf32; grid must be even (CTA pairs).  No counterpart in the reference.
+extern "C" int svdq_probe_mma_rate_pair(int kind, int n, int iters, int grid, long long* cycles, void* stream) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(cycles && grid > 0 && grid <= 1024 && grid % 2 == 0 && iters > 0 && n >= 32 && n <= 256 && n % 32 == 0 &&
+                       kind >= 0 && kind <= 1,
+                   "pair probe: bad argument");
+    if (int rc = check_arch()) return rc;
+    int* status = nullptr;
+    if (int rc = status_words(&status)) return rc;
+    const size_t smem = 1024 + 4 * 48 * 1024 + 64;
+    SVDQ_CUDA(cudaFuncSetAttribute(mma_rate_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(64, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, mma_rate_pair_kernel, kind, n, iters, cycles, status));
     return SVDQ_OK;
 }
 

@@ -43,6 +43,29 @@ def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_bu
     }
 
 
+def mma_rate_pair(kind: str, n: int, iters: int = 2000, grid: int | None = None):
+    """MMA rate of a CTA pair (cta_group::2, M = 256): cycles per MMA and the whole-GPU TFLOP/s."""
+    lib = _lib.load()
+    lib.svdq_probe_mma_rate_pair.restype = ctypes.c_int32
+    lib.svdq_probe_mma_rate_pair.argtypes = [ctypes.c_int32] * 4 + [ctypes.c_void_p, ctypes.c_void_p]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    grid = grid or (sms // 2) * 2
+    cyc = torch.zeros(grid * 2, dtype=torch.int64, device=dev)
+    code, k = KINDS[kind]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(2):
+        e0.record()
+        _lib.check(lib.svdq_probe_mma_rate_pair(code, n, iters, grid, cyc.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    c = cyc.view(grid, 2)[0::2].double().mean(0)     # the issuing CTAs
+    flops = 2.0 * 256 * n * k * 4 * iters * (grid // 2)
+    return {"kind": kind, "n": n, "pair": True, "cycles_per_mma_issue": c[0].item() / (4 * iters),
+            "cycles_per_mma": c[1].item() / (4 * iters), "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms}
+
+
 def ingest_rate(grid: int, chunk: int = 16384, depth: int = 4, iters: int = 4000, src_mb: int = 32, issuers: int = 2):
     """Bytes per clock per SM that bulk copies from an L2-resident buffer deliver to shared memory."""
     lib = _lib.load()
