@@ -15,9 +15,9 @@
 // tile's 192 weight rows; the even CTA ("leader") issues one 256-row MMA for both.  Per byte loaded the pair
 // does 1.4x the math of two independent 128 x 192 CTAs, so a five-stage ring covers the load latency that a
 // four-stage ring of full tiles could not.  In each CTA:
-//   warp 0      producer: TMA loads of its 128B-swizzled operand tiles (128 rows x 256 codes of A, 96 x 256 of B
-//               per stage; completion counted on the leader's barrier) and bulk copies of the 512-byte
-//               scale-factor atoms (its own 128 rows of A, all 192 rows of B; counted on a local barrier)
+//   warps 0, 10, 11  producers, one copy stream each: TMA loads of the 128B-swizzled operand tiles (128 rows x 256
+//               codes of A; 96 x 256 of B; completion counted on the leader's barrier) and bulk copies of the
+//               512-byte scale-factor atoms (own 128 rows of A, all 192 rows of B; counted on a local barrier)
 //   warp 1      leader only: MMA issuer, 4 x tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N192 K64)
 //               per stage; the low-rank branch is fed through the same ring as fp32 tiles and issued as
 //               kind::tf32 into the same accumulator; one multicast tcgen05.commit per stage releases the stage
@@ -56,7 +56,7 @@ constexpr int G_B_BYTES = G_BNH * 128;          // 12 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
 constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 34816 = 34 * 1024
-constexpr int G_THREADS = 10 * 32;
+constexpr int G_THREADS = 12 * 32;             // warps 0, 10, 11 produce; 1 issues MMAs; 2..5 epilogue; 6..9 scale loaders
 constexpr int G_SF_BUFS = 3;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
@@ -195,7 +195,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->full[s], 4);   // A and B producers of both CTAs
             mbar_init(&sh->sffull[s], 1);
             mbar_init(&sh->empty[s], 1);
         }
@@ -224,8 +224,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ producer (whole warp, elected lane issues)
+    if (warp == 0 || warp >= 10) {
+        // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
+        // The TMA unit retires the copies of one issuing thread one after the other (about 450 cycles each,
+        // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
+        // 1 = weight tile (both counted on the leader's barrier), 2 = scale-factor atoms (local barrier).
+        const int role = warp == 0 ? 0 : warp - 9;
         uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
         bool ok = true;
         for (int ti = 0; ti < tr.count && ok; ++ti) {
@@ -235,12 +239,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 const int s = it % G_STAGES;
-                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10));
+                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10 + role));
                 if (!ok) break;
                 uint8_t* st = smem + s * G_STAGE_BYTES;
                 const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
+                const bool lowrank = ks >= kstages;
+                const int kx = lowrank ? (ks - kstages) * 32 : ks * 128;
                 if (elect_one()) {
-                    if (ks < kstages) {
+                    if (role == 0) {
+                        mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES);
+                        tma_load_2d_pair(st, lowrank ? &tm_la : &tm_a, lfull, kx, m0);
+                    } else if (role == 1) {
+                        mbar_arrive_expect_tx_cluster(lfull, G_B_BYTES);
+                        tma_load_2d_pair(st + G_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, kx, nb0);
+                    } else if (!lowrank) {
                         const int nkb = min(4, KB - ks * 4);
                         const int natoms = min(2, NB - atom0);
                         mbar_arrive_expect_tx(&sh->sffull[s], nkb * 512 * (1 + natoms));
@@ -249,15 +261,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         for (int a = 0; a < natoms; ++a)
                             bulk_load(st + G_A_BYTES + G_B_BYTES + G_SFA_BYTES + a * 2048,
                                       p.sfb + (static_cast<size_t>(atom0 + a) * KB + ks * 4) * 512, nkb * 512, &sh->sffull[s]);
-                        mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES + G_B_BYTES);
-                        tma_load_2d_pair(st, &tm_a, lfull, ks * 128, m0);
-                        tma_load_2d_pair(st + G_A_BYTES, &tm_b, lfull, ks * 128, nb0);
                     } else {
-                        const int c = ks - kstages;
                         mbar_arrive(&sh->sffull[s]);   // no scale factors in this stage: keep the barrier's phase in step with the ring
-                        mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES + G_B_BYTES);
-                        tma_load_2d_pair(st, &tm_la, lfull, c * 32, m0);
-                        tma_load_2d_pair(st + G_A_BYTES, &tm_lu, lfull, c * 32, nb0);
                     }
                 }
                 __syncwarp();
@@ -335,7 +340,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 __syncwarp();
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < 10) {
         // ------------------------------------------------------------------ scale-factor loaders (warps 6..9)
         // tcgen05.cp would put the scale factors into TMEM through the tensor pipe, where each copy costs
         // about 60 cycles that no MMA can overlap (12 copies per stage against 4 MMAs of ~100 cycles).

@@ -205,7 +205,90 @@ ingest_rate_kernel(const uint8_t* src, size_t src_bytes, int chunk, int depth, i
     }
 }
 
+// The same for 2-D tiled TMA loads: boxes of 128 bytes x `box_rows` rows (128B swizzle) from a row-major
+// byte matrix of `pitch` bytes per row, walked along the row first (the access pattern of a K-major GEMM
+// operand).  Every warp is an issuer with its own ring.
+__global__ void __launch_bounds__(256, 1)
+ingest_tensor_kernel(const __grid_constant__ CUtensorMap tm, int pitch, int rows, int box_rows, int depth, int iters,
+                     int mode, long long* cycles, int* status) {
+    // mode 0: plain loads.  Modes 1 and 2 need a cluster of 2 and use the cta_group::2 form of the load, counting
+    // completion on the CTA's own barrier (1) or on the barrier at the same offset in the other CTA (2).
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int issuers = blockDim.x / 32, w = threadIdx.x / 32;
+    const int chunk = box_rows * 128;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(issuers) * depth * chunk) + w * depth;
+    smem += static_cast<size_t>(w) * depth * chunk;
+    if ((threadIdx.x & 31) == 0) {
+        for (int s = 0; s < depth; ++s) mbar_init(&full[s], 1);
+        fence_mbar_init();
+    }
+    if (mode) cluster_sync_all(); else __syncthreads();
+    const uint32_t rank = mode ? cluster_ctarank() : 0;
+    const int kboxes = pitch / 128, rblocks = rows / box_rows;
+    int rb = (blockIdx.x * issuers + w) % rblocks, kb = 0;
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int it = 0; it < iters + depth && ok; ++it) {
+        const int s = it % depth;
+        if (it >= depth) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ((it / depth) - 1) & 1));
+        if (it < iters && ok) {
+            if (elect_one()) {
+                if (mode == 0) {
+                    mbar_arrive_expect_tx(&full[s], chunk);
+                    tma_load_2d(smem + static_cast<size_t>(s) * chunk, &tm, &full[s], kb * 128, rb * box_rows);
+                } else {
+                    const uint32_t bar = mapa_shared(smem_u32(&full[s]), mode == 1 ? rank : rank ^ 1u);
+                    mbar_arrive_expect_tx_cluster(bar, chunk);
+                    tma_load_2d_pair(smem + static_cast<size_t>(s) * chunk, &tm, bar, kb * 128, rb * box_rows);
+                }
+            }
+            __syncwarp();
+            if (++kb == kboxes) {
+                kb = 0;
+                rb = (rb + gridDim.x * issuers) % rblocks;
+            }
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (!ok) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
+        if (w == 0) cycles[blockIdx.x] = clock64() - t0;
+    }
+    if (mode) cluster_sync_all();
+}
+
 }  // namespace svdq
+
+extern "C" int svdq_probe_ingest_tensor(const void* src, int pitch, int rows, int box_rows, int depth, int iters, int grid,
+                                        int issuers, long long* cycles, void* stream, int mode) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(src && cycles && grid > 0 && grid <= 1024 && iters > 0 && pitch >= 128 && pitch % 128 == 0 && box_rows >= 8 &&
+                       box_rows <= 256 && box_rows % 8 == 0 && rows % box_rows == 0 && depth >= 1 && issuers >= 1 && issuers <= 8 &&
+                       static_cast<size_t>(issuers) * depth * box_rows * 128 <= 200 * 1024,
+                   "tensor ingest probe: bad argument");
+    if (int rc = check_arch()) return rc;
+    int* status = nullptr;
+    if (int rc = status_words(&status)) return rc;
+    CUtensorMap tm;
+    if (int rc = make_tmap_2d(&tm, src, CU_TENSOR_MAP_DATA_TYPE_UINT8, pitch, rows, pitch, 128, box_rows)) return rc;
+    const size_t smem = 1024 + static_cast<size_t>(issuers) * depth * (box_rows * 128 + 8) + 64;
+    SVDQ_CUDA(cudaFuncSetAttribute(ingest_tensor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    SVDQ_CHECK_ARG(mode >= 0 && mode <= 2 && (mode == 0 || grid % 2 == 0), "tensor ingest probe: bad mode / odd grid");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(32 * issuers, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = mode ? 1 : 0;
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, ingest_tensor_kernel, tm, pitch, rows, box_rows, depth, iters, mode, cycles, status));
+    return SVDQ_OK;
+}
 
 extern "C" int svdq_probe_ingest_rate(const void* src, size_t src_bytes, int chunk, int depth, int iters, int grid,
                                       int issuers, long long* cycles, void* stream) {

@@ -83,6 +83,25 @@ def ingest_rate(grid: int, chunk: int = 16384, depth: int = 4, iters: int = 4000
             "bytes_per_clk_per_sm": issuers * chunk * iters / c.mean().item(), "min": issuers * chunk * iters / c.max().item()}
 
 
+def ingest_tensor_rate(grid: int, pitch: int = 1536, rows: int = 21504, box_rows: int = 128, depth: int = 4, iters: int = 2000,
+                       issuers: int = 1, mode: int = 0):
+    """Bytes per clock per SM delivered by 2-D tiled TMA loads of 128-byte x box_rows boxes (K-major operand pattern)."""
+    lib = _lib.load()
+    lib.svdq_probe_ingest_tensor.restype = ctypes.c_int32
+    lib.svdq_probe_ingest_tensor.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 7 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    src = torch.zeros(rows * pitch, dtype=torch.uint8, device=dev)
+    cyc = torch.zeros(grid, dtype=torch.int64, device=dev)
+    for rep in range(2):
+        _lib.check(lib.svdq_probe_ingest_tensor(src.data_ptr(), pitch, rows, box_rows, depth, iters, grid, issuers, cyc.data_ptr(),
+                                                torch.cuda.current_stream(dev).cuda_stream, mode))
+        torch.cuda.synchronize()
+    c = cyc.double()
+    per = issuers * box_rows * 128 * iters
+    return {"grid": grid, "pitch": pitch, "rows": rows, "box_rows": box_rows, "depth": depth, "issuers": issuers, "mode": mode,
+            "bytes_per_clk_per_sm": per / c.mean().item(), "min": per / c.max().item()}
+
+
 def main():
     out = []
     for kind, n in [("mxf4nvf4", 256), ("mxf4nvf4", 192), ("mxf4nvf4", 128), ("i8", 256), ("i8", 128), ("tf32", 192)]:
