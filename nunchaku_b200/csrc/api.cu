@@ -72,6 +72,23 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, u
     return SVDQ_OK;
 }
 
+int make_tmap_3d(CUtensorMap* map, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                 uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    SVDQ_CHECK_ARG(aligned(base, 16) && stride1_bytes % 16 == 0 && stride2_bytes % 16 == 0,
+                   "tensor map: base and strides must be 16-byte aligned");
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    const cuuint32_t box[3] = {box0, box1, box2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, static_cast<CUtensorMapDataType>(elem), 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", static_cast<int>(r));
+    return SVDQ_OK;
+}
+
 int check_gemm_common(const svdq_gemm_args* a) {
     SVDQ_CHECK_ARG(a != nullptr, "gemm: null args");
     SVDQ_CHECK_ARG(a->act && a->ascales && a->w.wgt && a->w.wscales && a->w.col_scale && a->w.col_bias,

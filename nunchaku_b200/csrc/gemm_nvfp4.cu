@@ -22,7 +22,6 @@
 //               per stage; the low-rank branch is fed through the same ring as fp32 tiles and issued as
 //               kind::tf32 into the same accumulator; one multicast tcgen05.commit per stage releases the stage
 //               and its scale-factor buffer in both CTAs, one per tile publishes the accumulator
-//   warps 6..9  scale-factor loaders: shared memory -> registers -> TMEM (tcgen05.st), one lane quadrant each
 //   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
 //               staging buffer, TMA store (coalesced, clipped at M and N by the hardware); when requantising,
 //               the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix + mma.sync) and the
@@ -56,12 +55,12 @@ constexpr int G_B_BYTES = G_BNH * 128;          // 12 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
 constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 34816 = 34 * 1024
-constexpr int G_THREADS = 12 * 32;             // warps 0, 10, 11 produce; 1 issues MMAs; 2..5 epilogue; 6..9 scale loaders
-constexpr int G_SF_BUFS = 3;                    // scale-factor buffers in TMEM
+constexpr int G_THREADS = 9 * 32;              // warp 1 issues MMAs; 2..5 epilogue; 0, 6, 7, 8 produce (A, B, scales of A, scales of B)
+constexpr int G_SF_BUFS = 2;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
 constexpr int G_TM_SF = 2 * G_BN;               // 384: scale-factor buffers of 40 columns each
-constexpr int G_TM_SF_STRIDE = 40;              // per buffer: 4 x 4 columns for A, 4 x 6 for B (one per 32 rows)
+constexpr int G_TM_SF_STRIDE = 48;              // per buffer: 4 x 4 columns for A, 4 x 8 for B (two 128-row atoms per k-block)
 constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
 constexpr int G_COLV_FLOATS = 3 * G_BN;                     // per epilogue warp: scale, bias, 1/smooth_next
@@ -93,12 +92,10 @@ struct GemmParams {
 };
 
 struct GemmShared {
-    uint64_t full[G_STAGES];        // leader: operand tiles of both CTAs have landed (2 arrivals + bytes)
-    uint64_t sffull[G_STAGES];      // each CTA: its scale-factor atoms have landed
+    uint64_t full[G_STAGES];        // leader: operand tiles and scale atoms of both CTAs have landed (8 arrivals + bytes)
     uint64_t empty[G_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
     uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
-    uint64_t sf_full[G_SF_BUFS];    // leader: scale factors of a stage are in TMEM (4 loader warps x 2 CTAs)
     uint64_t drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -177,7 +174,8 @@ template <int RTN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
-                  const __grid_constant__ CUtensorMap tm_out, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
+                  const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* epi_smem = smem + G_STAGES * G_STAGE_BYTES;
@@ -195,21 +193,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&sh->full[s], 4);   // A and B producers of both CTAs
-            mbar_init(&sh->sffull[s], 1);
+            mbar_init(&sh->full[s], 8);   // four producers in each CTA
             mbar_init(&sh->empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->tfull[i], 1);
             mbar_init(&sh->tempty[i], 8);
         }
-        for (int i = 0; i < G_SF_BUFS; ++i) mbar_init(&sh->sf_full[i], 8);
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
         prefetch_tmap(&tm_out);
+        prefetch_tmap(&tm_sfa);
+        prefetch_tmap(&tm_sfb);
         if (p.lora_chunks) {
             prefetch_tmap(&tm_la);
             prefetch_tmap(&tm_lu);
@@ -224,18 +222,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
 
-    if (warp == 0 || warp >= 10) {
+    if (warp == 0 || warp >= 6) {
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
-        // The TMA unit retires the copies of one issuing thread one after the other (about 450 cycles each,
+        // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
-        // 1 = weight tile (both counted on the leader's barrier), 2 = scale-factor atoms (local barrier).
-        const int role = warp == 0 ? 0 : warp - 9;
+        // 1 = weight tile, 2 = scale atoms of the activation rows, 3 = scale atoms of the 192 weight rows (whole
+        // 128-row atoms: two of them).  All are counted on the leader's barrier; a tile past the end of a
+        // tensor is filled with zeros by the hardware and still counts its full size.
+        const int role = warp == 0 ? 0 : warp - 5;
         uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
         bool ok = true;
         for (int ti = 0; ti < tr.count && ok; ++ti) {
             int m0, n0;
             tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
-            const int atom0 = n0 >> 7;
             const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 const int s = it % G_STAGES;
@@ -252,17 +251,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     } else if (role == 1) {
                         mbar_arrive_expect_tx_cluster(lfull, G_B_BYTES);
                         tma_load_2d_pair(st + G_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, kx, nb0);
-                    } else if (!lowrank) {
-                        const int nkb = min(4, KB - ks * 4);
-                        const int natoms = min(2, NB - atom0);
-                        mbar_arrive_expect_tx(&sh->sffull[s], nkb * 512 * (1 + natoms));
-                        bulk_load(st + G_A_BYTES + G_B_BYTES, p.sfa + (static_cast<size_t>(m0 >> 7) * KB + ks * 4) * 512,
-                                  nkb * 512, &sh->sffull[s]);
-                        for (int a = 0; a < natoms; ++a)
-                            bulk_load(st + G_A_BYTES + G_B_BYTES + G_SFA_BYTES + a * 2048,
-                                      p.sfb + (static_cast<size_t>(atom0 + a) * KB + ks * 4) * 512, nkb * 512, &sh->sffull[s]);
+                    } else if (lowrank) {
+                        mbar_arrive_cluster(lfull);   // no scale factors in a low-rank stage
+                    } else if (role == 2) {
+                        mbar_arrive_expect_tx_cluster(lfull, G_SFA_BYTES);
+                        tma_load_2d_pair(st + G_A_BYTES + G_B_BYTES, &tm_sfa, lfull, 0, (m0 >> 7) * KB + ks * 4);
                     } else {
-                        mbar_arrive(&sh->sffull[s]);   // no scale factors in this stage: keep the barrier's phase in step with the ring
+                        mbar_arrive_expect_tx_cluster(lfull, G_SFB_BYTES);
+                        tma_load_3d_pair(st + G_A_BYTES + G_B_BYTES + G_SFA_BYTES, &tm_sfb, lfull, 0, ks * 4, n0 >> 7);
                     }
                 }
                 __syncwarp();
@@ -276,10 +272,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (rank == 0) {
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(2 * G_BM, G_BN);
+            const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem));
+            const uint64_t sfdesc0 = smem_desc_sf(smem_u32(smem) + G_A_BYTES + G_B_BYTES);
             uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
             bool ok = true;
             for (int ti = 0; ti < tr.count && ok; ++ti) {
                 const uint32_t as = ti & 1;
+                int m0_, n0_;
+                tile_coords(p, tr.first + ti * tr.stride, 0, m0_, n0_);
+                const uint32_t sfb_off = (n0_ & 127) ? 2 : 0;  // tile starts 64 rows into a 128-row scale atom
                 ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -289,30 +290,39 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     const int s = it % G_STAGES;
                     ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
                     if (!ok) break;
-                    const uint32_t sa = smem_u32(smem + s * G_STAGE_BYTES);
-                    const uint64_t adesc = smem_desc_sw128(sa);
-                    const uint64_t bdesc = smem_desc_sw128(sa + G_A_BYTES);
+                    // descriptors of ring slot s: the start-address field counts 16-byte units
+                    const uint64_t adesc = adesc0 + static_cast<uint32_t>(s * (G_STAGE_BYTES >> 4));
+                    const uint64_t bdesc = adesc + (G_A_BYTES >> 4);
                     if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
-                        const uint32_t b = sq % G_SF_BUFS;
-                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->sf_full[b], (sq / G_SF_BUFS) & 1, sh, p.status, 22));
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        const uint32_t t_sfa = tmem + G_TM_SF + b * G_TM_SF_STRIDE;
+                        // Scale factors: shared memory -> TMEM with tcgen05.cp, issued just ahead of the MMA that
+                        // reads them (the tensor pipe keeps the order).  Per k-block one 512-byte atom for the 128
+                        // activation rows (4 columns) and two for the weight rows (8 columns; a tile that starts 64
+                        // rows into an atom reads from column 2 on).  Two TMEM buffers alternate.
+                        const uint32_t t_sfa = tmem + G_TM_SF + (sq & 1) * G_TM_SF_STRIDE;
                         const uint32_t t_sfb = t_sfa + 16;
+                        const uint64_t sfdesc = sfdesc0 + static_cast<uint32_t>(s * (G_STAGE_BYTES >> 4));
+                        tc_fence_after_sync();
                         if (elect_one()) {
                             if (nkb == 4) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j)
-                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
-                                                      j == 0 ? accumulate : 1u);
+                                for (int j = 0; j < 4; ++j) {
+                                    tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
+                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
+                                                      t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
+                                }
                             } else {
-                                for (int j = 0; j < nkb; ++j)
-                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j, t_sfb + 6 * j,
-                                                      j == 0 ? accumulate : 1u);
+                                for (int j = 0; j < nkb; ++j) {
+                                    tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
+                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
+                                                      t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
+                                }
                             }
-                            // one commit frees the stage and its scale-factor buffer, in both CTAs
-                            tc_commit_pair(&sh->empty[s], 3);
+                            tc_commit_pair(&sh->empty[s], 3);   // frees the stage in both CTAs
                         }
                         ++sq;
                     } else {
@@ -340,74 +350,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 __syncwarp();
             }
         }
-    } else if (warp >= 6 && warp < 10) {
-        // ------------------------------------------------------------------ scale-factor loaders (warps 6..9)
-        // tcgen05.cp would put the scale factors into TMEM through the tensor pipe, where each copy costs
-        // about 60 cycles that no MMA can overlap (12 copies per stage against 4 MMAs of ~100 cycles).
-        // Instead each of these four warps reads the stage's 512-byte atoms from shared memory (row r0 =
-        // lane, 16 bytes = the 4 row groups x 4 scale bytes) and writes them to its own TMEM lane quadrant
-        // with tcgen05.st: 16 columns for A, 24 for B per stage.
-        // A TMEM buffer is free again when the MMAs of the stage that used it (three scale-factor stages
-        // earlier) are done, which is what that stage's `empty` barrier says: `used_by` remembers its ring
-        // position.  G_STAGES > G_SF_BUFS, so that barrier cannot complete another phase before this wait.
-        const int q = warp & 3;
-        uint32_t it = 0, sq = 0;
-        uint32_t used_by[G_SF_BUFS] = {};
-        bool ok = true;
-        for (int ti = 0; ti < tr.count && ok; ++ti) {
-            int m0, n0;
-            tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
-            const bool mid_atom = (n0 & 127) != 0;  // tile starts 64 rows into a 128-row atom
-            for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                if (ks >= kstages) continue;  // low-rank stages carry no scale factors
-                const int s = it % G_STAGES;
-                const uint32_t b = sq % G_SF_BUFS;
-                if (!wait_or_abort(&sh->sffull[s], (it / G_STAGES) & 1, sh, p.status, 40)) {
-                    ok = false;
-                    break;
-                }
-                const uint8_t* sf = smem + s * G_STAGE_BYTES + G_A_BYTES + G_B_BYTES + lane * 16;
-                // registers 0..15: A (k-block j, row group c -> 4j + c); 16..39: B (6j + c), where the tile's
-                // 192 weight rows are row groups off..off+5 of the two 128-row atoms in shared memory.
-                // The shared-memory reads happen before the wait for the TMEM buffer: only the TMEM store is on
-                // the path between "the MMAs that used this buffer are done" and "the next MMAs may start".
-                uint32_t r32[32], r8[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 a = *reinterpret_cast<const uint4*>(sf + j * 512);
-                    const uint4 b0 = *reinterpret_cast<const uint4*>(sf + G_SFA_BYTES + j * 512);
-                    const uint4 b1 = *reinterpret_cast<const uint4*>(sf + G_SFA_BYTES + 2048 + j * 512);
-                    r32[4 * j] = a.x; r32[4 * j + 1] = a.y; r32[4 * j + 2] = a.z; r32[4 * j + 3] = a.w;
-                    uint32_t w[6];
-                    if (mid_atom) { w[0] = b0.z; w[1] = b0.w; w[2] = b1.x; w[3] = b1.y; w[4] = b1.z; w[5] = b1.w; }
-                    else          { w[0] = b0.x; w[1] = b0.y; w[2] = b0.z; w[3] = b0.w; w[4] = b1.x; w[5] = b1.y; }
-#pragma unroll
-                    for (int c = 0; c < 6; ++c) {
-                        const int idx = 16 + 6 * j + c;   // compile-time after unrolling
-                        if (idx < 32) r32[idx] = w[c]; else r8[idx - 32] = w[c];
-                    }
-                }
-                fence_proxy_async_smem();   // generic reads of the stage above, TMA refill below the MMA's commit
-                if (sq >= G_SF_BUFS) {
-                    const uint32_t pit = used_by[b];
-                    if (!wait_or_abort(&sh->empty[pit % G_STAGES], (pit / G_STAGES) & 1, sh, p.status, 41)) {
-                        ok = false;
-                        break;
-                    }
-                }
-                used_by[b] = it;
-                tc_fence_after_sync();
-                const uint32_t t_sf = tmem + (static_cast<uint32_t>(q * 32) << 16) + G_TM_SF + b * G_TM_SF_STRIDE;
-                tc_st_32x32b_x32(t_sf, r32);
-                tc_st_32x32b_x8(t_sf + 32, r8);
-                tc_wait_st();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sf_full[b]), 0));
-                ++sq;
-            }
-        }
-    } else {
+    } else if (warp >= 2 && warp < 6) {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
         // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
@@ -644,7 +587,8 @@ int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
 
 template <int RTN>
 static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
-                        const CUtensorMap& lu, const CUtensorMap& o, const GemmParams& p) {
+                        const CUtensorMap& lu, const CUtensorMap& o, const CUtensorMap& sfa, const CUtensorMap& sfb,
+                        const GemmParams& p) {
     static bool attr_done[64] = {};
     int dev = 0;
     SVDQ_CUDA(cudaGetDevice(&dev));
@@ -665,7 +609,7 @@ static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, con
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<RTN>, a, b, la, lu, o, p));
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<RTN>, a, b, la, lu, o, sfa, sfb, p));
     return SVDQ_OK;
 }
 
@@ -721,7 +665,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.slots = pl.slots;
     if (int rc = status_words(&p.status)) return rc;
 
-    CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
+    CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb;
     if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 128, G_BM)) return rc;
     if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->N, a->K / 2, 128, G_BNH)) return rc;
     if (a->R > 0) {
@@ -742,11 +686,19 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     } else {
         tm_out = tm_a;
     }
+    {   // scale atoms: [row atom][K/64][512 bytes]; a stage takes 4 k-blocks of one atom (A) / of two atoms (B)
+        const uint64_t KB = a->K / 64;
+        if (int rc = make_tmap_2d(&tm_sfa, a->ascales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 128, static_cast<uint64_t>(a->M_pad / 128) * KB,
+                                  512, 128, 4, /*swizzle128=*/false))
+            return rc;
+        if (int rc = make_tmap_3d(&tm_sfb, a->w.wscales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 128, KB, a->N / 128, 512, KB * 512, 128, 4, 2))
+            return rc;
+    }
     int rc;
-    if (!requant) rc = launch_nvfp4<0>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else if (a->R_next == 16) rc = launch_nvfp4<1>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else if (a->R_next == 32) rc = launch_nvfp4<2>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    else rc = launch_nvfp4<4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    if (!requant) rc = launch_nvfp4<0>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else if (a->R_next == 16) rc = launch_nvfp4<1>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else if (a->R_next == 32) rc = launch_nvfp4<2>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else rc = launch_nvfp4<4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
     if (rc) return rc;
     if (requant) {
         lora_partial_reduce_kernel<<<2 * pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,

@@ -51,6 +51,10 @@ int status_words(int** ptr);
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem /*CUtensorMapDataType*/, uint64_t inner,
                  uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128 = true);
 
+// 3-D tiled map without swizzle (dimension 0 innermost and contiguous); out-of-range boxes read zeros.
+int make_tmap_3d(CUtensorMap* map, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                 uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);
+
 // Pointer / shape / alignment / architecture checks shared by the GEMM entry points.
 int check_gemm_common(const svdq_gemm_args* a);
 

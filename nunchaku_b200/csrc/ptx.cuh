@@ -307,6 +307,17 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* tmap, ui
         ::"r"(smem_u32(dst)), "l"(tmap), "r"(mbar_cluster_addr), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const void* tmap, uint32_t mbar_cluster_addr, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tmap), "r"(mbar_cluster_addr), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// shared -> TMEM copy of a 32-row x 16-byte block, broadcast to the 4 lane quadrants, executed by both CTAs of
+// the pair: each copies from its own shared memory (same offset) into its own TMEM (same address).
+__device__ __forceinline__ void tc_cp_pair_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {  // one whole warp in each CTA
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
                  : "memory");
