@@ -220,6 +220,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc_fence_before_sync();
     cluster_sync_all();   // barriers of both CTAs are initialised before anything remote touches them
     tc_fence_after_sync();
+    pdl_launch_dependents();
+    pdl_wait();           // nothing above touches global memory; the quantiser's output is this kernel's input
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0 || warp >= 6) {
@@ -602,13 +604,15 @@ static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, con
     cfg.blockDim = dim3(G_THREADS, 1, 1);
     cfg.dynamicSmemBytes = G_SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap launch + prologue with the predecessor's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<RTN>, a, b, la, lu, o, sfa, sfb, p));
     return SVDQ_OK;
 }
