@@ -31,6 +31,23 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
                  : "r"(saddr));
 }
 
+// GLU gating of two (value, gate) bf16 pairs -> two bf16 results in one word.  Per pair
+// (gemm_base.cuh:612-623, gemm_utils.cuh:291-327): s = bf16(g * sigmoid(g)), sigmoid(g) = rcp.approx(1 + ex2.approx(-log2(e) g)),
+// result = bf16(v * s); words hold the value in the low half and the gate in the high half.
+__device__ __forceinline__ float glu_one(uint32_t w) {
+    const float v = __uint_as_float(w << 16);
+    const float g = __uint_as_float(w & 0xffff0000u);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.442695041f * g));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    const float s = __bfloat162float(__float2bfloat16_rn(g * r));
+    return v * s;
+}
+__device__ __forceinline__ uint32_t glu_pair2(uint32_t w0, uint32_t w1) {
+    const __nv_bfloat162 o = __floats2bfloat162_rn(glu_one(w0), glu_one(w1));
+    return *reinterpret_cast<const uint32_t*>(&o);
+}
+
 // position of channel n (0..127) inside a 128-block of a reference-packed vector
 // (gemm_base.cuh:100-112): n = a*16 + b*8 + c*2 + d  ->  a*16 + c*4 + b*2 + d
 __device__ __forceinline__ int packed_vec_pos(int n) {

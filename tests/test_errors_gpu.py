@@ -21,8 +21,10 @@ def test_bad_arguments_raise():
               smooth=sm[:96].contiguous(), fp4=True)                   # K not a multiple of 128
     with pytest.raises(ValueError):
         quant(x.cpu(), lora_down=ld, smooth=sm, fp4=True)             # no CPU path
-    with pytest.raises(NotImplementedError):
-        quant(torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda"), lora_down=ld, smooth=sm, fp4=True, fuse_glu=True)
+    with pytest.raises(ValueError):
+        # fuse_glu halves the channel count: a [256, 256] input is K = 128, which does not match smooth / lora_down
+        quant(torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda"), lora_down=ld, smooth=sm, fp4=True, fuse_glu=True,
+              output=torch.empty(256, 128, dtype=torch.uint8, device="cuda"))
     # the context is still healthy
     out = quant(x, lora_down=ld, smooth=sm, fp4=True)
     torch.cuda.synchronize()
