@@ -12,6 +12,7 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
 int relayout_impl(const svdq_relayout_args* a, cudaStream_t stream);
 int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream);
 int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);
+int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);
 int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream);
 
 std::string& last_error() {
@@ -126,6 +127,7 @@ int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes) {
     if (!args || !bytes) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, "workspace_bytes: null argument");
     *bytes = 0;
     if (args->fp4 && args->qout) return svdq::gemm_nvfp4_workspace_bytes(args, bytes);
+    if (!args->fp4 && args->qout) return svdq::gemm_int4_workspace_bytes(args, bytes);
     return SVDQ_OK;
 }
 

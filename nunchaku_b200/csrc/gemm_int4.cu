@@ -15,6 +15,11 @@
 //     epilogue warps drain each group: int32 -> fp32 (magic-number add, no I2F), times ascale[m,g] *
 //     wscale[n,g], accumulated in registers.  The low-rank branch is one more "group": a kind::tf32 MMA of
 //     the fp32 lora_act and LoRA-up tiles whose fp32 result is added as is.
+// Requantising epilogue (GELU + next layer, gemm_w4a4_launch_impl.cuh:282-309): an epilogue thread holds one row x 64
+// columns, which is exactly one INT4 group of the next layer, so the u4 codes of bf16(bf16(y + 0.171875) / smooth_next)
+// and their bf16 scale (max / 15) come out of registers; the staged bf16 tile feeds the next layer's LoRA-down
+// (ldmatrix + mma.sync), kept deterministic like in the NVFP4 kernel: contiguous tile runs per CTA, one partial per
+// row block, column half and CTA in caller scratch, a second small kernel adds them in a fixed order.
 // One persistent CTA per SM, 128 x 128 output tiles, K in steps of 128 (two groups per stage).
 //   warp 0       TMA producer      warp 1       MMA issuer       warps 2..5   nibble -> s8 converters
 //   warps 6..13  epilogue (lane quadrant = warp % 4, column half = (warp - 6) / 4)
@@ -25,6 +30,7 @@
 
 #include "host_common.h"
 #include "ptx.cuh"
+#include "quant_common.cuh"
 
 namespace svdq {
 
@@ -40,8 +46,9 @@ constexpr int I_EPI_BUF_BYTES = 32 * 128;           // 32 rows x 64 bf16
 constexpr int I_EPI_BYTES = 8 * I_EPI_BUF_BYTES;
 constexpr int I_THREADS = 14 * 32;
 constexpr int I_TBUFS = 4;                          // TMEM group buffers of 128 columns
+constexpr int I_RCP_BYTES = 8 * 64 * 4;             // per epilogue warp: 1 / smooth_next of its 64 columns
 constexpr size_t I_SMEM_BYTES =
-    1024 + static_cast<size_t>(I_U_STAGES) * I_U_BYTES + I_PK_STAGES * I_PK_BYTES + I_EPI_BYTES + 512;
+    1024 + static_cast<size_t>(I_U_STAGES) * I_U_BYTES + I_PK_STAGES * I_PK_BYTES + I_EPI_BYTES + I_RCP_BYTES + 512;
 
 struct Int4Params {
     const __nv_bfloat16* ascales;   // [K/64][M_pad]
@@ -53,7 +60,46 @@ struct Int4Params {
     int tiles_m, tiles_n;
     int activation;
     int act_unsigned;
+    int store_out;            // bf16 `out` is wanted
+    // tile schedule: 0: m-fastest, strided by gridDim; 1: n-fastest, each CTA a contiguous run of `run` tiles
+    int contiguous;
+    int run;
+    // requantising epilogue (GELU + next layer's INT4 quantisation + LoRA-down)
+    uint8_t* qout;                      // [M_pad][N/2]
+    __nv_bfloat16* oscales;             // [N/64][M_pad]
+    const __nv_bfloat16* next_smooth;   // [N] reference-packed
+    const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
+    float* lora_partial;                // scratch [CTA][slot][column half 2][128][Rn]
+    int slots;
+    int next_unsigned;                  // u4 codes of (y + 0.171875) / smooth, as the reference's INT4 chain uses
 };
+
+struct I4Run {
+    int first, stride, count;
+};
+__device__ __forceinline__ I4Run i4_run(const Int4Params& p) {
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    I4Run r;
+    if (p.contiguous) {
+        r.first = blockIdx.x * p.run;
+        r.stride = 1;
+        r.count = max(0, min(p.run, num_tiles - r.first));
+    } else {
+        r.first = blockIdx.x;
+        r.stride = gridDim.x;
+        r.count = num_tiles > r.first ? (num_tiles - r.first + r.stride - 1) / r.stride : 0;
+    }
+    return r;
+}
+__device__ __forceinline__ void i4_coords(const Int4Params& p, int tile, int& m0, int& n0) {
+    if (p.contiguous) {
+        m0 = (tile / p.tiles_n) * I_BM;
+        n0 = (tile % p.tiles_n) * I_BN;
+    } else {
+        m0 = (tile % p.tiles_m) * I_BM;
+        n0 = (tile / p.tiles_m) * I_BN;
+    }
+}
 
 struct Int4Shared {
     uint64_t pk_full[I_PK_STAGES];
@@ -99,6 +145,8 @@ __device__ __forceinline__ float i4_act(float v, int activation) {
     return v;
 }
 
+// RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
+template <int RTN>
 __global__ void __launch_bounds__(I_THREADS, 1)
 gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
@@ -108,13 +156,14 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint8_t* ubuf = smem;                                           // [I_U_STAGES][A 16K | B 16K]
     uint8_t* epi_smem = ubuf + I_U_STAGES * I_U_BYTES;              // 8 x 4 KB, 1024-aligned
     uint8_t* pkbuf = epi_smem + I_EPI_BYTES;                        // [I_PK_STAGES][8K]
-    Int4Shared* sh = reinterpret_cast<Int4Shared*>(pkbuf + I_PK_STAGES * I_PK_BYTES);
+    float* rcp_smem = reinterpret_cast<float*>(pkbuf + I_PK_STAGES * I_PK_BYTES);   // [8 warps][64]
+    Int4Shared* sh = reinterpret_cast<Int4Shared*>(pkbuf + I_PK_STAGES * I_PK_BYTES + I_RCP_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int kstages = p.K / 128;
     const int per_tile = kstages + p.lora_chunks;       // stages per tile
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const I4Run tr = i4_run(p);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < I_PK_STAGES; ++s) {
@@ -151,9 +200,9 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0, pk = 0;   // unpacked-ring position, packed-ring position
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % p.tiles_m) * I_BM;
-                const int n0 = (tile / p.tiles_m) * I_BN;
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
+                int m0, n0;
+                i4_coords(p, tr.first + ti * tr.stride, m0, n0);
                 for (int ks = 0; ks < per_tile; ++ks, ++it) {
                     const int u = it % I_U_STAGES;
                     uint8_t* ub = ubuf + u * I_U_BYTES;
@@ -184,7 +233,7 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t IDESC_TF32 = idesc_tf32(I_BM, I_BN);
             uint32_t it = 0, gq = 0;   // stage count, group (TMEM buffer) count
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
                 for (int ks = 0; ks < per_tile && ok; ++ks, ++it) {
                     const int u = it % I_U_STAGES;
                     if (!i4_wait(&sh->b_full[u], (it / I_U_STAGES) & 1, sh, p.status, 20) ||
@@ -223,7 +272,7 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const bool is_signed = !p.act_unsigned;
         uint32_t it = 0, pk = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 const int u = it % I_U_STAGES;
                 if (ks < kstages) {
@@ -276,11 +325,64 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int KB = p.K / 64;
         uint32_t gq = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile % p.tiles_m) * I_BM;
-            const int n0 = (tile / p.tiles_m) * I_BN;
+        // next layer's LoRA-down partial of this warp's 32 rows x its column half: [m-tile 2][rank tile][8]
+        constexpr int RTA = RTN > 0 ? RTN : 1;
+        float lacc[2][RTA][8];
+        float* rcs = rcp_smem + (warp - 6) * 64;
+        int cur_m0 = -1, slot = 0;
+        auto lacc_zero = [&]() {
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int b = 0; b < RTA; ++b)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) lacc[a][b][c] = 0.f;
+        };
+        auto lacc_flush = [&]() {   // partial of row block cur_m0 -> scratch[blockIdx][slot][h][128][Rn]
+            if constexpr (RTN > 0) {
+                constexpr int RN = RTN * 16;
+                float* dst = p.lora_partial + ((static_cast<size_t>(blockIdx.x) * p.slots + slot) * 2 + h) * (I_BM * RN);
+                const int gq4 = lane >> 2, t = lane & 3;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int rt = 0; rt < RTN; ++rt)
+#pragma unroll
+                        for (int nh = 0; nh < 2; ++nh)
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                const int row = q * 32 + mt * 16 + gq4 + half * 8;
+                                const int rank = rt * 16 + nh * 8 + 2 * t;
+                                *reinterpret_cast<float2*>(dst + row * RN + rank) =
+                                    make_float2(lacc[mt][rt][nh * 4 + half * 2], lacc[mt][rt][nh * 4 + half * 2 + 1]);
+                            }
+                ++slot;
+            }
+        };
+        lacc_zero();
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            int m0, n0;
+            i4_coords(p, tr.first + ti * tr.stride, m0, n0);
             const int m = m0 + q * 32 + lane;               // < M_pad always
             const int nb = n0 + h * 64;
+            if constexpr (RTN > 0) {
+                if (m0 != cur_m0) {
+                    if (cur_m0 >= 0) {
+                        lacc_flush();
+                        lacc_zero();
+                    }
+                    cur_m0 = m0;
+                }
+                // 1 / smooth_next of this warp's 64 columns (issued before the accumulators are needed)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int n = nb + lane + 32 * i;
+                    float r = 0.f;
+                    if (n < p.N) r = __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)]));
+                    rcs[lane + 32 * i] = r;
+                }
+                __syncwarp();
+            }
             float acc[64];
 #pragma unroll
             for (int i = 0; i < 64; ++i) acc[i] = 0.f;
@@ -336,8 +438,10 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (nb < p.N) {
                 const float4* cb = reinterpret_cast<const float4*>(p.col_bias + nb);
 #pragma unroll
+                uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
+#pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    uint32_t o[4];
+                    uint32_t* o = &ow[4 * j];
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const float4 b4 = __ldg(cb + 2 * j + i);
@@ -355,10 +459,69 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    if (m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, nb, m0 + q * 32);
+                    if (p.store_out && m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, nb, m0 + q * 32);
                     bulk_commit_group();
                 }
+                if constexpr (RTN > 0) {
+                    // ---- next layer's LoRA-down on the staged bf16 tile: [32 x 64] x Wd_next[64 x Rn]
+                    const int ch_tile0 = nb >> 4;           // 16-channel tile index of the chunk
+                    const uint32_t bufa = smem_u32(buf);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        uint4 bfrag[RTA];
+#pragma unroll
+                        for (int rt = 0; rt < RTN; ++rt)
+                            bfrag[rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * RTN + rt) * 32 + lane);
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            const int arow = mt * 16 + (lane & 15);
+                            uint32_t a[4];
+                            ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
+#pragma unroll
+                            for (int rt = 0; rt < RTN; ++rt) {
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[rt].x, bfrag[rt].y);
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[rt].z, bfrag[rt].w);
+                            }
+                        }
+                    }
+                    // ---- INT4 group quantisation: this thread's 64 values are exactly one group
+                    // (+0.171875 in bf16 when the codes are unsigned, gemm_w4a4_launch_impl.cuh:282-309) / smooth
+                    const float4* rc4 = reinterpret_cast<const float4*>(rcs);
+                    uint32_t qv[4][8];
+                    float amax = 0.f;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint32_t xw[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            uint32_t w = ow[8 * g + i];
+                            if (p.next_unsigned) {
+                                const float2 f = bf16x2_to_float2(w);
+                                const __nv_bfloat162 sft = __floats2bfloat162_rn(f.x + 0.171875f, f.y + 0.171875f);
+                                w = *reinterpret_cast<const uint32_t*>(&sft);
+                            }
+                            xw[i] = w;
+                        }
+                        amax = fmaxf(amax, smooth16(xw, rc4 + 4 * g, qv[g]));
+                    }
+                    uint32_t codes[8];
+                    float scale = 0.f;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint32_t cw[2];
+                        scale = p.next_unsigned ? int4_encode16<true>(qv[g], amax, cw) : int4_encode16<false>(qv[g], amax, cw);
+                        codes[2 * g] = cw[0];
+                        codes[2 * g + 1] = cw[1];
+                    }
+                    uint4* qdst = reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(m) * (p.N >> 1) + (nb >> 1));
+                    qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                    qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                    p.oscales[static_cast<size_t>(nb >> 6) * p.M_pad + m] = __float2bfloat16_rn(scale);
+                }
             }
+        }
+        if constexpr (RTN > 0) {
+            if (cur_m0 >= 0) lacc_flush();
         }
         if (lane == 0) bulk_wait_group<0>();
     }
@@ -371,10 +534,83 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
+// lora_act_out[row][r] = sum over the CTAs that touched the row's 128-row block, in CTA order, of the partials of
+// their two column halves.  Row block mb holds tiles [mb*tiles_n, (mb+1)*tiles_n); CTA c owns tiles [c*run, (c+1)*run).
+__global__ void int4_lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n,
+                                                int run, int slots, int grid_ctas) {
+    const int mb = blockIdx.x;
+    const int c_lo = (mb * tiles_n) / run;
+    const int c_hi = min(grid_ctas - 1, ((mb + 1) * tiles_n - 1) / run);
+    for (int i = threadIdx.x; i < I_BM * rn; i += blockDim.x) {
+        float s = 0.f;
+        for (int c = c_lo; c <= c_hi; ++c) {
+            const int first_mb = (c * run) / tiles_n;
+            const float* pp = partial + ((static_cast<size_t>(c) * slots + (mb - first_mb)) * 2) * (I_BM * rn);
+            s += pp[i];
+            s += pp[I_BM * rn + i];
+        }
+        out[static_cast<size_t>(mb) * I_BM * rn + i] = s;
+    }
+}
+
+struct Int4Plan {
+    int requant, tiles_m, tiles_n, grid, run, slots, rn;
+    size_t workspace;
+};
+
+static void plan_int4(const svdq_gemm_args* a, int sms, Int4Plan* pl) {
+    pl->requant = a->qout != nullptr;
+    pl->tiles_n = (a->N + I_BN - 1) / I_BN;
+    pl->tiles_m = pl->requant ? a->M_pad / I_BM : (a->M + I_BM - 1) / I_BM;
+    const int num_tiles = pl->tiles_m * pl->tiles_n;
+    pl->grid = num_tiles < sms ? num_tiles : sms;
+    pl->run = (num_tiles + pl->grid - 1) / pl->grid;
+    if (pl->requant) pl->grid = (num_tiles + pl->run - 1) / pl->run;
+    pl->slots = (pl->run + pl->tiles_n - 2) / pl->tiles_n + 1;
+    pl->rn = a->R_next;
+    pl->workspace = pl->requant ? static_cast<size_t>(pl->grid) * pl->slots * 2 * I_BM * pl->rn * sizeof(float) : 0;
+}
+
+int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
+    int dev = 0, sms = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    Int4Plan pl;
+    plan_int4(a, sms, &pl);
+    *bytes = pl.workspace;
+    return SVDQ_OK;
+}
+
+template <int RTN>
+static int launch_int4(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
+                       const CUtensorMap& lu, const CUtensorMap& o, const Int4Params& p) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !attr_done[dev]) {
+        SVDQ_CUDA(cudaFuncSetAttribute(gemm_int4_kernel<RTN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(I_SMEM_BYTES)));
+        attr_done[dev] = true;
+    }
+    gemm_int4_kernel<RTN><<<grid, I_THREADS, I_SMEM_BYTES, stream>>>(a, b, la, lu, o, p);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
 int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
-    SVDQ_CHECK_ARG(a->out != nullptr, "gemm(int4): `out` is required (next-layer requantisation is not built yet)");
-    if (a->qout || a->oscales || a->lora_act_out)
-        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): fused next-layer requantisation is not built yet");
+    const bool requant = a->qout != nullptr;
+    SVDQ_CHECK_ARG(a->out != nullptr || requant, "gemm(int4): neither `out` nor `qout` given");
+    if (requant) {
+        SVDQ_CHECK_ARG(a->oscales && a->lora_act_out && a->next_smooth && a->next_lora_down,
+                       "gemm(int4): requantisation needs oscales, lora_act_out, next_smooth and next_lora_down");
+        SVDQ_CHECK_ARG(!a->next_fp4, "gemm(int4): the requantised output must be INT4 as well");
+        SVDQ_CHECK_ARG(a->out_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): requantised output is written in SVDQ_LAYOUT_NATIVE");
+        SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
+                           aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
+                       "gemm(int4): requantisation tensors must be 16-byte aligned (workspace: 256)");
+        if (a->R_next != 16 && a->R_next != 32 && a->R_next != 64)
+            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
+    }
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                         "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
@@ -393,10 +629,24 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.N = a->N;
     p.K = a->K;
     p.lora_chunks = (a->R + 31) / 32;
-    p.tiles_m = (a->M + I_BM - 1) / I_BM;
-    p.tiles_n = (a->N + I_BN - 1) / I_BN;
+    Int4Plan pl;
+    plan_int4(a, sms, &pl);
+    SVDQ_CHECK_ARG(!requant || (a->workspace && a->workspace_bytes >= pl.workspace),
+                   "gemm(int4): workspace of %zu bytes required (svdq_gemm_w4a4_workspace_bytes)", pl.workspace);
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
     p.activation = a->activation;
     p.act_unsigned = a->act_unsigned;
+    p.store_out = a->out != nullptr;
+    p.contiguous = requant;
+    p.run = pl.run;
+    p.qout = static_cast<uint8_t*>(a->qout);
+    p.oscales = static_cast<__nv_bfloat16*>(a->oscales);
+    p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
+    p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
+    p.lora_partial = static_cast<float*>(a->workspace);
+    p.slots = pl.slots;
+    p.next_unsigned = 1;   // the reference's INT4 chain always requantises to u4 with the +0.171875 shift (launch_impl.cuh:282-309)
     if (int rc = status_words(&p.status)) return rc;
 
     CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
@@ -414,18 +664,23 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_la = tm_b;
         tm_lu = tm_b;
     }
-    if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
-        return rc;
-    static bool attr_done[64] = {};
-    if (dev < 64 && !attr_done[dev]) {
-        SVDQ_CUDA(cudaFuncSetAttribute(gemm_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(I_SMEM_BYTES)));
-        attr_done[dev] = true;
+    if (a->out) {
+        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+            return rc;
+    } else {
+        tm_out = tm_b;
     }
-    const int num_tiles = p.tiles_m * p.tiles_n;
-    const int grid = num_tiles < sms ? num_tiles : sms;
-    gemm_int4_kernel<<<grid, I_THREADS, I_SMEM_BYTES, stream>>>(tm_a, tm_b, tm_la, tm_lu, tm_out, p);
-    SVDQ_CUDA(cudaGetLastError());
+    int rc;
+    if (!requant) rc = launch_int4<0>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 16) rc = launch_int4<1>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else if (a->R_next == 32) rc = launch_int4<2>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    else rc = launch_int4<4>(pl.grid, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, p);
+    if (rc) return rc;
+    if (requant) {
+        int4_lora_partial_reduce_kernel<<<pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
+                                                                       pl.slots, pl.grid);
+        SVDQ_CUDA(cudaGetLastError());
+    }
     return SVDQ_OK;
 }
 

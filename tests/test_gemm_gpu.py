@@ -273,3 +273,77 @@ def test_fused_gelu_mlp_matches_oracle_chain():
     # and against the bf16 master weights: 4-bit quantisation error of two stacked layers
     ref = torch.nn.functional.gelu(x.float() @ fc1.master.t() + fc1.bias.float(), approximate="tanh") @ fc2.master.t() + fc2.bias.float()
     assert R.rel_l2(got, ref) <= 0.2
+
+
+def _int4_requant_case(M, K, N, R1, R2, seed, with_out=True):
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops.gemm import svdq_gemm_w4a4_cuda
+
+    x = R.make_activations(M, K, seed=seed)
+    fc1 = R.make_linear(K, N, R1, fp4=False, x_absmax=x.float().abs().amax(0), seed=seed + 1, mode="svd")
+    fc2 = R.make_linear(N, 256, R2, fp4=False, x_absmax=torch.rand(N) + 0.5, seed=seed + 2)
+    q = R.ref_quantize(x, fc1.smooth, fc1.lora_down, fp4=False)
+    M_pad = q.codes.shape[0]
+    sd1 = {k: v.cuda() for k, v in H.packed_params(fc1).items()}
+    sd2 = {k: v.cuda() for k, v in H.packed_params(fc2).items()}
+    codes, scales, lora = [t.cuda() for t in H.pack_quant_out(q, "native")]
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") if with_out else None
+    qout = torch.zeros(M_pad, N // 2, dtype=torch.uint8, device="cuda")
+    osc = torch.zeros(N // 64, M_pad, dtype=torch.bfloat16, device="cuda")
+    la2 = torch.full((M_pad, R2), float("nan"), dtype=torch.float32, device="cuda")
+    svdq_gemm_w4a4_cuda(act=codes, wgt=sd1["qweight"], out=out, qout=qout, ascales=scales, wscales=sd1["wscales"], oscales=osc,
+                        lora_act_in=lora, lora_up=sd1["proj_up"], lora_down=sd2["proj_down"], lora_act_out=la2,
+                        bias=sd1["bias"], smooth_factor=sd2["smooth_factor"], fp4=False,
+                        act_layout=_lib.LAYOUT_NATIVE, out_layout=_lib.LAYOUT_NATIVE)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    got = H.unpack_quant_out(qout, osc, la2, N, False, "native")
+    got.unsigned = True
+    return x, fc1, fc2, q, out, got, M_pad
+
+
+@pytest.mark.parametrize("M,K,N,R1,R2", [(256, 256, 384, 32, 32), (300, 512, 640, 32, 16), (1024, 1024, 3072, 32, 32), (256, 128, 256, 16, 64)])
+def test_int4_gemm_gelu_requant(M, K, N, R1, R2):
+    """INT4 chain of the reference (gemm_w4a4_launch_impl.cuh:282-309): GELU, LoRA-down of the next layer on the activated
+    value, then u4 codes of (y + 0.171875) / smooth with bf16 group-64 scales."""
+    x, fc1, fc2, q, out, got, M_pad = _int4_requant_case(M, K, N, R1, R2, seed=M + N)
+    y = R.ref_gemm(q, fc1, M=M, act="gelu")
+    assert R.rel_l2(out.float().cpu(), y) <= REL_L2_TIGHT
+    # given the kernel's own bf16 output, its codes / scales are bit-exact and its LoRA-down tight
+    exp = R.ref_requantize(out.float().cpu(), fc2, M_pad=M_pad, unsigned=True)
+    assert torch.equal(got.codes[:M], exp.codes[:M]), "requantised codes differ from quantising the kernel's own output"
+    assert torch.equal(got.scales[:, :M].view(torch.int16), exp.scales[:, :M].view(torch.int16))
+    err = (got.lora_act[:M] - exp.lora_act[:M]).abs().max().item()
+    assert err <= 2e-5 * max(exp.lora_act.abs().max().item(), 1.0) + 1e-6
+    # against the fp32 oracle chain: dequantised values within the GEMM tolerance of the 4-bit grid
+    exp2 = R.ref_requantize(y, fc2, M_pad=M_pad, unsigned=True)
+    assert R.rel_l2(R.dequant_act(got)[:M], R.dequant_act(exp2)[:M]) <= 2e-2
+
+
+def test_int4_gemm_requant_without_out_is_deterministic():
+    torch.manual_seed(0)   # the next layer's smoothing factors come from the global generator
+    a = _int4_requant_case(300, 256, 384, 32, 32, seed=3, with_out=False)[5]
+    torch.manual_seed(0)
+    b = _int4_requant_case(300, 256, 384, 32, 32, seed=3, with_out=False)[5]
+    assert torch.equal(a.codes, b.codes) and torch.equal(a.lora_act, b.lora_act)
+    assert torch.equal(a.scales.view(torch.int16), b.scales.view(torch.int16))
+
+
+def test_fused_gelu_mlp_int4_matches_oracle_chain():
+    """fused_gelu_mlp on an INT4 pair of layers: fc2 consumes the shifted u4 codes (act_unsigned); the oracle chain
+    does the same, so the +0.171875 shift appears on both sides (the reference folds its compensation into fc2's
+    bias offline)."""
+    from nunchaku_b200.ops import fused_gelu_mlp
+
+    M, K, N1 = 600, 512, 2048
+    x = R.make_activations(M, K, seed=5)
+    fc1 = R.make_linear(K, N1, 32, fp4=False, x_absmax=x.float().abs().amax(0), seed=6, mode="svd")
+    q1 = R.ref_quantize(x, fc1.smooth, fc1.lora_down, fp4=False)
+    h = R.ref_gemm(q1, fc1, M=M, act="gelu")
+    fc2 = R.make_linear(N1, K, 32, fp4=False, x_absmax=h.abs().amax(0).clamp(min=1e-3), seed=7, mode="svd")
+    q2 = R.ref_requantize(h, fc2, M_pad=q1.codes.shape[0], unsigned=True)
+    y = R.ref_gemm(q2, fc2, M=M)
+    m1, m2 = H.to_module(fc1), H.to_module(fc2)
+    m2.act_unsigned = True
+    got = fused_gelu_mlp(x.cuda().view(1, M, K), m1, m2).float().cpu().view(M, K)
+    assert R.rel_l2(got, y) <= 2e-2
