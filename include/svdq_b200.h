@@ -160,6 +160,42 @@ typedef struct svdq_relayout_args {
 int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream);
 
 /*
+ * RMSNorm of q and k per head + rotary embedding, in place on the bf16 output of a fused QKV projection
+ * [rows, 3 * heads * 128] (Q third, K third; V untouched).  What the reference does inside the QKV GEMM's
+ * epilogue: EpilogueRMSNormRope, src/kernels/zgemm/epilogues.cuh:269-425, called from
+ * nunchaku/ops/fused.py:50-110 (fused_qkv_norm_rottary); same arithmetic (fp32, one rounding), but the rotary table
+ * is two plain fp32 arrays [seq_len, 64] (cos, sin; row = token position, repeated over batches of seq_len rows)
+ * instead of the reference's fragment-packed [1, M, 128] tensor.
+ */
+typedef struct svdq_norm_rope_args {
+    void* qkv;                /* bf16 [rows, 3 * heads * 128], modified in place */
+    const void* weight_q;     /* bf16 [128] */
+    const void* weight_k;     /* bf16 [128] */
+    const float* cos;         /* fp32 [seq_len, 64] */
+    const float* sin;         /* fp32 [seq_len, 64] */
+    int64_t rows;
+    int32_t seq_len, heads;
+    float eps;                /* 1e-6 in the reference */
+} svdq_norm_rope_args;
+int svdq_qk_norm_rope(const svdq_norm_rope_args* args, void* stream);
+
+/*
+ * out = LayerNorm(x) * (1 + scale[b]) + shift[b]: no affine, fp32 statistics, bf16 in / out, b = row / rows_per_batch.
+ * The AdaLN-Zero step in front of each W4A4 projection of a FLUX block.  No counterpart on the reference's W4A4
+ * path (its blocks call separate fused norm kernels, src/kernels/layernorm_kernels.cu); provided for the block harness.
+ */
+typedef struct svdq_ln_modulate_args {
+    const void* x;            /* bf16 [rows, cols] */
+    const void* scale;        /* bf16 [batches, mod_stride], first `cols` entries of a row are used */
+    const void* shift;        /* bf16, same geometry */
+    void* out;                /* bf16 [rows, cols] */
+    int64_t rows, rows_per_batch, mod_stride;
+    int32_t cols;             /* 256, 1024, 2304 or 3072 */
+    float eps;                /* 1e-5 = torch.nn.functional.layer_norm default */
+} svdq_ln_modulate_args;
+int svdq_layernorm_modulate(const svdq_ln_modulate_args* args, void* stream);
+
+/*
  * Device-side status word of the current device: 0, or the SVDQ_ERR_TIMEOUT code a
  * kernel recorded when one of its bounded waits ran out.  Synchronises the device.
  * `detail` (may be NULL) receives a kernel-specific location code.  Reading clears it.

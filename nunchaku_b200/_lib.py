@@ -117,6 +117,34 @@ class RelayoutArgs(Structure):
     ]
 
 
+class NormRopeArgs(Structure):
+    _fields_ = [
+        ("qkv", c_void_p),
+        ("weight_q", c_void_p),
+        ("weight_k", c_void_p),
+        ("cos", c_void_p),
+        ("sin", c_void_p),
+        ("rows", ctypes.c_int64),
+        ("seq_len", c_int32),
+        ("heads", c_int32),
+        ("eps", c_float),
+    ]
+
+
+class LnModulateArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p),
+        ("scale", c_void_p),
+        ("shift", c_void_p),
+        ("out", c_void_p),
+        ("rows", ctypes.c_int64),
+        ("rows_per_batch", ctypes.c_int64),
+        ("mod_stride", ctypes.c_int64),
+        ("cols", c_int32),
+        ("eps", c_float),
+    ]
+
+
 # every symbol include/svdq_b200.h declares: (restype, argtypes)
 EXPORTS = {
     "svdq_quantize_w4a4_act_fuse_lora": (c_int32, [POINTER(QuantizeArgs), c_void_p]),
@@ -126,6 +154,8 @@ EXPORTS = {
     "svdq_gemm_w4a4": (c_int32, [POINTER(GemmArgs), c_void_p]),
     "svdq_gemm_w4a4_static_scratch": (c_int32, [POINTER(GemmArgs), c_void_p]),
     "svdq_w4a4_relayout_act": (c_int32, [POINTER(RelayoutArgs), c_void_p]),
+    "svdq_qk_norm_rope": (c_int32, [POINTER(NormRopeArgs), c_void_p]),
+    "svdq_layernorm_modulate": (c_int32, [POINTER(LnModulateArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),
     "svdq_version": (c_int32, []),

@@ -1,0 +1,178 @@
+// Row-wise kernels either side of the W4A4 linears in a FLUX block, sm_100a.  Both are HBM bound.
+//
+// qk_norm_rope_kernel — what the reference fuses into the QKV GEMM's epilogue (EpilogueRMSNormRope,
+// src/kernels/zgemm/epilogues.cuh:269-425; launcher gemm_w4a4_launch_impl.cuh:347-405), here as a kernel of its
+// own that works in place on the GEMM's bf16 output [rows, 3*heads*128]:
+//   for the Q third and the K third, per (row, head): coef = rsqrt(sum_128 float(y)^2 / 128 + eps);
+//   v = float(y) * (coef * float(w_norm[c])); every (even, odd) column pair is rotated by the row's angle,
+//   (a, b) -> (a*cos - b*sin, a*sin + b*cos), all in fp32 with one rounding to bf16 at the end.  V is untouched.
+//   The rotary table is two fp32 arrays [seq_len, 64] (cos, sin), row = token position, shared by all batches.
+// One warp per (row, head, q|k): 4 consecutive columns per lane (two pairs), an 8-byte load and store.
+// Algorithmic bytes per row: 2 * heads*128 * 2 (read) + the same (write) + 512 of table.
+//
+// layernorm_modulate_kernel — the AdaLN-Zero step in front of every W4A4 projection: LayerNorm without affine
+// (eps 1e-5) followed by x * (1 + scale[b]) + shift[b], bf16 in and out, fp32 statistics; one warp per row with the
+// row held in registers (two passes over registers, one over memory).  Not part of the reference's W4A4 path (the
+// reference has its own fused norm kernels); it is here so that the block harness is not bound by library glue.
+#include <cuda_bf16.h>
+
+#include "host_common.h"
+
+namespace svdq {
+
+__device__ __forceinline__ float2 bf2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
+    const __nv_bfloat162 o = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&o);
+}
+
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
+                    const float* __restrict__ cosp, const float* __restrict__ sinp, long long rows, int seq_len, int heads,
+                    float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const int dim = heads * 128;
+    const long long items = rows * heads * 2;    // (row, q|k, head)
+    // norm weights of this lane's 4 columns, for q and k
+    const uint2 wq2 = *reinterpret_cast<const uint2*>(wq + lane * 4);
+    const uint2 wk2 = *reinterpret_cast<const uint2*>(wk + lane * 4);
+    for (long long it = warp; it < items; it += nwarps) {
+        const long long row = it / (heads * 2);
+        const int rem = static_cast<int>(it - row * heads * 2);
+        const int which = rem / heads, head = rem - which * heads;
+        __nv_bfloat16* p = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + head * 128 + lane * 4;
+        const uint2 y = *reinterpret_cast<const uint2*>(p);
+        const float2 y0 = bf2(y.x), y1 = bf2(y.y);
+        float ss = y0.x * y0.x + y0.y * y0.y + y1.x * y1.x + y1.y * y1.y;
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float coef = rsqrtf(ss * (1.0f / 128.0f) + eps);
+        const uint2 w = which ? wk2 : wq2;
+        const float2 w0 = bf2(w.x), w1 = bf2(w.y);
+        const float a0 = y0.x * (coef * w0.x), b0 = y0.y * (coef * w0.y);
+        const float a1 = y1.x * (coef * w1.x), b1 = y1.y * (coef * w1.y);
+        const long long pos = row % seq_len;
+        const float2 c = *reinterpret_cast<const float2*>(cosp + pos * 64 + lane * 2);
+        const float2 s = *reinterpret_cast<const float2*>(sinp + pos * 64 + lane * 2);
+        uint2 o;
+        o.x = pack_bf2(a0 * c.x - b0 * s.x, a0 * s.x + b0 * c.x);
+        o.y = pack_bf2(a1 * c.y - b1 * s.y, a1 * s.y + b1 * c.y);
+        *reinterpret_cast<uint2*>(p) = o;
+    }
+}
+
+// C = 8 * 32 * V columns: each lane holds V chunks of 8 columns (16 bytes), chunk j at column (j*32 + lane) * 8
+template <int V>
+__global__ void __launch_bounds__(256)
+layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
+                          const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ out, long long rows,
+                          long long rows_per_batch, long long mod_stride, float eps) {
+    constexpr int C = V * 256;
+    const int lane = threadIdx.x & 31;
+    const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    for (long long row = warp; row < rows; row += nwarps) {
+        const uint4* xp = reinterpret_cast<const uint4*>(x + row * C);
+        float v[V][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const uint4 w = xp[j * 32 + lane];
+            const float2 f0 = bf2(w.x), f1 = bf2(w.y), f2 = bf2(w.z), f3 = bf2(w.w);
+            v[j][0] = f0.x; v[j][1] = f0.y; v[j][2] = f1.x; v[j][3] = f1.y;
+            v[j][4] = f2.x; v[j][5] = f2.y; v[j][6] = f3.x; v[j][7] = f3.y;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum += v[j][i];
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        const float mean = sum * (1.0f / C);
+        float var = 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float d = v[j][i] - mean;
+                var += d * d;
+            }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) var += __shfl_xor_sync(0xffffffffu, var, m);
+        const float rstd = rsqrtf(var * (1.0f / C) + eps);
+        const long long b = row / rows_per_batch;
+        const uint4* scp = reinterpret_cast<const uint4*>(scale + b * mod_stride);
+        const uint4* shp = reinterpret_cast<const uint4*>(shift + b * mod_stride);
+        uint4* op = reinterpret_cast<uint4*>(out + row * C);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const uint4 sc = scp[j * 32 + lane], sh = shp[j * 32 + lane];
+            const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 s2 = bf2(scw[i]), h2 = bf2(shw[i]);
+                // the library sequence it replaces rounds the normalised value to bf16 before modulating
+                const float n0 = __bfloat162float(__float2bfloat16_rn((v[j][2 * i] - mean) * rstd));
+                const float n1 = __bfloat162float(__float2bfloat16_rn((v[j][2 * i + 1] - mean) * rstd));
+                o[i] = pack_bf2(n0 * (1.0f + s2.x) + h2.x, n1 * (1.0f + s2.y) + h2.y);
+            }
+            op[j * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+static int grid_for(long long warps_needed) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long blocks = (warps_needed + 7) / 8;
+    const long long cap = static_cast<long long>(sms) * 8;
+    return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace svdq
+
+extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(a && a->qkv && a->weight_q && a->weight_k && a->cos && a->sin, "qk_norm_rope: null pointer");
+    SVDQ_CHECK_ARG(a->rows > 0 && a->seq_len > 0 && a->heads > 0 && a->rows % a->seq_len == 0,
+                   "qk_norm_rope: rows (%lld) must be a positive multiple of seq_len (%d)", static_cast<long long>(a->rows), a->seq_len);
+    SVDQ_CHECK_ARG(aligned(a->qkv, 16) && aligned(a->weight_q, 8) && aligned(a->weight_k, 8) && aligned(a->cos, 8) && aligned(a->sin, 8),
+                   "qk_norm_rope: misaligned tensor");
+    if (int rc = check_arch()) return rc;
+    const long long items = static_cast<long long>(a->rows) * a->heads * 2;
+    qk_norm_rope_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(a->qkv), static_cast<const __nv_bfloat16*>(a->weight_q),
+        static_cast<const __nv_bfloat16*>(a->weight_k), a->cos, a->sin, a->rows, a->seq_len, a->heads, a->eps);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+extern "C" int svdq_layernorm_modulate(const svdq_ln_modulate_args* a, void* stream) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(a && a->x && a->scale && a->shift && a->out, "layernorm_modulate: null pointer");
+    SVDQ_CHECK_ARG(a->rows > 0 && a->rows_per_batch > 0 && a->rows % a->rows_per_batch == 0 && a->mod_stride >= a->cols &&
+                       a->mod_stride % 8 == 0,
+                   "layernorm_modulate: bad row / batch geometry");
+    SVDQ_CHECK_ARG(aligned(a->x, 16) && aligned(a->scale, 16) && aligned(a->shift, 16) && aligned(a->out, 16),
+                   "layernorm_modulate: tensors must be 16-byte aligned");
+    if (int rc = check_arch()) return rc;
+    const int grid = grid_for(a->rows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
+    const __nv_bfloat16* sc = static_cast<const __nv_bfloat16*>(a->scale);
+    const __nv_bfloat16* sh = static_cast<const __nv_bfloat16*>(a->shift);
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a->out);
+    switch (a->cols) {
+        case 256: layernorm_modulate_kernel<1><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
+        case 1024: layernorm_modulate_kernel<4><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
+        case 2304: layernorm_modulate_kernel<9><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
+        case 3072: layernorm_modulate_kernel<12><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
+        default: return fail(SVDQ_ERR_UNSUPPORTED, "layernorm_modulate: built for 256, 1024, 2304 and 3072 columns (got %d)", a->cols);
+    }
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}

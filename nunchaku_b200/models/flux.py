@@ -23,7 +23,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ..ops.fused import fused_gelu_mlp
+from ..ops.fused import fused_gelu_mlp, layernorm_modulate, qk_norm_rope
 from ..weights import quantize_linear
 from .linear import SVDQW4A4Linear
 
@@ -62,6 +62,16 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return out.reshape(x.shape).to(x.dtype)
 
 
+_LN_COLS = (256, 1024, 2304, 3072)
+
+
+def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, fused: bool) -> torch.Tensor:
+    """layer_norm(x) * (1 + scale) + shift with scale / shift [B, C]."""
+    if fused and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in _LN_COLS:
+        return layernorm_modulate(x.contiguous(), scale, shift)
+    return F.layer_norm(x, x.shape[-1:]) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+
+
 class QKNorm(nn.Module):
     def __init__(self, dim: int, device, dtype):
         super().__init__()
@@ -76,8 +86,9 @@ def _attention(q, k, v, heads: int, cos, sin, norm: QKNorm | None, norms=None):
     q = q.view(B, S, heads, D).transpose(1, 2)
     k = k.view(B, S, heads, D).transpose(1, 2)
     v = v.view(B, S, heads, D).transpose(1, 2)
-    q = apply_rope(q, cos, sin)
-    k = apply_rope(k, cos, sin)
+    if cos is not None:
+        q = apply_rope(q, cos, sin)
+        k = apply_rope(k, cos, sin)
     o = F.scaled_dot_product_attention(q, k, v)
     return o.transpose(1, 2).reshape(B, S, C)
 
@@ -114,30 +125,40 @@ class FluxJointBlock(nn.Module):
         self.mlp_txt = FluxMLP(dim, mlp_dim, precision, rank, device, dtype)
 
     @staticmethod
-    def _qkv(lin, norm: QKNorm, x, heads):
+    def _qkv(lin, norm: QKNorm, x, heads, cos=None, sin=None):
+        """Fused projection, then RMSNorm of q and k per head.  With (cos, sin) of this stream's rows and a W4A4
+        projection the norm and the rotary embedding run as one in-place kernel (and the caller skips its own)."""
         B, S, C = x.shape
-        q, k, v = _apply(lin, x).chunk(3, dim=-1)
+        qkv = _apply(lin, x)
         D = C // heads
+        if cos is not None and isinstance(lin, SVDQW4A4Linear) and D == 128:
+            qkv = qk_norm_rope(qkv, norm.q.weight, norm.k.weight, cos.contiguous(), sin.contiguous(), heads, eps=1e-6)
+            q, k, v = qkv.chunk(3, dim=-1)
+            return q, k, v, True
+        q, k, v = qkv.chunk(3, dim=-1)
         q = norm.q(q.reshape(B, S, heads, D)).reshape(B, S, C)
         k = norm.k(k.reshape(B, S, heads, D)).reshape(B, S, C)
-        return q, k, v
+        return q, k, v, False
 
     def forward(self, img, txt, temb, cos, sin):
-        mi = self.mod_img(F.silu(temb)).unsqueeze(1).chunk(6, dim=-1)
-        mt = self.mod_txt(F.silu(temb)).unsqueeze(1).chunk(6, dim=-1)
-        ni = F.layer_norm(img, img.shape[-1:]) * (1 + mi[1]) + mi[0]
-        nt = F.layer_norm(txt, txt.shape[-1:]) * (1 + mt[1]) + mt[0]
-        qi, ki, vi = self._qkv(self.qkv_img, self.norm_img, ni, self.heads)
-        qt, kt, vt = self._qkv(self.qkv_txt, self.norm_txt, nt, self.heads)
+        fused = isinstance(self.qkv_img, SVDQW4A4Linear)
+        mi = self.mod_img(F.silu(temb)).chunk(6, dim=-1)     # each [B, dim]
+        mt = self.mod_txt(F.silu(temb)).chunk(6, dim=-1)
+        ni = _ln_mod(img, mi[1], mi[0], fused)
+        nt = _ln_mod(txt, mt[1], mt[0], fused)
         T = txt.shape[1]
-        attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads, cos, sin, None)
+        qi, ki, vi, ri = self._qkv(self.qkv_img, self.norm_img, ni, self.heads, cos[T:], sin[T:])
+        qt, kt, vt, rt = self._qkv(self.qkv_txt, self.norm_txt, nt, self.heads, cos[:T], sin[:T])
+        roped = ri and rt
+        attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads,
+                          None if roped else cos, None if roped else sin, None)
         at, ai = attn[:, :T], attn[:, T:]
-        img = img + mi[2] * _apply(self.out_img, ai.contiguous())
-        txt = txt + mt[2] * _apply(self.out_txt, at.contiguous())
-        ni = F.layer_norm(img, img.shape[-1:]) * (1 + mi[4]) + mi[3]
-        nt = F.layer_norm(txt, txt.shape[-1:]) * (1 + mt[4]) + mt[3]
-        img = img + mi[5] * self.mlp_img(ni)
-        txt = txt + mt[5] * self.mlp_txt(nt)
+        img = img + mi[2].unsqueeze(1) * _apply(self.out_img, ai.contiguous())
+        txt = txt + mt[2].unsqueeze(1) * _apply(self.out_txt, at.contiguous())
+        ni = _ln_mod(img, mi[4], mi[3], fused)
+        nt = _ln_mod(txt, mt[4], mt[3], fused)
+        img = img + mi[5].unsqueeze(1) * self.mlp_img(ni)
+        txt = txt + mt[5].unsqueeze(1) * self.mlp_txt(nt)
         return img, txt
 
 
@@ -154,11 +175,12 @@ class FluxSingleBlock(nn.Module):
         self.mlp = FluxMLP(dim, mlp_dim, precision, rank, device, dtype)
 
     def forward(self, x, temb, cos, sin):
-        m = self.mod(F.silu(temb)).unsqueeze(1).chunk(3, dim=-1)
-        n = F.layer_norm(x, x.shape[-1:]) * (1 + m[1]) + m[0]
-        q, k, v = FluxJointBlock._qkv(self.qkv, self.norm, n, self.heads)
-        a = _attention(q, k, v, self.heads, cos, sin, None)
-        return x + m[2] * (_apply(self.attn_out, a.contiguous()) + self.mlp(n))
+        fused = isinstance(self.qkv, SVDQW4A4Linear)
+        m = self.mod(F.silu(temb)).chunk(3, dim=-1)
+        n = _ln_mod(x, m[1], m[0], fused)
+        q, k, v, roped = FluxJointBlock._qkv(self.qkv, self.norm, n, self.heads, cos, sin)
+        a = _attention(q, k, v, self.heads, None if roped else cos, None if roped else sin, None)
+        return x + m[2].unsqueeze(1) * (_apply(self.attn_out, a.contiguous()) + self.mlp(n))
 
 
 class FluxTransformer(nn.Module):
@@ -203,6 +225,34 @@ class FluxTransformer(nn.Module):
                 child = getattr(mod, n, None)
                 if isinstance(child, nn.Linear):
                     setattr(mod, n, quantize_linear(child, None, rank=rank, precision=precision))
+        return self
+
+    @torch.no_grad()
+    def randomize_w4a4_(self, precision: str = "nvfp4", rank: int = 32, seed: int = 0):
+        """Replace the block linears by W4A4 layers with RANDOM packed parameters (no SVD, no calibration): random 4-bit
+        codes, one constant group scale sized so that weights look like N(0, 0.02), small random low-rank factors.
+        For step timing at full size, where quantising 12 B master weights on the CPU would take hours."""
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        names = ("qkv_img", "qkv_txt", "out_img", "out_txt", "qkv", "attn_out", "fc1", "fc2")
+        for mod in list(self.modules()):
+            for n in names:
+                child = getattr(mod, n, None)
+                if not isinstance(child, nn.Linear):
+                    continue
+                dev = child.weight.device
+                q = SVDQW4A4Linear(child.in_features, child.out_features, rank=rank, bias=True, precision=precision,
+                                   torch_dtype=child.weight.dtype, device=dev)
+                q.qweight.copy_(torch.randint(-128, 128, q.qweight.shape, generator=g, device=dev, dtype=torch.int8))
+                if precision == "nvfp4":
+                    q.wscales.copy_(torch.full(q.wscales.shape, 2.0 ** -7, device=dev).to(torch.float8_e4m3fn))
+                else:
+                    q.wscales.fill_(0.005)
+                q.smooth_factor.fill_(1.0)
+                q.smooth_factor_orig.fill_(1.0)
+                q.proj_down.copy_(torch.randn(q.proj_down.shape, generator=g, device=dev) * 0.02)
+                q.proj_up.copy_(torch.randn(q.proj_up.shape, generator=g, device=dev) * 0.02)
+                q.bias.zero_()
+                setattr(mod, n, q)
         return self
 
     def w4a4_linears(self):

@@ -310,3 +310,39 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.to(torch.float64)
     b = b.to(torch.float64)
     return float((a - b).norm() / b.norm().clamp(min=1e-30))
+
+
+# ---------------------------------------------------------------------------
+# Row-wise steps either side of the linears
+# ---------------------------------------------------------------------------
+def ref_qk_norm_rope(qkv: torch.Tensor, w_q: torch.Tensor, w_k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                     heads: int, eps: float = 1e-6) -> torch.Tensor:
+    """EpilogueRMSNormRope (src/kernels/zgemm/epilogues.cuh:330-405) on a bf16 [rows, 3*heads*128] QKV output:
+    per head of the Q and K thirds ``coef = rsqrt(sum(float(y)^2)/128 + eps)``, ``v = float(y) * (coef * float(w))``,
+    pairs (2p, 2p+1) rotated by (cos, sin)[row % S, p] in fp32, one rounding to bf16.  V is untouched.
+    cos, sin: fp32 [S, 64]."""
+    rows, C = qkv.shape
+    dim = heads * 128
+    assert C == 3 * dim
+    S = cos.shape[0]
+    out = qkv.clone()
+    pos = torch.arange(rows) % S
+    c, s = cos[pos].to(F32)[:, None, :], sin[pos].to(F32)[:, None, :]          # [rows, 1, 64]
+    for which, w in ((0, w_q), (1, w_k)):
+        y = qkv[:, which * dim:(which + 1) * dim].to(F32).view(rows, heads, 128)
+        coef = torch.rsqrt((y * y).sum(-1, keepdim=True) / 128.0 + eps)
+        v = y * (coef * w.to(F32)[None, None, :])
+        a, b = v[..., 0::2], v[..., 1::2]
+        r = torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(rows, dim)
+        out[:, which * dim:(which + 1) * dim] = r.to(BF16)
+    return out
+
+
+def ref_layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """bf16 [B, S, C]: layer_norm without affine (fp32 statistics, result rounded to bf16, as the library call it
+    replaces does), then ``* (1 + scale[b]) + shift[b]`` in fp32 with one rounding."""
+    xf = x.to(F32)
+    mean = xf.mean(-1, keepdim=True)
+    var = ((xf - mean) ** 2).mean(-1, keepdim=True)
+    n = ((xf - mean) * torch.rsqrt(var + eps)).to(BF16).to(F32)
+    return (n * (1.0 + scale.to(F32)[:, None, :]) + shift.to(F32)[:, None, :]).to(BF16)
