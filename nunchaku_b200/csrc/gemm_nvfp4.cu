@@ -542,19 +542,23 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 // lora_act_out[row][r] = sum over the pairs that touched the row's 256-row block, in pair order, of the partial
 // of the CTA that owns the row's half.  Row block mb2 (256 rows) holds pair tiles [mb2*tiles_n, (mb2+1)*tiles_n);
 // pair c owns tiles [c*run, (c+1)*run); CTA 2c + h of the pair owns rows h*128.. of each tile.
-__global__ void lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n,
-                                           int run, int slots, int npairs) {
+__global__ void __launch_bounds__(256)
+lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n, int run, int slots,
+                           int npairs) {
     const int mb = blockIdx.x;   // 128-row block
     const int mb2 = mb >> 1, h = mb & 1;
     const int c_lo = (mb2 * tiles_n) / run;
     const int c_hi = min(npairs - 1, ((mb2 + 1) * tiles_n - 1) / run);
-    for (int i = threadIdx.x; i < G_BM * rn; i += blockDim.x) {
-        float s = 0.f;
+    const int n4 = G_BM * rn / 4;   // float4 elements of one block; gridDim.y CTAs share them
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n4; i += gridDim.y * blockDim.x) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int c = c_lo; c <= c_hi; ++c) {
             const int first_mb2 = (c * run) / tiles_n;
-            s += partial[(static_cast<size_t>(2 * c + h) * slots + (mb2 - first_mb2)) * (G_BM * rn) + i];
+            const float4 v = __ldg(reinterpret_cast<const float4*>(
+                                       partial + (static_cast<size_t>(2 * c + h) * slots + (mb2 - first_mb2)) * (G_BM * rn)) + i);
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        out[static_cast<size_t>(mb) * G_BM * rn + i] = s;
+        reinterpret_cast<float4*>(out + static_cast<size_t>(mb) * G_BM * rn)[i] = s;
     }
 }
 
@@ -705,7 +709,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     else rc = launch_nvfp4<4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
     if (rc) return rc;
     if (requant) {
-        lora_partial_reduce_kernel<<<2 * pl.tiles_m, 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
+        lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
                                                                       pl.slots, pl.npairs);
         SVDQ_CUDA(cudaGetLastError());
     }
