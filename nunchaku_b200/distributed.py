@@ -43,6 +43,12 @@ def init_from_env(backend: str | None = None) -> tuple[int, int, int]:
     return rank, world, local
 
 
+def shutdown() -> None:
+    """Tear the process group down (NCCL warns when a process exits with it alive)."""
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
 def barrier() -> None:
     if dist.is_initialized():
         dist.barrier()

@@ -69,6 +69,7 @@ def main() -> None:
             "finite": bool(torch.isfinite(y).all()), "device_status": list(status),
         }))
     D.barrier()
+    D.shutdown()
 
 
 if __name__ == "__main__":
