@@ -196,73 +196,94 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            uint32_t it = 0, pk = 0;   // unpacked-ring position, packed-ring position
-            bool ok = true;
-            for (int ti = 0; ti < tr.count && ok; ++ti) {
-                int m0, n0;
-                i4_coords(p, tr.first + ti * tr.stride, m0, n0);
-                for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int u = it % I_U_STAGES;
-                    uint8_t* ub = ubuf + u * I_U_BYTES;
-                    if (ks < kstages) {
-                        // packed activations -> staging ring (independent of the unpacked ring's progress)
-                        const int s = pk % I_PK_STAGES;
-                        if (!i4_wait(&sh->pk_empty[s], ((pk / I_PK_STAGES) & 1) ^ 1, sh, p.status, 10)) { ok = false; break; }
+        // ------------------------------------------------------------------ producer (whole warp, elected lane issues)
+        uint32_t it = 0, pk = 0;   // unpacked-ring position, packed-ring position
+        bool ok = true;
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            int m0, n0;
+            i4_coords(p, tr.first + ti * tr.stride, m0, n0);
+            for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                const int u = it % I_U_STAGES;
+                uint8_t* ub = ubuf + u * I_U_BYTES;
+                if (ks < kstages) {
+                    // packed activations -> staging ring (independent of the unpacked ring's progress)
+                    const int s = pk % I_PK_STAGES;
+                    ok = __all_sync(0xffffffffu, i4_wait(&sh->pk_empty[s], ((pk / I_PK_STAGES) & 1) ^ 1, sh, p.status, 10));
+                    if (!ok) break;
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(&sh->pk_full[s], I_PK_BYTES);
                         tma_load_2d(pkbuf + s * I_PK_BYTES, &tm_a, &sh->pk_full[s], ks * 64, m0);
-                        ++pk;
-                        if (!i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 11)) { ok = false; break; }
+                    }
+                    __syncwarp();
+                    ++pk;
+                    ok = __all_sync(0xffffffffu, i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 11));
+                    if (!ok) break;
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(&sh->b_full[u], I_B_BYTES);
                         tma_load_2d(ub + I_A_BYTES, &tm_b, &sh->b_full[u], ks * 128, n0);
-                    } else {
-                        const int c = ks - kstages;
-                        if (!i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 12)) { ok = false; break; }
+                    }
+                    __syncwarp();
+                } else {
+                    const int c = ks - kstages;
+                    ok = __all_sync(0xffffffffu, i4_wait(&sh->u_empty[u], ((it / I_U_STAGES) & 1) ^ 1, sh, p.status, 12));
+                    if (!ok) break;
+                    if (elect_one()) {
                         mbar_arrive_expect_tx(&sh->b_full[u], I_A_BYTES + I_B_BYTES);
                         tma_load_2d(ub, &tm_la, &sh->b_full[u], c * 32, m0);
                         tma_load_2d(ub + I_A_BYTES, &tm_lu, &sh->b_full[u], c * 32, n0);
                     }
+                    __syncwarp();
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc_int8 = idesc_i8(I_BM, I_BN, !p.act_unsigned);
-            constexpr uint32_t IDESC_TF32 = idesc_tf32(I_BM, I_BN);
-            uint32_t it = 0, gq = 0;   // stage count, group (TMEM buffer) count
-            bool ok = true;
-            for (int ti = 0; ti < tr.count && ok; ++ti) {
-                for (int ks = 0; ks < per_tile && ok; ++ks, ++it) {
-                    const int u = it % I_U_STAGES;
-                    if (!i4_wait(&sh->b_full[u], (it / I_U_STAGES) & 1, sh, p.status, 20) ||
-                        !i4_wait(&sh->a_full[u], (it / I_U_STAGES) & 1, sh, p.status, 21)) { ok = false; break; }
+        // ------------------------------------------------------------------ MMA issuer (whole warp, elected lane issues:
+        // descriptors and TMEM addresses stay warp-uniform, see ptx.cuh elect_one)
+        const uint32_t idesc_int8 = idesc_i8(I_BM, I_BN, !p.act_unsigned);
+        constexpr uint32_t IDESC_TF32 = idesc_tf32(I_BM, I_BN);
+        const uint64_t adesc0 = smem_desc_sw128(smem_u32(ubuf));
+        uint32_t it = 0, gq = 0;   // stage count, group (TMEM buffer) count
+        bool ok = true;
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            for (int ks = 0; ks < per_tile && ok; ++ks, ++it) {
+                const int u = it % I_U_STAGES;
+                ok = __all_sync(0xffffffffu, i4_wait(&sh->b_full[u], (it / I_U_STAGES) & 1, sh, p.status, 20) &&
+                                                 i4_wait(&sh->a_full[u], (it / I_U_STAGES) & 1, sh, p.status, 21));
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t adesc = adesc0 + static_cast<uint32_t>(u * (I_U_BYTES >> 4));
+                const uint64_t bdesc = adesc + (I_A_BYTES >> 4);
+                const int ngroups = ks < kstages ? 2 : 1;
+                for (int g = 0; g < ngroups; ++g, ++gq) {
+                    const uint32_t tb = gq % I_TBUFS;
+                    ok = __all_sync(0xffffffffu, i4_wait(&sh->t_empty[tb], ((gq / I_TBUFS) & 1) ^ 1, sh, p.status, 22));
+                    if (!ok) break;
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(ubuf + u * I_U_BYTES);
-                    const uint64_t adesc = smem_desc_sw128(sa);
-                    const uint64_t bdesc = smem_desc_sw128(sa + I_A_BYTES);
-                    const int ngroups = ks < kstages ? 2 : 1;
-                    for (int g = 0; g < ngroups; ++g, ++gq) {
-                        const uint32_t tb = gq % I_TBUFS;
-                        if (!i4_wait(&sh->t_empty[tb], ((gq / I_TBUFS) & 1) ^ 1, sh, p.status, 22)) { ok = false; break; }
-                        tc_fence_after_sync();
-                        const uint32_t d = tmem + tb * 128;
+                    const uint32_t d = tmem + tb * 128;
+                    if (elect_one()) {
                         if (ks < kstages) {
                             tc_mma_i8(d, adesc + 4 * g, bdesc + 4 * g, idesc_int8, 0);
                             tc_mma_i8(d, adesc + 4 * g + 2, bdesc + 4 * g + 2, idesc_int8, 1);
                         } else {
+#pragma unroll
                             for (int j = 0; j < 4; ++j) tc_mma_tf32(d, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j ? 1u : 0u);
                         }
                         tc_commit(&sh->t_full[tb]);
                     }
-                    if (ok) tc_commit(&sh->u_empty[u]);
+                    __syncwarp();
+                }
+                if (ok) {
+                    if (elect_one()) tc_commit(&sh->u_empty[u]);
+                    __syncwarp();
                 }
             }
-            if (sh->abort_flag) {
+        }
+        if (sh->abort_flag) {
+            if (lane == 0) {
                 tc_commit(&sh->drain);
                 mbar_wait(&sh->drain, 0, 400000000ll);
             }
+            __syncwarp();
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------------ converters (warps 2..5)
