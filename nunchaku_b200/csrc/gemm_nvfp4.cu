@@ -56,6 +56,7 @@ constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
 constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 34816 = 34 * 1024
 constexpr int G_THREADS = 9 * 32;              // warp 1 issues MMAs; 2..5 epilogue; 0, 6, 7, 8 produce (A, B, scales of A, scales of B)
+constexpr int G_THREADS_RQ = 13 * 32;          // requantising variants up to rank 32: warps 9..12 are a second epilogue set
 constexpr int G_SF_BUFS = 2;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
@@ -64,7 +65,7 @@ constexpr int G_TM_SF_STRIDE = 48;              // per buffer: 4 x 4 columns for
 constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
 constexpr int G_COLV_FLOATS = 3 * G_BN;                     // per epilogue warp: scale, bias, 1/smooth_next
-constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;
+constexpr int G_COLV_BYTES = 8 * G_COLV_FLOATS * 4;           // up to 8 epilogue warps
 constexpr size_t G_SMEM_BYTES =
     1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + G_EPI_BYTES + G_COLV_BYTES + 256;
 
@@ -96,6 +97,8 @@ struct GemmShared {
     uint64_t empty[G_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
     uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
+    uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
+    uint64_t xempty[4];             // ... and has been added by the first
     uint64_t drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -170,8 +173,13 @@ __device__ __forceinline__ float apply_act(float v, int activation) {
 }
 
 // RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
+// Requantising epilogues do about three times the work of the plain one per chunk; up to rank 32 (where a warp's
+// LoRA-down partial fits its 4 KB staging buffer) a second set of four epilogue warps takes every other 64-column chunk.
 template <int RTN>
-__global__ void __launch_bounds__(G_THREADS, 1)
+constexpr int epi_sets() { return (RTN == 1 || RTN == 2) ? 2 : 1; }
+
+template <int RTN>
+__global__ void __launch_bounds__(epi_sets<RTN>() == 2 ? G_THREADS_RQ : G_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
@@ -198,7 +206,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->tfull[i], 1);
-            mbar_init(&sh->tempty[i], 8);
+            mbar_init(&sh->tempty[i], 8 * epi_sets<RTN>());
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&sh->xfull[i], 1);
+            mbar_init(&sh->xempty[i], 1);
         }
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
@@ -224,7 +236,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     pdl_wait();           // nothing above touches global memory; the quantiser's output is this kernel's input
     const uint32_t tmem = sh->tmem_base;
 
-    if (warp == 0 || warp >= 6) {
+    if (warp == 0 || (warp >= 6 && warp < 9)) {
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
         // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
@@ -352,15 +364,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 __syncwarp();
             }
         }
-    } else if (warp >= 2 && warp < 6) {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
+    } else if ((warp >= 2 && warp < 6) || warp >= 9) {
+        // ------------------------------------------------------------------ epilogue (warps 2..5, and 9..12 when requantising)
         // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
         // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
         // hardware clips rows >= M and columns >= N).  Two staging buffers per warp keep a store in flight.
+        constexpr int SETS = epi_sets<RTN>();
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
-        uint8_t* my_buf = epi_smem + q * 2 * G_EPI_BUF_BYTES;
-        float* cvs = colv + q * G_COLV_FLOATS;
-        uint32_t nstore = 0;
+        const int eset = warp >= 9 ? 1 : 0;
+        // one set: two staging buffers per warp (a store stays in flight); two sets: one buffer per warp
+        uint8_t* my_buf = epi_smem + (q * 2 + (SETS == 2 ? eset : 0)) * G_EPI_BUF_BYTES;
+        float* cvs = colv + (eset * 4 + q) * G_COLV_FLOATS;
+        uint32_t nstore = 0, nflush = 0;
         // next layer's LoRA-down partial of this warp's 32 rows: [m-tile 2][rank tile][8]
         constexpr int RTA = RTN > 0 ? RTN : 1;
         float lacc[2][RTA][8];
@@ -376,6 +391,42 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         auto lacc_flush = [&]() {   // partial of row block cur_m0 -> scratch[blockIdx][slot][128][Rn]
             if constexpr (RTN > 0) {
                 constexpr int RN = RTN * 16;
+                if constexpr (SETS == 2) {
+                    // The second warp of the quadrant hands its partial over through its staging buffer (bounded
+                    // mbarrier hand-shake, fixed order of addition), the first adds it and writes the sum.
+                    float* xb = reinterpret_cast<float*>(epi_smem + (q * 2 + 1) * G_EPI_BUF_BYTES);
+                    if (eset == 1) {
+                        if (lane == 0) bulk_wait_group_read<0>();   // the buffer's last TMA store has been read
+                        __syncwarp();
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                            for (int rt = 0; rt < RTN; ++rt)
+#pragma unroll
+                                for (int c = 0; c < 8; c += 4)
+                                    *reinterpret_cast<float4*>(xb + (((mt * RTN + rt) * 2 + (c >> 2)) * 32 + lane) * 4) =
+                                        make_float4(lacc[mt][rt][c], lacc[mt][rt][c + 1], lacc[mt][rt][c + 2], lacc[mt][rt][c + 3]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sh->xfull[q]);
+                        // the buffer goes back to staging only after the first warp has read it
+                        (void)wait_or_abort(&sh->xempty[q], nflush & 1, sh, p.status, 50);
+                        ++nflush;
+                        return;
+                    }
+                    if (!wait_or_abort(&sh->xfull[q], nflush & 1, sh, p.status, 51)) return;
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                        for (int rt = 0; rt < RTN; ++rt)
+#pragma unroll
+                            for (int c = 0; c < 8; c += 4) {
+                                const float4 v = *reinterpret_cast<const float4*>(xb + (((mt * RTN + rt) * 2 + (c >> 2)) * 32 + lane) * 4);
+                                lacc[mt][rt][c] += v.x; lacc[mt][rt][c + 1] += v.y; lacc[mt][rt][c + 2] += v.z; lacc[mt][rt][c + 3] += v.w;
+                            }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->xempty[q]);
+                    ++nflush;
+                }
                 float* dst = p.lora_partial + (static_cast<size_t>(blockIdx.x) * p.slots + slot) * (G_BM * RN);
                 const int gq = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -436,11 +487,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll 1
             for (int h = 0; h < G_BN / 64; ++h) {
                 if (n0 + h * 64 >= p.N) break;
+                if (SETS == 2 && ((h + ti) & 1) != eset) continue;   // the other warp of this quadrant takes it
                 uint32_t r0[32], r1[32];
                 tc_ld_32x32b_x32(taddr + h * 64, r0);
                 tc_ld_32x32b_x32(taddr + h * 64 + 32, r1);
-                uint8_t* buf = my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
-                if (lane == 0) bulk_wait_group_read<1>();  // the store that used this buffer two chunks ago
+                uint8_t* buf = SETS == 2 ? my_buf : my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
+                if (lane == 0) {   // the store that last used this buffer has been read
+                    if (SETS == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
+                }
                 __syncwarp();
                 tc_wait_ld();
                 const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
@@ -605,7 +659,7 @@ static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, con
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);   // 2 CTAs per pair
-    cfg.blockDim = dim3(G_THREADS, 1, 1);
+    cfg.blockDim = dim3(epi_sets<RTN>() == 2 ? G_THREADS_RQ : G_THREADS, 1, 1);
     cfg.dynamicSmemBytes = G_SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
