@@ -52,7 +52,7 @@ constexpr size_t I_SMEM_BYTES =
 
 struct Int4Params {
     const __nv_bfloat16* ascales;   // [K/64][M_pad]
-    const float* wscales;           // [K/64][N]
+    const __nv_bfloat16* wscales;   // [K/64][N]
     const float* col_bias;          // [N]
     int* status;
     int M, M_pad, N, K;
@@ -404,7 +404,7 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
                 __syncwarp();
             }
-            float acc[64];
+            __align__(8) float acc[64];
 #pragma unroll
             for (int i = 0; i < 64; ++i) acc[i] = 0.f;
             const __nv_bfloat16* asp = p.ascales + m;
@@ -414,38 +414,45 @@ gemm_int4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const uint32_t tb = gq % I_TBUFS;
                 const float as_g = as_next;
                 if (g + 1 < KB) as_next = __bfloat162float(asp[static_cast<size_t>(g + 1) * p.M_pad]);
+                // this group's 64 weight scales (bf16, the same for every row): in flight while the MMAs finish
+                uint4 wsr[8];
+                if (g < KB) {
+                    const uint4* wsp = reinterpret_cast<const uint4*>(p.wscales + static_cast<size_t>(g) * p.N + nb);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) wsr[i] = __ldg(wsp + i);
+                }
                 if (!i4_wait(&sh->t_full[tb], (gq / I_TBUFS) & 1, sh, p.status, 40)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + tb * 128 + h * 64;
                 if (g < KB) {
-                    const float4* wsp = reinterpret_cast<const float4*>(p.wscales + static_cast<size_t>(g) * p.N + nb);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t r[32];
-                        tc_ld_32x32b_x32(taddr + half * 32, r);
+                    for (int qt = 0; qt < 4; ++qt) {
+                        uint32_t r[16];
+                        tc_ld_32x32b_x16(taddr + qt * 16, r);
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float4 w4 = __ldg(wsp + half * 8 + i);
-                            // int32 -> fp32 without I2F: |partial| <= 64*15*8 < 2^22, so 1.5*2^23 + p is exact
-                            const float x0 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 0])) - 12582912.0f;
-                            const float x1 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 1])) - 12582912.0f;
-                            const float x2 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 2])) - 12582912.0f;
-                            const float x3 = __int_as_float(0x4B400000 + static_cast<int>(r[4 * i + 3])) - 12582912.0f;
-                            acc[half * 32 + 4 * i + 0] = fmaf(x0, as_g * w4.x, acc[half * 32 + 4 * i + 0]);
-                            acc[half * 32 + 4 * i + 1] = fmaf(x1, as_g * w4.y, acc[half * 32 + 4 * i + 1]);
-                            acc[half * 32 + 4 * i + 2] = fmaf(x2, as_g * w4.z, acc[half * 32 + 4 * i + 2]);
-                            acc[half * 32 + 4 * i + 3] = fmaf(x3, as_g * w4.w, acc[half * 32 + 4 * i + 3]);
+                        for (int i = 0; i < 8; ++i) {       // word i of the quarter = columns 2i, 2i+1
+                            const uint4 wq = wsr[2 * qt + (i >> 2)];
+                            const uint32_t ww = (i & 3) == 0 ? wq.x : (i & 3) == 1 ? wq.y : (i & 3) == 2 ? wq.z : wq.w;
+                            const float2 w2 = make_float2(__uint_as_float(ww << 16), __uint_as_float(ww & 0xffff0000u));
+                            // int32 -> fp32 without I2F: |partial| <= 64*15*8 < 2^22, so 1.5*2^23 + p is exact;
+                            // the rest is packed two-wide fp32 arithmetic (the rescale is instruction bound)
+                            float2 x2 = make_float2(__int_as_float(0x4B400000 + static_cast<int>(r[2 * i])),
+                                                    __int_as_float(0x4B400000 + static_cast<int>(r[2 * i + 1])));
+                            x2 = __fadd2_rn(x2, make_float2(-12582912.0f, -12582912.0f));
+                            const float2 s2 = __fmul2_rn(make_float2(as_g, as_g), w2);
+                            float2* a2 = reinterpret_cast<float2*>(&acc[qt * 16 + 2 * i]);
+                            *a2 = __ffma2_rn(x2, s2, *a2);
                         }
                     }
                 } else {
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t r[32];
-                        tc_ld_32x32b_x32(taddr + half * 32, r);
+                    for (int qt = 0; qt < 4; ++qt) {
+                        uint32_t r[16];
+                        tc_ld_32x32b_x16(taddr + qt * 16, r);
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[half * 32 + i] += __uint_as_float(r[i]);
+                        for (int i = 0; i < 16; ++i) acc[qt * 16 + i] += __uint_as_float(r[i]);
                     }
                 }
                 tc_fence_before_sync();
@@ -643,7 +650,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 
     Int4Params p = {};
     p.ascales = static_cast<const __nv_bfloat16*>(a->ascales);
-    p.wscales = static_cast<const float*>(a->w.wscales);
+    p.wscales = static_cast<const __nv_bfloat16*>(a->w.wscales);
     p.col_bias = a->w.col_bias;
     p.M = a->M;
     p.M_pad = a->M_pad;

@@ -172,6 +172,46 @@ __device__ __forceinline__ float apply_act(float v, int activation) {
     return v;
 }
 
+template <int ACT>
+__device__ __forceinline__ float act_fn(float v) {
+    if constexpr (ACT == SVDQ_ACT_SILU) {
+        return v / (1.0f + __expf(-v));
+    } else if constexpr (ACT == SVDQ_ACT_GELU) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.79788456f * (v + 0.044715f * v * v * v)));
+        return v * (0.5f + 0.5f * t);
+    } else {
+        return v;
+    }
+}
+
+// One thread's 64 accumulator columns -> scale, bias, activation -> 64 bf16 (kept in `ow`) -> its row of the
+// 128B-swizzled staging tile.  The activation is a template parameter: selected per element at run time it put a
+// branch between every two values and kept the compiler from interleaving them.
+template <int ACT>
+__device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const float4* cs, const float4* cb,
+                                            uint32_t (&ow)[32], uint8_t* buf, int lane) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {   // 16-byte chunk j = columns 8j .. 8j+7 of this 64-column block
+        const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float4 s4 = cs[2 * j + i];
+            const float4 b4 = cb[2 * j + i];
+            const float v0 = act_fn<ACT>(fmaf(__uint_as_float(r[4 * i + 0]), s4.x, b4.x));
+            const float v1 = act_fn<ACT>(fmaf(__uint_as_float(r[4 * i + 1]), s4.y, b4.y));
+            const float v2 = act_fn<ACT>(fmaf(__uint_as_float(r[4 * i + 2]), s4.z, b4.z));
+            const float v3 = act_fn<ACT>(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w));
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
+            ow[4 * j + 2 * i] = *reinterpret_cast<uint32_t*>(&p0);
+            ow[4 * j + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+        }
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(ow[4 * j], ow[4 * j + 1], ow[4 * j + 2], ow[4 * j + 3]);
+    }
+}
+
 // RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
 // Requantising epilogues do about three times the work of the plain one per chunk; up to rank 32 (where a warp's
 // LoRA-down partial fits its 4 KB staging buffer) a second set of four epilogue warps takes every other 64-column chunk.
@@ -500,25 +540,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
                 const float4* cb = reinterpret_cast<const float4*>(cvs + G_BN + h * 64);
                 uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {   // 16-byte chunk j = columns 8j .. 8j+7 of this 64-column block
-                    const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const float4 s4 = cs[2 * j + i];
-                        const float4 b4 = cb[2 * j + i];
-                        const float v0 = apply_act(fmaf(__uint_as_float(r[4 * i + 0]), s4.x, b4.x), p.activation);
-                        const float v1 = apply_act(fmaf(__uint_as_float(r[4 * i + 1]), s4.y, b4.y), p.activation);
-                        const float v2 = apply_act(fmaf(__uint_as_float(r[4 * i + 2]), s4.z, b4.z), p.activation);
-                        const float v3 = apply_act(fmaf(__uint_as_float(r[4 * i + 3]), s4.w, b4.w), p.activation);
-                        __nv_bfloat162 p0 = __floats2bfloat162_rn(v0, v1);
-                        __nv_bfloat162 p1 = __floats2bfloat162_rn(v2, v3);
-                        ow[4 * j + 2 * i] = *reinterpret_cast<uint32_t*>(&p0);
-                        ow[4 * j + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
-                    }
-                    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                        make_uint4(ow[4 * j], ow[4 * j + 1], ow[4 * j + 2], ow[4 * j + 3]);
-                }
+                if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
+                else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU>(r0, r1, cs, cb, ow, buf, lane);
+                else stage_chunk<SVDQ_ACT_NONE>(r0, r1, cs, cb, ow, buf, lane);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {

@@ -75,8 +75,8 @@ __global__ void retile_wgt_mscales_kernel(const uint32_t* __restrict__ src, uint
 }
 
 // INT4 weight scales.  Reference (packer.py:241-301): [N/128][K/64][a 8][c 4][b 2][d 2] bf16,
-// n = a*16 + b*8 + c*2 + d.  Native: fp32 [K/64][N].
-__global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, int N, int K) {
+// n = a*16 + b*8 + c*2 + d.  Native: bf16 [K/64][N] (the values are bf16 in the checkpoint; alpha is 1 for INT4).
+__global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int N, int K) {
     const int KB = K / 64;
     const size_t total = static_cast<size_t>(N) * KB;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -87,7 +87,7 @@ __global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, 
         const int bn = blk / KB;
         const int a = pos >> 4, c = (pos >> 2) & 3, b = (pos >> 1) & 1, d = pos & 1;
         const int n = bn * 128 + a * 16 + b * 8 + c * 2 + d;
-        dst[static_cast<size_t>(bk) * N + n] = __bfloat162float(src[i]);
+        dst[static_cast<size_t>(bk) * N + n] = src[i];
     }
 }
 
@@ -225,7 +225,7 @@ int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]) {
                    "prepared_bytes: need N%%128==0, K%%128==0, R%%16==0 (N=%d K=%d R=%d)", N, K, R);
     const size_t R32 = (static_cast<size_t>(R) + 31) / 32 * 32;
     bytes[0] = fp4 ? static_cast<size_t>(N) * K / 2 : static_cast<size_t>(N) * K;
-    bytes[1] = fp4 ? static_cast<size_t>(N) * K / 16 : static_cast<size_t>(N) * (K / 64) * 4;
+    bytes[1] = fp4 ? static_cast<size_t>(N) * K / 16 : static_cast<size_t>(N) * (K / 64) * 2;
     bytes[2] = static_cast<size_t>(N) * R32 * 4;
     bytes[3] = static_cast<size_t>(N) * 4;
     bytes[4] = static_cast<size_t>(N) * 4;
@@ -257,7 +257,7 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
     } else {
         const size_t sw = static_cast<size_t>(a->N) * (a->K / 64);
         retile_wgt_scales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a->wscales),
-                                                                  static_cast<float*>(o->wscales), a->N, a->K);
+                                                                  static_cast<__nv_bfloat16*>(o->wscales), a->N, a->K);
     }
     LoraScales ls;
     for (int i = 0; i < 8; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
