@@ -140,9 +140,13 @@ __device__ __forceinline__ void raise_abort(GemmShared* sh) {
     st_shared_cluster_u32(mapa_shared(smem_u32(const_cast<int*>(&sh->abort_flag)), cluster_ctarank() ^ 1u), 1u);
 }
 
+// Bounded wait.  BACKOFF > 0 puts the warp to sleep for that many nanoseconds between polls: a warp that spins on a
+// barrier is always eligible and takes issue slots from the working warps of its scheduler, so the roles with slack
+// (producers waiting for a free slot, epilogue warps waiting for an accumulator) back off; the MMA warp does not.
+template <int BACKOFF = 0>
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
 #pragma unroll 1
-    for (int i = 0; i < 512; ++i) {
+    for (int i = 0; i < (BACKOFF ? 2 : 512); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     const long long t0 = clock64();
@@ -150,6 +154,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ge
 #pragma unroll 1
         for (int i = 0; i < 128; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+            if (BACKOFF) __nanosleep(BACKOFF);
         }
         if (sh->abort_flag) return false;
         if (clock64() - t0 > 4000000000ll) {  // about 2 s
@@ -159,17 +164,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, Ge
             return false;
         }
     }
-}
-
-__device__ __forceinline__ float apply_act(float v, int activation) {
-    if (activation == SVDQ_ACT_SILU) {
-        return v / (1.0f + __expf(-v));
-    } else if (activation == SVDQ_ACT_GELU) {
-        float t;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.79788456f * (v + 0.044715f * v * v * v)));
-        return v * (0.5f + 0.5f * t);
-    }
-    return v;
 }
 
 template <int ACT>
@@ -292,7 +286,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 const int s = it % G_STAGES;
-                ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10 + role));
+                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10 + role));
                 if (!ok) break;
                 uint8_t* st = smem + s * G_STAGE_BYTES;
                 const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
@@ -520,7 +514,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 }
             }
             __syncwarp();
-            if (!wait_or_abort(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
+            if (!wait_or_abort<64>(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
             const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
