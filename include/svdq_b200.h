@@ -119,7 +119,7 @@ typedef struct svdq_gemm_args {
     int32_t M, M_pad, N, K, R, R_next;
     int32_t fp4;              /* precision of act / weights                                  */
     int32_t act_unsigned;     /* INT4 only: activations are u4 codes                         */
-    int32_t activation;       /* SVDQ_ACT_*                                                  */
+    int32_t activation;       /* SVDQ_ACT_*; must be SVDQ_ACT_GELU when qout is given        */
     int32_t act_layout;       /* layout of act / ascales / lora_act_in                       */
     int32_t out_layout;       /* layout of qout / oscales / lora_act_out                     */
     int32_t next_fp4;         /* precision of the requantised output                         */

@@ -633,6 +633,8 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
                        "gemm(int4): requantisation needs oscales, lora_act_out, next_smooth and next_lora_down");
         SVDQ_CHECK_ARG(!a->next_fp4, "gemm(int4): the requantised output must be INT4 as well");
         SVDQ_CHECK_ARG(a->out_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): requantised output is written in SVDQ_LAYOUT_NATIVE");
+        SVDQ_CHECK_ARG(a->activation == SVDQ_ACT_GELU, "gemm(int4): the requantising epilogue applies GELU "
+                                                       "(gemm_w4a4_launch_impl.cuh:282-309); set activation = SVDQ_ACT_GELU");
         SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
                            aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
                        "gemm(int4): requantisation tensors must be 16-byte aligned (workspace: 256)");

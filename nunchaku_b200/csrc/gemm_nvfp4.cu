@@ -534,9 +534,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
                 const float4* cb = reinterpret_cast<const float4*>(cvs + G_BN + h * 64);
                 uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
-                if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
-                else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU>(r0, r1, cs, cb, ow, buf, lane);
-                else stage_chunk<SVDQ_ACT_NONE>(r0, r1, cs, cb, ow, buf, lane);
+                if constexpr (RTN > 0) {
+                    // the reference's requantising branch always applies GELU (gemm_w4a4_launch_impl.cuh:282-309)
+                    stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
+                } else {
+                    if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
+                    else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU>(r0, r1, cs, cb, ow, buf, lane);
+                    else stage_chunk<SVDQ_ACT_NONE>(r0, r1, cs, cb, ow, buf, lane);
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -706,6 +711,8 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
                        "gemm(nvfp4): requantisation needs oscales, lora_act_out, next_smooth and next_lora_down");
         SVDQ_CHECK_ARG(a->next_fp4, "gemm(nvfp4): the requantised output must be NVFP4 as well");
         SVDQ_CHECK_ARG(a->out_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): requantised output is written in SVDQ_LAYOUT_NATIVE");
+        SVDQ_CHECK_ARG(a->activation == SVDQ_ACT_GELU, "gemm(nvfp4): the requantising epilogue applies GELU "
+                                                       "(gemm_w4a4_launch_impl.cuh:282-309); set activation = SVDQ_ACT_GELU");
         SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
                            aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
                        "gemm(nvfp4): requantisation tensors must be 16-byte aligned (workspace: 256)");
