@@ -37,6 +37,7 @@
 // adds up its tiles of one 128-row block in registers, writes one partial per row block it touches to caller
 // scratch, and a second small kernel adds the partials in pair order.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <mutex>
 
@@ -66,12 +67,28 @@ constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
 constexpr int G_COLV_FLOATS = 3 * G_BN;                     // per epilogue warp: scale, bias, 1/smooth_next
 constexpr int G_COLV_BYTES = 8 * G_COLV_FLOATS * 4;           // up to 8 epilogue warps
-constexpr size_t G_SMEM_BYTES =
-    1024 + static_cast<size_t>(G_STAGES) * G_STAGE_BYTES + G_EPI_BYTES + G_COLV_BYTES + 256;
+// INT4 variant (template parameter I4): a stage is 64 k of fp16 operands, the activation half converted from packed
+// codes by converter warps; the packed codes come through a small ring of their own.
+constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
+constexpr int H_B_BYTES = G_BNH * 128;          // 96 rows x 64 fp16
+constexpr int H_STAGE_BYTES = H_A_BYTES + H_B_BYTES;   // 28672 = 28 * 1024
+constexpr int H_PK_STAGES = 4;
+constexpr int H_PK_BYTES = G_BM * 32;           // 128 rows x 64 packed codes
+constexpr int H_CONV_WARPS = 8;
+constexpr int H_THREADS = (7 + H_CONV_WARPS) * 32;   // warps 0 A codes, 1 MMA, 2..5 epilogue, 6 weights, 7..14 converters
+template <bool I4>
+constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
+template <bool I4>
+constexpr size_t smem_bytes() {
+    return 1024 + static_cast<size_t>(G_STAGES) * stage_bytes<I4>() + (I4 ? H_PK_STAGES * H_PK_BYTES : 0) + G_EPI_BYTES +
+           G_COLV_BYTES + 512;
+}
 
 struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
     const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
+    const __nv_bfloat16* ascales_i4;   // INT4: activation group scales [K/64][M_pad]
+    int act_unsigned;                  // INT4: activation codes are u4
     const float* col_scale;   // [N]
     const float* col_bias;    // [N]
     int* status;
@@ -100,6 +117,8 @@ struct GemmShared {
     uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
     uint64_t xempty[4];             // ... and has been added by the first
     uint64_t drain;
+    uint64_t pk_full[H_PK_STAGES];  // INT4: packed activation codes of a k-block have landed
+    uint64_t pk_empty[H_PK_STAGES]; // INT4: the converter warps have read them
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -217,25 +236,49 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
 // RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
 // Requantising epilogues do about three times the work of the plain one per chunk; up to rank 32 (where a warp's
 // LoRA-down partial fits its 4 KB staging buffer) a second set of four epilogue warps takes every other 64-column chunk.
-template <int RTN>
-constexpr int epi_sets() { return (RTN == 1 || RTN == 2) ? 2 : 1; }
+template <int RTN, bool I4>
+constexpr int epi_sets() { return (!I4 && (RTN == 1 || RTN == 2)) ? 2 : 1; }
+template <int RTN, bool I4>
+constexpr int cta_threads() { return I4 ? H_THREADS : (epi_sets<RTN, I4>() == 2 ? G_THREADS_RQ : G_THREADS); }
 
-template <int RTN>
-__global__ void __launch_bounds__(epi_sets<RTN>() == 2 ? G_THREADS_RQ : G_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+// Eight packed s4 / u4 codes -> eight fp16 values code * scale, in the order (0, 4, 1, 5, 2, 6, 3, 7).
+// (x & 0x000f000f) | 0x6400 is the fp16 number 1024 + code, (x & 0x00f000f0) | 0x6400 is 1024 + 16 * code; one exact
+// subtraction (or fused multiply-add by 1/16) removes the offset, signed codes are biased by 8 first (flip bit 3).
+__device__ __forceinline__ uint4 int4x8_to_f16(uint32_t x, uint32_t flip, __half2 off_lo, __half2 off_hi, __half2 s2) {
+    x ^= flip;
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    uint32_t h[4];
+    h[0] = (x & 0x000f000fu) | 0x64006400u;
+    h[1] = (x & 0x00f000f0u) | 0x64006400u;
+    const uint32_t y = x >> 8;
+    h[2] = (y & 0x000f000fu) | 0x64006400u;
+    h[3] = (y & 0x00f000f0u) | 0x64006400u;
+    const __half2 v0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&h[0]), off_lo), s2);
+    const __half2 v1 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&h[1]), sixteenth, off_hi), s2);
+    const __half2 v2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&h[2]), off_lo), s2);
+    const __half2 v3 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&h[3]), sixteenth, off_hi), s2);
+    return make_uint4(*reinterpret_cast<const uint32_t*>(&v0), *reinterpret_cast<const uint32_t*>(&v1),
+                      *reinterpret_cast<const uint32_t*>(&v2), *reinterpret_cast<const uint32_t*>(&v3));
+}
+
+template <int RTN, bool I4>
+__global__ void __launch_bounds__(cta_threads<RTN, I4>(), 1)
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
                   const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* epi_smem = smem + G_STAGES * G_STAGE_BYTES;
+    constexpr int SB = stage_bytes<I4>();
+    uint8_t* pk_smem = smem + G_STAGES * SB;                                  // INT4: packed-code ring
+    uint8_t* epi_smem = pk_smem + (I4 ? H_PK_STAGES * H_PK_BYTES : 0);
     float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
     GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + G_COLV_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int KB = p.K / 64;                         // 64-code blocks along K
-    const int kstages = (KB + 3) / 4;
+    const int kstages = I4 ? KB : (KB + 3) / 4;      // NVFP4: 256 codes of K per stage; INT4: 64
     const int per_tile = kstages + p.lora_chunks;
     const int NB = p.N / 128;                        // weight scale atoms along N
     const TileRun tr = tile_run(p);
@@ -243,25 +286,31 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&sh->full[s], 8);   // four producers in each CTA
+            mbar_init(&sh->full[s], I4 ? 2 * (1 + H_CONV_WARPS) : 8);   // producers (and converter warps) of both CTAs
             mbar_init(&sh->empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->tfull[i], 1);
-            mbar_init(&sh->tempty[i], 8 * epi_sets<RTN>());
+            mbar_init(&sh->tempty[i], 8 * epi_sets<RTN, I4>());
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&sh->xfull[i], 1);
             mbar_init(&sh->xempty[i], 1);
         }
         mbar_init(&sh->drain, 1);
+        for (int i = 0; i < H_PK_STAGES; ++i) {
+            mbar_init(&sh->pk_full[i], 1);
+            mbar_init(&sh->pk_empty[i], H_CONV_WARPS);
+        }
         sh->abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_a);
         prefetch_tmap(&tm_b);
         prefetch_tmap(&tm_out);
-        prefetch_tmap(&tm_sfa);
-        prefetch_tmap(&tm_sfb);
+        if (!I4) {
+            prefetch_tmap(&tm_sfa);
+            prefetch_tmap(&tm_sfb);
+        }
         if (p.lora_chunks) {
             prefetch_tmap(&tm_la);
             prefetch_tmap(&tm_lu);
@@ -278,7 +327,95 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     pdl_wait();           // nothing above touches global memory; the quantiser's output is this kernel's input
     const uint32_t tmem = sh->tmem_base;
 
-    if (warp == 0 || (warp >= 6 && warp < 9)) {
+    if (I4 && (warp == 0 || warp >= 6)) {
+        // ------------------------------------------------------------------ INT4 producers and converter warps
+        // warp 0: packed activation codes (128 rows x 32 bytes per k-block, own ring, local barrier) and the fp32
+        // lora_act tile of a low-rank stage; warp 6: this CTA's 96 rows of the fp16 weights (or of LoRA-up);
+        // warps 7..14: codes -> fp16(code * group scale) straight into the 128B-swizzled K-major tile the MMA reads.
+        // Each converter warp takes 16 rows, a lane half a row (32 codes = one 16-byte word of the packed box), so
+        // both the packed read and the four swizzled 16-byte writes are free of bank conflicts.
+        if constexpr (I4) {
+            const int cw = warp - 7;
+            const int row = cw * 16 + (lane >> 1), hh = lane & 1;
+            const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
+            const __half2 off_lo = __float2half2_rn(p.act_unsigned ? 1024.f : 1032.f);
+            const __half2 off_hi = __float2half2_rn(p.act_unsigned ? -64.f : -72.f);
+            uint32_t it = 0, pk = 0;
+            bool ok = true;
+            for (int ti = 0; ti < tr.count && ok; ++ti) {
+                int m0, n0;
+                tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+                const int nb0 = n0 + rank * G_BNH;
+                const __nv_bfloat16* asp = p.ascales_i4 + m0 + row;
+                float as_next = 0.f;
+                if (warp >= 7) as_next = __bfloat162float(__ldg(asp));
+                for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                    const int s = it % G_STAGES;
+                    uint8_t* st = smem + s * SB;
+                    const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
+                    const bool lowrank = ks >= kstages;
+                    const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
+                    if (warp == 0) {
+                        if (lowrank) {
+                            ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 10));
+                            if (!ok) break;
+                            if (elect_one()) {
+                                mbar_arrive_expect_tx_cluster(lfull, H_A_BYTES);
+                                tma_load_2d_pair(st, &tm_la, lfull, (ks - kstages) * 32, m0);
+                            }
+                        } else {
+                            const int ps = pk % H_PK_STAGES;
+                            ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->pk_empty[ps], ((pk / H_PK_STAGES) & 1) ^ 1, sh, p.status, 14));
+                            if (!ok) break;
+                            if (elect_one()) {
+                                mbar_arrive_expect_tx(&sh->pk_full[ps], H_PK_BYTES);
+                                tma_load_2d(pk_smem + ps * H_PK_BYTES, &tm_a, &sh->pk_full[ps], ks * 32, m0);
+                            }
+                            ++pk;
+                        }
+                        __syncwarp();
+                    } else if (warp == 6) {
+                        ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 11));
+                        if (!ok) break;
+                        if (elect_one()) {
+                            mbar_arrive_expect_tx_cluster(lfull, H_B_BYTES);
+                            tma_load_2d_pair(st + H_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, lowrank ? (ks - kstages) * 32 : ks * 64, nb0);
+                        }
+                        __syncwarp();
+                    } else {
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], eparity, sh, p.status, 12));
+                        if (!ok) break;
+                        if (lowrank) {   // warp 0's expect_tx arrival stands in for converter warp 0
+                            if (cw != 0 && lane == 0) mbar_arrive_cluster(lfull);
+                            __syncwarp();
+                            continue;
+                        }
+                        const float as_cur = as_next;
+                        if (ks + 1 < kstages) as_next = __bfloat162float(__ldg(asp + static_cast<size_t>(ks + 1) * p.M_pad));
+                        const int ps = pk % H_PK_STAGES;
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
+                        if (!ok) break;
+                        const uint4 w = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + cw * 512 + lane * 16);
+                        // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
+                        const __half2 s2 = __float2half2_rn(fminf(as_cur, 4094.f));
+                        uint8_t* dst = st + row * 128;
+                        const int sw = row & 7;
+                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 0) ^ sw) << 4)) = int4x8_to_f16(w.x, flip, off_lo, off_hi, s2);
+                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 1) ^ sw) << 4)) = int4x8_to_f16(w.y, flip, off_lo, off_hi, s2);
+                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w.z, flip, off_lo, off_hi, s2);
+                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w.w, flip, off_lo, off_hi, s2);
+                        fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive_cluster(lfull);
+                            mbar_arrive(&sh->pk_empty[ps]);
+                        }
+                        ++pk;
+                    }
+                }
+            }
+        }
+    } else if (!I4 && (warp == 0 || (warp >= 6 && warp < 9))) {
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
         // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
@@ -328,6 +465,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (rank == 0) {
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(2 * G_BM, G_BN);
+            constexpr uint32_t IDESC_F16 = idesc_f16(2 * G_BM, G_BN);
             const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem));
             const uint64_t sfdesc0 = smem_desc_sf(smem_u32(smem) + G_A_BYTES + G_B_BYTES);
             uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
@@ -347,9 +485,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                     ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
                     if (!ok) break;
                     // descriptors of ring slot s: the start-address field counts 16-byte units
-                    const uint64_t adesc = adesc0 + static_cast<uint32_t>(s * (G_STAGE_BYTES >> 4));
+                    const uint64_t adesc = adesc0 + static_cast<uint32_t>(s * (SB >> 4));
                     const uint64_t bdesc = adesc + (G_A_BYTES >> 4);
-                    if (ks < kstages) {
+                    if (I4 && ks < kstages) {
+                        // INT4: four K=16 fp16 MMAs over the stage's 64 k (operands already carry their group scales)
+                        tc_fence_after_sync();
+                        if (elect_one()) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                tc_mma_pair_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_F16, j == 0 ? accumulate : 1u);
+                            tc_commit_pair(&sh->empty[s], 3);
+                        }
+                    } else if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
                         // Scale factors: shared memory -> TMEM with tcgen05.cp, issued just ahead of the MMA that
                         // reads them (the tensor pipe keeps the order).  Per k-block one 512-byte atom for the 128
@@ -357,7 +504,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         // rows into an atom reads from column 2 on).  Two TMEM buffers alternate.
                         const uint32_t t_sfa = tmem + G_TM_SF + (sq & 1) * G_TM_SF_STRIDE;
                         const uint32_t t_sfb = t_sfa + 16;
-                        const uint64_t sfdesc = sfdesc0 + static_cast<uint32_t>(s * (G_STAGE_BYTES >> 4));
+                        const uint64_t sfdesc = sfdesc0 + static_cast<uint32_t>(s * (SB >> 4));
                         tc_fence_after_sync();
                         if (elect_one()) {
                             if (nkb == 4) {
@@ -406,12 +553,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 __syncwarp();
             }
         }
-    } else if ((warp >= 2 && warp < 6) || warp >= 9) {
+    } else if ((warp >= 2 && warp < 6) || (!I4 && warp >= 9)) {
         // ------------------------------------------------------------------ epilogue (warps 2..5, and 9..12 when requantising)
         // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
         // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
         // hardware clips rows >= M and columns >= N).  Two staging buffers per warp keep a store in flight.
-        constexpr int SETS = epi_sets<RTN>();
+        constexpr int SETS = epi_sets<RTN, I4>();
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
         const int eset = warp >= 9 ? 1 : 0;
         // one set: two staging buffers per warp (a store stays in flight); two sets: one buffer per warp
@@ -580,27 +727,58 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                             }
                         }
                     }
-                    // ---- NVFP4 group quantisation of this thread's 64 values (4 groups of 16)
                     const float4* rcn = reinterpret_cast<const float4*>(cvs + 2 * G_BN + h * 64);
-                    uint32_t codes[8];
-                    uint32_t sw = 0;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const uint32_t xw[8] = {ow[8 * g], ow[8 * g + 1], ow[8 * g + 2], ow[8 * g + 3],
-                                                ow[8 * g + 4], ow[8 * g + 5], ow[8 * g + 6], ow[8 * g + 7]};
-                        uint32_t qv[8];
-                        const float amax = smooth16(xw, rcn + 4 * g, qv);
-                        uint32_t cw[2];
-                        sw |= nvfp4_encode16(qv, amax, cw) << (8 * g);
-                        codes[2 * g] = cw[0];
-                        codes[2 * g + 1] = cw[1];
-                    }
                     uint4* qdst = reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(grow) * (p.N >> 1) + ((n0 + h * 64) >> 1));
-                    qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-                    qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-                    const size_t soff = (static_cast<size_t>(grow >> 7) * (p.N >> 6) + ((n0 + h * 64) >> 6)) * 512 +
-                                        (grow & 31) * 16 + ((grow >> 5) & 3) * 4;
-                    *reinterpret_cast<uint32_t*>(p.oscales + soff) = sw;
+                    if constexpr (I4) {
+                        // ---- INT4 group quantisation: this thread's 64 values are exactly one group of the next layer;
+                        // u4 codes of bf16(bf16(y + 0.171875) / smooth), scale = max / 15 (gemm_w4a4_launch_impl.cuh:282-309)
+                        uint32_t qv[4][8];
+                        float amax = 0.f;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t xw[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float2 f = bf16x2_to_float2(ow[8 * g + i]);
+                                const __nv_bfloat162 sft = __floats2bfloat162_rn(f.x + 0.171875f, f.y + 0.171875f);
+                                xw[i] = *reinterpret_cast<const uint32_t*>(&sft);
+                            }
+                            amax = fmaxf(amax, smooth16(xw, rcn + 4 * g, qv[g]));
+                        }
+                        uint32_t codes[8];
+                        float scale = 0.f;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t cw[2];
+                            scale = int4_encode16<true>(qv[g], amax, cw);
+                            codes[2 * g] = cw[0];
+                            codes[2 * g + 1] = cw[1];
+                        }
+                        qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                        qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                        reinterpret_cast<__nv_bfloat16*>(p.oscales)[static_cast<size_t>((n0 + h * 64) >> 6) * p.M_pad + grow] =
+                            __float2bfloat16_rn(scale);
+                    } else {
+                        // ---- NVFP4 group quantisation of this thread's 64 values (4 groups of 16)
+                        uint32_t codes[8];
+                        uint32_t sw = 0;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const uint32_t xw[8] = {ow[8 * g], ow[8 * g + 1], ow[8 * g + 2], ow[8 * g + 3],
+                                                    ow[8 * g + 4], ow[8 * g + 5], ow[8 * g + 6], ow[8 * g + 7]};
+                            uint32_t qv[8];
+                            const float amax = smooth16(xw, rcn + 4 * g, qv);
+                            uint32_t cw[2];
+                            sw |= nvfp4_encode16(qv, amax, cw) << (8 * g);
+                            codes[2 * g] = cw[0];
+                            codes[2 * g + 1] = cw[1];
+                        }
+                        qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+                        qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+                        const size_t soff = (static_cast<size_t>(grow >> 7) * (p.N >> 6) + ((n0 + h * 64) >> 6)) * 512 +
+                                            (grow & 31) * 16 + ((grow >> 5) & 3) * 4;
+                        *reinterpret_cast<uint32_t*>(p.oscales + soff) = sw;
+                    }
                 }
             }
             tc_fence_before_sync();
@@ -676,22 +854,22 @@ int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
     return SVDQ_OK;
 }
 
-template <int RTN>
-static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
+template <int RTN, bool I4>
+static int launch_pair(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
                         const CUtensorMap& lu, const CUtensorMap& o, const CUtensorMap& sfa, const CUtensorMap& sfb,
                         const GemmParams& p) {
     static bool attr_done[64] = {};
     int dev = 0;
     SVDQ_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !attr_done[dev]) {
-        SVDQ_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel<RTN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(G_SMEM_BYTES)));
+        SVDQ_CUDA(cudaFuncSetAttribute(gemm_w4a4_kernel<RTN, I4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_bytes<I4>())));
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);   // 2 CTAs per pair
-    cfg.blockDim = dim3(epi_sets<RTN>() == 2 ? G_THREADS_RQ : G_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = G_SMEM_BYTES;
+    cfg.blockDim = dim3(cta_threads<RTN, I4>(), 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes<I4>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -702,7 +880,7 @@ static int launch_nvfp4(int grid, cudaStream_t stream, const CUtensorMap& a, con
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<RTN>, a, b, la, lu, o, sfa, sfb, p));
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<RTN, I4>, a, b, la, lu, o, sfa, sfb, p));
     return SVDQ_OK;
 }
 
@@ -790,14 +968,118 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
             return rc;
     }
     int rc;
-    if (!requant) rc = launch_nvfp4<0>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else if (a->R_next == 16) rc = launch_nvfp4<1>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else if (a->R_next == 32) rc = launch_nvfp4<2>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else rc = launch_nvfp4<4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    if (!requant) rc = launch_pair<0, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else if (a->R_next == 16) rc = launch_pair<1, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else if (a->R_next == 32) rc = launch_pair<2, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else rc = launch_pair<4, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
     if (rc) return rc;
     if (requant) {
         lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
                                                                       pl.slots, pl.npairs);
+        SVDQ_CUDA(cudaGetLastError());
+    }
+    return SVDQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// INT4 (group 64).  Reference: gemm_w4a4_kernel, src/kernels/zgemm/gemm_w4a4.cuh:832-928,1046-1095; scale application
+// gemm_base.cuh:367-409:
+//   acc[m, n] = sum_g ascale[m, g] * wscale[n, g] * ( sum_{k in group g} a[m, k] * w[n, k] ) + sum_r lora_act[m, r] * Wu[n, r]
+// sm_100 has no 4-bit integer MMA kind and no block-scaled kind with bf16 scales, and rescaling an integer accumulator
+// per group on the SIMT pipes costs M*N*K/64 multiply-adds plus as many TMEM reads.  Both operands are therefore turned
+// into fp16 numbers that already carry their group scale - the weights once at preparation time, the activations by
+// converter warps as the packed codes arrive in shared memory - and the same pair kernel runs kind::f16 MMAs into one
+// fp32 accumulator.  code * scale is exact in fp16 (4 + 8 significant bits), every product is exact in fp32, so the
+// only difference to the integer formulation is the order of fp32 additions.  (The reference adds the per-group terms
+// in bf16.)  Activation scales above 4094 are capped so that code * scale stays finite in fp16.
+// ---------------------------------------------------------------------------------------------------
+int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) { return gemm_nvfp4_workspace_bytes(a, bytes); }
+
+int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
+    const bool requant = a->qout != nullptr;
+    SVDQ_CHECK_ARG(a->out != nullptr || requant, "gemm(int4): neither `out` nor `qout` given");
+    if (requant) {
+        SVDQ_CHECK_ARG(a->oscales && a->lora_act_out && a->next_smooth && a->next_lora_down,
+                       "gemm(int4): requantisation needs oscales, lora_act_out, next_smooth and next_lora_down");
+        SVDQ_CHECK_ARG(!a->next_fp4, "gemm(int4): the requantised output must be INT4 as well");
+        SVDQ_CHECK_ARG(a->out_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): requantised output is written in SVDQ_LAYOUT_NATIVE");
+        SVDQ_CHECK_ARG(a->activation == SVDQ_ACT_GELU, "gemm(int4): the requantising epilogue applies GELU "
+                                                       "(gemm_w4a4_launch_impl.cuh:282-309); set activation = SVDQ_ACT_GELU");
+        SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
+                           aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
+                       "gemm(int4): requantisation tensors must be 16-byte aligned (workspace: 256)");
+        if (a->R_next != 16 && a->R_next != 32 && a->R_next != 64)
+            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
+    }
+    SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): activations must be in SVDQ_LAYOUT_NATIVE "
+                                                        "(convert with svdq_w4a4_relayout_act)");
+    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
+
+    int dev = 0, sms = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    NvfpPlan pl;
+    plan_nvfp4(a, sms, &pl);
+    SVDQ_CHECK_ARG(!requant || (a->workspace && a->workspace_bytes >= pl.workspace),
+                   "gemm(int4): workspace of %zu bytes required (svdq_gemm_w4a4_workspace_bytes)", pl.workspace);
+
+    GemmParams p = {};
+    p.ascales_i4 = static_cast<const __nv_bfloat16*>(a->ascales);
+    p.act_unsigned = a->act_unsigned;
+    p.col_scale = a->w.col_scale;
+    p.col_bias = a->w.col_bias;
+    p.M = a->M;
+    p.M_pad = a->M_pad;
+    p.N = a->N;
+    p.K = a->K;
+    p.lora_chunks = (a->R + 31) / 32;
+    p.tiles_m = pl.tiles_m;
+    p.tiles_n = pl.tiles_n;
+    p.activation = a->activation;
+    p.store_out = a->out != nullptr;
+    p.contiguous = requant;
+    p.run = pl.run;
+    p.qout = static_cast<uint8_t*>(a->qout);
+    p.oscales = static_cast<uint8_t*>(a->oscales);
+    p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
+    p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
+    p.lora_partial = static_cast<float*>(a->workspace);
+    p.slots = pl.slots;
+    if (int rc = status_words(&p.status)) return rc;
+
+    CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out;
+    // packed codes: 32 bytes (64 codes) x 128 rows per k-block, unswizzled; weights: fp16 [N][K], 64 x 96 boxes
+    if (int rc = make_tmap_2d(&tm_a, a->act, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->K / 2, a->M_pad, a->K / 2, 32, G_BM, false)) return rc;
+    if (int rc = make_tmap_2d(&tm_b, a->w.wgt, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a->K, a->N, static_cast<uint64_t>(a->K) * 2, 64, G_BNH))
+        return rc;
+    if (a->R > 0) {
+        const int R32 = (a->R + 31) / 32 * 32;
+        if (int rc = make_tmap_2d(&tm_la, a->lora_act_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
+                                  static_cast<uint64_t>(a->R) * 4, 32, G_BM))
+            return rc;
+        if (int rc = make_tmap_2d(&tm_lu, a->w.lora_up, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, R32, a->N,
+                                  static_cast<uint64_t>(R32) * 4, 32, G_BNH))
+            return rc;
+    } else {
+        tm_la = tm_b;
+        tm_lu = tm_b;
+    }
+    if (a->out) {
+        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+            return rc;
+    } else {
+        tm_out = tm_b;
+    }
+    int rc;
+    if (!requant) rc = launch_pair<0, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
+    else if (a->R_next == 16) rc = launch_pair<1, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
+    else if (a->R_next == 32) rc = launch_pair<2, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
+    else rc = launch_pair<4, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
+    if (rc) return rc;
+    if (requant) {
+        lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(
+            p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run, pl.slots, pl.npairs);
         SVDQ_CUDA(cudaGetLastError());
     }
     return SVDQ_OK;

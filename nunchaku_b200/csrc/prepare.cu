@@ -3,6 +3,7 @@
 // per layer for weights), one thread per 32-bit word, fully coalesced on the
 // reading side.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "host_common.h"
 
@@ -34,10 +35,30 @@ __global__ void retile_wgt_codes_kernel(const uint32_t* __restrict__ src, uint32
     }
 }
 
-// INT4 weights: same source order, but expanded to one signed byte per code, row-major [N][K], so that
-// the kind::i8 GEMM streams them with TMA without a per-tile unpack (weights are static; activations are
-// unpacked in shared memory by the GEMM).
-__global__ void retile_wgt_codes_s8_kernel(const uint32_t* __restrict__ src, uint2* __restrict__ dst, int N, int K) {
+// INT4 weights.  sm_100 has no 4-bit integer MMA kind, and a kind::i8 GEMM would have to rescale every group of 64 k
+// on the SIMT pipes.  Instead each code is multiplied by its group scale once, here, and stored as fp16:
+//   w16[n][k'] = fp16( code[n][k] * wscale[n][k/64] / col_scale[n] ),   col_scale[n] = 2^floor(log2(max_g wscale[n][g]))
+// code (4 bits) times a bf16 scale (8 bits) is exact in fp16 (11 bits) while the scaled scale is a normal fp16 number;
+// the power-of-two column factor keeps the largest scale of a channel in [1, 2) so that only scales more than 2^14
+// below it lose bits, and is applied again in the GEMM epilogue.  Within each block of 8 k the order is
+// (0, 4, 1, 5, 2, 6, 3, 7): the order in which the GEMM's converter warps produce the activations of a packed word
+// (a dot product does not care about the order as long as both operands agree).  Row-major [N][K].
+__global__ void int4_col_scale_kernel(const __nv_bfloat16* __restrict__ ws, float* __restrict__ col_scale, int N, int KB) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    float mx = 0.f;
+    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(__bfloat162float(ws[static_cast<size_t>(g) * N + n])));
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) {
+        (void)frexpf(mx, &e);   // mx = f * 2^e, f in [0.5, 1)
+        e -= 1;
+    }
+    e = max(-100, min(100, e));
+    col_scale[n] = ldexpf(1.0f, e);
+}
+
+__global__ void retile_wgt_codes_f16_kernel(const uint32_t* __restrict__ src, const __nv_bfloat16* __restrict__ ws,
+                                            const float* __restrict__ col_scale, uint4* __restrict__ dst, int N, int K) {
     const size_t total = static_cast<size_t>(N) * K / 8;
     const int KB = K / 64;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -53,10 +74,16 @@ __global__ void retile_wgt_codes_s8_kernel(const uint32_t* __restrict__ src, uin
         const int n = bn * 128 + nt * 16 + half * 8 + g;
         const int k = bk * 64 + kh * 32 + t * 8;
         const uint32_t w = src[i];
-        uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-        lo |= (lo & 0x08080808u) * 0x1Eu;   // sign-extend each nibble to a byte
-        hi |= (hi & 0x08080808u) * 0x1Eu;
-        dst[(static_cast<size_t>(n) * K + k) / 8] = make_uint2(__byte_perm(lo, hi, 0x5140), __byte_perm(lo, hi, 0x7362));
+        const float s = __bfloat162float(ws[static_cast<size_t>(bk) * N + n]) / col_scale[n];
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {   // output pair j = codes j and j + 4
+            const int c0 = (static_cast<int>(w << (28 - 4 * j))) >> 28;          // sign-extended nibble j
+            const int c1 = (static_cast<int>(w << (12 - 4 * j))) >> 28;          // nibble j + 4
+            const __half2 h = __floats2half2_rn(static_cast<float>(c0) * s, static_cast<float>(c1) * s);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        dst[(static_cast<size_t>(n) * K + k) / 8] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -103,12 +130,12 @@ struct LoraScales {
 __global__ void prepare_columns_kernel(const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ wcscales,
                                        const __nv_bfloat16* __restrict__ lora_up, float* __restrict__ col_scale,
                                        float* __restrict__ col_bias, float* __restrict__ lora_out, float alpha, int N,
-                                       int R, int R32, LoraScales ls) {
+                                       int R, int R32, LoraScales ls, bool col_scale_given) {
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N) return;
     const int pos = (n & ~127) + packed_vec_pos128(n & 127);
     const float wc = wcscales ? __bfloat162float(wcscales[pos]) : 1.0f;
-    const float cs = alpha * wc;
+    const float cs = (col_scale_given ? col_scale[n] : 1.0f) * alpha * wc;   // INT4: times the power of two taken out of the weights
     col_scale[n] = cs;
     col_bias[n] = bias ? __bfloat162float(bias[pos]) : 0.0f;
     if (lora_out == nullptr) return;
@@ -224,7 +251,7 @@ int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]) {
     SVDQ_CHECK_ARG(N > 0 && N % 128 == 0 && K > 0 && K % 128 == 0 && R >= 0 && R % 16 == 0,
                    "prepared_bytes: need N%%128==0, K%%128==0, R%%16==0 (N=%d K=%d R=%d)", N, K, R);
     const size_t R32 = (static_cast<size_t>(R) + 31) / 32 * 32;
-    bytes[0] = fp4 ? static_cast<size_t>(N) * K / 2 : static_cast<size_t>(N) * K;
+    bytes[0] = fp4 ? static_cast<size_t>(N) * K / 2 : static_cast<size_t>(N) * K * 2;   // INT4: fp16 per code
     bytes[1] = fp4 ? static_cast<size_t>(N) * K / 16 : static_cast<size_t>(N) * (K / 64) * 2;
     bytes[2] = static_cast<size_t>(N) * R32 * 4;
     bytes[3] = static_cast<size_t>(N) * 4;
@@ -244,13 +271,9 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
                    "prepare_weights: tensors must be 16-byte aligned");
     if (int rc = check_arch()) return rc;
     const size_t words = static_cast<size_t>(a->N) * a->K / 8;
-    if (a->fp4)
+    if (a->fp4) {
         retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
                                                                     static_cast<uint32_t*>(o->wgt), a->N, a->K);
-    else
-        retile_wgt_codes_s8_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
-                                                                       static_cast<uint2*>(o->wgt), a->N, a->K);
-    if (a->fp4) {
         const size_t sw = static_cast<size_t>(a->N) * a->K / 64;
         retile_wgt_mscales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint32_t*>(a->wscales),
                                                                    static_cast<uint32_t*>(o->wscales), a->N, a->K);
@@ -258,6 +281,11 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
         const size_t sw = static_cast<size_t>(a->N) * (a->K / 64);
         retile_wgt_scales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a->wscales),
                                                                   static_cast<__nv_bfloat16*>(o->wscales), a->N, a->K);
+        int4_col_scale_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(o->wscales), o->col_scale,
+                                                                     a->N, a->K / 64);
+        retile_wgt_codes_f16_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                        static_cast<const __nv_bfloat16*>(o->wscales), o->col_scale,
+                                                                        static_cast<uint4*>(o->wgt), a->N, a->K);
     }
     LoraScales ls;
     for (int i = 0; i < 8; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
@@ -265,7 +293,7 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
     prepare_columns_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a->bias), static_cast<const __nv_bfloat16*>(a->wcscales),
         static_cast<const __nv_bfloat16*>(a->lora_up), o->col_scale, o->col_bias, a->R ? o->lora_up : nullptr, a->alpha,
-        a->N, a->R, R32, ls);
+        a->N, a->R, R32, ls, !a->fp4);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }
