@@ -1,4 +1,4 @@
-// NVFP4 W4A4 GEMM with the fused SVDQuant epilogue, sm_100a.
+// W4A4 GEMM (NVFP4 and INT4) with the fused SVDQuant epilogue, sm_100a.
 //
 // What it computes (reference: gemm_w4a4_fp4_kernel, src/kernels/zgemm/gemm_w4a4.cuh:273-405,
 // epilogue chain gemm_w4a4_launch_impl.cuh:172-420):
@@ -8,26 +8,33 @@
 // (Wu' is the LoRA-up weight pre-divided by col_scale, so both branches share one fp32 accumulator.)
 // Plain epilogue: out = bf16(y).  Requantising epilogue (GELU + next layer, launch_impl.cuh:282-309,
 // gemm_w4a4.cuh:930-1043, lora.cuh:243-353): yb = bf16(y);  lora_act_out = yb @ Wd_next^T (fp32);
-// codes/scales = NVFP4 group quantisation of bf16(yb / smooth_next);  out (optional) = yb.
+// codes/scales = group quantisation of bf16(yb / smooth_next);  out (optional) = yb.
+// The INT4 variant (template parameter I4; what it computes is stated above gemm_int4_impl) differs only in how the
+// operands reach the tensor core and in the group format of the requantised output.
 //
 // How it maps to a B200.  The two SMs of a CTA pair (cluster of 2) walk 256 x 192 output tiles together with
 // tcgen05 cta_group::2: each CTA holds 128 rows of A, 128 rows of the accumulator (its own TMEM) and 96 of the
 // tile's 192 weight rows; the even CTA ("leader") issues one 256-row MMA for both.  Per byte loaded the pair
-// does 1.4x the math of two independent 128 x 192 CTAs, so a five-stage ring covers the load latency that a
-// four-stage ring of full tiles could not.  In each CTA:
-//   warps 0, 10, 11  producers, one copy stream each: TMA loads of the 128B-swizzled operand tiles (128 rows x 256
-//               codes of A; 96 x 256 of B; completion counted on the leader's barrier) and bulk copies of the
-//               512-byte scale-factor atoms (own 128 rows of A, all 192 rows of B; counted on a local barrier)
-//   warp 1      leader only: MMA issuer, 4 x tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N192 K64)
-//               per stage; the low-rank branch is fed through the same ring as fp32 tiles and issued as
-//               kind::tf32 into the same accumulator; one multicast tcgen05.commit per stage releases the stage
-//               and its scale-factor buffer in both CTAs, one per tile publishes the accumulator
+// does 1.4x the math of two independent 128 x 192 CTAs.  Five-stage operand ring.  In each CTA (NVFP4):
+//   warps 0, 6, 7, 8  producers, one TMA stream each (the TMA unit retires the copies of one issuing warp one
+//               after the other): per stage (256 codes of K) the 128B-swizzled 128 x 128 B box of A, the 96 x 128 B
+//               box of B, the 2 KB of scale atoms of the CTA's activation rows and the 4 KB of the two 128-row
+//               weight scale atoms; the cta_group::2 form of the load counts all of them on the leader's barrier
+//   warp 1      leader only: MMA issuer.  Per k-block three tcgen05.cp (scale atoms, shared memory -> TMEM) and one
+//               tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N192 K64); the low-rank branch is fed
+//               through the same ring as fp32 tiles and issued as kind::tf32 into the same accumulator; one
+//               multicast tcgen05.commit per stage releases the stage in both CTAs, one per tile publishes the
+//               accumulator
 //   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
 //               staging buffer, TMA store (coalesced, clipped at M and N by the hardware); when requantising,
 //               the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix + mma.sync) and the
 //               thread's own row chunk is group-quantised in registers
+//   warps 9..12 (NVFP4 requantising variants up to rank 32) a second epilogue set; the two warps of a lane quadrant
+//               take alternate 64-column chunks
+// INT4: warp 0 brings the packed activation codes (own ring), warp 6 the fp16 weights, warps 7..14 convert codes to
+// fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
 // TMEM per CTA: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
-// plus three 40-column scale-factor buffers (16 for A, 24 for B) = 504 of 512 columns.
+// plus two 48-column scale-factor buffers (16 for A, 32 for B) = 480 of 512 columns.
 // Every loop that issues tcgen05 / TMA instructions is run by a whole warp with one elected lane issuing, so
 // that descriptors and coordinates stay warp-uniform.  Every wait is bounded; a wait that runs out raises the
 // abort flag of both CTAs, all roles leave their loops, and the status words tell the host.
@@ -342,75 +349,100 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const __half2 off_hi = __float2half2_rn(p.act_unsigned ? -64.f : -72.f);
             uint32_t it = 0, pk = 0;
             bool ok = true;
-            for (int ti = 0; ti < tr.count && ok; ++ti) {
-                int m0, n0;
-                tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
-                const int nb0 = n0 + rank * G_BNH;
-                const __nv_bfloat16* asp = p.ascales_i4 + m0 + row;
-                float as_next = 0.f;
-                if (warp >= 7) as_next = __bfloat162float(__ldg(asp));
-                for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int s = it % G_STAGES;
-                    uint8_t* st = smem + s * SB;
-                    const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
-                    const bool lowrank = ks >= kstages;
-                    const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
-                    if (warp == 0) {
-                        if (lowrank) {
-                            ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 10));
+            if (warp >= 7) {
+                // converter warps.  A lane needs one group scale per k-block; they are fetched eight k-blocks at a time,
+                // one batch ahead, so that the L2 latency is paid once per eight stages and off the critical path.
+                for (int ti = 0; ti < tr.count && ok; ++ti) {
+                    int m0, n0;
+                    tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+                    const __nv_bfloat16* asp = p.ascales_i4 + m0 + row;
+                    __nv_bfloat16 nxt[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) nxt[j] = j < kstages ? __ldg(asp + static_cast<size_t>(j) * p.M_pad) : __nv_bfloat16(0.f);
+                    for (int kb0 = 0; kb0 < kstages && ok; kb0 += 8) {
+                        __nv_bfloat16 cur[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            cur[j] = nxt[j];
+                            if (kb0 + 8 + j < kstages) nxt[j] = __ldg(asp + static_cast<size_t>(kb0 + 8 + j) * p.M_pad);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (kb0 + j >= kstages) break;
+                            const int s = it % G_STAGES;
+                            uint8_t* st = smem + s * SB;
+                            const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
+                            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 12));
                             if (!ok) break;
-                            if (elect_one()) {
-                                mbar_arrive_expect_tx_cluster(lfull, H_A_BYTES);
-                                tma_load_2d_pair(st, &tm_la, lfull, (ks - kstages) * 32, m0);
-                            }
-                        } else {
                             const int ps = pk % H_PK_STAGES;
-                            ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->pk_empty[ps], ((pk / H_PK_STAGES) & 1) ^ 1, sh, p.status, 14));
+                            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
                             if (!ok) break;
-                            if (elect_one()) {
-                                mbar_arrive_expect_tx(&sh->pk_full[ps], H_PK_BYTES);
-                                tma_load_2d(pk_smem + ps * H_PK_BYTES, &tm_a, &sh->pk_full[ps], ks * 32, m0);
+                            const uint4 w = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + cw * 512 + lane * 16);
+                            // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
+                            const __half2 s2 = __float2half2_rn(fminf(__bfloat162float(cur[j]), 4094.f));
+                            uint8_t* dst = st + row * 128;
+                            const int sw = row & 7;
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 0) ^ sw) << 4)) = int4x8_to_f16(w.x, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 1) ^ sw) << 4)) = int4x8_to_f16(w.y, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w.z, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w.w, flip, off_lo, off_hi, s2);
+                            fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
+                            __syncwarp();
+                            if (lane == 0) {
+                                mbar_arrive_cluster(lfull);
+                                mbar_arrive(&sh->pk_empty[ps]);
                             }
                             ++pk;
+                            ++it;
+                        }
+                    }
+                    for (int c = 0; c < p.lora_chunks && ok; ++c, ++it) {   // low-rank stages: nothing to convert
+                        const int s = it % G_STAGES;
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 12));
+                        if (!ok) break;
+                        // warp 0's expect_tx arrival stands in for converter warp 0
+                        if (cw != 0 && lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->full[s]), 0));
+                        __syncwarp();
+                    }
+                }
+            } else {
+                for (int ti = 0; ti < tr.count && ok; ++ti) {
+                    int m0, n0;
+                    tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+                    const int nb0 = n0 + rank * G_BNH;
+                    for (int ks = 0; ks < per_tile; ++ks, ++it) {
+                        const int s = it % G_STAGES;
+                        uint8_t* st = smem + s * SB;
+                        const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
+                        const bool lowrank = ks >= kstages;
+                        const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
+                        if (warp == 0) {
+                            if (lowrank) {
+                                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 10));
+                                if (!ok) break;
+                                if (elect_one()) {
+                                    mbar_arrive_expect_tx_cluster(lfull, H_A_BYTES);
+                                    tma_load_2d_pair(st, &tm_la, lfull, (ks - kstages) * 32, m0);
+                                }
+                            } else {
+                                const int ps = pk % H_PK_STAGES;
+                                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->pk_empty[ps], ((pk / H_PK_STAGES) & 1) ^ 1, sh, p.status, 14));
+                                if (!ok) break;
+                                if (elect_one()) {
+                                    mbar_arrive_expect_tx(&sh->pk_full[ps], H_PK_BYTES);
+                                    tma_load_2d(pk_smem + ps * H_PK_BYTES, &tm_a, &sh->pk_full[ps], ks * 32, m0);
+                                }
+                                ++pk;
+                            }
+                        } else {
+                            ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 11));
+                            if (!ok) break;
+                            if (elect_one()) {
+                                mbar_arrive_expect_tx_cluster(lfull, H_B_BYTES);
+                                tma_load_2d_pair(st + H_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, lowrank ? (ks - kstages) * 32 : ks * 64, nb0);
+                            }
                         }
                         __syncwarp();
-                    } else if (warp == 6) {
-                        ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 11));
-                        if (!ok) break;
-                        if (elect_one()) {
-                            mbar_arrive_expect_tx_cluster(lfull, H_B_BYTES);
-                            tma_load_2d_pair(st + H_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, lowrank ? (ks - kstages) * 32 : ks * 64, nb0);
-                        }
-                        __syncwarp();
-                    } else {
-                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], eparity, sh, p.status, 12));
-                        if (!ok) break;
-                        if (lowrank) {   // warp 0's expect_tx arrival stands in for converter warp 0
-                            if (cw != 0 && lane == 0) mbar_arrive_cluster(lfull);
-                            __syncwarp();
-                            continue;
-                        }
-                        const float as_cur = as_next;
-                        if (ks + 1 < kstages) as_next = __bfloat162float(__ldg(asp + static_cast<size_t>(ks + 1) * p.M_pad));
-                        const int ps = pk % H_PK_STAGES;
-                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
-                        if (!ok) break;
-                        const uint4 w = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + cw * 512 + lane * 16);
-                        // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
-                        const __half2 s2 = __float2half2_rn(fminf(as_cur, 4094.f));
-                        uint8_t* dst = st + row * 128;
-                        const int sw = row & 7;
-                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 0) ^ sw) << 4)) = int4x8_to_f16(w.x, flip, off_lo, off_hi, s2);
-                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 1) ^ sw) << 4)) = int4x8_to_f16(w.y, flip, off_lo, off_hi, s2);
-                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w.z, flip, off_lo, off_hi, s2);
-                        *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w.w, flip, off_lo, off_hi, s2);
-                        fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive_cluster(lfull);
-                            mbar_arrive(&sh->pk_empty[ps]);
-                        }
-                        ++pk;
                     }
                 }
             }

@@ -119,7 +119,7 @@ mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status)
     tc_fence_after_sync();
     const uint32_t tmem = sh->tmem_base;
     if (threadIdx.x < 32) {
-        const uint32_t idesc = kind == 0 ? idesc_nvfp4(256, n) : idesc_tf32(256, n);
+        const uint32_t idesc = kind == 0 ? idesc_nvfp4(256, n) : kind == 3 ? idesc_f16(256, n) : idesc_tf32(256, n);
         const long long t0 = clock64();
         if (rank == 0) {
             for (int it = 0; it < iters; ++it) {
@@ -132,6 +132,8 @@ mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status)
                     for (int j = 0; j < 4; ++j) {
                         if (kind == 0)
                             tc_mma_pair_nvfp4(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + 4 * j, t_sf + 16 + 8 * j, 1);
+                        else if (kind == 3)
+                            tc_mma_pair_f16(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
                         else
                             tc_mma_pair_tf32(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, 1);
                     }
@@ -308,11 +310,11 @@ extern "C" int svdq_probe_ingest_rate(const void* src, size_t src_bytes, int chu
     return SVDQ_OK;
 }
 
-// kind 0 = mxf4nvf4, 1 = tf32; grid must be even (CTA pairs).  No counterpart in the reference.
+// kind 0 = mxf4nvf4, 1 = tf32, 3 = f16 (K = 16); grid must be even (CTA pairs).  No counterpart in the reference.
 extern "C" int svdq_probe_mma_rate_pair(int kind, int n, int iters, int grid, long long* cycles, void* stream) {
     using namespace svdq;
     SVDQ_CHECK_ARG(cycles && grid > 0 && grid <= 1024 && grid % 2 == 0 && iters > 0 && n >= 32 && n <= 256 && n % 32 == 0 &&
-                       kind >= 0 && kind <= 1,
+                       (kind == 0 || kind == 1 || kind == 3),
                    "pair probe: bad argument");
     if (int rc = check_arch()) return rc;
     int* status = nullptr;

@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-KINDS = {"mxf4nvf4": (0, 64), "tf32": (1, 8), "i8": (2, 32)}
+KINDS = {"mxf4nvf4": (0, 64), "tf32": (1, 8), "i8": (2, 32), "f16": (3, 16)}   # f16: pair probe only
 
 
 def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_buffers: int = 1, grid: int | None = None,
