@@ -79,9 +79,10 @@ constexpr int G_COLV_BYTES = 8 * G_COLV_FLOATS * 4;           // up to 8 epilogu
 constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
 constexpr int H_B_BYTES = G_BNH * 128;          // 96 rows x 64 fp16
 constexpr int H_STAGE_BYTES = H_A_BYTES + H_B_BYTES;   // 28672 = 28 * 1024
-constexpr int H_PK_STAGES = 4;
+constexpr int H_PK_STAGES = 6;
 constexpr int H_PK_BYTES = G_BM * 32;           // 128 rows x 64 packed codes
 constexpr int H_CONV_WARPS = 8;
+constexpr int H_CONV_PER_STAGE = 2;             // converter warps that share one stage (64 rows each); four such groups take turns
 constexpr int H_THREADS = (7 + H_CONV_WARPS) * 32;   // warps 0 A codes, 1 MMA, 2..5 epilogue, 6 weights, 7..14 converters
 template <bool I4>
 constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
@@ -293,7 +294,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
         for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&sh->full[s], I4 ? 2 * (1 + H_CONV_WARPS) : 8);   // producers (and converter warps) of both CTAs
+            mbar_init(&sh->full[s], I4 ? 2 * (1 + H_CONV_PER_STAGE) : 8);   // producers (and converter warps) of both CTAs
             mbar_init(&sh->empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -307,7 +308,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         mbar_init(&sh->drain, 1);
         for (int i = 0; i < H_PK_STAGES; ++i) {
             mbar_init(&sh->pk_full[i], 1);
-            mbar_init(&sh->pk_empty[i], H_CONV_WARPS);
+            mbar_init(&sh->pk_empty[i], H_CONV_PER_STAGE);
         }
         sh->abort_flag = 0;
         fence_mbar_init();
@@ -336,74 +337,84 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (I4 && (warp == 0 || warp >= 6)) {
         // ------------------------------------------------------------------ INT4 producers and converter warps
-        // warp 0: packed activation codes (128 rows x 32 bytes per k-block, own ring, local barrier) and the fp32
-        // lora_act tile of a low-rank stage; warp 6: this CTA's 96 rows of the fp16 weights (or of LoRA-up);
+        // warp 0: packed activation codes (128 rows x 32 bytes per k-block, own ring, local barrier); warp 6: this CTA's
+        // 96 rows of the fp16 weights, or both fp32 tiles (lora_act, LoRA-up) of a low-rank stage;
         // warps 7..14: codes -> fp16(code * group scale) straight into the 128B-swizzled K-major tile the MMA reads.
-        // Each converter warp takes 16 rows, a lane half a row (32 codes = one 16-byte word of the packed box), so
-        // both the packed read and the four swizzled 16-byte writes are free of bank conflicts.
         if constexpr (I4) {
             const int cw = warp - 7;
-            const int row = cw * 16 + (lane >> 1), hh = lane & 1;
+            const int hh = lane & 1;
             const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
             const __half2 off_lo = __float2half2_rn(p.act_unsigned ? 1024.f : 1032.f);
             const __half2 off_hi = __float2half2_rn(p.act_unsigned ? -64.f : -72.f);
             uint32_t it = 0, pk = 0;
             bool ok = true;
             if (warp >= 7) {
-                // converter warps.  A lane needs one group scale per k-block; they are fetched eight k-blocks at a time,
-                // one batch ahead, so that the L2 latency is paid once per eight stages and off the critical path.
+                // converter warps.  Every shared-memory and barrier operation of a SIMT warp queues behind the tensor core's
+                // operand reads, so the fixed chain of a stage's hand-shake (two barrier waits, load, stores, proxy fence,
+                // arrivals) costs several hundred cycles however little is converted.  The eight warps therefore form four
+                // groups that take every fourth stage each, two warps per stage with 64 rows apiece: four stages are in
+                // conversion at once.  A lane converts half a row (32 codes) of rows r0, r0 + 16, r0 + 32, r0 + 48: the packed
+                // loads of a warp cover 512 contiguous bytes and its swizzled 16-byte stores are free of bank conflicts.
+                // The group scales of the next stage the warp will convert are fetched while it converts this one.
+                const int grp = cw >> 1, g2 = cw & 1;
+                const int r0 = g2 * 64 + (lane >> 1);
+                uint32_t it_base = 0, pk_base = 0;
                 for (int ti = 0; ti < tr.count && ok; ++ti) {
                     int m0, n0;
                     tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
-                    const __nv_bfloat16* asp = p.ascales_i4 + m0 + row;
-                    __nv_bfloat16 nxt[8];
+                    const __nv_bfloat16* asp = p.ascales_i4 + m0 + r0;
+                    int ks = static_cast<int>((static_cast<uint32_t>(grp) - it_base) & 3u);   // first stage of this tile that is ours
+                    __nv_bfloat16 nxt[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) nxt[j] = j < kstages ? __ldg(asp + static_cast<size_t>(j) * p.M_pad) : __nv_bfloat16(0.f);
-                    for (int kb0 = 0; kb0 < kstages && ok; kb0 += 8) {
-                        __nv_bfloat16 cur[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            cur[j] = nxt[j];
-                            if (kb0 + 8 + j < kstages) nxt[j] = __ldg(asp + static_cast<size_t>(kb0 + 8 + j) * p.M_pad);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (kb0 + j >= kstages) break;
-                            const int s = it % G_STAGES;
-                            uint8_t* st = smem + s * SB;
-                            const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
-                            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 12));
-                            if (!ok) break;
-                            const int ps = pk % H_PK_STAGES;
-                            ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
-                            if (!ok) break;
-                            const uint4 w = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + cw * 512 + lane * 16);
-                            // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
-                            const __half2 s2 = __float2half2_rn(fminf(__bfloat162float(cur[j]), 4094.f));
-                            uint8_t* dst = st + row * 128;
-                            const int sw = row & 7;
-                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 0) ^ sw) << 4)) = int4x8_to_f16(w.x, flip, off_lo, off_hi, s2);
-                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 1) ^ sw) << 4)) = int4x8_to_f16(w.y, flip, off_lo, off_hi, s2);
-                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w.z, flip, off_lo, off_hi, s2);
-                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w.w, flip, off_lo, off_hi, s2);
-                            fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
-                            __syncwarp();
-                            if (lane == 0) {
-                                mbar_arrive_cluster(lfull);
-                                mbar_arrive(&sh->pk_empty[ps]);
-                            }
-                            ++pk;
-                            ++it;
-                        }
-                    }
-                    for (int c = 0; c < p.lora_chunks && ok; ++c, ++it) {   // low-rank stages: nothing to convert
+                    for (int i = 0; i < 4; ++i)
+                        nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : __nv_bfloat16(0.f);
+                    for (; ks < per_tile; ks += 4) {
+                        const uint32_t it = it_base + ks;
                         const int s = it % G_STAGES;
+                        uint8_t* st = smem + s * SB;
+                        const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
                         ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 12));
                         if (!ok) break;
-                        // warp 0's expect_tx arrival stands in for converter warp 0
-                        if (cw != 0 && lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->full[s]), 0));
+                        if (ks >= kstages) {   // low-rank stage: nothing to convert, but the arrival keeps this warp in step
+                            if (lane == 0) mbar_arrive_cluster(lfull);
+                            __syncwarp();
+                            continue;
+                        }
+                        __nv_bfloat16 cur[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            cur[i] = nxt[i];
+                            if (ks + 4 < kstages) nxt[i] = __ldg(asp + static_cast<size_t>(ks + 4) * p.M_pad + 16 * i);
+                        }
+                        const uint32_t pk = pk_base + ks;
+                        const int ps = pk % H_PK_STAGES;
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
+                        if (!ok) break;
+                        uint4 w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + (g2 * 64 + 16 * i) * 32 + lane * 16);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
+                            const __half2 s2 = __float2half2_rn(fminf(__bfloat162float(cur[i]), 4094.f));
+                            const int row = r0 + 16 * i;
+                            uint8_t* dst = st + row * 128;
+                            const int sw = row & 7;
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 0) ^ sw) << 4)) = int4x8_to_f16(w[i].x, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 1) ^ sw) << 4)) = int4x8_to_f16(w[i].y, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w[i].z, flip, off_lo, off_hi, s2);
+                            *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w[i].w, flip, off_lo, off_hi, s2);
+                        }
+                        fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
                         __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive_cluster(lfull);
+                            mbar_arrive(&sh->pk_empty[ps]);
+                        }
                     }
+                    it_base += per_tile;
+                    pk_base += kstages;
                 }
             } else {
                 for (int ti = 0; ti < tr.count && ok; ++ti) {
@@ -417,14 +428,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         const bool lowrank = ks >= kstages;
                         const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
                         if (warp == 0) {
-                            if (lowrank) {
-                                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 10));
-                                if (!ok) break;
-                                if (elect_one()) {
-                                    mbar_arrive_expect_tx_cluster(lfull, H_A_BYTES);
-                                    tma_load_2d_pair(st, &tm_la, lfull, (ks - kstages) * 32, m0);
-                                }
-                            } else {
+                            // Only the packed codes: this warp runs ahead of the operand ring by the depth of the packed
+                            // ring, so it must not wait on the ring's barriers (a parity wait two phases early passes).
+                            if (!lowrank) {
                                 const int ps = pk % H_PK_STAGES;
                                 ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->pk_empty[ps], ((pk / H_PK_STAGES) & 1) ^ 1, sh, p.status, 14));
                                 if (!ok) break;
@@ -438,8 +444,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 11));
                             if (!ok) break;
                             if (elect_one()) {
-                                mbar_arrive_expect_tx_cluster(lfull, H_B_BYTES);
-                                tma_load_2d_pair(st + H_A_BYTES, lowrank ? &tm_lu : &tm_b, lfull, lowrank ? (ks - kstages) * 32 : ks * 64, nb0);
+                                if (lowrank) {   // both fp32 tiles of the low-rank stage
+                                    mbar_arrive_expect_tx_cluster(lfull, H_A_BYTES + H_B_BYTES);
+                                    tma_load_2d_pair(st, &tm_la, lfull, (ks - kstages) * 32, m0);
+                                    tma_load_2d_pair(st + H_A_BYTES, &tm_lu, lfull, (ks - kstages) * 32, nb0);
+                                } else {
+                                    mbar_arrive_expect_tx_cluster(lfull, H_B_BYTES);
+                                    tma_load_2d_pair(st + H_A_BYTES, &tm_b, lfull, ks * 64, nb0);
+                                }
                             }
                         }
                         __syncwarp();
