@@ -50,3 +50,71 @@ def test_two_gloo_ranks_reproduce_single_rank():
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret["equal"] is True
     assert ret["tmax"] == 2.0
+
+
+# ------------------------------------------------------------------------------------------------ N-split variant
+def test_column_shards_partition_columns():
+    from nunchaku_b200.distributed import column_shard
+
+    for total in (128, 384, 3072, 21504, 2304):
+        for world in (1, 2, 3, 4, 8):
+            spans = [column_shard(total, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == total
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c and a % 128 == 0 and b % 128 == 0
+    import pytest
+
+    with pytest.raises(ValueError):
+        column_shard(200, 2, 0)
+
+
+def test_column_shard_of_packed_parameters_is_the_logical_slice():
+    """Slicing the reference-packed tensors by byte range gives the packed form of the logical column slice."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as H
+    from oracle import layouts as L
+    from oracle import svdq_ref as R
+    from nunchaku_b200.distributed import column_shard, shard_linear_columns
+
+    K, N = 256, 640
+    for fp4 in (True, False):
+        x = R.make_activations(300, K, seed=3)
+        lin = R.make_linear(K, N, 32, fp4=fp4, x_absmax=x.float().abs().amax(0), seed=4, wcscales=fp4)
+        full = H.to_module(lin, "cpu")
+        for world in (2, 5):
+            for rank in range(world):
+                n0, n1 = column_shard(N, world, rank)
+                sh = shard_linear_columns(full, world, rank)
+                assert torch.equal(L.ref_unpack_wgt_codes(sh.qweight.view(torch.uint8), K), lin.wcodes[n0:n1])
+                assert torch.equal(L.ref_unpack_lora_up(sh.proj_up), lin.lora_up[n0:n1])
+                assert torch.equal(L.ref_unpack_vector(sh.bias), lin.bias[n0:n1])
+                if fp4:
+                    assert torch.equal(L.ref_unpack_wmscales(sh.wscales.view(torch.uint8)), lin.wscales[:, n0:n1])
+                    assert torch.equal(L.ref_unpack_vector(sh.wcscales), lin.wcscales[n0:n1])
+                    assert torch.equal(sh.wtscale, full.wtscale)
+                else:
+                    assert torch.equal(L.ref_unpack_wscales(sh.wscales), lin.wscales[:, n0:n1])
+                assert torch.equal(sh.proj_down, full.proj_down) and torch.equal(sh.smooth_factor, full.smooth_factor)
+
+
+def _col_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    from nunchaku_b200.distributed import column_shard, gather_columns
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok = True
+    for N in (512, 384):   # even and ragged split
+        full = torch.arange(37 * N, dtype=torch.float32).view(37, N)
+        n0, n1 = column_shard(N, world, rank)
+        ok = ok and torch.equal(gather_columns(full[:, n0:n1].contiguous(), N), full)
+    ret[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_gather_columns():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_col_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret[0] is True and ret[1] is True
