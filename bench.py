@@ -35,7 +35,7 @@ FLOP_STEP = FLOP_GEMM                                   # the metric counts GEMM
 QUANT_BYTES = 2 * M * K + M * K // 2 + M * K // 16 + 4 * M * R + 2 * K * R + 2 * K
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size gemm_nvfp4_kernel launch (48.7 MB + 144.6 MB)
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size gemm_w4a4_kernel (NVFP4) launch (48.7 MB + 144.6 MB)
 GEMM_DRAM_TRAFFIC = 48716544 + 144581632
 
 
@@ -314,7 +314,7 @@ def main():
             "sharding": "rows (M) per rank, no data-path collective",
         },
         "roofline": {
-            "kernel": "gemm_nvfp4_kernel", "bound": "tensor", "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
+            "kernel": "gemm_w4a4_kernel<NVFP4>", "bound": "tensor", "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
             "frac": gemm_tflops / fp4_peak, "traffic": GEMM_DRAM_TRAFFIC if (M, K, N) == (4608, 3072, 21504) else None,
             "traffic_unit": "bytes per launch (dram read + write, one ncu capture of this workload)",
             "peak_source": "measured live: operand-resident tcgen05.mma kind::mxf4nvf4 M128 N256 K64 loop on all SMs "

@@ -196,6 +196,23 @@ typedef struct svdq_ln_modulate_args {
 int svdq_layernorm_modulate(const svdq_ln_modulate_args* args, void* stream);
 
 /*
+ * ReLU linear attention of SANA on the bf16 output of the fused QKV projection: per (batch, head)
+ * vk = [V | 1]^T relu(K) over the tokens (fp32), then out = (relu(Q) vk^T)[:32] / ((relu(Q) vk^T)[32] + eps).
+ * What the reference does in the QKV GEMM's epilogue plus a second kernel: EpilogueLiteLA and vk_mul_q_kernel,
+ * src/kernels/zgemm/epilogues.cuh:552-761, launched from gemm_w4a4_launch_impl.cuh:311-345,426-448 and called by
+ * SanaLinearAttention::forward (src/SanaModel.cpp:25-106).  Column order of qkv as there: Q of all heads in [0, D),
+ * then 64 columns [K_h | V_h] per head, D = heads * 32.  Deterministic (no atomics, nothing to zero).
+ */
+typedef struct svdq_litela_args {
+    const void* qkv;          /* bf16 [batches, tokens, 3 * heads * 32] */
+    void* out;                /* bf16 [batches, tokens, heads * 32] */
+    float* vk;                /* fp32 [batches, heads, 33, 32] or NULL: the reference's out_vk */
+    int32_t batches, tokens, heads;
+    float eps;                /* 1e-6 in the reference */
+} svdq_litela_args;
+int svdq_litela(const svdq_litela_args* args, void* stream);
+
+/*
  * Device-side status word of the current device: 0, or the SVDQ_ERR_TIMEOUT code a
  * kernel recorded when one of its bounded waits ran out.  Synchronises the device.
  * `detail` (may be NULL) receives a kernel-specific location code.  Reading clears it.

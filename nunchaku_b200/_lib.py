@@ -145,6 +145,18 @@ class LnModulateArgs(Structure):
     ]
 
 
+class LiteLAArgs(Structure):
+    _fields_ = [
+        ("qkv", c_void_p),
+        ("out", c_void_p),
+        ("vk", c_void_p),
+        ("batches", c_int32),
+        ("tokens", c_int32),
+        ("heads", c_int32),
+        ("eps", c_float),
+    ]
+
+
 # every symbol include/svdq_b200.h declares: (restype, argtypes)
 EXPORTS = {
     "svdq_quantize_w4a4_act_fuse_lora": (c_int32, [POINTER(QuantizeArgs), c_void_p]),
@@ -156,6 +168,7 @@ EXPORTS = {
     "svdq_w4a4_relayout_act": (c_int32, [POINTER(RelayoutArgs), c_void_p]),
     "svdq_qk_norm_rope": (c_int32, [POINTER(NormRopeArgs), c_void_p]),
     "svdq_layernorm_modulate": (c_int32, [POINTER(LnModulateArgs), c_void_p]),
+    "svdq_litela": (c_int32, [POINTER(LiteLAArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),
     "svdq_version": (c_int32, []),

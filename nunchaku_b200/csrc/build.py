@@ -11,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["api.cu", "quantize.cu", "prepare.cu", "gemm_w4a4.cu", "norm_rope.cu", "peak_probe.cu"]
+SOURCES = ["api.cu", "quantize.cu", "prepare.cu", "gemm_w4a4.cu", "norm_rope.cu", "litela.cu", "peak_probe.cu"]
 LIB = os.path.join(PKG, "libsvdq_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [

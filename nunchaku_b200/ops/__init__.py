@@ -1,5 +1,5 @@
-from .fused import fused_gelu_mlp, layernorm_modulate, qk_norm_rope
+from .fused import fused_gelu_mlp, layernorm_modulate, litela_attention, qk_norm_rope
 from .gemm import svdq_gemm_w4a4_cuda
 from .quantize import svdq_quantize_w4a4_act_fuse_lora_cuda
 
-__all__ = ["svdq_quantize_w4a4_act_fuse_lora_cuda", "svdq_gemm_w4a4_cuda", "fused_gelu_mlp", "qk_norm_rope", "layernorm_modulate"]
+__all__ = ["svdq_quantize_w4a4_act_fuse_lora_cuda", "svdq_gemm_w4a4_cuda", "fused_gelu_mlp", "qk_norm_rope", "layernorm_modulate", "litela_attention"]

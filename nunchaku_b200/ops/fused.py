@@ -81,3 +81,27 @@ def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().svdq_layernorm_modulate(ctypes.byref(args), stream_ptr(x.device)))
     return out
+
+
+def litela_attention(qkv: torch.Tensor, heads: int, eps: float = 1e-6, return_vk: bool = False):
+    """ReLU linear attention of SANA on the bf16 output of the fused QKV projection (what ``EpilogueLiteLA`` in the QKV
+    GEMM plus ``linearattn_vk_mul_q`` compute for ``SanaLinearAttention::forward``, ``src/SanaModel.cpp:25-106``).
+
+    qkv: bf16 [B, S, 3*heads*32], columns [Q of all heads | (K_h, V_h) 64 per head].  Returns bf16 [B, S, heads*32]
+    (and the fp32 ``vk`` [B, heads, 33, 32] when asked)."""
+    import ctypes
+
+    from .. import _lib
+    from ..utils import ptr, require_cuda_contiguous, stream_ptr
+
+    require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
+    if qkv.dim() != 3 or qkv.shape[-1] != 3 * heads * 32:
+        raise ValueError("litela_attention: qkv must be [B, S, 3*heads*32]")
+    B, S, _ = qkv.shape
+    out = torch.empty(B, S, heads * 32, dtype=torch.bfloat16, device=qkv.device)
+    vk = torch.empty(B, heads, 33, 32, dtype=torch.float32, device=qkv.device) if return_vk else None
+    args = _lib.LiteLAArgs(qkv=ptr(qkv), out=ptr(out), vk=ptr(vk) if vk is not None else None, batches=B, tokens=S,
+                           heads=heads, eps=eps)
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(qkv.device)))
+    return (out, vk) if return_vk else out

@@ -179,13 +179,15 @@ def svdq_gemm_w4a4_cuda(
     ``lora_act_out``, ``smooth_factor``) select the GELU + next-layer requantisation
     epilogue (gemm_w4a4_launch_impl.cuh:282-309); ``out`` the plain one with optional
     SiLU.  The attention epilogues (``norm_q``/``rotary_emb``/``out_q``..., ``out_vk``/
-    ``out_linearattn``) are not built and raise NotImplementedError.  ``act_layout`` /
+    ``out_linearattn``) raise NotImplementedError: both exist as kernels that run on the GEMM's bf16 output
+    (``qk_norm_rope``, ``litela_attention``).  ``act_layout`` /
     ``out_layout`` give the memory order of the incoming / produced activation tensors.
     """
     if any(t is not None for t in (norm_q, norm_k, rotary_emb, out_q, out_k, out_v)):
         raise NotImplementedError("svdq_b200: the RMSNorm+RoPE / packed-QKV epilogue is not built")
     if out_vk is not None or out_linearattn is not None:
-        raise NotImplementedError("svdq_b200: the linear-attention epilogue is not built")
+        raise NotImplementedError("svdq_b200: linear attention is not a GEMM epilogue here: write `out` and call "
+                                  "nunchaku_b200.ops.litela_attention on it")
     if poolout is not None:
         raise NotImplementedError("poolout is unused by the reference launcher as well")
     if ascales is None or wscales is None:

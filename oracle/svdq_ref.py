@@ -346,3 +346,22 @@ def ref_layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Te
     var = ((xf - mean) ** 2).mean(-1, keepdim=True)
     n = ((xf - mean) * torch.rsqrt(var + eps)).to(BF16).to(F32)
     return (n * (1.0 + scale.to(F32)[:, None, :]) + shift.to(F32)[:, None, :]).to(BF16)
+
+
+def ref_litela(qkv: torch.Tensor, heads: int, eps: float = 1e-6):
+    """ReLU linear attention on a fused QKV output [B, S, 3*heads*32] (bf16), columns [Q | (K_h, V_h) per head]
+    (EpilogueLiteLA + vk_mul_q_kernel, src/kernels/zgemm/epilogues.cuh:552-761):
+    vk[b,h,r,c] = sum_t V[t,r] relu(K[t,c]) (r < 32), vk[b,h,32,c] = sum_t relu(K[t,c]);
+    o = relu(Q) @ vk^T; out = bf16(o[:32] / (o[32] + eps)).  Sums in float64 (the order of the fp32 sums on the GPU is
+    an implementation choice); returns (out bf16 [B, S, heads*32], vk float32 [B, heads, 33, 32])."""
+    B, S, C = qkv.shape
+    D = heads * 32
+    assert C == 3 * D
+    q = qkv[..., :D].double().clamp_min(0).view(B, S, heads, 32)
+    kv = qkv[..., D:].double().view(B, S, heads, 64)
+    k, v = kv[..., :32].clamp_min(0), kv[..., 32:]
+    v1 = torch.cat([v, torch.ones(B, S, heads, 1, dtype=torch.float64)], dim=-1)       # [B,S,H,33]
+    vk = torch.einsum("bshr,bshc->bhrc", v1, k)                                         # [B,H,33,32]
+    o = torch.einsum("bshc,bhrc->bshr", q, vk.float().double())                         # [B,S,H,33]
+    out = (o[..., :32].float() / (o[..., 32:].float() + eps)).to(torch.bfloat16)
+    return out.reshape(B, S, D), vk.float()

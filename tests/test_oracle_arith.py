@@ -74,3 +74,32 @@ def test_requantize_unsigned_shift():
     deq = R.dequant_act(q)
     want = (act.to(torch.bfloat16).float() + R.INT4_UNSIGNED_SHIFT) / nxt.smooth.float()
     assert R.rel_l2(deq, want) < 0.08
+
+
+def test_ref_litela_against_explicit_loops():
+    """The vectorised linear-attention restatement equals the formula written out token by token
+    (epilogues.cuh:599-656 for vk, :730-756 for the product with q and the division)."""
+    import torch
+
+    from oracle import svdq_ref as R
+
+    g = torch.Generator().manual_seed(0)
+    B, S, heads = 2, 5, 2
+    D = heads * 32
+    qkv = torch.randn(B, S, 3 * D, generator=g).to(torch.bfloat16)
+    out, vk = R.ref_litela(qkv, heads)
+    x = qkv.double()
+    for b in range(B):
+        for h in range(heads):
+            ref_vk = torch.zeros(33, 32, dtype=torch.float64)
+            for t in range(S):
+                k = x[b, t, D + 64 * h: D + 64 * h + 32].clamp_min(0)
+                v = x[b, t, D + 64 * h + 32: D + 64 * h + 64]
+                ref_vk[:32] += v[:, None] * k[None, :]
+                ref_vk[32] += k
+            assert torch.allclose(vk[b, h].double(), ref_vk, rtol=1e-6, atol=1e-6)
+            for t in range(S):
+                q = x[b, t, 32 * h: 32 * h + 32].clamp_min(0)
+                o = ref_vk.float().double() @ q
+                exp = (o[:32].float() / (o[32].float() + 1e-6)).to(torch.bfloat16)
+                assert torch.equal(out[b, t, 32 * h: 32 * h + 32], exp)

@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+from nunchaku_b200 import _lib
 from oracle import svdq_ref as R
 
 pytestmark = pytest.mark.gpu
@@ -44,3 +45,23 @@ def test_layernorm_modulate_matches_oracle(B, S, C):
     modg = mod.cuda()
     got = layernorm_modulate(x.cuda(), modg[:, C:2 * C], modg[:, :C]).cpu()
     _bf16_close(got, exp, ulps=1.0, frac=0.995)
+
+
+@pytest.mark.parametrize("B,S,heads", [(1, 37, 2), (2, 1024, 72), (3, 300, 5)])
+def test_litela_matches_oracle(B, S, heads):
+    """ReLU linear attention: vk within fp32 summation error of the float64 oracle, the bf16 output within one bf16
+    rounding of it (relative L2 <= 3e-3, no element off by more than 2 ulp of bf16 = 2^-7 relative)."""
+    from nunchaku_b200.ops import litela_attention
+
+    g = torch.Generator().manual_seed(B * 1000 + S)
+    qkv = torch.randn(B, S, 3 * heads * 32, generator=g).to(torch.bfloat16)
+    exp, exp_vk = R.ref_litela(qkv, heads)
+    got, vk = litela_attention(qkv.cuda(), heads, return_vk=True)
+    got2 = litela_attention(qkv.cuda(), heads)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert torch.equal(got, got2)                                   # deterministic, with and without the vk output
+    assert R.rel_l2(vk.cpu(), exp_vk) <= 1e-5
+    g32, e32 = got.float().cpu(), exp.float()
+    assert R.rel_l2(g32, e32) <= 3e-3
+    assert ((g32 - e32).abs() <= 2.0 ** -7 * e32.abs() + 1e-6).all()
