@@ -5,8 +5,8 @@ its 4-bit quantisation fused into the GEMM epilogue, then fc2 (4 x hidden -> hid
 
 Weights are random packed W4A4 parameters (``SVDQW4A4Linear.randomize_``-style: random codes, constant group scales,
 N(0, 0.02) low-rank factors); activations N(0, 1) bf16.  Prints one JSON line: the chain's time (CUDA events over
-``--steps`` back-to-back calls) and each kernel's own time, all in microseconds.  ``--only requant`` launches just the
-requantising fc1 GEMM (for a profiler capture of that kernel alone).
+``--steps`` back-to-back calls) and each kernel's own time, all in microseconds.  ``--only requant`` / ``--only plain``
+launch just the requantising / the plain fc1 GEMM (for a profiler capture of that kernel alone).
 """
 from __future__ import annotations
 
@@ -58,7 +58,7 @@ def main() -> None:
     ap.add_argument("--rank", type=int, default=32)
     ap.add_argument("--precision", default="nvfp4", choices=["nvfp4", "int4"])
     ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--only", default=None, choices=[None, "requant"])
+    ap.add_argument("--only", default=None, choices=[None, "requant", "plain"])
     args = ap.parse_args()
     M, H, fp4 = args.tokens, args.hidden, args.precision == "nvfp4"
     fc1 = random_linear(H, 4 * H, args.rank, args.precision, 1)
@@ -88,6 +88,14 @@ def main() -> None:
 
     out1 = torch.empty(M, 4 * H, dtype=torch.bfloat16, device="cuda")
     out2 = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    if args.only == "plain":
+        us = timed(lambda: fc1.forward_quant(q, s, la, out1), args.steps)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0, 0)
+        fl = 2.0 * M * H * 4 * H + 2.0 * M * 4 * H * args.rank
+        print(json.dumps({"fc1_plain_gemm_us": round(us, 1), "tflops": round(fl / us / 1e6, 1), "tokens": M, "hidden": H,
+                          "rank": args.rank, "precision": args.precision}))
+        return
     res = {
         "mlp_chain_us": timed(lambda: fused_gelu_mlp(x, fc1, fc2), args.steps),
         "fc1_quantize_us": timed(lambda: fc1.quantize(x.view(M, H)), args.steps),
