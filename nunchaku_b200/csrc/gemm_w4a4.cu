@@ -31,8 +31,8 @@
 //               thread's own row chunk is group-quantised in registers
 //   warps 9..12 (NVFP4 requantising variants up to rank 32) a second epilogue set; the two warps of a lane quadrant
 //               take alternate 64-column chunks
-// INT4: warp 0 brings the packed activation codes (own ring), warp 6 the fp16 weights, warps 7..14 convert codes to
-// fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
+// INT4: warp 6 brings the fp16 weights, warps 7..14 read the packed activation codes from global memory and convert
+// them to fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
 // TMEM per CTA: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
 // plus two 48-column scale-factor buffers (16 for A, 32 for B) = 480 of 512 columns.
 // Every loop that issues tcgen05 / TMA instructions is run by a whole warp with one elected lane issuing, so
@@ -96,6 +96,7 @@ struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
     const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
     const __nv_bfloat16* ascales_i4;   // INT4: activation group scales [K/64][M_pad]
+    const uint8_t* act_i4;             // INT4: packed activation codes [M_pad][K/2], read directly by the converter warps
     int act_unsigned;                  // INT4: activation codes are u4
     const float* col_scale;   // [N]
     const float* col_bias;    // [N]
@@ -337,37 +338,44 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (I4 && (warp == 0 || warp >= 6)) {
         // ------------------------------------------------------------------ INT4 producers and converter warps
-        // warp 0: packed activation codes (128 rows x 32 bytes per k-block, own ring, local barrier); warp 6: this CTA's
-        // 96 rows of the fp16 weights, or both fp32 tiles (lora_act, LoRA-up) of a low-rank stage;
-        // warps 7..14: codes -> fp16(code * group scale) straight into the 128B-swizzled K-major tile the MMA reads.
+        // warp 0: idle; warp 6: this CTA's 96 rows of the fp16 weights, or both fp32 tiles (lora_act, LoRA-up) of a
+        // low-rank stage; warps 7..14: packed codes from global memory (prefetched into registers one turn ahead) ->
+        // fp16(code * group scale) straight into the 128B-swizzled K-major tile the MMA reads.
         if constexpr (I4) {
             const int cw = warp - 7;
             const int hh = lane & 1;
             const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
             const __half2 off_lo = __float2half2_rn(p.act_unsigned ? 1024.f : 1032.f);
             const __half2 off_hi = __float2half2_rn(p.act_unsigned ? -64.f : -72.f);
-            uint32_t it = 0, pk = 0;
+            uint32_t it = 0;
             bool ok = true;
             if (warp >= 7) {
                 // converter warps.  Every shared-memory and barrier operation of a SIMT warp queues behind the tensor core's
                 // operand reads, so the fixed chain of a stage's hand-shake (two barrier waits, load, stores, proxy fence,
                 // arrivals) costs several hundred cycles however little is converted.  The eight warps therefore form four
                 // groups that take every fourth stage each, two warps per stage with 64 rows apiece: four stages are in
-                // conversion at once.  A lane converts half a row (32 codes) of rows r0, r0 + 16, r0 + 32, r0 + 48: the packed
-                // loads of a warp cover 512 contiguous bytes and its swizzled 16-byte stores are free of bank conflicts.
-                // The group scales of the next stage the warp will convert are fetched while it converts this one.
+                // conversion at once.  A lane converts half a row (32 codes) of rows r0, r0 + 16, r0 + 32, r0 + 48: its 16-byte
+                // global loads fill whole 32-byte sectors and its swizzled 16-byte stores are free of bank conflicts.
+                // The packed codes and group scales of the next stage the warp will convert are fetched while it converts
+                // this one, so no shared-memory load and only one barrier wait are left in the chain.
                 const int grp = cw >> 1, g2 = cw & 1;
                 const int r0 = g2 * 64 + (lane >> 1);
-                uint32_t it_base = 0, pk_base = 0;
+                uint32_t it_base = 0;
                 for (int ti = 0; ti < tr.count && ok; ++ti) {
                     int m0, n0;
                     tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
                     const __nv_bfloat16* asp = p.ascales_i4 + m0 + r0;
                     int ks = static_cast<int>((static_cast<uint32_t>(grp) - it_base) & 3u);   // first stage of this tile that is ours
+                    // the lane's 16 bytes (32 codes) of row r0 + 16 i in k-block ks sit at apk + 16 i * pitch + 32 ks
+                    const size_t pitch = static_cast<size_t>(p.K) >> 1;
+                    const uint8_t* apk = p.act_i4 + static_cast<size_t>(m0 + r0) * pitch + hh * 16;
                     __nv_bfloat16 nxt[4];
+                    uint4 wnxt[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int i = 0; i < 4; ++i) {
                         nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : __nv_bfloat16(0.f);
+                        wnxt[i] = ks < kstages ? __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * ks)) : make_uint4(0, 0, 0, 0);
+                    }
                     for (; ks < per_tile; ks += 4) {
                         const uint32_t it = it_base + ks;
                         const int s = it % G_STAGES;
@@ -381,19 +389,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             continue;
                         }
                         __nv_bfloat16 cur[4];
+                        uint4 w[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             cur[i] = nxt[i];
-                            if (ks + 4 < kstages) nxt[i] = __ldg(asp + static_cast<size_t>(ks + 4) * p.M_pad + 16 * i);
+                            w[i] = wnxt[i];
+                            if (ks + 4 < kstages) {
+                                nxt[i] = __ldg(asp + static_cast<size_t>(ks + 4) * p.M_pad + 16 * i);
+                                wnxt[i] = __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * (ks + 4)));
+                            }
                         }
-                        const uint32_t pk = pk_base + ks;
-                        const int ps = pk % H_PK_STAGES;
-                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->pk_full[ps], (pk / H_PK_STAGES) & 1, sh, p.status, 13));
-                        if (!ok) break;
-                        uint4 w[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            w[i] = *reinterpret_cast<const uint4*>(pk_smem + ps * H_PK_BYTES + (g2 * 64 + 16 * i) * 32 + lane * 16);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
@@ -406,15 +411,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             *reinterpret_cast<uint4*>(dst + (((hh * 4 + 2) ^ sw) << 4)) = int4x8_to_f16(w[i].z, flip, off_lo, off_hi, s2);
                             *reinterpret_cast<uint4*>(dst + (((hh * 4 + 3) ^ sw) << 4)) = int4x8_to_f16(w[i].w, flip, off_lo, off_hi, s2);
                         }
-                        fence_proxy_async_smem();   // the tile is read by the tensor core, the packed slot refilled by TMA
+                        fence_proxy_async_smem();   // the tile is read by the tensor core
                         __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive_cluster(lfull);
-                            mbar_arrive(&sh->pk_empty[ps]);
-                        }
+                        if (lane == 0) mbar_arrive_cluster(lfull);
                     }
                     it_base += per_tile;
-                    pk_base += kstages;
                 }
             } else {
                 for (int ti = 0; ti < tr.count && ok; ++ti) {
@@ -428,18 +429,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         const bool lowrank = ks >= kstages;
                         const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
                         if (warp == 0) {
-                            // Only the packed codes: this warp runs ahead of the operand ring by the depth of the packed
-                            // ring, so it must not wait on the ring's barriers (a parity wait two phases early passes).
-                            if (!lowrank) {
-                                const int ps = pk % H_PK_STAGES;
-                                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->pk_empty[ps], ((pk / H_PK_STAGES) & 1) ^ 1, sh, p.status, 14));
-                                if (!ok) break;
-                                if (elect_one()) {
-                                    mbar_arrive_expect_tx(&sh->pk_full[ps], H_PK_BYTES);
-                                    tma_load_2d(pk_smem + ps * H_PK_BYTES, &tm_a, &sh->pk_full[ps], ks * 32, m0);
-                                }
-                                ++pk;
-                            }
+                            break;   // nothing to bring: the converter warps read the packed codes from global memory themselves
                         } else {
                             ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], eparity, sh, p.status, 11));
                             if (!ok) break;
@@ -1070,6 +1060,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 
     GemmParams p = {};
     p.ascales_i4 = static_cast<const __nv_bfloat16*>(a->ascales);
+    p.act_i4 = static_cast<const uint8_t*>(a->act);
     p.act_unsigned = a->act_unsigned;
     p.col_scale = a->w.col_scale;
     p.col_bias = a->w.col_bias;
