@@ -60,6 +60,10 @@ typedef struct svdq_quantize_args {
     int32_t fp4;           /* 1: NVFP4 group 16, 0: INT4 group 64                             */
     int32_t fuse_glu;      /* 1: input holds (value, gate) pairs, quantise value*silu(gate)   */
     int32_t layout;        /* SVDQ_LAYOUT_* of codes / scales / lora_act                      */
+    int32_t K_in;          /* 0, or the input's real channel count when K is its padding to 128:
+                              the input is [M, K_in] ([M, 2 K_in] when fuse_glu), columns [K_in, K) read as
+                              zero (the reference's in_features / in_features_pad, src/Linear.cpp:92,452);
+                              K - 128 < K_in <= K, multiple of 8                                  */
 } svdq_quantize_args;
 
 int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* stream);
@@ -123,6 +127,9 @@ typedef struct svdq_gemm_args {
     int32_t act_layout;       /* layout of act / ascales / lora_act_in                       */
     int32_t out_layout;       /* layout of qout / oscales / lora_act_out                     */
     int32_t next_fp4;         /* precision of the requantised output                         */
+    int32_t N_out;            /* 0, or the real column count of `out` when N is its padding to 128: out is
+                                 [M, N_out] and columns [N_out, N) are dropped (the reference's actualN,
+                                 gemm_base.cuh:544-548); N - 128 < N_out <= N, multiple of 8      */
 } svdq_gemm_args;
 
 int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes);

@@ -42,6 +42,7 @@ class QuantizeArgs(Structure):
         ("fp4", c_int32),
         ("fuse_glu", c_int32),
         ("layout", c_int32),
+        ("K_in", c_int32),
     ]
 
 
@@ -97,6 +98,7 @@ class GemmArgs(Structure):
         ("act_layout", c_int32),
         ("out_layout", c_int32),
         ("next_fp4", c_int32),
+        ("N_out", c_int32),
     ]
 
 

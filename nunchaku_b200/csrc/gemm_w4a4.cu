@@ -878,6 +878,12 @@ static void plan_nvfp4(const svdq_gemm_args* a, int sms, NvfpPlan* pl) {
     pl->workspace = pl->requant ? static_cast<size_t>(2 * pl->npairs) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
 }
 
+// real column count of `out`: the store's tensor map ends there, so the hardware drops the padded columns
+static inline int n_out(const svdq_gemm_args* a) { return a->N_out ? a->N_out : a->N; }
+static inline bool n_out_ok(const svdq_gemm_args* a) {
+    return n_out(a) <= a->N && n_out(a) > a->N - 128 && n_out(a) % 8 == 0;
+}
+
 int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
     int dev = 0, sms = 0;
     SVDQ_CUDA(cudaGetDevice(&dev));
@@ -925,6 +931,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
                                                          "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(!a->act_unsigned, "gemm(nvfp4): act_unsigned is INT4 only (gemm_w4a4_launch_impl.cuh:127)");
     SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(n_out_ok(a), "gemm: N_out (%d) must be a multiple of 8 with N - 128 < N_out <= N (%d)", a->N_out, a->N);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
     if (requant) {
         SVDQ_CHECK_ARG(a->oscales && a->lora_act_out && a->next_smooth && a->next_lora_down,
@@ -988,7 +995,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_lu = tm_b;
     }
     if (a->out) {
-        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_a;
@@ -1048,6 +1055,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                         "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(n_out_ok(a), "gemm: N_out (%d) must be a multiple of 8 with N - 128 < N_out <= N (%d)", a->N_out, a->N);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
 
     int dev = 0, sms = 0;
@@ -1101,7 +1109,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_lu = tm_b;
     }
     if (a->out) {
-        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a->N, a->M, static_cast<uint64_t>(a->N) * 2, 64, 32))
+        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_b;

@@ -10,8 +10,8 @@ gates the (value, gate) pairs: ``fuse_glu``).  The depthwise 3 x 3 convolution, 
 ``kv_linear`` of the caption and the modulation are plain bf16 torch ops, as they are outside the W4A4 path.
 
 Padding as in the reference (``src/Linear.cpp:92-93``, ``SanaModel.cpp:15``): feature counts are rounded up to 128 for
-the 4-bit tensors (2240 -> 2304, 2 x 5600 -> 2 x 5632); the harness pads activations with zero columns in front of a
-projection and drops the padded output columns after it.  Weights are random packed W4A4 parameters: this module is for
+the 4-bit tensors (2240 -> 2304, 2 x 5600 -> 2 x 5632); activations keep their real width: the quantiser reads the missing
+columns as zeros and the GEMM does not store the padded output columns.  Weights are random packed W4A4 parameters: this module is for
 step timing and for checking that the call sequence runs; there are no checkpoints offline.
 """
 from __future__ import annotations
@@ -50,7 +50,8 @@ def _random_w4a4(in_f: int, out_f: int, rank: int, precision: str, bias: bool, g
 
 
 class PaddedW4A4(nn.Module):
-    """A W4A4 linear whose logical feature counts are not multiples of 128: zero columns in, padded columns dropped."""
+    """A W4A4 linear whose logical feature counts are not multiples of 128: the quantiser reads the missing input columns
+    as zeros and the GEMM's store drops the padded output columns (``K_in`` / ``N_out`` of the C ABI)."""
 
     def __init__(self, in_f, out_f, rank, precision, bias, g, device, keep_out_pad: bool = False):
         super().__init__()
@@ -61,19 +62,14 @@ class PaddedW4A4(nn.Module):
         """x: [B, S, in_f] (or already padded; [B, S, 2*in_pad] of (value, gate) pairs with fuse_glu)."""
         lin = self.lin
         B, S, C = x.shape
-        want = lin.in_features * (2 if fuse_glu else 1)
-        if C != want:
-            x = F.pad(x, (0, want - C))
         q, s, la = svdq_quantize_w4a4_act_fuse_lora_cuda(
-            x.reshape(B * S, want), lora_down=lin.proj_down, smooth=lin.smooth_factor, fp4=lin.precision == "nvfp4", fuse_glu=fuse_glu)
-        out = torch.empty(B * S, lin.out_features, dtype=x.dtype, device=x.device)
+            x.reshape(B * S, C), lora_down=lin.proj_down, smooth=lin.smooth_factor, fp4=lin.precision == "nvfp4", fuse_glu=fuse_glu)
+        n_out = lin.out_features if self.keep_out_pad else self.out_f
+        out = torch.empty(B * S, n_out, dtype=x.dtype, device=x.device)
         svdq_gemm_w4a4_cuda(act=q, wgt=lin.qweight, out=out, ascales=s, wscales=lin.wscales, lora_act_in=la, lora_up=lin.proj_up,
                             bias=lin.bias, fp4=lin.precision == "nvfp4", alpha=lin.wtscale, wcscales=lin.wcscales,
                             fuse_silu=fuse_silu)
-        out = out.view(B, S, lin.out_features)
-        if self.keep_out_pad or lin.out_features == self.out_f:
-            return out
-        return out[..., : self.out_f]
+        return out.view(B, S, n_out)
 
 
 class SanaLinearAttention(nn.Module):

@@ -236,6 +236,8 @@ def svdq_gemm_w4a4_cuda(
         M=M, M_pad=M_pad, N=N, K=K, R=R, R_next=lora_down.shape[1] if requant else 0,
         fp4=int(fp4), act_unsigned=int(act_unsigned), activation=activation,
         act_layout=act_layout, out_layout=out_layout, next_fp4=int(next_fp4),
+        # `out` narrower than the padded weights (the reference's actualN): the padded columns are dropped by the store
+        N_out=out.shape[-1] if out is not None and out.shape[-1] != N else 0,
     )
     lib = _lib.load()
     ws = None

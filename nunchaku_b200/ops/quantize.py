@@ -41,6 +41,11 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
     batch_size, channels = input.shape
     if fuse_glu:
         channels //= 2
+    # an input narrower than the (128-padded) parameters is read as if padded with zero columns
+    # (in_features vs in_features_pad, src/Linear.cpp:92,452)
+    k_in = 0
+    if smooth.numel() != channels and 0 < smooth.numel() - channels < 128:
+        k_in, channels = channels, smooth.numel()
     rank = lora_down.shape[1]
     batch_size_pad = ceil_divide(batch_size, pad_size) * pad_size
     dev = input.device
@@ -70,7 +75,7 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
         smooth=ptr(smooth), lora_down=ptr(lora_down),
         M=batch_size, M_pad=batch_size_pad, K=channels, R=rank,
         fp4=int(fp4), fuse_glu=int(fuse_glu),
-        layout=default_act_layout() if layout is None else layout,
+        layout=default_act_layout() if layout is None else layout, K_in=k_in,
     )
     with torch.cuda.device(dev):
         _lib.check(_lib.load().svdq_quantize_w4a4_act_fuse_lora(ctypes.byref(args), stream_ptr(dev)))

@@ -29,14 +29,31 @@ def test_small_sana_runs_finite_and_repeatable(precision):
     assert y1.shape == (B, Hh * Ww, 32) and torch.isfinite(y1).all() and torch.equal(y1, y2)
 
 
-def test_sana_layer_shape_int4_matches_oracle():
-    """One image of SANA at 1024 px: 1024 tokens, hidden 2240 padded to 2304 with zero columns, INT4 group 64."""
-    M, K, Kp, N = 1024, 2240, 2304, 2304
+@pytest.mark.parametrize("fp4", [False, True])
+def test_sana_layer_shape_matches_oracle(fp4):
+    """One image of SANA at 1024 px: 1024 tokens, hidden 2240 against parameters padded to 2304.  The quantiser is given
+    the unpadded input (K_in: missing columns read as zeros) and the GEMM an unpadded output (N_out: padded columns
+    dropped); both must equal what padding with zero columns and slicing gives: codes and scales bit for bit."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops import svdq_gemm_w4a4_cuda, svdq_quantize_w4a4_act_fuse_lora_cuda
+
+    M, K, Kp, N, Np = 1000, 2240, 2304, 2240, 2304
+    xs = R.make_activations(M, K, seed=7)
     x = torch.zeros(M, Kp, dtype=torch.bfloat16)
-    x[:, :K] = R.make_activations(M, K, seed=7)
+    x[:, :K] = xs
     absmax = x.float().abs().amax(0).clamp_min(1e-3)
-    lin = R.make_linear(Kp, N, 32, fp4=False, x_absmax=absmax, seed=8, mode="svd")
+    lin = R.make_linear(Kp, Np, 32, fp4=fp4, x_absmax=absmax, seed=8, mode="svd", wcscales=fp4)
     m = H.to_module(lin, "cuda:0")
-    y = m(x.cuda().view(1, M, Kp)).float().cpu().view(M, N)
-    q = R.ref_quantize(x, lin.smooth, lin.lora_down, fp4=False)
-    assert R.rel_l2(y, R.ref_gemm(q, lin, M=M)) <= 1e-2     # tolerance of the path: relative L2 <= 1e-2
+    q_pad = m.quantize(x.cuda())
+    q_in = svdq_quantize_w4a4_act_fuse_lora_cuda(xs.cuda(), lora_down=m.proj_down, smooth=m.smooth_factor, fp4=fp4)
+    for a, b in zip(q_pad, q_in):
+        assert a.shape == b.shape and torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    svdq_gemm_w4a4_cuda(act=q_in[0], wgt=m.qweight, out=out, ascales=q_in[1], wscales=m.wscales, lora_act_in=q_in[2],
+                        lora_up=m.proj_up, bias=m.bias, fp4=fp4, alpha=m.wtscale, wcscales=m.wcscales)
+    full = m.forward_quant(*q_pad, torch.empty(M, Np, dtype=torch.bfloat16, device="cuda"))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert torch.equal(out, full[:, :N])
+    q = R.ref_quantize(x, lin.smooth, lin.lora_down, fp4=fp4)
+    assert R.rel_l2(out.float().cpu(), R.ref_gemm(q, lin, M=M)[:, :N]) <= 1e-2     # tolerance of the path: relative L2 <= 1e-2
