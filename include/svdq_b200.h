@@ -197,7 +197,7 @@ typedef struct svdq_ln_modulate_args {
     const void* shift;        /* bf16, same geometry */
     void* out;                /* bf16 [rows, cols] */
     int64_t rows, rows_per_batch, mod_stride;
-    int32_t cols;             /* 256, 1024, 2304 or 3072 */
+    int32_t cols;             /* 256, 1024, 2240, 2304 or 3072 */
     float eps;                /* 1e-5 = torch.nn.functional.layer_norm default */
 } svdq_ln_modulate_args;
 int svdq_layernorm_modulate(const svdq_ln_modulate_args* args, void* stream);

@@ -65,14 +65,16 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
     }
 }
 
-// C = 8 * 32 * V columns: each lane holds V chunks of 8 columns (16 bytes), chunk j at column (j*32 + lane) * 8
-template <int V>
+// C = 8 * (32 * (V - 1) + TAIL) columns: each lane holds V chunks of 8 columns (16 bytes), chunk j at column
+// (j*32 + lane) * 8; only the first TAIL lanes hold a last chunk (TAIL = 32: C = 256 V)
+template <int V, int TAIL = 32>
 __global__ void __launch_bounds__(256)
 layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
                           const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ out, long long rows,
                           long long rows_per_batch, long long mod_stride, float eps) {
-    constexpr int C = V * 256;
+    constexpr int C = (V - 1) * 256 + TAIL * 8;
     const int lane = threadIdx.x & 31;
+    const bool last = TAIL == 32 || lane < TAIL;   // this lane holds a chunk V - 1
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
     for (long long row = warp; row < rows; row += nwarps) {
@@ -81,7 +83,7 @@ layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            const uint4 w = xp[j * 32 + lane];
+            const uint4 w = (j < V - 1 || last) ? xp[j * 32 + lane] : make_uint4(0, 0, 0, 0);
             const float2 f0 = bf2(w.x), f1 = bf2(w.y), f2 = bf2(w.z), f3 = bf2(w.w);
             v[j][0] = f0.x; v[j][1] = f0.y; v[j][2] = f1.x; v[j][3] = f1.y;
             v[j][4] = f2.x; v[j][5] = f2.y; v[j][6] = f3.x; v[j][7] = f3.y;
@@ -97,7 +99,7 @@ layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float d = v[j][i] - mean;
-                var += d * d;
+                var += (j < V - 1 || last) ? d * d : 0.f;
             }
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) var += __shfl_xor_sync(0xffffffffu, var, m);
@@ -108,6 +110,7 @@ layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
         uint4* op = reinterpret_cast<uint4*>(out + row * C);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
+            if (j == V - 1 && !last) break;
             const uint4 sc = scp[j * 32 + lane], sh = shp[j * 32 + lane];
             const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
             uint32_t o[4];
@@ -169,9 +172,10 @@ extern "C" int svdq_layernorm_modulate(const svdq_ln_modulate_args* a, void* str
     switch (a->cols) {
         case 256: layernorm_modulate_kernel<1><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
         case 1024: layernorm_modulate_kernel<4><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
+        case 2240: layernorm_modulate_kernel<9, 24><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
         case 2304: layernorm_modulate_kernel<9><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
         case 3072: layernorm_modulate_kernel<12><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
-        default: return fail(SVDQ_ERR_UNSUPPORTED, "layernorm_modulate: built for 256, 1024, 2304 and 3072 columns (got %d)", a->cols);
+        default: return fail(SVDQ_ERR_UNSUPPORTED, "layernorm_modulate: built for 256, 1024, 2240, 2304 and 3072 columns (got %d)", a->cols);
     }
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;

@@ -22,7 +22,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ..ops.fused import litela_attention
+from ..ops.fused import layernorm_modulate, litela_attention
 from ..ops.gemm import svdq_gemm_w4a4_cuda
 from ..ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda
 from .linear import SVDQW4A4Linear
@@ -126,6 +126,13 @@ class SanaGLUMBConv(nn.Module):
         return self.point_conv(y, fuse_glu=True)
 
 
+def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
+    """layer_norm(x, eps 1e-6) * (1 + scale) + shift with scale / shift [B, C]: one row-wise kernel for the widths it is built for."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (256, 1024, 2240, 2304, 3072):
+        return layernorm_modulate(x.contiguous(), scale, shift, eps=1e-6)
+    return F.layer_norm(x, x.shape[-1:], eps=1e-6) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
+
+
 class SanaBlock(nn.Module):
     """SanaModel.cpp:215-320."""
 
@@ -139,10 +146,10 @@ class SanaBlock(nn.Module):
     def forward(self, x, cond, t6, H, W):
         B, S, C = x.shape
         m = (self.scale_shift_table[None] + t6.view(B, 6, C)).unbind(1)   # shift, scale, gate (attention), shift, scale, gate (MLP)
-        n = F.layer_norm(x, (C,), eps=1e-6) * (1 + m[1].unsqueeze(1)) + m[0].unsqueeze(1)
+        n = _ln_mod(x, m[1], m[0])
         x = x + m[2].unsqueeze(1) * self.attn(n)
         x = x + self.cross_attn(x, cond)
-        n = F.layer_norm(x, (C,), eps=1e-6) * (1 + m[4].unsqueeze(1)) + m[3].unsqueeze(1)
+        n = _ln_mod(x, m[4], m[3])
         return x + m[5].unsqueeze(1) * self.ff(n, H, W)
 
 

@@ -33,7 +33,7 @@ def test_qk_norm_rope_matches_oracle(B, S, heads):
     _bf16_close(got[:, :2 * dim], exp[:, :2 * dim])
 
 
-@pytest.mark.parametrize("B,S,C", [(2, 70, 256), (1, 333, 3072), (2, 64, 2304)])
+@pytest.mark.parametrize("B,S,C", [(2, 70, 256), (1, 333, 3072), (2, 64, 2304), (3, 50, 2240)])
 def test_layernorm_modulate_matches_oracle(B, S, C):
     from nunchaku_b200.ops import layernorm_modulate
 
