@@ -25,6 +25,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=32, help="global batch (images per step over all ranks)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--graph", action="store_true", help="capture one forward in a CUDA graph and time its replays "
+                    "(small per-GPU batches are bound by launch overhead otherwise)")
     ap.add_argument("--precision", default="int4", choices=["nvfp4", "int4"])
     ap.add_argument("--blocks", type=int, default=20)
     args = ap.parse_args()
@@ -42,12 +44,27 @@ def main() -> None:
     with torch.no_grad():
         for _ in range(args.warmup):
             y = model(lat, cap, t, (H, W))
+        graph = None
+        if args.graph:
+            # every prepared-weight cache and status word exists after the warm-up, so nothing allocates outside torch's
+            # capture-aware pool and nothing synchronises inside the captured region
+            y_eager = y.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                y = model(lat, cap, t, (H, W))
+            graph.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(y, y_eager):
+                raise SystemExit("graph replay differs from the eager forward")
         D.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            y = model(lat, cap, t, (H, W))
+            if graph is not None:
+                graph.replay()
+            else:
+                y = model(lat, cap, t, (H, W))
         e1.record()
         torch.cuda.synchronize()
     ms = D.max_over_ranks(e0.elapsed_time(e1) / args.steps, "cuda")
@@ -57,7 +74,7 @@ def main() -> None:
         print(json.dumps({
             "metric": "SANA-1.6B-architecture 1024px image-steps/s", "value": round(args.batch / ms * 1e3, 2), "ms_per_step": round(ms, 3),
             "n_gpus": world, "global_batch": args.batch, "per_gpu_batch": B, "precision": args.precision, "blocks": args.blocks,
-            "w4a4_linears": len(model.w4a4_linears()), "finite": finite, "weights": "random packed W4A4", "scaling": "strong",
+            "w4a4_linears": len(model.w4a4_linears()), "finite": finite, "cuda_graph": bool(args.graph), "weights": "random packed W4A4", "scaling": "strong",
         }))
     D.shutdown()
 
