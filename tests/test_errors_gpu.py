@@ -25,6 +25,9 @@ def test_bad_arguments_raise():
         # fuse_glu halves the channel count: a [256, 256] input is K = 128, which does not match smooth / lora_down
         quant(torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda"), lora_down=ld, smooth=sm, fp4=True, fuse_glu=True,
               output=torch.empty(256, 128, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(ValueError):
+        # an input narrower than the parameters is allowed (K_in), but only in steps of 8 columns
+        quant(torch.zeros(256, 100, dtype=torch.bfloat16, device="cuda"), lora_down=ld, smooth=sm, fp4=True)
     # the context is still healthy
     out = quant(x, lora_down=ld, smooth=sm, fp4=True)
     torch.cuda.synchronize()
