@@ -31,8 +31,8 @@
 //               thread's own row chunk is group-quantised in registers
 //   warps 9..12 (NVFP4 requantising variants up to rank 32) a second epilogue set; the two warps of a lane quadrant
 //               take alternate 64-column chunks
-// INT4: warp 6 brings the fp16 weights, warps 7..14 read the packed activation codes from global memory and convert
-// them to fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
+// INT4 (16 warps, six-stage ring of 28 KB): warp 6 brings the fp16 weights, warps 0 and 7..15 read the packed activation
+// codes from global memory and convert them to fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
 // TMEM per CTA: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
 // plus two 48-column scale-factor buffers (16 for A, 32 for B) = 480 of 512 columns.
 // Every loop that issues tcgen05 / TMA instructions is run by a whole warp with one elected lane issuing, so
@@ -79,17 +79,16 @@ constexpr int G_COLV_BYTES = 8 * G_COLV_FLOATS * 4;           // up to 8 epilogu
 constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
 constexpr int H_B_BYTES = G_BNH * 128;          // 96 rows x 64 fp16
 constexpr int H_STAGE_BYTES = H_A_BYTES + H_B_BYTES;   // 28672 = 28 * 1024
-constexpr int H_PK_STAGES = 6;
-constexpr int H_PK_BYTES = G_BM * 32;           // 128 rows x 64 packed codes
-constexpr int H_CONV_WARPS = 8;
+constexpr int H_STAGES = 6;                     // INT4 operand ring (28 KB stages)
+constexpr int H_GROUPS = 5;                     // converter groups: stages in conversion at once
+constexpr int H_CONV_WARPS = 2 * H_GROUPS;
 constexpr int H_CONV_PER_STAGE = 2;             // converter warps that share one stage (64 rows each); four such groups take turns
-constexpr int H_THREADS = (7 + H_CONV_WARPS) * 32;   // warps 0 A codes, 1 MMA, 2..5 epilogue, 6 weights, 7..14 converters
+constexpr int H_THREADS = (6 + H_CONV_WARPS) * 32;   // warps 0 and 7..15 converters, 1 MMA, 2..5 epilogue, 6 weights: 16 warps
 template <bool I4>
 constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
 template <bool I4>
 constexpr size_t smem_bytes() {
-    return 1024 + static_cast<size_t>(G_STAGES) * stage_bytes<I4>() + (I4 ? H_PK_STAGES * H_PK_BYTES : 0) + G_EPI_BYTES +
-           G_COLV_BYTES + 512;
+    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + G_COLV_BYTES + 512;
 }
 
 struct GemmParams {
@@ -119,15 +118,13 @@ struct GemmParams {
 };
 
 struct GemmShared {
-    uint64_t full[G_STAGES];        // leader: operand tiles and scale atoms of both CTAs have landed (8 arrivals + bytes)
-    uint64_t empty[G_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
+    uint64_t full[H_STAGES];        // leader: operand tiles and scale atoms of both CTAs have landed (8 arrivals + bytes)
+    uint64_t empty[H_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
     uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
     uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
     uint64_t xempty[4];             // ... and has been added by the first
     uint64_t drain;
-    uint64_t pk_full[H_PK_STAGES];  // INT4: packed activation codes of a k-block have landed
-    uint64_t pk_empty[H_PK_STAGES]; // INT4: the converter warps have read them
     uint32_t tmem_base;
     volatile int abort_flag;
 };
@@ -279,8 +276,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int SB = stage_bytes<I4>();
-    uint8_t* pk_smem = smem + G_STAGES * SB;                                  // INT4: packed-code ring
-    uint8_t* epi_smem = pk_smem + (I4 ? H_PK_STAGES * H_PK_BYTES : 0);
+    constexpr int NS = I4 ? H_STAGES : G_STAGES;                              // depth of the operand ring
+    uint8_t* epi_smem = smem + NS * SB;
     float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
     GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + G_COLV_BYTES);
 
@@ -294,7 +291,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
     if (threadIdx.x == 0) {
-        for (int s = 0; s < G_STAGES; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&sh->full[s], I4 ? 2 * (1 + H_CONV_PER_STAGE) : 8);   // producers (and converter warps) of both CTAs
             mbar_init(&sh->empty[s], 1);
         }
@@ -307,10 +304,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(&sh->xempty[i], 1);
         }
         mbar_init(&sh->drain, 1);
-        for (int i = 0; i < H_PK_STAGES; ++i) {
-            mbar_init(&sh->pk_full[i], 1);
-            mbar_init(&sh->pk_empty[i], H_CONV_PER_STAGE);
-        }
         sh->abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tm_a);
@@ -338,23 +331,23 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     if (I4 && (warp == 0 || warp >= 6)) {
         // ------------------------------------------------------------------ INT4 producers and converter warps
-        // warp 0: idle; warp 6: this CTA's 96 rows of the fp16 weights, or both fp32 tiles (lora_act, LoRA-up) of a
-        // low-rank stage; warps 7..14: packed codes from global memory (prefetched into registers one turn ahead) ->
+        // warp 6: this CTA's 96 rows of the fp16 weights, or both fp32 tiles (lora_act, LoRA-up) of a
+        // low-rank stage; warps 0 and 7..15: packed codes from global memory (prefetched into registers one turn ahead) ->
         // fp16(code * group scale) straight into the 128B-swizzled K-major tile the MMA reads.
         if constexpr (I4) {
-            const int cw = warp - 7;
+            const int cw = warp == 0 ? 0 : warp - 6;   // converter index 0..9
             const int hh = lane & 1;
             const uint32_t flip = p.act_unsigned ? 0u : 0x88888888u;
             const __half2 off_lo = __float2half2_rn(p.act_unsigned ? 1024.f : 1032.f);
             const __half2 off_hi = __float2half2_rn(p.act_unsigned ? -64.f : -72.f);
             uint32_t it = 0;
             bool ok = true;
-            if (warp >= 7) {
+            if (warp != 6) {
                 // converter warps.  Every shared-memory and barrier operation of a SIMT warp queues behind the tensor core's
                 // operand reads, so the fixed chain of a stage's hand-shake (two barrier waits, load, stores, proxy fence,
-                // arrivals) costs several hundred cycles however little is converted.  The eight warps therefore form four
-                // groups that take every fourth stage each, two warps per stage with 64 rows apiece: four stages are in
-                // conversion at once.  A lane converts half a row (32 codes) of rows r0, r0 + 16, r0 + 32, r0 + 48: its 16-byte
+                // arrivals) costs several hundred cycles however little is converted.  The ten warps therefore form five
+                // groups that take every fifth stage each, two warps per stage with 64 rows apiece: five of the ring's six
+                // stages are in conversion at once.  A lane converts half a row (32 codes) of rows r0, r0 + 16, r0 + 32, r0 + 48: its 16-byte
                 // global loads fill whole 32-byte sectors and its swizzled 16-byte stores are free of bank conflicts.
                 // The packed codes and group scales of the next stage the warp will convert are fetched while it converts
                 // this one, so no shared-memory load and only one barrier wait are left in the chain.
@@ -365,7 +358,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     int m0, n0;
                     tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
                     const __nv_bfloat16* asp = p.ascales_i4 + m0 + r0;
-                    int ks = static_cast<int>((static_cast<uint32_t>(grp) - it_base) & 3u);   // first stage of this tile that is ours
+                    int ks = (grp + H_GROUPS - static_cast<int>(it_base % H_GROUPS)) % H_GROUPS;   // first stage of this tile that is ours
                     // the lane's 16 bytes (32 codes) of row r0 + 16 i in k-block ks sit at apk + 16 i * pitch + 32 ks
                     const size_t pitch = static_cast<size_t>(p.K) >> 1;
                     const uint8_t* apk = p.act_i4 + static_cast<size_t>(m0 + r0) * pitch + hh * 16;
@@ -376,12 +369,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : __nv_bfloat16(0.f);
                         wnxt[i] = ks < kstages ? __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * ks)) : make_uint4(0, 0, 0, 0);
                     }
-                    for (; ks < per_tile; ks += 4) {
+                    for (; ks < per_tile; ks += H_GROUPS) {
                         const uint32_t it = it_base + ks;
-                        const int s = it % G_STAGES;
+                        const int s = it % NS;
                         uint8_t* st = smem + s * SB;
                         const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
-                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 12));
+                        ok = __all_sync(0xffffffffu, wait_or_abort(&sh->empty[s], ((it / NS) & 1) ^ 1, sh, p.status, 12));
                         if (!ok) break;
                         if (ks >= kstages) {   // low-rank stage: nothing to convert, but the arrival keeps this warp in step
                             if (lane == 0) mbar_arrive_cluster(lfull);
@@ -394,9 +387,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         for (int i = 0; i < 4; ++i) {
                             cur[i] = nxt[i];
                             w[i] = wnxt[i];
-                            if (ks + 4 < kstages) {
-                                nxt[i] = __ldg(asp + static_cast<size_t>(ks + 4) * p.M_pad + 16 * i);
-                                wnxt[i] = __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * (ks + 4)));
+                            if (ks + H_GROUPS < kstages) {
+                                nxt[i] = __ldg(asp + static_cast<size_t>(ks + H_GROUPS) * p.M_pad + 16 * i);
+                                wnxt[i] = __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * (ks + H_GROUPS)));
                             }
                         }
 #pragma unroll
@@ -423,11 +416,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
                     const int nb0 = n0 + rank * G_BNH;
                     for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                        const int s = it % G_STAGES;
+                        const int s = it % NS;
                         uint8_t* st = smem + s * SB;
                         const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
                         const bool lowrank = ks >= kstages;
-                        const uint32_t eparity = ((it / G_STAGES) & 1) ^ 1;
+                        const uint32_t eparity = ((it / NS) & 1) ^ 1;
                         if (warp == 0) {
                             break;   // nothing to bring: the converter warps read the packed codes from global memory themselves
                         } else {
@@ -464,8 +457,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
             const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                const int s = it % G_STAGES;
-                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], ((it / G_STAGES) & 1) ^ 1, sh, p.status, 10 + role));
+                const int s = it % NS;
+                ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], ((it / NS) & 1) ^ 1, sh, p.status, 10 + role));
                 if (!ok) break;
                 uint8_t* st = smem + s * G_STAGE_BYTES;
                 const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
@@ -515,8 +508,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const uint32_t d_tmem = tmem + as * G_TM_ACC1;
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int s = it % G_STAGES;
-                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / G_STAGES) & 1, sh, p.status, 21));
+                    const int s = it % NS;
+                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / NS) & 1, sh, p.status, 21));
                     if (!ok) break;
                     // descriptors of ring slot s: the start-address field counts 16-byte units
                     const uint64_t adesc = adesc0 + static_cast<uint32_t>(s * (SB >> 4));
