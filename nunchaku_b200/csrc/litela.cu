@@ -87,10 +87,10 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
     }
     __syncthreads();
 
-    // phase 2: one token per thread; q stays in registers, vk rows come as 16-byte broadcasts from shared memory
-    for (int t = threadIdx.x; t < tokens; t += LA_WARPS * 32) {
+    // phase 2: two tokens per thread (t and t + 256); q stays in registers, every vk row comes once as 16-byte
+    // broadcasts from shared memory and serves both tokens
+    auto load_q = [&](int t, float* q) {
         const uint4* qp = reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h);
-        float q[LA_HD];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint4 w = qp[j];
@@ -101,32 +101,51 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
                 q[8 * j + 2 * i + 1] = fmaxf(__uint_as_float(ww[i] & 0xffff0000u), 0.f);
             }
         }
-        auto dot = [&](int row) {
+    };
+    for (int t = threadIdx.x; t < tokens; t += 2 * LA_WARPS * 32) {
+        const int t1 = t + LA_WARPS * 32;
+        const bool has1 = t1 < tokens;
+        float q0[LA_HD], q1[LA_HD];
+        load_q(t, q0);
+        load_q(has1 ? t1 : t, q1);
+        auto dot2 = [&](int row, float& s0, float& s1) {
             const float4* vr = reinterpret_cast<const float4*>(vk[row]);
-            float s = 0.f;
+            s0 = 0.f;
+            s1 = 0.f;
 #pragma unroll
             for (int i = 0; i < LA_HD / 4; ++i) {
                 const float4 v4 = vr[i];
-                s = fmaf(q[4 * i], v4.x, s);
-                s = fmaf(q[4 * i + 1], v4.y, s);
-                s = fmaf(q[4 * i + 2], v4.z, s);
-                s = fmaf(q[4 * i + 3], v4.w, s);
+                s0 = fmaf(q0[4 * i], v4.x, s0);
+                s1 = fmaf(q1[4 * i], v4.x, s1);
+                s0 = fmaf(q0[4 * i + 1], v4.y, s0);
+                s1 = fmaf(q1[4 * i + 1], v4.y, s1);
+                s0 = fmaf(q0[4 * i + 2], v4.z, s0);
+                s1 = fmaf(q1[4 * i + 2], v4.z, s1);
+                s0 = fmaf(q0[4 * i + 3], v4.w, s0);
+                s1 = fmaf(q1[4 * i + 3], v4.w, s1);
             }
-            return s;
         };
-        const float den = dot(LA_HD) + eps;
-        uint4* op = reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h);
+        float den0, den1;
+        dot2(LA_HD, den0, den1);
+        den0 += eps;
+        den1 += eps;
+        uint4* op0 = reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h);
+        uint4* op1 = reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + (has1 ? t1 : t)) * D + LA_HD * h);
 #pragma unroll 1
         for (int j = 0; j < 4; ++j) {
-            uint32_t o[4];
+            uint32_t o0[4], o1[4];
 #pragma unroll
             for (int i2 = 0; i2 < 4; ++i2) {
-                const float n0 = __fdividef(dot(8 * j + 2 * i2), den);
-                const float n1 = __fdividef(dot(8 * j + 2 * i2 + 1), den);
-                const __nv_bfloat162 pr = __floats2bfloat162_rn(n0, n1);
-                o[i2] = *reinterpret_cast<const uint32_t*>(&pr);
+                float a0, a1, b0, b1;
+                dot2(8 * j + 2 * i2, a0, a1);
+                dot2(8 * j + 2 * i2 + 1, b0, b1);
+                const __nv_bfloat162 p0 = __floats2bfloat162_rn(__fdividef(a0, den0), __fdividef(b0, den0));
+                const __nv_bfloat162 p1 = __floats2bfloat162_rn(__fdividef(a1, den1), __fdividef(b1, den1));
+                o0[i2] = *reinterpret_cast<const uint32_t*>(&p0);
+                o1[i2] = *reinterpret_cast<const uint32_t*>(&p1);
             }
-            op[j] = make_uint4(o[0], o[1], o[2], o[3]);
+            op0[j] = make_uint4(o0[0], o0[1], o0[2], o0[3]);
+            if (has1) op1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
         }
     }
 }
