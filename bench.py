@@ -9,6 +9,9 @@ of the benchmark description (N(0,1) activations with 1% outlier channels x20, N
 weights with the rank-32 SVD component removed, N(0,0.02) low-rank factors and bias).
 One step = one pass of the path over one batch: activation quantiser + GEMM.  At N > 1 every rank
 runs the same step on its own batch (the path shards along M without communication): weak scaling.
+After that leg the same process times, into sub-objects of the same JSON line: the INT4 variant on the M=4096,
+K=N=3072 case (`int4_config0`), a FLUX.1-dev-architecture transformer step at global batch 8 (`flux_step`) and a
+SANA-1.6B-architecture step at global batch 32 (`sana_step`), both sharded along the batch over the ranks.
 Prints one JSON line on rank 0.
 """
 from __future__ import annotations
@@ -151,9 +154,20 @@ def cpu_oracle_step(lin, wdeq, x_rows):
     return y.to(torch.bfloat16)
 
 
+def workload_config():
+    return {
+        "workload": f"NVFP4 W4A4+LoRA linear M={M} K={K} N={N} R={R} (FLUX single-block fused input projection)",
+        "per_gpu_rows": M, "l2": "working set per step (28 MB in, 41 MB weights+codes, 198 MB out) exceeds the 126 MB L2",
+        "sharding": "rows (M) per rank, no data-path collective",
+    }
+
+
+DTYPE = "fp4 (e2m1 x e2m1, ue4m3 group-16 scales), fp32 accumulate"
+
+
 def run_reference(args, rank):
     """Reference arm: the CPU restatement of the reference's arithmetic (the reference has no CPU
-    implementation and its CUDA kernels have no sm_100 path), all host threads, bounded sample per step."""
+    implementation and its NVFP4 kernels have no sm_100 path), all host threads, bounded sample per step."""
     if rank != 0:
         return
     cores = os.cpu_count() or 1
@@ -178,12 +192,91 @@ def run_reference(args, rank):
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3 * M / rows, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp4 (e2m1 x e2m1, ue4m3 group-16 scales), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"NVFP4 W4A4+LoRA linear M={M} K={K} N={N} R={R} (FLUX single-block fused input projection)"},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": workload_config(),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def event_times(fn_list, reps):
+    """Average device time (ms) of each callable in ``fn_list`` run back to back ``reps`` times, one CUDA event between
+    every two launches (on torch's current stream, where the library launches)."""
+    n = len(fn_list)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(reps)]
+    for r in range(reps):
+        ev[r][0].record()
+        for i, fn in enumerate(fn_list):
+            fn()
+            ev[r][i + 1].record()
+    torch.cuda.synchronize()
+    return [sum(ev[r][i].elapsed_time(ev[r][i + 1]) for r in range(reps)) / reps for i in range(n)]
+
+
+def int4_config0(dev, peaks):
+    """The INT4 group-64 variant on the reference's own CPU-runnable case (M=4096, K=N=3072, rank 32): quantiser and GEMM
+    times by CUDA events over 50 launches, as absolute TFLOP/s and against the measured tensor-pipe rates of the MMA kind
+    the kernel uses (kind::f16, CTA pair) and of the integer kind (kind::i8)."""
+    from nunchaku_b200.models.random_init import random_w4a4_linear
+    from nunchaku_b200.peak_probe import mma_rate, mma_rate_pair
+
+    M0, K0, N0 = 4096, 3072, 3072
+    g = torch.Generator(device=dev).manual_seed(7)
+    m = random_w4a4_linear(K0, N0, R, "int4", True, g, dev)
+    x = torch.randn(M0, K0, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty(M0, N0, dtype=torch.bfloat16, device=dev)
+    st = {}
+
+    def q():
+        st["q"] = m.quantize(x)
+
+    def gm():
+        m.forward_quant(*st["q"], out)
+
+    for _ in range(3):
+        q(); gm()
+    tq, tg = event_times([q, gm], 50)
+    flop = 2.0 * M0 * N0 * K0 + 2.0 * M0 * N0 * R
+    tf = flop / (tg * 1e-3) / 1e12
+    f16 = mma_rate_pair("f16", 192, iters=2000)["tflops"]
+    i8 = mma_rate("i8", 256, iters=2000)["tflops"]
+    qbytes = 2 * M0 * K0 + M0 * K0 // 2 + M0 * (K0 // 64) * 2 + 4 * M0 * R + 2 * K0 * R + 2 * K0
+    return {"workload": f"INT4 W4A4+LoRA linear M={M0} K={K0} N={N0} R={R}", "gemm_us": tg * 1e3, "gemm_tflops": tf,
+            "frac_of_f16_pair_mma_rate": tf / f16, "f16_pair_mma_tflops": f16, "frac_of_i8_mma_rate": tf / i8, "i8_mma_tflops": i8,
+            "frac_of_bf16_measured": tf / peaks["bf16_tflops"], "quantizer_us": tq * 1e3,
+            "quantizer_gbs": qbytes / (tq * 1e-3) / 1e9, "quantizer_frac_hbm": qbytes / (tq * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "launches_timed": 50}
+
+
+def reference_int4_kernels(dev):
+    """The reference's own INT4 kernels (compiled from the reference tree into oracle/_ref, mma.sync, no sm_100 tuning)
+    timed on this GPU on the same case as ``int4_config0``: a baseline beside the CPU port, not the product path."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import ref_int4 as REF
+    if not REF.available():
+        return None
+    from nunchaku_b200.models.random_init import random_w4a4_linear
+    M0, K0, N0 = 4096, 3072, 3072
+    g = torch.Generator(device=dev).manual_seed(7)
+    m = random_w4a4_linear(K0, N0, R, "int4", True, g, dev)
+    x = torch.randn(M0, K0, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty(M0, N0, dtype=torch.bfloat16, device=dev)
+    st = {}
+
+    def q():
+        st["q"] = REF.quantize(x, m.smooth_factor, m.proj_down)
+
+    def gm():
+        c, s, la = st["q"]
+        REF.gemm(c, m.qweight, s, m.wscales, out=out, lora_act_in=la, lora_up=m.proj_up, bias=m.bias)
+
+    for _ in range(3):
+        q(); gm()
+    tq, tg = event_times([q, gm], 20)
+    flop = 2.0 * M0 * N0 * K0 + 2.0 * M0 * N0 * R
+    return {"workload": f"INT4 W4A4+LoRA linear M={M0} K={K0} N={N0} R={R}", "kind": "reference kernels (mma.sync s4, "
+            "bf16 accumulation) compiled for sm_100a", "gemm_us": tg * 1e3, "gemm_tflops": flop / (tg * 1e-3) / 1e12,
+            "quantizer_us": tq * 1e3, "launches_timed": 20}
 
 
 def main():
@@ -193,8 +286,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-model-steps", action="store_true", help="skip the FLUX / SANA transformer-step legs and the INT4 case")
     ap.add_argument("--shape", default=None, help="M,K,N override: a smaller case of the same path for profiler captures "
-                    "(the default is the benchmark workload)")
+                    "(the default is the benchmark workload); implies --no-model-steps")
     args = ap.parse_args()
     if args.shape:
         global M, K, N, FLOP_GEMM, FLOP_STEP, QUANT_BYTES
@@ -202,6 +296,7 @@ def main():
         FLOP_GEMM = 2.0 * M * N * K + 2.0 * M * N * R
         FLOP_STEP = FLOP_GEMM
         QUANT_BYTES = 2 * M * K + M * K // 2 + M * K // 16 + 4 * M * R + 2 * K * R + 2 * K
+        args.no_model_steps = True
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     from nunchaku_b200 import distributed as D
@@ -220,54 +315,71 @@ def main():
 
     x = make_inputs(dev, rank)
     m = build_layer(dev, 0, x)
-    xv = x.view(1, M, K)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    st = {}
+
+    def quant():
+        st["q"] = m.quantize(x)
+
+    def gemm():
+        m.forward_quant(*st["q"], out)
 
     def step():
-        q, s, la = m.quantize(x)
-        m.forward_quant(q, s, la, out)
+        quant()
+        gemm()
 
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
 
-    # ---- timed region: K steps, inputs resident in HBM; per-kernel events for the roofline figures
-    # Per-kernel durations come from CUDA events inside the timed region, on a sample of its steps (every 4th, at
-    # least 3): an event between two kernels costs a few microseconds of a 185 us step and keeps the second kernel's
-    # launch from overlapping the first one's tail, so timing every launch would slow down what is being measured.
-    stride = 4 if args.steps >= 12 else 1
-    sampled = [i for i in range(args.steps) if i % stride == 0]
-    ev = {i: [torch.cuda.Event(enable_timing=True) for _ in range(3)] for i in sampled}
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
-    sampler.start()
+    # ---- timed region: K steps on inputs resident in HBM.  A step is `inner` back-to-back passes of the path (chosen so
+    # that the region lasts >= 50 ms: with a 0.17 ms pass and a MAX over ranks, a region of a few ms is set by the one
+    # rank whose host hiccuped); ms_per_step is per pass.  No event is recorded inside the region.
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    est = max(e0.elapsed_time(e1) / 3, 1e-3)
+    inner = max(1, int(50.0 / (est * args.steps) + 0.999))
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
     D.barrier()
     torch.cuda.synchronize()
-    e_start.record()
-    for i in range(args.steps):
-        if i in ev:
-            ev[i][0].record()
-            q, s, la = m.quantize(x)
-            ev[i][1].record()
-            m.forward_quant(q, s, la, out)
-            ev[i][2].record()
-        else:
-            q, s, la = m.quantize(x)
-            m.forward_quant(q, s, la, out)
-    e_stop.record()
+    t_host = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps * inner):
+        step()
+    e1.record()
+    host_ms = (time.perf_counter() - t_host) * 1e3 / (args.steps * inner)
     torch.cuda.synchronize()
     D.barrier()
-    ms_total = e_start.elapsed_time(e_stop)
-    # keep the sampler alive for at least a few samples on very short regions
-    if ms_total < 400:
-        t_end = time.time() + 0.4
+    ms_local = e0.elapsed_time(e1) / (args.steps * inner)
+    if sampler:   # keep the load up until the sampler has a few samples of it
+        t_end = time.time() + 0.5
         while time.time() < t_end:
-            step()
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ms_step = D.max_over_ranks(ms_total / args.steps, dev)
-    quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev.values()) / len(ev)
-    gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev.values()) / len(ev)
+            for _ in range(50):
+                step()
+            torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    ms_step = D.max_over_ranks(ms_local, dev)
+    per_rank = {"ms_per_step": {"min": -D.max_over_ranks(-ms_local, dev), "max": ms_step},
+                "host_enqueue_ms_per_step": {"min": -D.max_over_ranks(-host_ms, dev), "max": D.max_over_ranks(host_ms, dev)}}
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms_local], dtype=torch.float64, device=dev)
+        allt = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        vals = sorted(float(v.item()) for v in allt)
+        per_rank["ms_per_step"]["median"] = vals[len(vals) // 2]
+        per_rank["ms_per_step"]["all"] = [round(v, 5) for v in vals]
+    # ---- per-kernel durations for the roofline figures: the same passes again with an event between the two kernels,
+    # >= 50 launches of each (an event between two kernels keeps the second one's launch from overlapping the first one's
+    # tail, which is why the region above carries none)
+    launches = max(50, args.steps)
+    quant_ms, gemm_ms = event_times([quant, gemm], launches)
     status = _lib.device_status()
     if status != (0, 0):
         raise SystemExit(f"device status {status}: a bounded wait ran out")
@@ -287,16 +399,17 @@ def main():
     pipe.join()
     D.barrier()
     torch.cuda.synchronize()
-    e_start.record()
+    e0.record()
     pipe.fork()
     for i in range(e2e_steps):
         pipe.submit(xh[i % 2], oh[i % 2])
     pipe.join()
-    e_stop.record()
+    e1.record()
     torch.cuda.synchronize()
     if not torch.equal(oh[0], out.cpu()) or not torch.equal(oh[1], oh[0]):
         raise SystemExit("end-to-end result differs from the device-resident result")
-    e2e_ms = D.max_over_ranks(e_start.elapsed_time(e_stop) / e2e_steps, dev)
+    e2e_ms = D.max_over_ranks(e0.elapsed_time(e1) / e2e_steps, dev)
+    del pipe, xh, oh
 
     peaks, peak_kind = load_peaks()
     # FP4 has no entry in MEASURED_PEAKS.json: measure the tensor-pipe peak here, on this GPU, with the
@@ -307,12 +420,10 @@ def main():
     line = {
         "metric": METRIC, "value": world * FLOP_STEP / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "fp4 (e2m1 x e2m1, ue4m3 group-16 scales), fp32 accumulate", "data": "synthetic",
-        "config": {
-            "workload": f"NVFP4 W4A4+LoRA linear M={M} K={K} N={N} R={R} (FLUX single-block fused input projection)",
-            "per_gpu_rows": M, "l2": "working set per step (28 MB in, 41 MB weights+codes, 198 MB out) exceeds the 126 MB L2",
-            "sharding": "rows (M) per rank, no data-path collective",
-        },
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": workload_config(),
+        "timed_region": {"passes_per_step": inner, "passes": args.steps * inner, "ms": ms_step * args.steps * inner,
+                         "note": "ms_per_step and value are per pass of the path (quantiser + GEMM)"},
+        "per_rank": per_rank,
         "roofline": {
             "kernel": "gemm_w4a4_kernel<NVFP4>", "bound": "tensor", "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s",
             "frac": gemm_tflops / fp4_peak, "traffic": GEMM_DRAM_TRAFFIC if (M, K, N) == (4608, 3072, 21504) else None,
@@ -320,22 +431,35 @@ def main():
             "peak_source": "measured live: operand-resident tcgen05.mma kind::mxf4nvf4 M128 N256 K64 loop on all SMs "
                            "(burst; MEASURED_PEAKS.json has no FP4 entry); nominal dense FP4 is 9000",
             "frac_of_4x_bf16_measured": gemm_tflops / (4.0 * peaks["bf16_tflops"]), "bf16_peak_kind": peak_kind,
-            "avg_launch_us": gemm_ms * 1e3, "launches_timed": len(ev),
+            "avg_launch_us": gemm_ms * 1e3, "launches_timed": launches,
             "quantizer": {"bound": "hbm", "achieved": QUANT_BYTES / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                           "unit": "GB/s", "frac": QUANT_BYTES / (quant_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                          "avg_launch_us": quant_ms * 1e3},
+                          "avg_launch_us": quant_ms * 1e3, "launches_timed": launches},
         },
-        "e2e": {"value": world * FLOP_STEP / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": xh[0].numel() * 2,
-                "d2h_bytes_per_step": oh[0].numel() * 2, "ms_per_step": e2e_ms},
-        "gpu_launches": 2 * args.steps,
+        "e2e": {"value": world * FLOP_STEP / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_ms,
+                "note": "bound by the copy of the bf16 result to the host (PCIe); all ranks share one host memory complex. "
+                        "A consumer that is another W4A4 layer takes the requantised 4-bit output instead (4x fewer bytes)"},
+        "gpu_launches": 2 * args.steps * inner,
         "clocks": clocks,
     }
+    del out, x
+    if not args.no_model_steps:
+        torch.cuda.empty_cache()
+        if rank == 0:
+            line["int4_config0"] = int4_config0(dev, peaks)
+        D.barrier()
+        from nunchaku_b200.models import flux_bench, sana_bench
+        line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2)
+        torch.cuda.empty_cache()
+        line["sana_step"] = sana_bench.run(global_batch=32, reps=10, warmup=2)
+        torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
         lin, wdeq = cpu_oracle_setup(m)
         rows = 576
-        xc = x[:rows].cpu()
+        xc = make_inputs(dev, rank)[:rows].cpu()
         cpu_oracle_step(lin, wdeq, xc[:64])
         t0 = time.perf_counter(); reps = 0
         while reps < 3 or time.perf_counter() - t0 < 10.0:
@@ -346,11 +470,14 @@ def main():
         line["cpu_baseline"] = {
             "value": FLOP_STEP * rows / M / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{rows} of {M} rows x {reps} reps (quantise + fp32 dequant-matmul + epilogue; weights kept dequantised)"}
+        if not args.no_model_steps:
+            try:
+                line["reference_int4_kernels"] = reference_int4_kernels(dev)
+            except Exception as exc:   # a baseline beside the port: never fail the benchmark over it
+                line["reference_int4_kernels"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    D.shutdown()
 
 
 if __name__ == "__main__":

@@ -5,8 +5,14 @@
  * entry point returns 0 on success or a negative SVDQ_ERR_* code, never throws,
  * aborts or traps; svdq_last_error_string() gives the reason (thread local).
  * Launches are asynchronous on the given stream (a cudaStream_t passed as
- * void*), on the current CUDA device.  Nothing is allocated by the library: all
- * buffers, including scratch, are caller owned.
+ * void*), on the current CUDA device.  The library calls no allocator: all
+ * buffers, including scratch, are caller owned.  The one exception is the fixed
+ * SVDQ_STATIC_SCRATCH_BYTES array that svdq_gemm_w4a4_static_scratch() uses, which
+ * is part of the library image on every GPU that loads it.
+ * The first call of any entry point on a device looks up a few per-device facts
+ * (SM count, addresses of the library's device symbols) and caches them: make one
+ * ordinary call per device before starting a stream capture.  Device ordinals up
+ * to 63 are supported.
  *
  * The two compute entry points replace the reference's
  *   nunchaku::ops::quantize_w4a4_act_fuse_lora   (nunchaku/csrc/ops.h:82-110,
@@ -77,8 +83,10 @@ int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* strea
  * sizes svdq_w4a4_prepared_bytes() reports.
  */
 typedef struct svdq_prepared_weights {
-    void* wgt;        /* NVFP4: uint8 [N, K/2] row-major codes; INT4: int8 [N, K], one code per byte */
-    void* wscales;    /* NVFP4: 512-byte e4m3 atoms [N/128][K/64]; INT4: fp32 [K/64, N]    */
+    void* wgt;        /* NVFP4: uint8 [N, K/2] row-major codes; INT4: fp16 [N, K] = code * group scale * 2^-e[n]
+                         (2 bytes per weight; within each 16-byte chunk the k order is 0,4,1,5,2,6,3,7)      */
+    void* wscales;    /* NVFP4: 512-byte e4m3 atoms [N/128][K/64]; INT4: bf16 [K/64, N] (kept for inspection,
+                         the GEMM does not read it: the scales are folded into wgt)                          */
     float* lora_up;   /* fp32 [N, R32] (R32 = R rounded up to 32), pre-divided by col_scale */
     float* col_scale; /* fp32 [N] = alpha * wcscales                                       */
     float* col_bias;  /* fp32 [N]                                                          */
@@ -118,7 +126,9 @@ typedef struct svdq_gemm_args {
     float* lora_act_out;      /* fp32 [M_pad, R_next]                                        */
     const void* next_smooth;    /* bf16 [N] reference-packed                                 */
     const void* next_lora_down; /* bf16 [N, R_next] reference-packed                         */
-    void* workspace;          /* scratch, svdq_gemm_w4a4_workspace_bytes() bytes, 256-aligned */
+    void* workspace;          /* scratch, svdq_gemm_w4a4_workspace_bytes() bytes, 256-aligned: needed by the
+                                 requantising epilogue (per-CTA LoRA-down partials) and by every INT4 GEMM
+                                 (per-row power-of-two normalisation of the activation scales); else may be NULL */
     size_t workspace_bytes;
     int32_t M, M_pad, N, K, R, R_next;
     int32_t fp4;              /* precision of act / weights                                  */
@@ -144,9 +154,9 @@ int svdq_gemm_w4a4(const svdq_gemm_args* args, void* stream);
  * and outputs are still the caller's.  No counterpart in the reference, which allocates nothing in this op
  * because its LoRA-down uses atomics.
  *   - Limit: problems that need more than SVDQ_STATIC_SCRATCH_BYTES (see svdq_gemm_w4a4_workspace_bytes) are
- *     refused with SVDQ_ERR_INVALID_ARGUMENT; NVFP4 only.
+ *     refused with SVDQ_ERR_INVALID_ARGUMENT.  Both precisions.
  *   - The first call on each device looks up the array's device address; make that call before starting any
- *     stream capture.
+ *     stream capture.  The address is cached per device and is stale after a cudaDeviceReset.
  *   - All calls share the array: do not let two of them run on the same GPU at the same time.
  */
 #define SVDQ_STATIC_SCRATCH_BYTES (8u << 20)
@@ -171,8 +181,8 @@ int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream);
  * [rows, 3 * heads * 128] (Q third, K third; V untouched).  What the reference does inside the QKV GEMM's
  * epilogue: EpilogueRMSNormRope, src/kernels/zgemm/epilogues.cuh:269-425, called from
  * nunchaku/ops/fused.py:50-110 (fused_qkv_norm_rottary); same arithmetic (fp32, one rounding), but the rotary table
- * is two plain fp32 arrays [seq_len, 64] (cos, sin; row = token position, repeated over batches of seq_len rows)
- * instead of the reference's fragment-packed [1, M, 128] tensor.
+ * is either two plain fp32 arrays [seq_len, 64] (cos, sin; row = token position, repeated over batches of seq_len rows)
+ * or the reference's fragment-packed [1, M, 128] tensor (rotary_packed below).
  */
 typedef struct svdq_norm_rope_args {
     void* qkv;                /* bf16 [rows, 3 * heads * 128], modified in place */
@@ -183,6 +193,18 @@ typedef struct svdq_norm_rope_args {
     int64_t rows;
     int32_t seq_len, heads;
     float eps;                /* 1e-6 in the reference */
+    /* Optional (all NULL / 0 for the plain in-place form):
+     * rotary_packed - the reference's own rotary tensor instead of cos / sin: fp32 [seq_len, 128] in the fragment
+     *   order pack_rotemb produces (nunchaku/models/embeddings.py:88-120; seq_len a multiple of 16);
+     * out_q / out_k / out_v - write the three thirds head-major, bf16 [rows / seq_len, heads, tokens_pad, 128], instead
+     *   of in place (the job of EpiloguePackQKV, epilogues.cuh:427-550; there the destination is the fragment order of
+     *   the reference's own fp16 attention kernel with NaN-masked K padding, here it is plain row-major for a
+     *   TMA / library attention, and rows at or beyond attn_tokens, when attn_tokens > 0, are written as zeros). */
+    const float* rotary_packed;
+    void* out_q;
+    void* out_k;
+    void* out_v;
+    int32_t tokens_pad, attn_tokens;
 } svdq_norm_rope_args;
 int svdq_qk_norm_rope(const svdq_norm_rope_args* args, void* stream);
 
@@ -216,6 +238,9 @@ typedef struct svdq_litela_args {
     float* vk;                /* fp32 [batches, heads, 33, 32] or NULL: the reference's out_vk */
     int32_t batches, tokens, heads;
     float eps;                /* 1e-6 in the reference */
+    int32_t mode;             /* 0: all of it.  The reference's two launches on their own: 1 = what EpilogueLiteLA leaves
+                                 (vk, and relu(Q) as bf16 in `out`; vk required); 2 = vk_mul_q_kernel (`out` holds
+                                 relu(Q) and is finished in place from vk; qkv is not read and may be NULL)        */
 } svdq_litela_args;
 int svdq_litela(const svdq_litela_args* args, void* stream);
 

@@ -130,6 +130,12 @@ class NormRopeArgs(Structure):
         ("seq_len", c_int32),
         ("heads", c_int32),
         ("eps", c_float),
+        ("rotary_packed", c_void_p),
+        ("out_q", c_void_p),
+        ("out_k", c_void_p),
+        ("out_v", c_void_p),
+        ("tokens_pad", c_int32),
+        ("attn_tokens", c_int32),
     ]
 
 
@@ -156,6 +162,7 @@ class LiteLAArgs(Structure):
         ("tokens", c_int32),
         ("heads", c_int32),
         ("eps", c_float),
+        ("mode", c_int32),
     ]
 
 

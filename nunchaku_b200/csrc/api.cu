@@ -1,5 +1,7 @@
 // C-ABI entry points of libsvdq_b200 (declared in include/svdq_b200.h) and the
 // host-side plumbing they share.
+#include <atomic>
+#include <cstring>
 #include <mutex>
 
 #include "host_common.h"
@@ -23,19 +25,65 @@ std::string& last_error() {
 // {code, detail}: written by kernels whose bounded waits ran out.
 __device__ int g_status_words[2];
 
-int status_words(int** ptr) {
-    void* p = nullptr;
-    SVDQ_CUDA(cudaGetSymbolAddress(&p, g_status_words));
-    *ptr = static_cast<int*>(p);
+// Per-device facts that every launch needs, looked up once per device (under a mutex) with that device current:
+// SM count, compute capability and the device address of the status words.  Entry points that run inside a stream
+// capture find them cached, provided one ordinary call was made on the device before the capture began.  The
+// cached address belongs to the context that was current at the time: it does not survive a cudaDeviceReset.
+struct DeviceState {
+    std::atomic<bool> ready{false};
+    int sms = 0, cc_major = 0;
+    int* status = nullptr;
+};
+static DeviceState g_dev[SVDQ_MAX_DEVICES];
+static std::mutex g_dev_mu;
+
+static int device_state(const DeviceState** out, int* dev_out = nullptr) {
+    int dev = 0;
+    SVDQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= SVDQ_MAX_DEVICES)
+        return fail(SVDQ_ERR_UNSUPPORTED, "device ordinal %d is outside the supported range [0, %d)", dev, SVDQ_MAX_DEVICES);
+    DeviceState& d = g_dev[dev];
+    if (!d.ready.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_dev_mu);
+        if (!d.ready.load(std::memory_order_relaxed)) {
+            SVDQ_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+            SVDQ_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+            void* p = nullptr;
+            SVDQ_CUDA(cudaGetSymbolAddress(&p, g_status_words));
+            d.status = static_cast<int*>(p);
+            d.ready.store(true, std::memory_order_release);
+        }
+    }
+    *out = &d;
+    if (dev_out) *dev_out = dev;
     return SVDQ_OK;
 }
 
+int status_words(int** ptr) {
+    const DeviceState* d = nullptr;
+    if (int rc = device_state(&d)) return rc;
+    *ptr = d->status;
+    return SVDQ_OK;
+}
+
+int sm_count(int* sms) {
+    const DeviceState* d = nullptr;
+    if (int rc = device_state(&d)) return rc;
+    *sms = d->sms;
+    return SVDQ_OK;
+}
+
+int current_device(int* dev) {
+    const DeviceState* d = nullptr;
+    return device_state(&d, dev);
+}
+
 int check_arch() {
-    int dev = 0, major = 0;
-    SVDQ_CUDA(cudaGetDevice(&dev));
-    SVDQ_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-    if (major != 10)
-        return fail(SVDQ_ERR_UNSUPPORTED_ARCH, "device %d has compute capability %d.x; this library is sm_100a only", dev, major);
+    const DeviceState* d = nullptr;
+    int dev = 0;
+    if (int rc = device_state(&d, &dev)) return rc;
+    if (d->cc_major != 10)
+        return fail(SVDQ_ERR_UNSUPPORTED_ARCH, "device %d has compute capability %d.x; this library is sm_100a only", dev, d->cc_major);
     return SVDQ_OK;
 }
 
@@ -56,38 +104,75 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, uint64_t rows, uint64_t row_bytes,
-                 uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+// Encoded tensor maps are kept in a small per-thread, direct-mapped table keyed by everything that goes into the
+// encoding: a layer called again with the same buffers (the steady state of an inference loop, where the caching
+// allocator hands back the same addresses) costs a hash and a compare instead of a driver call per map.
+struct TmapKey {
+    const void* base;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int32_t elem, rank, swizzle;
+};
+struct alignas(64) TmapEntry {
+    CUtensorMap map;
+    TmapKey key;
+    bool valid;
+};
+constexpr int TMAP_CACHE_ENTRIES = 1024;
+
+static int cached_tmap(CUtensorMap* out, const TmapKey& k) {
+    static thread_local TmapEntry* table = nullptr;
+    if (!table) table = new TmapEntry[TMAP_CACHE_ENTRIES]();
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.dims[0] * 0xC2B2AE3D27D4EB4Full) ^ (k.dims[1] * 0x165667B19E3779F9ull) ^ (k.dims[2] << 17) ^ (k.strides[0] * 31) ^
+         (static_cast<uint64_t>(k.box[0]) << 40) ^ (static_cast<uint64_t>(k.box[1]) << 48) ^ (static_cast<uint64_t>(k.elem) << 56);
+    TmapEntry& e = table[(h >> 20) & (TMAP_CACHE_ENTRIES - 1)];
+    if (e.valid && std::memcmp(&e.key, &k, sizeof(TmapKey)) == 0) {
+        *out = e.map;
+        return SVDQ_OK;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    SVDQ_CHECK_ARG(aligned(base, 16) && row_bytes % 16 == 0, "tensor map: base and row pitch must be 16-byte aligned");
-    const cuuint64_t dims[2] = {inner, rows};
-    const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {box_inner, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, static_cast<CUtensorMapDataType>(elem), 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(&e.map, static_cast<CUtensorMapDataType>(k.elem), static_cast<cuuint32_t>(k.rank), const_cast<void*>(k.base),
+                          k.dims, k.strides, k.box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          k.swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    if (r != CUDA_SUCCESS) {
+        e.valid = false;
+        return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled (%d-D) failed with CUresult %d", k.rank, static_cast<int>(r));
+    }
+    e.key = k;
+    e.valid = true;
+    *out = e.map;
     return SVDQ_OK;
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem, uint64_t inner, uint64_t rows, uint64_t row_bytes,
+                 uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+    SVDQ_CHECK_ARG(aligned(base, 16) && row_bytes % 16 == 0, "tensor map: base and row pitch must be 16-byte aligned");
+    TmapKey k;
+    std::memset(&k, 0, sizeof(k));   // padding bytes take part in the compare
+    k.base = base;
+    k.dims[0] = inner; k.dims[1] = rows;
+    k.strides[0] = row_bytes;
+    k.box[0] = box_inner; k.box[1] = box_rows;
+    k.elem = elem; k.rank = 2; k.swizzle = swizzle128 ? 1 : 0;
+    return cached_tmap(map, k);
 }
 
 int make_tmap_3d(CUtensorMap* map, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                  uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     SVDQ_CHECK_ARG(aligned(base, 16) && stride1_bytes % 16 == 0 && stride2_bytes % 16 == 0,
                    "tensor map: base and strides must be 16-byte aligned");
-    const cuuint64_t dims[3] = {d0, d1, d2};
-    const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
-    const cuuint32_t box[3] = {box0, box1, box2};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, static_cast<CUtensorMapDataType>(elem), 3, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", static_cast<int>(r));
-    return SVDQ_OK;
+    TmapKey k;
+    std::memset(&k, 0, sizeof(k));
+    k.base = base;
+    k.dims[0] = d0; k.dims[1] = d1; k.dims[2] = d2;
+    k.strides[0] = stride1_bytes; k.strides[1] = stride2_bytes;
+    k.box[0] = box0; k.box[1] = box1; k.box[2] = box2;
+    k.elem = elem; k.rank = 3; k.swizzle = 0;
+    return cached_tmap(map, k);
 }
 
 int check_gemm_common(const svdq_gemm_args* a) {
@@ -127,7 +212,7 @@ int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes) {
     if (!args || !bytes) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, "workspace_bytes: null argument");
     *bytes = 0;
     if (args->fp4 && args->qout) return svdq::gemm_nvfp4_workspace_bytes(args, bytes);
-    if (!args->fp4 && args->qout) return svdq::gemm_int4_workspace_bytes(args, bytes);
+    if (!args->fp4) return svdq::gemm_int4_workspace_bytes(args, bytes);   // always: per-row normalisation scratch
     return SVDQ_OK;
 }
 

@@ -46,6 +46,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "host_common.h"
@@ -96,6 +97,7 @@ struct GemmParams {
     const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
     const __nv_bfloat16* ascales_i4;   // INT4: activation group scales [K/64][M_pad]
     const uint8_t* act_i4;             // INT4: packed activation codes [M_pad][K/2], read directly by the converter warps
+    const float* row_scale;            // INT4: power of two taken out of each row's group scales [M_pad] (see int4_row_norm_kernel)
     int act_unsigned;                  // INT4: activation codes are u4
     const float* col_scale;   // [N]
     const float* col_bias;    // [N]
@@ -115,7 +117,16 @@ struct GemmParams {
     const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
     float* lora_partial;                // scratch [CTA][slots][128][Rn]
     int slots;
+#ifdef SVDQ_ABLATE
+    int ablate;   // timing experiments only (results are wrong): bit 0 no epilogue work, 1 no tcgen05.cp, 2 no scale loads,
+                  // 3 no MMAs, 4 no operand loads
+#endif
 };
+#ifdef SVDQ_ABLATE
+#define ABLATE(p, bit) ((p).ablate & (1 << (bit)))
+#else
+#define ABLATE(p, bit) false
+#endif
 
 struct GemmShared {
     uint64_t full[H_STAGES];        // leader: operand tiles and scale atoms of both CTAs have landed (8 arrivals + bytes)
@@ -215,9 +226,10 @@ __device__ __forceinline__ float2 act2(float2 v) {
 // One thread's 64 accumulator columns -> scale, bias, activation -> 64 bf16 (kept in `ow`) -> its row of the
 // 128B-swizzled staging tile.  The activation is a template parameter: selected per element at run time it put a
 // branch between every two values and kept the compiler from interleaving them.
-template <int ACT>
+// ROWSCALE: the accumulator is first multiplied by this row's power of two `rs` (INT4 operands are normalised per row).
+template <int ACT, bool ROWSCALE = false>
 __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const float4* cs, const float4* cb,
-                                            uint32_t (&ow)[32], uint8_t* buf, int lane) {
+                                            uint32_t (&ow)[32], uint8_t* buf, int lane, float rs = 1.0f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {   // 16-byte chunk j = columns 8j .. 8j+7 of this 64-column block
         const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
@@ -225,10 +237,14 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
         for (int i = 0; i < 2; ++i) {
             const float4 s4 = cs[2 * j + i];
             const float4 b4 = cb[2 * j + i];
-            const float2 v01 = act2<ACT>(__ffma2_rn(make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])),
-                                                     make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
-            const float2 v23 = act2<ACT>(__ffma2_rn(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])),
-                                                     make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
+            float2 a01 = make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1]));
+            float2 a23 = make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            if constexpr (ROWSCALE) {   // exact: a power of two
+                a01 = __fmul2_rn(a01, make_float2(rs, rs));
+                a23 = __fmul2_rn(a23, make_float2(rs, rs));
+            }
+            const float2 v01 = act2<ACT>(__ffma2_rn(a01, make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
+            const float2 v23 = act2<ACT>(__ffma2_rn(a23, make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
             __nv_bfloat162 p0 = __floats2bfloat162_rn(v01.x, v01.y);
             __nv_bfloat162 p1 = __floats2bfloat162_rn(v23.x, v23.y);
             ow[4 * j + 2 * i] = *reinterpret_cast<uint32_t*>(&p0);
@@ -364,6 +380,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint8_t* apk = p.act_i4 + static_cast<size_t>(m0 + r0) * pitch + hh * 16;
                     __nv_bfloat16 nxt[4];
                     uint4 wnxt[4];
+                    float inv[4];   // 1 / (this row's power-of-two normalisation): exact
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) inv[i] = __frcp_rn(__ldg(p.row_scale + m0 + r0 + 16 * i));
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : __nv_bfloat16(0.f);
@@ -394,8 +413,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         }
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            // code * scale must stay finite in fp16: |code| <= 15, so scales are capped at 4094
-                            const __half2 s2 = __float2half2_rn(fminf(__bfloat162float(cur[i]), 4094.f));
+                            // the row's largest group scale is in [1, 2) after normalisation, so |code * scale| < 30 in fp16
+                            const __half2 s2 = __float2half2_rn(__bfloat162float(cur[i]) * inv[i]);
                             const int row = r0 + 16 * i;
                             uint8_t* dst = st + row * 128;
                             const int sw = row & 7;
@@ -464,7 +483,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
                 const bool lowrank = ks >= kstages;
                 const int kx = lowrank ? (ks - kstages) * 32 : ks * 128;
-                if (elect_one()) {
+                if ((role < 2 && ABLATE(p, 4)) || (role >= 2 && ABLATE(p, 2))) {
+                    if (elect_one()) mbar_arrive_cluster(lfull);
+                } else if (elect_one()) {
                     if (role == 0) {
                         mbar_arrive_expect_tx_cluster(lfull, G_A_BYTES);
                         tma_load_2d_pair(st, lowrank ? &tm_la : &tm_a, lfull, kx, m0);
@@ -537,11 +558,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             if (nkb == 4) {
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
-                                    tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
-                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
-                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
-                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
-                                                      t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
+                                    if (!ABLATE(p, 1)) {
+                                        tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
+                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
+                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
+                                    }
+                                    if (!ABLATE(p, 3))
+                                        tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
+                                                          t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
                                 }
                             } else {
                                 for (int j = 0; j < nkb; ++j) {
@@ -700,9 +724,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
             const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
+            float rowsc = 1.0f;
+            if constexpr (I4) rowsc = __ldg(p.row_scale + grow);
 #pragma unroll 1
             for (int h = 0; h < G_BN / 64; ++h) {
-                if (n0 + h * 64 >= p.N) break;
+                if (n0 + h * 64 >= p.N || ABLATE(p, 0)) break;
                 if (SETS == 2 && ((h + ti) & 1) != eset) continue;   // the other warp of this quadrant takes it
                 uint32_t r0[32], r1[32];
                 tc_ld_32x32b_x32(taddr + h * 64, r0);
@@ -718,11 +744,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
                 if constexpr (RTN > 0) {
                     // the reference's requantising branch always applies GELU (gemm_w4a4_launch_impl.cuh:282-309)
-                    stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
+                    stage_chunk<SVDQ_ACT_GELU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
                 } else {
-                    if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU>(r0, r1, cs, cb, ow, buf, lane);
-                    else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU>(r0, r1, cs, cb, ow, buf, lane);
-                    else stage_chunk<SVDQ_ACT_NONE>(r0, r1, cs, cb, ow, buf, lane);
+                    if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    else stage_chunk<SVDQ_ACT_NONE, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -852,6 +878,35 @@ lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict_
     }
 }
 
+// INT4 activations reach the tensor core as fp16(code * group scale).  fp16 has 5 exponent bits, bf16 scales have 8: a
+// power of two is taken out of every ROW first (2^e with the row's largest group scale / 2^e in [1, 2)), the accumulator
+// is multiplied by it again in the epilogue.  So no scale is clamped and only groups more than 2^14 below their row's
+// largest lose bits.  The low-rank activations share the accumulator and are divided by the same factor (into scratch).
+// One CTA per 128 rows: thread = row for the maximum, then all threads copy the block's low-rank rows.
+__global__ void __launch_bounds__(128)
+int4_row_norm_kernel(const __nv_bfloat16* __restrict__ ascales, int KB, int M_pad, const float* __restrict__ lora_in, int R,
+                     float* __restrict__ row_scale, float* __restrict__ lora_out) {
+    __shared__ float inv[128];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 128 + threadIdx.x;
+    float mx = 0.f;
+    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(__bfloat162float(ascales[static_cast<size_t>(g) * M_pad + row])));
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) {
+        (void)frexpf(mx, &e);   // mx = f * 2^e, f in [0.5, 1)
+        e -= 1;
+    }
+    e = max(-120, min(120, e));
+    row_scale[row] = ldexpf(1.0f, e);
+    inv[threadIdx.x] = ldexpf(1.0f, -e);
+    __syncthreads();
+    if (lora_in != nullptr) {
+        const size_t base = static_cast<size_t>(blockIdx.x) * 128 * R;
+        for (int i = threadIdx.x; i < 128 * R; i += 128) lora_out[base + i] = lora_in[base + i] * inv[i / R];
+    }
+}
+
 struct NvfpPlan {
     int requant, tiles_m, tiles_n, npairs, run, slots, rn;   // tiles are 256 x 192 pair tiles
     size_t workspace;
@@ -878,9 +933,8 @@ static inline bool n_out_ok(const svdq_gemm_args* a) {
 }
 
 int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
-    int dev = 0, sms = 0;
-    SVDQ_CUDA(cudaGetDevice(&dev));
-    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
     NvfpPlan pl;
     plan_nvfp4(a, sms, &pl);
     *bytes = pl.workspace;
@@ -891,14 +945,8 @@ template <int RTN, bool I4>
 static int launch_pair(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
                         const CUtensorMap& lu, const CUtensorMap& o, const CUtensorMap& sfa, const CUtensorMap& sfb,
                         const GemmParams& p) {
-    static bool attr_done[64] = {};
-    int dev = 0;
-    SVDQ_CUDA(cudaGetDevice(&dev));
-    if (dev < 64 && !attr_done[dev]) {
-        SVDQ_CUDA(cudaFuncSetAttribute(gemm_w4a4_kernel<RTN, I4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem_bytes<I4>())));
-        attr_done[dev] = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};
+    if (int rc = ensure_dynamic_smem(gemm_w4a4_kernel<RTN, I4>, smem_bytes<I4>(), attr_done)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);   // 2 CTAs per pair
     cfg.blockDim = dim3(cta_threads<RTN, I4>(), 1, 1);
@@ -940,9 +988,8 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
             return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
     }
 
-    int dev = 0, sms = 0;
-    SVDQ_CUDA(cudaGetDevice(&dev));
-    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
     NvfpPlan pl;
     plan_nvfp4(a, sms, &pl);
     SVDQ_CHECK_ARG(!requant || (a->workspace && a->workspace_bytes >= pl.workspace),
@@ -970,6 +1017,9 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
     p.lora_partial = static_cast<float*>(a->workspace);
     p.slots = pl.slots;
+#ifdef SVDQ_ABLATE
+    if (const char* e = getenv("SVDQ_ABLATE")) p.ablate = atoi(e);
+#endif
     if (int rc = status_words(&p.status)) return rc;
 
     CUtensorMap tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb;
@@ -1023,11 +1073,26 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 // per group on the SIMT pipes costs M*N*K/64 multiply-adds plus as many TMEM reads.  Both operands are therefore turned
 // into fp16 numbers that already carry their group scale - the weights once at preparation time, the activations by
 // converter warps as the packed codes arrive in shared memory - and the same pair kernel runs kind::f16 MMAs into one
-// fp32 accumulator.  code * scale is exact in fp16 (4 + 8 significant bits), every product is exact in fp32, so the
+// fp32 accumulator.  A signed code has at most 3 significant bits and a bf16 scale 8, so code * scale is exact in fp16
+// (11 bits); an unsigned code (act_unsigned, up to 15) has 4, and an odd code >= 9 times a scale with a full mantissa is
+// rounded by at most 2^-12 relative.  Every product of two fp16 operands is exact in fp32, so apart from that rounding the
 // only difference to the integer formulation is the order of fp32 additions.  (The reference adds the per-group terms
-// in bf16.)  Activation scales above 4094 are capped so that code * scale stays finite in fp16.
+// in bf16.)  Range: a power of two is taken out of every activation row and every weight column beforehand and put
+// back in the epilogue (int4_row_norm_kernel, prepare.cu), so nothing is clamped.
 // ---------------------------------------------------------------------------------------------------
-int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) { return gemm_nvfp4_workspace_bytes(a, bytes); }
+// scratch of the INT4 GEMM: [row scales M_pad fp32 | normalised low-rank activations M_pad x R fp32 | LoRA-down partials]
+static inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+static inline size_t int4_rows_bytes(const svdq_gemm_args* a) { return align256(static_cast<size_t>(a->M_pad) * 4); }
+static inline size_t int4_lora_bytes(const svdq_gemm_args* a) { return align256(static_cast<size_t>(a->M_pad) * a->R * 4); }
+
+int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
+    size_t partials = 0;
+    if (a->qout) {
+        if (int rc = gemm_nvfp4_workspace_bytes(a, &partials)) return rc;
+    }
+    *bytes = int4_rows_bytes(a) + int4_lora_bytes(a) + partials;
+    return SVDQ_OK;
+}
 
 int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     const bool requant = a->qout != nullptr;
@@ -1051,16 +1116,20 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     SVDQ_CHECK_ARG(n_out_ok(a), "gemm: N_out (%d) must be a multiple of 8 with N - 128 < N_out <= N (%d)", a->N_out, a->N);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
 
-    int dev = 0, sms = 0;
-    SVDQ_CUDA(cudaGetDevice(&dev));
-    SVDQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    if (int rc = sm_count(&sms)) return rc;
     NvfpPlan pl;
     plan_nvfp4(a, sms, &pl);
-    SVDQ_CHECK_ARG(!requant || (a->workspace && a->workspace_bytes >= pl.workspace),
-                   "gemm(int4): workspace of %zu bytes required (svdq_gemm_w4a4_workspace_bytes)", pl.workspace);
+    const size_t need = int4_rows_bytes(a) + int4_lora_bytes(a) + pl.workspace;
+    SVDQ_CHECK_ARG(a->workspace && a->workspace_bytes >= need && aligned(a->workspace, 256),
+                   "gemm(int4): a 256-byte aligned workspace of %zu bytes is required (svdq_gemm_w4a4_workspace_bytes)", need);
+    float* row_scale = static_cast<float*>(a->workspace);
+    float* lora_scaled = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + int4_rows_bytes(a));
+    float* partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + int4_rows_bytes(a) + int4_lora_bytes(a));
 
     GemmParams p = {};
     p.ascales_i4 = static_cast<const __nv_bfloat16*>(a->ascales);
+    p.row_scale = row_scale;
     p.act_i4 = static_cast<const uint8_t*>(a->act);
     p.act_unsigned = a->act_unsigned;
     p.col_scale = a->w.col_scale;
@@ -1080,7 +1149,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.oscales = static_cast<uint8_t*>(a->oscales);
     p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
-    p.lora_partial = static_cast<float*>(a->workspace);
+    p.lora_partial = partials;
     p.slots = pl.slots;
     if (int rc = status_words(&p.status)) return rc;
 
@@ -1091,7 +1160,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         return rc;
     if (a->R > 0) {
         const int R32 = (a->R + 31) / 32 * 32;
-        if (int rc = make_tmap_2d(&tm_la, a->lora_act_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
+        if (int rc = make_tmap_2d(&tm_la, lora_scaled, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a->R, a->M_pad,
                                   static_cast<uint64_t>(a->R) * 4, 32, G_BM))
             return rc;
         if (int rc = make_tmap_2d(&tm_lu, a->w.lora_up, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, R32, a->N,
@@ -1106,6 +1175,19 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
             return rc;
     } else {
         tm_out = tm_b;
+    }
+    {   // per-row normalisation of the activation scales (and of the low-rank activations that share the accumulator)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(a->M_pad / 128, 1, 1);
+        cfg.blockDim = dim3(128, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        SVDQ_CUDA(cudaLaunchKernelEx(&cfg, int4_row_norm_kernel, p.ascales_i4, a->K / 64, a->M_pad,
+                                     a->R > 0 ? a->lora_act_in : static_cast<const float*>(nullptr), a->R, row_scale, lora_scaled));
     }
     int rc;
     if (!requant) rc = launch_pair<0, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
@@ -1124,7 +1206,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 }  // namespace svdq
 
 // ---------------------------------------------------------------------------------------------------
-// svdq_gemm_w4a4_static_scratch: the requantising NVFP4 GEMM for hosts that have no way to hand over a
+// svdq_gemm_w4a4_static_scratch: the requantising GEMM (either precision) for hosts that have no way to hand over a
 // workspace.  Think of a C or C++ serving loop that carved up its device memory once at start-up and has no
 // allocator to ask per call, of a host whose policy forbids allocation calls after initialisation (they can
 // synchronise the device), or of an op layer that is only ever given the operator's tensors.  For them the
@@ -1134,6 +1216,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
 // loads this library, held until the process exits.  On the host its name is only a handle, not an address,
 // so the device address is looked up with cudaGetSymbolAddress - once per device, on the first call made with
 // that device current.  That first call per device should therefore happen before any stream capture begins.
+// (The cached address belongs to the device's context of that moment; it is stale after a cudaDeviceReset.)
 // Nothing is allocated or freed, here or in anything this calls.
 //
 // All calls share the one array.  Every partial a launch reads was written earlier by the same launch, so
@@ -1166,10 +1249,10 @@ static int static_scratch_ptr(void** out) {
 extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* stream) {
     using namespace svdq;
     if (int rc = check_gemm_common(args)) return rc;
-    if (!args->fp4)
-        return fail(SVDQ_ERR_UNSUPPORTED, "gemm(static scratch): only the NVFP4 GEMM has a variant with library-owned scratch");
     size_t need = 0;
-    if (args->qout) {
+    if (!args->fp4) {
+        if (int rc = gemm_int4_workspace_bytes(args, &need)) return rc;
+    } else if (args->qout) {
         if (int rc = gemm_nvfp4_workspace_bytes(args, &need)) return rc;
     }
     if (need > SVDQ_STATIC_SCRATCH_BYTES)
@@ -1182,7 +1265,8 @@ extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* s
     svdq_gemm_args local = *args;
     local.workspace = scratch;
     local.workspace_bytes = SVDQ_STATIC_SCRATCH_BYTES;
-    return gemm_nvfp4_impl(&local, static_cast<cudaStream_t>(stream));
+    if (local.fp4) return gemm_nvfp4_impl(&local, static_cast<cudaStream_t>(stream));
+    return gemm_int4_impl(&local, static_cast<cudaStream_t>(stream));
 }
 
 

@@ -4,9 +4,11 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 #include <string>
 
 #include "../../include/svdq_b200.h"
@@ -43,8 +45,31 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 // Checks that the current device is compute capability 10.x (B200 / GB200).
 int check_arch();
 
-// Device pointer to the library's status words {code, detail} on the current device.
+// Highest device ordinal + 1 the per-device caches cover; beyond it entry points return SVDQ_ERR_UNSUPPORTED.
+constexpr int SVDQ_MAX_DEVICES = 64;
+
+// Device pointer to the library's status words {code, detail} on the current device (cached per device).
 int status_words(int** ptr);
+// SM count / ordinal of the current device (cached per device; the ordinal is checked against SVDQ_MAX_DEVICES).
+int sm_count(int* sms);
+int current_device(int* dev);
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device): `done` is a function-local static
+// bit mask, one bit per device ordinal, guarded by one mutex for all kernels (set-up only happens a few times).
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, size_t bytes, std::atomic<uint64_t>& done) {
+    int dev = 0;
+    if (int rc = current_device(&dev)) return rc;
+    const uint64_t bit = 1ull << dev;
+    if (done.load(std::memory_order_acquire) & bit) return SVDQ_OK;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.load(std::memory_order_relaxed) & bit) return SVDQ_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e != cudaSuccess) return fail(SVDQ_ERR_CUDA, "cudaFuncSetAttribute(max dynamic shared memory = %zu) failed: %s", bytes, cudaGetErrorString(e));
+    done.fetch_or(bit, std::memory_order_release);
+    return SVDQ_OK;
+}
 
 // 2-D tiled tensor map: inner dimension contiguous, `row_bytes` between rows.
 // `elem` is a CUtensorMapDataType, box_inner*elem_size must be <= 128 with 128B swizzle.

@@ -25,7 +25,7 @@ constexpr int LA_U = 16;                         // tokens a warp has in flight
 
 __global__ void __launch_bounds__(LA_WARPS * 32)
 litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, float* __restrict__ vk_out,
-              int tokens, int heads, float eps) {
+              int tokens, int heads, float eps, int mode) {
     __shared__ __align__(16) float part[LA_WARPS][LA_HD + 1][LA_HD];   // 33.8 KB
     __shared__ __align__(16) float vk[LA_HD + 1][LA_HD];
     const int h = blockIdx.x, b = blockIdx.y;
@@ -34,6 +34,14 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
     const size_t pitch = static_cast<size_t>(3) * D;
     const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * tokens * pitch;
     const __nv_bfloat16* kv = base + D + 64 * h;
+    // mode 0: everything.  The reference does it in two launches, and the two halves exist on their own for callers
+    // that follow it: mode 1 = what its GEMM epilogue leaves behind (vk, and relu(Q) as bf16 in `out`), mode 2 = its
+    // vk_mul_q_kernel (reads relu(Q) from `out` and vk from `vk_out`, finishes `out` in place; qkv is not read).
+    if (mode == 2) {
+        for (int i = threadIdx.x; i < (LA_HD + 1) * LA_HD; i += LA_WARPS * 32)
+            vk[i >> 5][i & 31] = vk_out[(static_cast<size_t>(b) * heads + h) * (LA_HD + 1) * LA_HD + i];
+        __syncthreads();
+    } else {
 
     // phase 1: a warp takes runs of LA_U consecutive tokens; lane = column c of K;
     // acc[r] = sum over the warp's tokens of V[tok, r] * relu(K[tok, c]).  V goes through a warp-private fp32 slab of
@@ -86,11 +94,29 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
         if (vk_out) vk_out[(static_cast<size_t>(b) * heads + h) * (LA_HD + 1) * LA_HD + i] = s;
     }
     __syncthreads();
+    }
+    if (mode == 1) {   // relu(Q) of this head -> out, 16 bytes per thread and step
+        for (int i = threadIdx.x; i < tokens * 4; i += LA_WARPS * 32) {
+            const int t = i >> 2, j = i & 3;
+            const uint4 w = reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h)[j];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 r = __floats2bfloat162_rn(fmaxf(__uint_as_float(ww[e] << 16), 0.f),
+                                                               fmaxf(__uint_as_float(ww[e] & 0xffff0000u), 0.f));
+                o[e] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+            reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)[j] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
 
     // phase 2: two tokens per thread (t and t + 256); q stays in registers, every vk row comes once as 16-byte
     // broadcasts from shared memory and serves both tokens
     auto load_q = [&](int t, float* q) {
-        const uint4* qp = reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h);
+        const uint4* qp = mode == 2 ? reinterpret_cast<const uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)
+                                    : reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint4 w = qp[j];
@@ -154,13 +180,14 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
 
 extern "C" int svdq_litela(const svdq_litela_args* a, void* stream) {
     using namespace svdq;
-    SVDQ_CHECK_ARG(a && a->qkv && a->out, "litela: null pointer");
+    SVDQ_CHECK_ARG(a && a->out && (a->qkv || a->mode == 2) && (a->vk || a->mode == 0), "litela: null pointer");
+    SVDQ_CHECK_ARG(a->mode >= 0 && a->mode <= 2, "litela: mode must be 0 (all), 1 (vk and relu(Q) only) or 2 (finish from vk)");
     SVDQ_CHECK_ARG(a->batches > 0 && a->batches <= 65535 && a->tokens > 0 && a->heads > 0,
                    "litela: batches (%d, at most 65535), tokens (%d) and heads (%d) must be positive", a->batches, a->tokens, a->heads);
     SVDQ_CHECK_ARG(aligned(a->qkv, 16) && aligned(a->out, 16) && aligned(a->vk, 16), "litela: tensors must be 16-byte aligned");
     if (int rc = check_arch()) return rc;
     litela_kernel<<<dim3(a->heads, a->batches), LA_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(a->qkv), static_cast<__nv_bfloat16*>(a->out), a->vk, a->tokens, a->heads, a->eps);
+        static_cast<const __nv_bfloat16*>(a->qkv), static_cast<__nv_bfloat16*>(a->out), a->vk, a->tokens, a->heads, a->eps, a->mode);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }

@@ -28,40 +28,67 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&o);
 }
 
+// PACKED: the rotary table is the reference's fragment-packed fp32 tensor (pack_rotemb, nunchaku/models/embeddings.py:88-120):
+// for row m = 16 mb + 8 h + g and column pair p = 4 j + t, {sin, cos} sit at ((((mb*16 + j)*8 + g)*4 + t)*2 + h)*2.
+// SPLIT: instead of working in place, write q, k (normalised + rotated) and v (copied) head-major to
+// out_q / out_k / out_v [batch, heads, tokens_pad, 128]; rows at or beyond attn_tokens (when given) become zeros.
+template <bool PACKED, bool SPLIT>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                     const float* __restrict__ cosp, const float* __restrict__ sinp, long long rows, int seq_len, int heads,
-                    float eps) {
+                    float eps, __nv_bfloat16* __restrict__ out_q, __nv_bfloat16* __restrict__ out_k,
+                    __nv_bfloat16* __restrict__ out_v, int tokens_pad, int attn_tokens) {
     const int lane = threadIdx.x & 31;
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
     const int dim = heads * 128;
-    const long long items = rows * heads * 2;    // (row, q|k, head)
+    constexpr int PARTS = SPLIT ? 3 : 2;
+    const long long items = rows * heads * PARTS;    // (row, q|k|v, head)
     // norm weights of this lane's 4 columns, for q and k
     const uint2 wq2 = *reinterpret_cast<const uint2*>(wq + lane * 4);
     const uint2 wk2 = *reinterpret_cast<const uint2*>(wk + lane * 4);
     for (long long it = warp; it < items; it += nwarps) {
-        const long long row = it / (heads * 2);
-        const int rem = static_cast<int>(it - row * heads * 2);
+        const long long row = it / (heads * PARTS);
+        const int rem = static_cast<int>(it - row * heads * PARTS);
         const int which = rem / heads, head = rem - which * heads;
         __nv_bfloat16* p = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + head * 128 + lane * 4;
-        const uint2 y = *reinterpret_cast<const uint2*>(p);
-        const float2 y0 = bf2(y.x), y1 = bf2(y.y);
-        float ss = y0.x * y0.x + y0.y * y0.y + y1.x * y1.x + y1.y * y1.y;
-#pragma unroll
-        for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-        const float coef = rsqrtf(ss * (1.0f / 128.0f) + eps);
-        const uint2 w = which ? wk2 : wq2;
-        const float2 w0 = bf2(w.x), w1 = bf2(w.y);
-        const float a0 = y0.x * (coef * w0.x), b0 = y0.y * (coef * w0.y);
-        const float a1 = y1.x * (coef * w1.x), b1 = y1.y * (coef * w1.y);
         const long long pos = row % seq_len;
-        const float2 c = *reinterpret_cast<const float2*>(cosp + pos * 64 + lane * 2);
-        const float2 s = *reinterpret_cast<const float2*>(sinp + pos * 64 + lane * 2);
-        uint2 o;
-        o.x = pack_bf2(a0 * c.x - b0 * s.x, a0 * s.x + b0 * c.x);
-        o.y = pack_bf2(a1 * c.y - b1 * s.y, a1 * s.y + b1 * c.y);
-        *reinterpret_cast<uint2*>(p) = o;
+        uint2 o = *reinterpret_cast<const uint2*>(p);
+        if (which < 2) {
+            const float2 y0 = bf2(o.x), y1 = bf2(o.y);
+            float ss = y0.x * y0.x + y0.y * y0.y + y1.x * y1.x + y1.y * y1.y;
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+            const float coef = rsqrtf(ss * (1.0f / 128.0f) + eps);
+            const uint2 w = which ? wk2 : wq2;
+            const float2 w0 = bf2(w.x), w1 = bf2(w.y);
+            const float a0 = y0.x * (coef * w0.x), b0 = y0.y * (coef * w0.y);
+            const float a1 = y1.x * (coef * w1.x), b1 = y1.y * (coef * w1.y);
+            float2 c, s;
+            if constexpr (PACKED) {
+                // pairs 2*lane and 2*lane + 1: j = lane / 2, t = 2 * (lane & 1) + {0, 1}
+                const long long mb = pos >> 4;
+                const int h = (pos >> 3) & 1, g = pos & 7;
+                const float* e = cosp + ((((mb * 16 + (lane >> 1)) * 8 + g) * 4 + 2 * (lane & 1)) * 2 + h) * 2;
+                const float2 sc0 = *reinterpret_cast<const float2*>(e);       // {sin, cos} of pair 2*lane
+                const float2 sc1 = *reinterpret_cast<const float2*>(e + 4);   // next t
+                s = make_float2(sc0.x, sc1.x);
+                c = make_float2(sc0.y, sc1.y);
+            } else {
+                c = *reinterpret_cast<const float2*>(cosp + pos * 64 + lane * 2);
+                s = *reinterpret_cast<const float2*>(sinp + pos * 64 + lane * 2);
+            }
+            o.x = pack_bf2(a0 * c.x - b0 * s.x, a0 * s.x + b0 * c.x);
+            o.y = pack_bf2(a1 * c.y - b1 * s.y, a1 * s.y + b1 * c.y);
+        }
+        if constexpr (SPLIT) {
+            if (attn_tokens > 0 && pos >= attn_tokens) o = make_uint2(0u, 0u);
+            __nv_bfloat16* dst = which == 0 ? out_q : which == 1 ? out_k : out_v;
+            const long long b = row / seq_len;
+            *reinterpret_cast<uint2*>(dst + ((b * heads + head) * tokens_pad + pos) * 128 + lane * 4) = o;
+        } else {
+            *reinterpret_cast<uint2*>(p) = o;
+        }
     }
 }
 
@@ -128,9 +155,8 @@ layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 }
 
 static int grid_for(long long warps_needed) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int sms = 148;
+    (void)sm_count(&sms);
     const long long blocks = (warps_needed + 7) / 8;
     const long long cap = static_cast<long long>(sms) * 8;
     return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
@@ -140,16 +166,32 @@ static int grid_for(long long warps_needed) {
 
 extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
     using namespace svdq;
-    SVDQ_CHECK_ARG(a && a->qkv && a->weight_q && a->weight_k && a->cos && a->sin, "qk_norm_rope: null pointer");
+    SVDQ_CHECK_ARG(a && a->qkv && a->weight_q && a->weight_k && ((a->cos && a->sin) || a->rotary_packed), "qk_norm_rope: null pointer");
     SVDQ_CHECK_ARG(a->rows > 0 && a->seq_len > 0 && a->heads > 0 && a->rows % a->seq_len == 0,
                    "qk_norm_rope: rows (%lld) must be a positive multiple of seq_len (%d)", static_cast<long long>(a->rows), a->seq_len);
-    SVDQ_CHECK_ARG(aligned(a->qkv, 16) && aligned(a->weight_q, 8) && aligned(a->weight_k, 8) && aligned(a->cos, 8) && aligned(a->sin, 8),
+    SVDQ_CHECK_ARG(aligned(a->qkv, 16) && aligned(a->weight_q, 8) && aligned(a->weight_k, 8) && aligned(a->cos, 8) && aligned(a->sin, 8) &&
+                       aligned(a->rotary_packed, 16) && aligned(a->out_q, 16) && aligned(a->out_k, 16) && aligned(a->out_v, 16),
                    "qk_norm_rope: misaligned tensor");
+    SVDQ_CHECK_ARG(!a->rotary_packed || a->seq_len % 16 == 0, "qk_norm_rope: a packed rotary table has a multiple of 16 rows (got %d)", a->seq_len);
+    const bool split = a->out_q || a->out_k || a->out_v;
+    SVDQ_CHECK_ARG(!split || (a->out_q && a->out_k && a->out_v && a->tokens_pad >= a->seq_len && a->attn_tokens >= 0 &&
+                              a->attn_tokens <= a->seq_len),
+                   "qk_norm_rope: out_q, out_k and out_v go together, with tokens_pad >= seq_len and 0 <= attn_tokens <= seq_len");
     if (int rc = check_arch()) return rc;
-    const long long items = static_cast<long long>(a->rows) * a->heads * 2;
-    qk_norm_rope_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16*>(a->qkv), static_cast<const __nv_bfloat16*>(a->weight_q),
-        static_cast<const __nv_bfloat16*>(a->weight_k), a->cos, a->sin, a->rows, a->seq_len, a->heads, a->eps);
+    const long long items = static_cast<long long>(a->rows) * a->heads * (split ? 3 : 2);
+    const float* tab = a->rotary_packed ? a->rotary_packed : a->cos;
+    auto launch = [&](auto kernel) {
+        kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<__nv_bfloat16*>(a->qkv), static_cast<const __nv_bfloat16*>(a->weight_q),
+            static_cast<const __nv_bfloat16*>(a->weight_k), tab, a->sin, a->rows, a->seq_len, a->heads, a->eps,
+            static_cast<__nv_bfloat16*>(a->out_q), static_cast<__nv_bfloat16*>(a->out_k), static_cast<__nv_bfloat16*>(a->out_v),
+            a->tokens_pad, a->attn_tokens);
+    };
+    if (a->rotary_packed) {
+        if (split) launch(qk_norm_rope_kernel<true, true>); else launch(qk_norm_rope_kernel<true, false>);
+    } else {
+        if (split) launch(qk_norm_rope_kernel<false, true>); else launch(qk_norm_rope_kernel<false, false>);
+    }
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }

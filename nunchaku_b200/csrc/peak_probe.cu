@@ -98,7 +98,7 @@ mma_rate_kernel(int kind, int n, int iters, int cps_per_group, int sf_buffers, i
 // The same loop on a CTA pair: cluster of 2, TMEM allocated with cta_group::2 by both CTAs, the even CTA
 // issues 256-row MMAs (each CTA's tensor core does 128 x n), the completion is multicast to both.
 __global__ void __launch_bounds__(64, 1)
-mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status) {
+mma_rate_pair_kernel(int kind, int n, int iters, int cps_per_group, long long* cycles, int* status) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int STAGE = 48 * 1024;
@@ -128,8 +128,11 @@ mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status)
                 const uint64_t bdesc = smem_desc_sw128(sa + 16384);
                 const uint32_t t_sf = tmem + 384;
                 if (elect_one()) {
+                    // the scale-factor copies a block-scaled stage needs, interleaved with the MMAs as in the GEMM
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        for (int c = 0; c * 4 < cps_per_group; ++c)
+                            if (c * 4 + j < cps_per_group) tc_cp_pair_32x128b_warpx4(t_sf + 4 * (c * 4 + j), smem_desc_sf(sa + 40960 + (c * 4 + j) * 512));
                         if (kind == 0)
                             tc_mma_pair_nvfp4(tmem, adesc + 2 * j, bdesc + 2 * j, idesc, t_sf + 4 * j, t_sf + 16 + 8 * j, 1);
                         else if (kind == 3)
@@ -172,149 +175,13 @@ mma_rate_pair_kernel(int kind, int n, int iters, long long* cycles, int* status)
     }
 }
 
-// L2 -> shared-memory ingest probe: one thread per CTA keeps `depth` bulk copies of `chunk` bytes in
-// flight from a buffer that fits in L2, and reports the cycles for `iters` chunks.  Run with few and
-// with all SMs it tells a per-SM port limit from an aggregate L2 limit.
-__global__ void __launch_bounds__(256, 1)
-ingest_rate_kernel(const uint8_t* src, size_t src_bytes, int chunk, int depth, int iters, long long* cycles, int* status) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    // every warp is an independent issuer with its own ring of `depth` stages
-    const int issuers = blockDim.x / 32, w = threadIdx.x / 32;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(issuers) * depth * chunk) + w * depth;
-    smem += static_cast<size_t>(w) * depth * chunk;
-    if ((threadIdx.x & 31) == 0) {
-        for (int s = 0; s < depth; ++s) mbar_init(&full[s], 1);
-        fence_mbar_init();
-    }
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) {
-        const size_t nchunks = src_bytes / chunk;
-        size_t pos = (static_cast<size_t>(blockIdx.x * issuers + w) * 7919) % nchunks;
-        const long long t0 = clock64();
-        bool ok = true;
-        for (int it = 0; it < iters + depth && ok; ++it) {
-            const int s = it % depth;
-            if (it >= depth) ok = mbar_wait(&full[s], ((it / depth) - 1) & 1);
-            if (it < iters && ok) {
-                mbar_arrive_expect_tx(&full[s], chunk);
-                bulk_load(smem + static_cast<size_t>(s) * chunk, src + pos * chunk, chunk, &full[s]);
-                pos = pos + 1 == nchunks ? 0 : pos + 1;
-            }
-        }
-        if (!ok) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
-        if (w == 0) cycles[blockIdx.x] = clock64() - t0;
-    }
-}
-
-// The same for 2-D tiled TMA loads: boxes of 128 bytes x `box_rows` rows (128B swizzle) from a row-major
-// byte matrix of `pitch` bytes per row, walked along the row first (the access pattern of a K-major GEMM
-// operand).  Every warp is an issuer with its own ring.
-__global__ void __launch_bounds__(256, 1)
-ingest_tensor_kernel(const __grid_constant__ CUtensorMap tm, int pitch, int rows, int box_rows, int depth, int iters,
-                     int mode, long long* cycles, int* status) {
-    // mode 0: plain loads.  Modes 1 and 2 need a cluster of 2 and use the cta_group::2 form of the load, counting
-    // completion on the CTA's own barrier (1) or on the barrier at the same offset in the other CTA (2).
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int issuers = blockDim.x / 32, w = threadIdx.x / 32;
-    const int chunk = box_rows * 128;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(issuers) * depth * chunk) + w * depth;
-    smem += static_cast<size_t>(w) * depth * chunk;
-    if ((threadIdx.x & 31) == 0) {
-        for (int s = 0; s < depth; ++s) mbar_init(&full[s], 1);
-        fence_mbar_init();
-    }
-    if (mode) cluster_sync_all(); else __syncthreads();
-    const uint32_t rank = mode ? cluster_ctarank() : 0;
-    const int kboxes = pitch / 128, rblocks = rows / box_rows;
-    int rb = (blockIdx.x * issuers + w) % rblocks, kb = 0;
-    const long long t0 = clock64();
-    bool ok = true;
-    for (int it = 0; it < iters + depth && ok; ++it) {
-        const int s = it % depth;
-        if (it >= depth) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ((it / depth) - 1) & 1));
-        if (it < iters && ok) {
-            if (elect_one()) {
-                if (mode == 0) {
-                    mbar_arrive_expect_tx(&full[s], chunk);
-                    tma_load_2d(smem + static_cast<size_t>(s) * chunk, &tm, &full[s], kb * 128, rb * box_rows);
-                } else {
-                    const uint32_t bar = mapa_shared(smem_u32(&full[s]), mode == 1 ? rank : rank ^ 1u);
-                    mbar_arrive_expect_tx_cluster(bar, chunk);
-                    tma_load_2d_pair(smem + static_cast<size_t>(s) * chunk, &tm, bar, kb * 128, rb * box_rows);
-                }
-            }
-            __syncwarp();
-            if (++kb == kboxes) {
-                kb = 0;
-                rb = (rb + gridDim.x * issuers) % rblocks;
-            }
-        }
-    }
-    if ((threadIdx.x & 31) == 0) {
-        if (!ok) atomicExch(&status[0], SVDQ_ERR_TIMEOUT);
-        if (w == 0) cycles[blockIdx.x] = clock64() - t0;
-    }
-    if (mode) cluster_sync_all();
-}
-
 }  // namespace svdq
 
-extern "C" int svdq_probe_ingest_tensor(const void* src, int pitch, int rows, int box_rows, int depth, int iters, int grid,
-                                        int issuers, long long* cycles, void* stream, int mode) {
-    using namespace svdq;
-    SVDQ_CHECK_ARG(src && cycles && grid > 0 && grid <= 1024 && iters > 0 && pitch >= 128 && pitch % 128 == 0 && box_rows >= 8 &&
-                       box_rows <= 256 && box_rows % 8 == 0 && rows % box_rows == 0 && depth >= 1 && issuers >= 1 && issuers <= 8 &&
-                       static_cast<size_t>(issuers) * depth * box_rows * 128 <= 200 * 1024,
-                   "tensor ingest probe: bad argument");
-    if (int rc = check_arch()) return rc;
-    int* status = nullptr;
-    if (int rc = status_words(&status)) return rc;
-    CUtensorMap tm;
-    if (int rc = make_tmap_2d(&tm, src, CU_TENSOR_MAP_DATA_TYPE_UINT8, pitch, rows, pitch, 128, box_rows)) return rc;
-    const size_t smem = 1024 + static_cast<size_t>(issuers) * depth * (box_rows * 128 + 8) + 64;
-    SVDQ_CUDA(cudaFuncSetAttribute(ingest_tensor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    SVDQ_CHECK_ARG(mode >= 0 && mode <= 2 && (mode == 0 || grid % 2 == 0), "tensor ingest probe: bad mode / odd grid");
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(32 * issuers, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = mode ? 1 : 0;
-    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, ingest_tensor_kernel, tm, pitch, rows, box_rows, depth, iters, mode, cycles, status));
-    return SVDQ_OK;
-}
-
-extern "C" int svdq_probe_ingest_rate(const void* src, size_t src_bytes, int chunk, int depth, int iters, int grid,
-                                      int issuers, long long* cycles, void* stream) {
-    using namespace svdq;
-    SVDQ_CHECK_ARG(src && cycles && grid > 0 && grid <= 1024 && iters > 0 && chunk >= 1024 && chunk % 1024 == 0 &&
-                       depth >= 1 && issuers >= 1 && issuers <= 8 &&
-                       static_cast<size_t>(issuers) * depth * chunk <= 200 * 1024 && src_bytes >= static_cast<size_t>(chunk),
-                   "ingest probe: bad argument");
-    if (int rc = check_arch()) return rc;
-    int* status = nullptr;
-    if (int rc = status_words(&status)) return rc;
-    const size_t smem = 1024 + static_cast<size_t>(issuers) * depth * (chunk + 8) + 64;
-    SVDQ_CUDA(cudaFuncSetAttribute(ingest_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    ingest_rate_kernel<<<grid, 32 * issuers, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(src), src_bytes, chunk,
-                                                                           depth, iters, cycles, status);
-    SVDQ_CUDA(cudaGetLastError());
-    return SVDQ_OK;
-}
-
 // kind 0 = mxf4nvf4, 1 = tf32, 3 = f16 (K = 16); grid must be even (CTA pairs).  No counterpart in the reference.
-extern "C" int svdq_probe_mma_rate_pair(int kind, int n, int iters, int grid, long long* cycles, void* stream) {
+extern "C" int svdq_probe_mma_rate_pair(int kind, int n, int iters, int grid, long long* cycles, void* stream, int cps_per_group) {
     using namespace svdq;
     SVDQ_CHECK_ARG(cycles && grid > 0 && grid <= 1024 && grid % 2 == 0 && iters > 0 && n >= 32 && n <= 256 && n % 32 == 0 &&
-                       (kind == 0 || kind == 1 || kind == 3),
+                       (kind == 0 || kind == 1 || kind == 3) && cps_per_group >= 0 && cps_per_group <= 12,
                    "pair probe: bad argument");
     if (int rc = check_arch()) return rc;
     int* status = nullptr;
@@ -333,7 +200,7 @@ extern "C" int svdq_probe_mma_rate_pair(int kind, int n, int iters, int grid, lo
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, mma_rate_pair_kernel, kind, n, iters, cycles, status));
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, mma_rate_pair_kernel, kind, n, iters, cps_per_group, cycles, status));
     return SVDQ_OK;
 }
 

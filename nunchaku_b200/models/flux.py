@@ -26,6 +26,7 @@ from torch import nn
 from ..ops.fused import fused_gelu_mlp, layernorm_modulate, qk_norm_rope
 from ..weights import quantize_linear
 from .linear import SVDQW4A4Linear
+from .random_init import random_w4a4_linear
 
 
 def _make_linear(in_f: int, out_f: int, precision: str | None, rank: int, device, dtype, std: float = 0.02):
@@ -239,19 +240,8 @@ class FluxTransformer(nn.Module):
                 child = getattr(mod, n, None)
                 if not isinstance(child, nn.Linear):
                     continue
-                dev = child.weight.device
-                q = SVDQW4A4Linear(child.in_features, child.out_features, rank=rank, bias=True, precision=precision,
-                                   torch_dtype=child.weight.dtype, device=dev)
-                q.qweight.copy_(torch.randint(-128, 128, q.qweight.shape, generator=g, device=dev, dtype=torch.int8))
-                if precision == "nvfp4":
-                    q.wscales.copy_(torch.full(q.wscales.shape, 2.0 ** -7, device=dev).to(torch.float8_e4m3fn))
-                else:
-                    q.wscales.fill_(0.005)
-                q.smooth_factor.fill_(1.0)
-                q.smooth_factor_orig.fill_(1.0)
-                q.proj_down.copy_(torch.randn(q.proj_down.shape, generator=g, device=dev) * 0.02)
-                q.proj_up.copy_(torch.randn(q.proj_up.shape, generator=g, device=dev) * 0.02)
-                q.bias.zero_()
+                q = random_w4a4_linear(child.in_features, child.out_features, rank, precision, True, g, child.weight.device,
+                                       child.weight.dtype)
                 setattr(mod, n, q)
         return self
 

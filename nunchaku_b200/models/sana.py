@@ -8,6 +8,8 @@ reference's: ``qkv_proj`` (its output feeds the linear attention kernel), ``out_
 ``q_linear`` and ``out_proj``, ``inverted_conv`` (SiLU fused into its GEMM epilogue) and ``point_conv`` (its quantiser
 gates the (value, gate) pairs: ``fuse_glu``).  The depthwise 3 x 3 convolution, cross attention (torch SDPA), the
 ``kv_linear`` of the caption and the modulation are plain bf16 torch ops, as they are outside the W4A4 path.
+``precision=None`` builds the same model from bf16 ``nn.Linear`` masters (the twin the quantised model is compared
+with in the tests); ``quantize_`` turns such a model into the W4A4 one.
 
 Padding as in the reference (``src/Linear.cpp:92-93``, ``SanaModel.cpp:15``): feature counts are rounded up to 128 for
 the 4-bit tensors (2240 -> 2304, 2 x 5600 -> 2 x 5632); activations keep their real width: the quantiser reads the missing
@@ -26,6 +28,7 @@ from ..ops.fused import layernorm_modulate, litela_attention
 from ..ops.gemm import svdq_gemm_w4a4_cuda
 from ..ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda
 from .linear import SVDQW4A4Linear
+from .random_init import random_w4a4_linear
 
 
 def _pad128(n: int) -> int:
@@ -33,33 +36,49 @@ def _pad128(n: int) -> int:
 
 
 def _random_w4a4(in_f: int, out_f: int, rank: int, precision: str, bias: bool, g: torch.Generator, device) -> SVDQW4A4Linear:
-    q = SVDQW4A4Linear(in_f, out_f, rank=rank, bias=bias, precision=precision, device=device)
-    with torch.no_grad():
-        q.qweight.copy_(torch.randint(-128, 128, q.qweight.shape, generator=g, device=device, dtype=torch.int16).to(torch.int8))
-        if precision == "nvfp4":
-            q.wscales.copy_(torch.full(q.wscales.shape, 2.0 ** -7, device=device).to(torch.float8_e4m3fn))
-        else:
-            q.wscales.fill_(0.005)
-        q.smooth_factor.fill_(1.0)
-        q.smooth_factor_orig.fill_(1.0)
-        q.proj_down.copy_(torch.randn(q.proj_down.shape, generator=g, device=device) * 0.02)
-        q.proj_up.copy_(torch.randn(q.proj_up.shape, generator=g, device=device) * 0.02)
-        if bias:
-            q.bias.zero_()
-    return q
+    return random_w4a4_linear(in_f, out_f, rank, precision, bias, g, device)
 
 
 class PaddedW4A4(nn.Module):
     """A W4A4 linear whose logical feature counts are not multiples of 128: the quantiser reads the missing input columns
-    as zeros and the GEMM's store drops the padded output columns (``K_in`` / ``N_out`` of the C ABI)."""
+    as zeros and the GEMM's store drops the padded output columns (``K_in`` / ``N_out`` of the C ABI).
+    With ``precision=None`` it holds the bf16 master ``nn.Linear`` instead (same call interface, plain torch arithmetic):
+    the model the quantised one is compared with; :meth:`quantize_` turns it into the W4A4 layer."""
 
-    def __init__(self, in_f, out_f, rank, precision, bias, g, device, keep_out_pad: bool = False):
+    def __init__(self, in_f, out_f, rank, precision, bias, g, device, keep_out_pad: bool = False, dtype=torch.bfloat16):
         super().__init__()
-        self.in_f, self.out_f, self.keep_out_pad = in_f, out_f, keep_out_pad
-        self.lin = _random_w4a4(_pad128(in_f), _pad128(out_f), rank, precision, bias, g, device)
+        self.in_f, self.out_f, self.keep_out_pad, self.rank = in_f, out_f, keep_out_pad, rank
+        self.lin = None
+        self.master = None
+        if precision is None:
+            self.master = nn.Linear(in_f, out_f, bias=bias, device=device, dtype=dtype)
+        else:
+            self.lin = _random_w4a4(_pad128(in_f), _pad128(out_f), rank, precision, bias, g, device)
+
+    @torch.no_grad()
+    def quantize_(self, precision: str):
+        """bf16 master -> SVDQuant W4A4 layer with feature counts padded to 128 (zero rows / columns)."""
+        from ..weights import quantize_linear
+
+        m = self.master
+        ip, op = _pad128(self.in_f), _pad128(self.out_f)
+        padded = nn.Linear(ip, op, bias=m.bias is not None, device=m.weight.device, dtype=m.weight.dtype)
+        padded.weight.zero_()
+        padded.weight[: self.out_f, : self.in_f] = m.weight
+        if m.bias is not None:
+            padded.bias.zero_()
+            padded.bias[: self.out_f] = m.bias
+        self.lin = quantize_linear(padded, None, rank=self.rank, precision=precision)
+        self.master = None
+        return self
 
     def forward(self, x: torch.Tensor, fuse_silu: bool = False, fuse_glu: bool = False) -> torch.Tensor:
         """x: [B, S, in_f] (or already padded; [B, S, 2*in_pad] of (value, gate) pairs with fuse_glu)."""
+        if self.master is not None:
+            if fuse_glu:
+                x = (x[..., 0::2].float() * F.silu(x[..., 1::2].float())).to(x.dtype)
+            y = self.master(x[..., : self.in_f])
+            return F.silu(y) if fuse_silu else y
         lin = self.lin
         B, S, C = x.shape
         q, s, la = svdq_quantize_w4a4_act_fuse_lora_cuda(
@@ -70,6 +89,19 @@ class PaddedW4A4(nn.Module):
                             bias=lin.bias, fp4=lin.precision == "nvfp4", alpha=lin.wtscale, wcscales=lin.wcscales,
                             fuse_silu=fuse_silu)
         return out.view(B, S, n_out)
+
+
+def _litela_torch(qkv: torch.Tensor, heads: int, eps: float = 1e-6) -> torch.Tensor:
+    """ReLU linear attention in plain torch (fp32), column order as the kernel's: [Q | (K_h, V_h) per head]."""
+    B, S, C = qkv.shape
+    D = heads * 32
+    q = qkv[..., :D].float().clamp_min(0).view(B, S, heads, 32)
+    kv = qkv[..., D:].float().view(B, S, heads, 64)
+    k, v = kv[..., :32].clamp_min(0), kv[..., 32:]
+    v1 = torch.cat([v, torch.ones_like(v[..., :1])], dim=-1)
+    vk = torch.einsum("bshr,bshc->bhrc", v1, k)
+    o = torch.einsum("bshc,bhrc->bshr", q, vk)
+    return (o[..., :32] / (o[..., 32:] + eps)).to(qkv.dtype).reshape(B, S, D)
 
 
 class SanaLinearAttention(nn.Module):
@@ -84,6 +116,8 @@ class SanaLinearAttention(nn.Module):
 
     def forward(self, x):
         qkv = self.qkv_proj(x)                                   # [B, S, 3 * dim_pad]
+        if self.qkv_proj.master is not None:
+            return self.out_proj(_litela_torch(qkv, self.heads))
         return self.out_proj(litela_attention(qkv.contiguous(), self.heads))
 
 
@@ -126,9 +160,9 @@ class SanaGLUMBConv(nn.Module):
         return self.point_conv(y, fuse_glu=True)
 
 
-def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
+def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, fused: bool = True) -> torch.Tensor:
     """layer_norm(x, eps 1e-6) * (1 + scale) + shift with scale / shift [B, C]: one row-wise kernel for the widths it is built for."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (256, 1024, 2240, 2304, 3072):
+    if fused and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (256, 1024, 2240, 2304, 3072):
         return layernorm_modulate(x.contiguous(), scale, shift, eps=1e-6)
     return F.layer_norm(x, x.shape[-1:], eps=1e-6) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
 
@@ -146,10 +180,11 @@ class SanaBlock(nn.Module):
     def forward(self, x, cond, t6, H, W):
         B, S, C = x.shape
         m = (self.scale_shift_table[None] + t6.view(B, 6, C)).unbind(1)   # shift, scale, gate (attention), shift, scale, gate (MLP)
-        n = _ln_mod(x, m[1], m[0])
+        fused = self.attn.qkv_proj.master is None
+        n = _ln_mod(x, m[1], m[0], fused)
         x = x + m[2].unsqueeze(1) * self.attn(n)
         x = x + self.cross_attn(x, cond)
-        n = _ln_mod(x, m[4], m[3])
+        n = _ln_mod(x, m[4], m[3], fused)
         return x + m[5].unsqueeze(1) * self.ff(n, H, W)
 
 
@@ -173,13 +208,22 @@ class SanaTransformer(nn.Module):
             for mod in self.modules():
                 if isinstance(mod, nn.Linear):
                     mod.weight.normal_(0.0, 0.02)
-                    mod.bias.zero_()
+                    if mod.bias is not None:
+                        mod.bias.zero_()
                 elif isinstance(mod, nn.Conv2d):
                     mod.weight.normal_(0.0, 0.1)
                     mod.bias.zero_()
 
     def w4a4_linears(self):
         return [m for m in self.modules() if isinstance(m, SVDQW4A4Linear)]
+
+    @torch.no_grad()
+    def quantize_(self, precision: str = "int4"):
+        """Turn every bf16 master projection of the blocks (a model built with ``precision=None``) into its W4A4 layer."""
+        for mod in self.modules():
+            if isinstance(mod, PaddedW4A4) and mod.master is not None:
+                mod.quantize_(precision)
+        return self
 
     def forward(self, latents, caption, timestep, img_hw: tuple[int, int]):
         """latents [B, H*W, C_in], caption [B, T, caption_dim], timestep [B]."""

@@ -1,81 +1,96 @@
-"""Step time of a SANA-1.6B-architecture linear DiT whose block linears run on the W4A4 path (INT4 group 64 by default).
+"""Step time of a SANA-1.6B-architecture linear DiT whose block linears run on the W4A4 path (INT4 group 64).
 
-    python -m nunchaku_b200.models.sana_bench [--batch 32] [--steps 5] [--precision int4]
+    python -m nunchaku_b200.models.sana_bench [--batch 32] [--reps 10]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \\
         -m nunchaku_b200.models.sana_bench --batch 32
 
-1024 x 1024 pixels = 32 x 32 latent tokens of 32 channels per image, 300 caption tokens; the global batch is sharded along
-the batch dimension over the ranks (no data-path collective).  Weights are random packed W4A4 parameters (no checkpoints
-offline).  Prints one JSON line on rank 0: image-steps per second over all ranks (time = max over ranks, CUDA events).
+1024 px = 32 x 32 latent tokens of 32 channels, 300 caption tokens; the global batch is sharded along the batch dimension
+over the ranks (no data-path collective).  Weights are random packed W4A4 parameters (no checkpoints offline).
+Prints one JSON line on rank 0.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import time
 
 import torch
 
 from .. import _lib
 from .. import distributed as D
 from .sana import SanaTransformer
+from .step_timing import device_time_split, timed_steps
+
+
+def run(global_batch: int = 32, reps: int = 10, warmup: int = 2, precision: str = "int4", blocks: int = 20, graph: bool = False,
+        split: bool = True) -> dict:
+    rank, world, local = D.init_from_env()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    if global_batch % world:
+        raise ValueError("the global batch must be a multiple of the number of ranks")
+    B = global_batch // world
+    torch.manual_seed(rank)
+    model = SanaTransformer(n_blocks=blocks, precision=precision, seed=rank, device=dev)
+    H = W = 32
+    lat = torch.randn(B, H * W, 32, device=dev, dtype=torch.bfloat16)
+    cap = torch.randn(B, 300, 2304, device=dev, dtype=torch.bfloat16)
+    t = torch.full((B,), 0.5, device=dev)
+    out = {}
+
+    def eager():
+        out["y"] = model(lat, cap, t, (H, W))
+
+    with torch.no_grad():
+        step = eager
+        if graph:
+            for _ in range(2):
+                eager()
+            y_eager = out["y"].clone()
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg):
+                eager()
+            cg.replay()
+            torch.cuda.synchronize()
+            if not torch.equal(out["y"], y_eager):
+                raise RuntimeError("graph replay differs from the eager forward")
+            step = cg.replay
+        D.barrier()
+        t_host = time.perf_counter()
+        ms, per_run = timed_steps(step, reps, warmup)
+        wall_ms = (time.perf_counter() - t_host) * 1e3 / (reps + warmup)
+        prof = device_time_split(eager) if (split and rank == 0) else None
+    ms_max = D.max_over_ranks(ms, dev)
+    ms_min = -D.max_over_ranks(-ms, dev)
+    status = _lib.device_status()
+    if status != (0, 0):
+        raise RuntimeError(f"device status {status}: a bounded wait ran out")
+    return {
+        "workload": f"SANA-1.6B-architecture linear DiT step, 1024px (1024 tokens), {blocks} blocks, {precision} W4A4 linears, "
+                    f"global batch {global_batch}",
+        "image_steps_per_s": global_batch / (ms_max * 1e-3), "ms_per_step": ms_max, "ms_per_step_min_rank": ms_min,
+        "per_gpu_batch": B, "global_batch": global_batch, "n_gpus": world, "scaling": "strong", "speedup_basis": "image_steps_per_s", "reps": reps, "warmup": warmup,
+        "protocol": "2 warm-ups, timed runs with CUDA events, fastest and slowest 20 % dropped, max over ranks",
+        "w4a4_linears": len(model.w4a4_linears()), "weights": "random packed W4A4", "host_ms_per_step": round(wall_ms, 2),
+        "cuda_graph": bool(graph), "finite": bool(torch.isfinite(out["y"]).all()), "device_time_split": prof,
+        "per_run_ms": [round(v, 2) for v in per_run],
+    }
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=32, help="global batch (images per step over all ranks)")
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=2)
-    ap.add_argument("--graph", action="store_true", help="capture one forward in a CUDA graph and time its replays "
-                    "(small per-GPU batches are bound by launch overhead otherwise)")
+    ap.add_argument("--graph", action="store_true", help="capture one forward in a CUDA graph and time its replays")
     ap.add_argument("--precision", default="int4", choices=["nvfp4", "int4"])
     ap.add_argument("--blocks", type=int, default=20)
     args = ap.parse_args()
     rank, world, local = D.init_from_env()
     torch.cuda.set_device(local)
-    if args.batch % world:
-        raise SystemExit("--batch must be a multiple of the number of ranks")
-    B = args.batch // world
-    torch.manual_seed(rank)
-    model = SanaTransformer(n_blocks=args.blocks, precision=args.precision, seed=rank)
-    H = W = 32
-    lat = torch.randn(B, H * W, 32, device="cuda", dtype=torch.bfloat16)
-    cap = torch.randn(B, 300, 2304, device="cuda", dtype=torch.bfloat16)
-    t = torch.full((B,), 0.5, device="cuda")
-    with torch.no_grad():
-        for _ in range(args.warmup):
-            y = model(lat, cap, t, (H, W))
-        graph = None
-        if args.graph:
-            # every prepared-weight cache and status word exists after the warm-up, so nothing allocates outside torch's
-            # capture-aware pool and nothing synchronises inside the captured region
-            y_eager = y.clone()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                y = model(lat, cap, t, (H, W))
-            graph.replay()
-            torch.cuda.synchronize()
-            if not torch.equal(y, y_eager):
-                raise SystemExit("graph replay differs from the eager forward")
-        D.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            if graph is not None:
-                graph.replay()
-            else:
-                y = model(lat, cap, t, (H, W))
-        e1.record()
-        torch.cuda.synchronize()
-    ms = D.max_over_ranks(e0.elapsed_time(e1) / args.steps, "cuda")
-    finite = bool(torch.isfinite(y).all())
-    assert _lib.device_status() == (0, 0)
+    rec = run(args.batch, args.reps, args.warmup, args.precision, args.blocks, args.graph)
     if rank == 0:
-        print(json.dumps({
-            "metric": "SANA-1.6B-architecture 1024px image-steps/s", "value": round(args.batch / ms * 1e3, 2), "ms_per_step": round(ms, 3),
-            "n_gpus": world, "global_batch": args.batch, "per_gpu_batch": B, "precision": args.precision, "blocks": args.blocks,
-            "w4a4_linears": len(model.w4a4_linears()), "finite": finite, "cuda_graph": bool(args.graph), "weights": "random packed W4A4", "scaling": "strong",
-        }))
+        print(json.dumps(rec))
+    D.barrier()
     D.shutdown()
 
 

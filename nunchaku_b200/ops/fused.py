@@ -1,9 +1,12 @@
 """Fused call patterns built from the two W4A4 ops (mirror of ``nunchaku/ops/fused.py``)."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
-from ..utils import ceil_divide
+from .. import _lib
+from ..utils import ceil_divide, on_device, ptr, require_cuda_contiguous, stream_ptr
 from .gemm import svdq_gemm_w4a4_cuda
 
 
@@ -34,6 +37,90 @@ def fused_gelu_mlp(x: torch.Tensor, fc1, fc2, pad_size: int = 256) -> torch.Tens
     return output.view(batch_size, seq_len, -1)
 
 
+def fused_qkv_norm_rottary(x: torch.Tensor, proj, norm_q, norm_k, rotary_emb: torch.Tensor,
+                           output: torch.Tensor | tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+                           attn_tokens: int = 0):
+    """Fused QKV projection + RMSNorm of q / k per head + rotary embedding (``nunchaku/ops/fused.py:50-110``, the
+    name is the reference's).  ``norm_q`` / ``norm_k`` are RMSNorm modules (their ``weight`` [128] is used),
+    ``rotary_emb`` is the packed fp32 tensor of ``pack_rotemb`` with ``shape[0] * shape[1]`` equal to the padded row
+    count.  ``output`` is a [rows, 3*dim] tensor (default: allocated), or a tuple ``(out_q, out_k, out_v)`` of
+    head-major [B, heads, tokens_pad, 128] tensors."""
+    batch_size, seq_len, channels = x.shape
+    x = x.view(batch_size * seq_len, channels)
+    quantized_x, ascales, lora_act = proj.quantize(x)
+    if output is None:
+        output = torch.empty(quantized_x.shape[0], proj.out_features, dtype=x.dtype, device=x.device)
+    common = dict(act=quantized_x, wgt=proj.qweight, ascales=ascales, wscales=proj.wscales, lora_act_in=lora_act,
+                  lora_up=proj.proj_up, bias=proj.bias, fp4=proj.precision == "nvfp4", alpha=proj.wtscale,
+                  wcscales=proj.wcscales, norm_q=norm_q.weight, norm_k=norm_k.weight, rotary_emb=rotary_emb)
+    if isinstance(output, tuple):
+        if len(output) != 3:
+            raise ValueError("output must be (out_q, out_k, out_v)")
+        svdq_gemm_w4a4_cuda(out_q=output[0], out_k=output[1], out_v=output[2], attn_tokens=attn_tokens, **common)
+        return output
+    svdq_gemm_w4a4_cuda(out=output, **common)
+    return output.view(batch_size, seq_len, -1)
+
+
+def _norm_rope_packed(qkv, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn_tokens: int) -> None:
+    """The RMSNorm + RoPE (+ head-major split) step of the QKV epilogue on the projection's bf16 tile ``qkv`` [rows, 3*dim],
+    with the reference's packed rotary tensor [B_r, M_r, 128] (B_r * M_r rows; the table repeats over ``qkv``'s rows)."""
+    require_cuda_contiguous("norm_q", norm_q, (torch.bfloat16,))
+    require_cuda_contiguous("norm_k", norm_k, (torch.bfloat16,))
+    require_cuda_contiguous("rotary_emb", rotary_emb, (torch.float32,))
+    if rotary_emb.dim() != 3 or rotary_emb.shape[2] != 128:
+        raise ValueError("rotary_emb must be the packed fp32 tensor [B, M, 128] (gemm_w4a4_launch_impl.cuh:351-354)")
+    rows = qkv.numel() // qkv.shape[-1]
+    table_rows = rotary_emb.shape[0] * rotary_emb.shape[1]
+    dim = qkv.shape[-1] // 3
+    if dim % 128 or rows % table_rows:
+        raise ValueError("the QKV width must be 3 * heads * 128 and the row count a multiple of the rotary table's rows")
+    heads = dim // 128
+    args = _lib.NormRopeArgs(qkv=ptr(qkv), weight_q=ptr(norm_q), weight_k=ptr(norm_k), cos=None, sin=None, rows=rows,
+                             seq_len=table_rows, heads=heads, eps=1e-6, rotary_packed=ptr(rotary_emb))
+    if out_q is not None:
+        for n, t in (("out_q", out_q), ("out_k", out_k), ("out_v", out_v)):
+            if t is None:
+                raise ValueError("out_q, out_k and out_v go together")
+            require_cuda_contiguous(n, t, (torch.bfloat16,))
+            if t.dim() != 4 or t.shape[1] != heads or t.shape[3] != 128 or t.shape[0] * table_rows != rows or t.shape[2] < table_rows:
+                raise ValueError(f"{n} must be [rows / table rows, heads, tokens_pad >= table rows, 128]")
+        args.out_q, args.out_k, args.out_v = ptr(out_q), ptr(out_k), ptr(out_v)
+        args.tokens_pad = out_q.shape[2]
+        args.attn_tokens = attn_tokens
+    _lib.check(_lib.load().svdq_qk_norm_rope(ctypes.byref(args), stream_ptr(qkv.device)))
+
+
+def _litela_epilogue(qkv: torch.Tensor, out_vk: torch.Tensor, out_linearattn: torch.Tensor) -> None:
+    """What ``EpilogueLiteLA`` leaves behind (gemm_w4a4_launch_impl.cuh:311-345): ``out_vk`` [B, heads, 33, 32] fp32 and
+    relu(Q) as bf16 in ``out_linearattn`` [B, tokens, N/3], from the projection's bf16 tile ``qkv`` [B*tokens, N]."""
+    require_cuda_contiguous("out_vk", out_vk, (torch.float32,))
+    require_cuda_contiguous("out_linearattn", out_linearattn, (torch.bfloat16,))
+    if out_vk.dim() != 4 or out_vk.shape[2:] != (33, 32) or out_linearattn.dim() != 3:
+        raise ValueError("out_vk must be [B, heads, 33, 32] and out_linearattn [B, tokens, N/3]")
+    B, heads = out_vk.shape[0], out_vk.shape[1]
+    tokens = out_linearattn.shape[1]
+    if heads * 96 != qkv.shape[-1] or out_linearattn.shape != (B, tokens, heads * 32) or qkv.numel() != B * tokens * heads * 96:
+        raise ValueError("linear attention: N must be 3 * heads * 32 and the rows B * tokens")
+    args = _lib.LiteLAArgs(qkv=ptr(qkv), out=ptr(out_linearattn), vk=ptr(out_vk), batches=B, tokens=tokens, heads=heads,
+                           eps=1e-6, mode=1)
+    _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(qkv.device)))
+
+
+def linearattn_vk_mul_q(q: torch.Tensor, vk: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """In place on ``q`` [B, tokens, heads*32] (relu(Q), bf16): ``o = q @ vk^T`` per head, ``q <- o[:32] / (o[32] + eps)``
+    (``linearattn_vk_mul_q``, gemm_w4a4_launch_impl.cuh:426-448; ``vk_mul_q_kernel``, epilogues.cuh:704-759)."""
+    require_cuda_contiguous("q", q, (torch.bfloat16,))
+    require_cuda_contiguous("vk", vk, (torch.float32,))
+    B, tokens, D = q.shape
+    if vk.shape != (B, D // 32, 33, 32):
+        raise ValueError("vk must be [B, heads, 33, 32]")
+    args = _lib.LiteLAArgs(qkv=None, out=ptr(q), vk=ptr(vk), batches=B, tokens=tokens, heads=D // 32, eps=eps, mode=2)
+    with on_device(q.device):
+        _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(q.device)))
+    return q
+
+
 def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                  heads: int, eps: float = 1e-6) -> torch.Tensor:
     """RMSNorm of q and k per 128-wide head and rotary embedding, in place on the output of a fused QKV projection
@@ -41,11 +128,6 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
 
     qkv: bf16 [B, S, 3*heads*128] (or [B*S, ...] with ``cos.shape[0]`` dividing the rows); cos, sin: fp32 [S, 64].
     """
-    import ctypes
-
-    from .. import _lib
-    from ..utils import ptr, require_cuda_contiguous, stream_ptr
-
     require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
     require_cuda_contiguous("weight_q", weight_q, (torch.bfloat16,))
     require_cuda_contiguous("weight_k", weight_k, (torch.bfloat16,))
@@ -56,7 +138,7 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
     rows = qkv.numel() // qkv.shape[-1]
     args = _lib.NormRopeArgs(qkv=ptr(qkv), weight_q=ptr(weight_q), weight_k=ptr(weight_k), cos=ptr(cos), sin=ptr(sin),
                              rows=rows, seq_len=cos.shape[0], heads=heads, eps=eps)
-    with torch.cuda.device(qkv.device):
+    with on_device(qkv.device):
         _lib.check(_lib.load().svdq_qk_norm_rope(ctypes.byref(args), stream_ptr(qkv.device)))
     return qkv
 
@@ -64,11 +146,6 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
 def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     """``layer_norm(x) * (1 + scale) + shift`` (no affine) for x bf16 [B, S, C] and per-batch scale / shift bf16 [B, C]
     (views into a wider modulation tensor are fine as long as rows are contiguous)."""
-    import ctypes
-
-    from .. import _lib
-    from ..utils import ptr, require_cuda_contiguous, stream_ptr
-
     require_cuda_contiguous("x", x, (torch.bfloat16,))
     B, S, C = x.shape
     if scale.shape != (B, C) or shift.shape != (B, C) or scale.stride(1) != 1 or shift.stride(1) != 1:
@@ -78,7 +155,7 @@ def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor
     out = torch.empty_like(x)
     args = _lib.LnModulateArgs(x=ptr(x), scale=scale.data_ptr(), shift=shift.data_ptr(), out=ptr(out), rows=B * S,
                                rows_per_batch=S, mod_stride=scale.stride(0) if B > 1 else max(scale.stride(0), C), cols=C, eps=eps)
-    with torch.cuda.device(x.device):
+    with on_device(x.device):
         _lib.check(_lib.load().svdq_layernorm_modulate(ctypes.byref(args), stream_ptr(x.device)))
     return out
 
@@ -89,11 +166,6 @@ def litela_attention(qkv: torch.Tensor, heads: int, eps: float = 1e-6, return_vk
 
     qkv: bf16 [B, S, 3*heads*32], columns [Q of all heads | (K_h, V_h) 64 per head].  Returns bf16 [B, S, heads*32]
     (and the fp32 ``vk`` [B, heads, 33, 32] when asked)."""
-    import ctypes
-
-    from .. import _lib
-    from ..utils import ptr, require_cuda_contiguous, stream_ptr
-
     require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
     if qkv.dim() != 3 or qkv.shape[-1] != 3 * heads * 32:
         raise ValueError("litela_attention: qkv must be [B, S, 3*heads*32]")
@@ -102,6 +174,6 @@ def litela_attention(qkv: torch.Tensor, heads: int, eps: float = 1e-6, return_vk
     vk = torch.empty(B, heads, 33, 32, dtype=torch.float32, device=qkv.device) if return_vk else None
     args = _lib.LiteLAArgs(qkv=ptr(qkv), out=ptr(out), vk=ptr(vk) if vk is not None else None, batches=B, tokens=S,
                            heads=heads, eps=eps)
-    with torch.cuda.device(qkv.device):
+    with on_device(qkv.device):
         _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(qkv.device)))
     return (out, vk) if return_vk else out

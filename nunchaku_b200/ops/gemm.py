@@ -3,39 +3,58 @@
 
 Weights arrive in the reference's packed order (the checkpoint format).  The sm_100a
 kernel streams K-major tiles with TMA, so each layer's weights are re-tiled once
-(`svdq_w4a4_prepare_weights`) and cached here, keyed by the identity of the packed
-parameter tensors.
+(`svdq_w4a4_prepare_weights`).  The re-tiled copy hangs off the packed ``qweight`` tensor
+itself (an attribute of the parameter object), so it lives and dies with the layer; it is
+rebuilt when any of the packed tensors is replaced or modified in place.  A write through
+``param.data`` does not bump the tensor's version counter: after such a write call
+:func:`invalidate_prepared` (``SVDQW4A4Linear`` does it when a state dict is loaded).
 """
 from __future__ import annotations
 
 import ctypes
 import math
-import weakref
+import threading
 
 import torch
 
 from .. import _lib
-from ..utils import default_act_layout, ptr, require_cuda_contiguous, stream_ptr
+from ..utils import default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr
+
+_ATTR = "_svdq_b200_prepared"
+_lock = threading.Lock()   # guards creation / replacement of a layer's prepared weights (the C entry points are re-entrant)
 
 
 class PreparedWeights:
-    """Device buffers holding one layer's weights in the kernel's streaming order."""
+    """Device buffers holding one layer's weights in the kernel's streaming order, plus the host-side state a call
+    needs: a pre-filled argument struct and the scratch sizes already asked for."""
 
     def __init__(self, N: int, K: int, R: int, fp4: bool, device: torch.device):
         sizes = (ctypes.c_size_t * 5)()
         _lib.check(_lib.load().svdq_w4a4_prepared_bytes(N, K, R, int(fp4), sizes))
         self.N, self.K, self.R, self.fp4 = N, K, R, fp4
+        self.device = device
         self.wgt = torch.empty(sizes[0], dtype=torch.uint8, device=device)
         self.wscales = torch.empty(sizes[1], dtype=torch.uint8, device=device)
         self.lora_up = torch.empty(max(sizes[2], 16), dtype=torch.uint8, device=device)
         self.col_scale = torch.empty(sizes[3], dtype=torch.uint8, device=device)
         self.col_bias = torch.empty(sizes[4], dtype=torch.uint8, device=device)
+        self.workspace_bytes: dict[tuple, int] = {}
+        self.key = None
+        self.tls = threading.local()   # per-thread argument struct (two threads may run the same layer)
 
     def as_struct(self) -> _lib.PreparedWeights:
         return _lib.PreparedWeights(
             wgt=ptr(self.wgt), wscales=ptr(self.wscales), lora_up=ptr(self.lora_up) if self.R else None,
             col_scale=ptr(self.col_scale), col_bias=ptr(self.col_bias),
         )
+
+    def args(self) -> _lib.GemmArgs:
+        a = getattr(self.tls, "args", None)
+        if a is None:
+            a = _lib.GemmArgs(w=self.as_struct(), N=self.N, K=self.K, R=self.R, fp4=int(self.fp4))
+            self.tls.args = a
+            self.tls.ref = ctypes.byref(a)
+        return a
 
 
 def prepare_weights(
@@ -57,70 +76,70 @@ def prepare_weights(
     R = 0 if lora_up is None else lora_up.shape[1]
     out = PreparedWeights(N, K, R, fp4, wgt.device)
     ls = None
-    if lora_scales is not None:
+    if lora_scales is not None and not all(s == 1.0 for s in lora_scales):
         ls = (ctypes.c_float * len(lora_scales))(*lora_scales)
     args = _lib.WeightsArgs(
         qweight=ptr(wgt), wscales=ptr(wscales), lora_up=ptr(lora_up), bias=ptr(bias), wcscales=ptr(wcscales),
         lora_scales=ls, alpha=float(alpha), N=N, K=K, R=R, fp4=int(fp4),
     )
     st = out.as_struct()
-    with torch.cuda.device(wgt.device):
+    with on_device(wgt.device):
         _lib.check(_lib.load().svdq_w4a4_prepare_weights(ctypes.byref(args), ctypes.byref(st), stream_ptr(wgt.device)))
     return out
 
 
-_cache: dict[tuple, tuple[PreparedWeights, list]] = {}
-_alpha_cache: dict[tuple, tuple[float, weakref.ref]] = {}
-
-
-def _ident(t: torch.Tensor | None):
-    return None if t is None else (t.data_ptr(), t._version, tuple(t.shape))
-
-
 def _alpha_value(alpha) -> float:
-    """``alpha`` is ``SVDQW4A4Linear.wtscale`` (a CUDA parameter) or a float.  The reference
-    converts the tensor to a C++ float on every call (an implicit device sync,
-    nunchaku/csrc/ops.h:33); here the value is read once per tensor version."""
+    """``alpha`` is ``SVDQW4A4Linear.wtscale`` (a CUDA parameter) or a float.  The reference converts the tensor to
+    a C++ float on every call (an implicit device sync, nunchaku/csrc/ops.h:33); here the value is read when the
+    layer's weights are (re-)prepared, i.e. once per tensor object and version."""
     if alpha is None:
         return 1.0
     if isinstance(alpha, torch.Tensor):
-        # keyed by address + version, and only valid while that very tensor object is alive: the allocator
-        # hands the address of a freed one-element tensor to the next one
-        key = _ident(alpha)
-        hit = _alpha_cache.get(key)
-        if hit is not None and hit[1]() is alpha:
-            return hit[0]
-        value = float(alpha.detach().float().reshape(-1)[0].item())
-        if len(_alpha_cache) > 4096:
-            for k in [k for k, v in _alpha_cache.items() if v[1]() is None]:
-                del _alpha_cache[k]
-        _alpha_cache[key] = (value, weakref.ref(alpha))
-        return value
+        return float(alpha.detach().float().reshape(-1)[0].item())
     return float(alpha)
 
 
+def _key(wgt, wscales, lora_up, bias, wcscales, alpha, lora_scales, fp4):
+    """Identity (object ids, kept alive by the entry itself) and version of everything the prepared copy was built from."""
+    ts = (wgt, wscales, lora_up, bias, wcscales, alpha if isinstance(alpha, torch.Tensor) else None)
+    return (tuple(None if t is None else t._version for t in ts), None if isinstance(alpha, torch.Tensor) else alpha,
+            None if lora_scales is None else tuple(lora_scales), bool(fp4))
+
+
 def cached_prepared_weights(wgt, wscales, lora_up, bias, wcscales, alpha, lora_scales, fp4) -> PreparedWeights:
-    a = _alpha_value(alpha)
-    key = (_ident(wgt), _ident(wscales), _ident(lora_up), _ident(bias), _ident(wcscales), a,
-           None if lora_scales is None else tuple(lora_scales), bool(fp4))
-    hit = _cache.get(key)
-    live = [t for t in (wgt, wscales, lora_up, bias, wcscales) if t is not None]
-    if hit is not None and len(hit[1]) == len(live) and all(r() is t for r, t in zip(hit[1], live)):
-        return hit[0]
-    if lora_scales is not None and all(s == 1.0 for s in lora_scales):
-        lora_scales = None
-    prepared = prepare_weights(wgt, wscales, lora_up, bias, wcscales, a, lora_scales, fp4)
-    refs = [weakref.ref(t) for t in live]
-    _cache[key] = (prepared, refs)
-    if len(_cache) > 4096:  # drop entries whose parameters are gone
-        for k in [k for k, v in _cache.items() if any(r() is None for r in v[1])]:
-            del _cache[k]
+    hit = wgt.__dict__.get(_ATTR)
+    key = _key(wgt, wscales, lora_up, bias, wcscales, alpha, lora_scales, fp4)
+    if hit is not None:
+        prepared, others = hit
+        o = others
+        if (prepared.key == key and o[0] is wscales and o[1] is lora_up and o[2] is bias and o[3] is wcscales
+                and (o[4] is alpha or not isinstance(alpha, torch.Tensor))):
+            return prepared
+    with _lock:
+        prepared = prepare_weights(wgt, wscales, lora_up, bias, wcscales, _alpha_value(alpha), lora_scales, fp4)
+        prepared.key = key
+        # the entry keeps the companion tensors alive, so `is` comparisons cannot be fooled by a recycled address;
+        # the entry itself is owned by `wgt` and goes away with it (no reference from `others` back to `wgt`)
+        setattr(wgt, _ATTR, (prepared, (wscales, lora_up, bias, wcscales, alpha if isinstance(alpha, torch.Tensor) else None)))
     return prepared
 
 
-def clear_prepared_cache() -> None:
-    _cache.clear()
-    _alpha_cache.clear()
+def invalidate_prepared(*tensors: torch.Tensor | None) -> None:
+    """Drop the re-tiled copy that hangs off each given packed ``qweight``: needed after a write that does not go
+    through the tensor's version counter (``param.data.copy_()``, ``param.data = ...``, a raw pointer)."""
+    for t in tensors:
+        if t is not None:
+            t.__dict__.pop(_ATTR, None)
+
+
+def clear_prepared_cache(module: torch.nn.Module | None = None) -> None:
+    """Drop the prepared weights of every ``qweight`` below ``module`` (with no argument there is nothing global to
+    clear: the copies are owned by the parameters)."""
+    if module is None:
+        return
+    for name, p in module.named_parameters():
+        if name.endswith("qweight"):
+            invalidate_prepared(p)
 
 
 def relayout_act(codes, scales, lora_act, K: int, fp4: bool, from_layout: int, to_layout: int):
@@ -134,7 +153,7 @@ def relayout_act(codes, scales, lora_act, K: int, fp4: bool, from_layout: int, t
         M_pad=codes.shape[0], K=K, R=0 if lora_act is None else lora_act.shape[1], fp4=int(fp4),
         from_layout=from_layout, to_layout=to_layout,
     )
-    with torch.cuda.device(codes.device):
+    with on_device(codes.device):
         _lib.check(_lib.load().svdq_w4a4_relayout_act(ctypes.byref(args), stream_ptr(codes.device)))
     return co, so, lo
 
@@ -175,19 +194,22 @@ def svdq_gemm_w4a4_cuda(
 ) -> None:
     """W4A4 GEMM with the fused SVDQuant epilogue; results are written in place.
 
-    Argument meaning follows the reference.  ``qout``/``oscales`` (+ ``lora_down``,
-    ``lora_act_out``, ``smooth_factor``) select the GELU + next-layer requantisation
-    epilogue (gemm_w4a4_launch_impl.cuh:282-309); ``out`` the plain one with optional
-    SiLU.  The attention epilogues (``norm_q``/``rotary_emb``/``out_q``..., ``out_vk``/
-    ``out_linearattn``) raise NotImplementedError: both exist as kernels that run on the GEMM's bf16 output
-    (``qk_norm_rope``, ``litela_attention``).  ``act_layout`` /
-    ``out_layout`` give the memory order of the incoming / produced activation tensors.
+    Argument meaning follows the reference (``GEMM_W4A4_Launch::gemm_w4a4``,
+    gemm_w4a4_launch_impl.cuh:7-424), including which arguments select which epilogue:
+
+    * ``qout`` + ``oscales`` (+ ``lora_down``, ``lora_act_out``, ``smooth_factor``): GELU and the next layer's
+      LoRA-down + requantisation (launch_impl.cuh:282-309); ``out`` may be given as well;
+    * ``out_linearattn`` + ``out_vk``: SANA's ReLU linear attention (launch_impl.cuh:311-345): the Q third (ReLU)
+      goes to ``out_linearattn`` [B, tokens, N/3], the per-head ``[V | 1]^T relu(K)`` sums to ``out_vk``
+      [B, heads, 33, 32] fp32; :func:`linearattn_vk_mul_q` then finishes it as in the reference;
+    * ``rotary_emb`` + ``norm_q`` + ``norm_k``: RMSNorm of q / k per 128-wide head and rotary embedding
+      (launch_impl.cuh:347-405), written either to ``out`` [M, N] or, head-major, to ``out_q / out_k / out_v``
+      [B, heads, tokens_pad, 128] (``attn_tokens`` valid tokens per batch, padding rows zero);
+      ``rotary_emb`` is the reference's packed fp32 [1, M_pad, 128] tensor (``pack_rotemb``);
+    * otherwise ``out`` with optional SiLU.
+
+    ``act_layout`` / ``out_layout`` give the memory order of the incoming / produced activation tensors.
     """
-    if any(t is not None for t in (norm_q, norm_k, rotary_emb, out_q, out_k, out_v)):
-        raise NotImplementedError("svdq_b200: the RMSNorm+RoPE / packed-QKV epilogue is not built")
-    if out_vk is not None or out_linearattn is not None:
-        raise NotImplementedError("svdq_b200: linear attention is not a GEMM epilogue here: write `out` and call "
-                                  "nunchaku_b200.ops.litela_attention on it")
     if poolout is not None:
         raise NotImplementedError("poolout is unused by the reference launcher as well")
     if ascales is None or wscales is None:
@@ -200,52 +222,98 @@ def svdq_gemm_w4a4_cuda(
         raise ValueError("lora_act_in and lora_up must be given together")
     if lora_scales is None and lora_up is not None:
         lora_scales = [1.0] * math.ceil(lora_up.shape[1] / 16)  # nunchaku/ops/gemm.py:123-125
-    act_layout = default_act_layout() if act_layout is None else act_layout
-    out_layout = default_act_layout() if out_layout is None else out_layout
+    if act_layout is None:
+        act_layout = default_act_layout()
+    dev = act.device
 
     M_pad = act.shape[0]
     K = act.shape[1] * 2
-    N = wgt.shape[0]
-    R = 0 if lora_up is None else lora_up.shape[1]
     prepared = cached_prepared_weights(wgt, wscales, lora_up, bias, wcscales, alpha, lora_scales, fp4)
+    N = prepared.N
 
     if act_layout == _lib.LAYOUT_REFERENCE:
         act, ascales, lora_act_in = relayout_act(act, ascales, lora_act_in, K, fp4, _lib.LAYOUT_REFERENCE, _lib.LAYOUT_NATIVE)
-        act_layout = _lib.LAYOUT_NATIVE
 
     requant = qout is not None and oscales is not None
+    litela = out_linearattn is not None
+    rope = rotary_emb is not None
+    packqkv = out_q is not None
+    tmp_out = None
     if requant:
         if lora_down is None or lora_act_out is None or smooth_factor is None:
             raise ValueError("next-layer requantisation needs lora_down, lora_act_out and smooth_factor")
         activation = _lib.ACT_GELU
         M = out.shape[0] if out is not None else M_pad
+        want_layout = default_act_layout() if out_layout is None else out_layout
+    elif litela or (rope and packqkv):
+        # these epilogues consume the projection's bf16 tile and write derived tensors only: the tile goes to a
+        # scratch tensor and the row-wise kernels below finish the job
+        if litela and out_vk is None:
+            raise ValueError("out_linearattn needs out_vk (gemm_w4a4_launch_impl.cuh:313)")
+        activation = _lib.ACT_NONE
+        M = M_pad
+        tmp_out = out = torch.empty(M_pad, N, dtype=torch.bfloat16, device=dev)
     else:
         if out is None:
             raise ValueError("either `out` or (`qout`, `oscales`) must be given")
         activation = _lib.ACT_SILU if fuse_silu else _lib.ACT_NONE
-        M = out.shape[0]
+        M = out.numel() // out.shape[-1]
+    if rope and (norm_q is None or norm_k is None):
+        raise ValueError("rotary_emb needs norm_q and norm_k (gemm_w4a4_launch_impl.cuh:348-349)")
     if next_fp4 is None:
         next_fp4 = fp4
 
-    args = _lib.GemmArgs(
-        act=ptr(act), ascales=ptr(ascales), lora_act_in=ptr(lora_act_in), w=prepared.as_struct(),
-        out=ptr(out), qout=ptr(qout) if requant else None, oscales=ptr(oscales) if requant else None,
-        lora_act_out=ptr(lora_act_out) if requant else None,
-        next_smooth=ptr(smooth_factor) if requant else None, next_lora_down=ptr(lora_down) if requant else None,
-        workspace=None, workspace_bytes=0,
-        M=M, M_pad=M_pad, N=N, K=K, R=R, R_next=lora_down.shape[1] if requant else 0,
-        fp4=int(fp4), act_unsigned=int(act_unsigned), activation=activation,
-        act_layout=act_layout, out_layout=out_layout, next_fp4=int(next_fp4),
-        # `out` narrower than the padded weights (the reference's actualN): the padded columns are dropped by the store
-        N_out=out.shape[-1] if out is not None and out.shape[-1] != N else 0,
-    )
-    lib = _lib.load()
+    a = prepared.args()
+    a.act = act.data_ptr()
+    a.ascales = ascales.data_ptr()
+    a.lora_act_in = ptr(lora_act_in)
+    a.out = ptr(out)
+    a.M = M
+    a.M_pad = M_pad
+    a.act_unsigned = int(act_unsigned)
+    a.activation = activation
+    a.act_layout = _lib.LAYOUT_NATIVE
+    # `out` narrower than the padded weights (the reference's actualN): the padded columns are dropped by the store
+    a.N_out = out.shape[-1] if out is not None and out.shape[-1] != N else 0
     ws = None
-    need = ctypes.c_size_t(0)
-    _lib.check(lib.svdq_gemm_w4a4_workspace_bytes(ctypes.byref(args), ctypes.byref(need)))
-    if need.value:
-        ws = torch.empty(need.value, dtype=torch.uint8, device=act.device)
-        args.workspace = ptr(ws)
-        args.workspace_bytes = need.value
-    with torch.cuda.device(act.device):
-        _lib.check(lib.svdq_gemm_w4a4(ctypes.byref(args), stream_ptr(act.device)))
+    if requant:
+        a.qout = qout.data_ptr()
+        a.oscales = oscales.data_ptr()
+        a.lora_act_out = lora_act_out.data_ptr()
+        a.next_smooth = smooth_factor.data_ptr()
+        a.next_lora_down = lora_down.data_ptr()
+        a.R_next = lora_down.shape[1]
+        a.out_layout = _lib.LAYOUT_NATIVE   # what the kernel writes; converted below when the caller wants the reference order
+        a.next_fp4 = int(next_fp4)
+    else:
+        a.qout = a.oscales = a.lora_act_out = a.next_smooth = a.next_lora_down = None
+        a.R_next = 0
+    lib = _lib.load()
+    wkey = (M_pad, a.R_next, int(requant))
+    need = prepared.workspace_bytes.get(wkey)
+    if need is None:
+        n = ctypes.c_size_t(0)
+        a.workspace = None
+        a.workspace_bytes = 0
+        _lib.check(lib.svdq_gemm_w4a4_workspace_bytes(prepared.tls.ref, ctypes.byref(n)))
+        need = prepared.workspace_bytes[wkey] = n.value
+    if need:
+        ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        a.workspace = ws.data_ptr()
+        a.workspace_bytes = need
+    else:
+        a.workspace = None
+        a.workspace_bytes = 0
+    with on_device(dev):
+        _lib.check(lib.svdq_gemm_w4a4(prepared.tls.ref, stream_ptr(dev)))
+        if requant and want_layout == _lib.LAYOUT_REFERENCE:
+            co, so, lo = relayout_act(qout, oscales, lora_act_out, N, bool(next_fp4), _lib.LAYOUT_NATIVE, _lib.LAYOUT_REFERENCE)
+            qout.copy_(co)
+            oscales.copy_(so)
+            lora_act_out.copy_(lo)
+        if rope:
+            from .fused import _norm_rope_packed
+            _norm_rope_packed(out, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn_tokens)
+        if litela:
+            from .fused import _litela_epilogue
+            _litela_epilogue(tmp_out, out_vk, out_linearattn)

@@ -7,7 +7,7 @@ import ctypes
 import torch
 
 from .. import _lib
-from ..utils import ceil_divide, default_act_layout, ptr, require_cuda_contiguous, stream_ptr
+from ..utils import ceil_divide, default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr
 
 
 def svdq_quantize_w4a4_act_fuse_lora_cuda(
@@ -77,6 +77,6 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
         fp4=int(fp4), fuse_glu=int(fuse_glu),
         layout=default_act_layout() if layout is None else layout, K_in=k_in,
     )
-    with torch.cuda.device(dev):
+    with on_device(dev):
         _lib.check(_lib.load().svdq_quantize_w4a4_act_fuse_lora(ctypes.byref(args), stream_ptr(dev)))
     return output, oscales, lora_act_out

@@ -43,11 +43,11 @@ def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_bu
     }
 
 
-def mma_rate_pair(kind: str, n: int, iters: int = 2000, grid: int | None = None):
+def mma_rate_pair(kind: str, n: int, iters: int = 2000, grid: int | None = None, cps_per_group: int = 0):
     """MMA rate of a CTA pair (cta_group::2, M = 256): cycles per MMA and the whole-GPU TFLOP/s."""
     lib = _lib.load()
     lib.svdq_probe_mma_rate_pair.restype = ctypes.c_int32
-    lib.svdq_probe_mma_rate_pair.argtypes = [ctypes.c_int32] * 4 + [ctypes.c_void_p, ctypes.c_void_p]
+    lib.svdq_probe_mma_rate_pair.argtypes = [ctypes.c_int32] * 4 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]
     dev = torch.device("cuda", torch.cuda.current_device())
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     grid = grid or (sms // 2) * 2
@@ -56,50 +56,15 @@ def mma_rate_pair(kind: str, n: int, iters: int = 2000, grid: int | None = None)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for rep in range(2):
         e0.record()
-        _lib.check(lib.svdq_probe_mma_rate_pair(code, n, iters, grid, cyc.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+        _lib.check(lib.svdq_probe_mma_rate_pair(code, n, iters, grid, cyc.data_ptr(), torch.cuda.current_stream(dev).cuda_stream,
+                                                cps_per_group))
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     c = cyc.view(grid, 2)[0::2].double().mean(0)     # the issuing CTAs
     flops = 2.0 * 256 * n * k * 4 * iters * (grid // 2)
-    return {"kind": kind, "n": n, "pair": True, "cycles_per_mma_issue": c[0].item() / (4 * iters),
+    return {"kind": kind, "n": n, "pair": True, "cps_per_group": cps_per_group, "cycles_per_mma_issue": c[0].item() / (4 * iters),
             "cycles_per_mma": c[1].item() / (4 * iters), "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms}
-
-
-def ingest_rate(grid: int, chunk: int = 16384, depth: int = 4, iters: int = 4000, src_mb: int = 32, issuers: int = 2):
-    """Bytes per clock per SM that bulk copies from an L2-resident buffer deliver to shared memory."""
-    lib = _lib.load()
-    lib.svdq_probe_ingest_rate.restype = ctypes.c_int32
-    lib.svdq_probe_ingest_rate.argtypes = [ctypes.c_void_p, ctypes.c_size_t] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
-    dev = torch.device("cuda", torch.cuda.current_device())
-    src = torch.zeros(src_mb << 20, dtype=torch.uint8, device=dev)
-    cyc = torch.zeros(grid, dtype=torch.int64, device=dev)
-    for rep in range(2):
-        _lib.check(lib.svdq_probe_ingest_rate(src.data_ptr(), src.numel(), chunk, depth, iters, grid, issuers, cyc.data_ptr(),
-                                              torch.cuda.current_stream(dev).cuda_stream))
-        torch.cuda.synchronize()
-    c = cyc.double()
-    return {"grid": grid, "chunk": chunk, "depth": depth, "issuers": issuers, "src_mb": src_mb,
-            "bytes_per_clk_per_sm": issuers * chunk * iters / c.mean().item(), "min": issuers * chunk * iters / c.max().item()}
-
-
-def ingest_tensor_rate(grid: int, pitch: int = 1536, rows: int = 21504, box_rows: int = 128, depth: int = 4, iters: int = 2000,
-                       issuers: int = 1, mode: int = 0):
-    """Bytes per clock per SM delivered by 2-D tiled TMA loads of 128-byte x box_rows boxes (K-major operand pattern)."""
-    lib = _lib.load()
-    lib.svdq_probe_ingest_tensor.restype = ctypes.c_int32
-    lib.svdq_probe_ingest_tensor.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 7 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32]
-    dev = torch.device("cuda", torch.cuda.current_device())
-    src = torch.zeros(rows * pitch, dtype=torch.uint8, device=dev)
-    cyc = torch.zeros(grid, dtype=torch.int64, device=dev)
-    for rep in range(2):
-        _lib.check(lib.svdq_probe_ingest_tensor(src.data_ptr(), pitch, rows, box_rows, depth, iters, grid, issuers, cyc.data_ptr(),
-                                                torch.cuda.current_stream(dev).cuda_stream, mode))
-        torch.cuda.synchronize()
-    c = cyc.double()
-    per = issuers * box_rows * 128 * iters
-    return {"grid": grid, "pitch": pitch, "rows": rows, "box_rows": box_rows, "depth": depth, "issuers": issuers, "mode": mode,
-            "bytes_per_clk_per_sm": per / c.mean().item(), "min": per / c.max().item()}
 
 
 def main():

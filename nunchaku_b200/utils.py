@@ -1,6 +1,7 @@
 """Small host-side helpers (mirrors of nunchaku/utils.py:77-93 where they exist)."""
 from __future__ import annotations
 
+import contextlib
 import os
 
 import torch
@@ -13,6 +14,9 @@ def ceil_divide(x: int, divisor: int) -> int:
     return (x + divisor - 1) // divisor
 
 
+_layout_env: tuple[str | None, int] | None = None
+
+
 def default_act_layout() -> int:
     """Memory order of the activation-side tensors handed from the quantiser to the GEMM.
 
@@ -20,10 +24,15 @@ def default_act_layout() -> int:
     reference's mma.sync fragment order (set ``SVDQ_B200_ACT_LAYOUT=reference``), which the
     GEMM converts back before use.
     """
-    v = os.environ.get("SVDQ_B200_ACT_LAYOUT", "native").lower()
+    global _layout_env
+    raw = os.environ.get("SVDQ_B200_ACT_LAYOUT")
+    if _layout_env is not None and _layout_env[0] == raw:
+        return _layout_env[1]
+    v = (raw or "native").lower()
     if v not in ("native", "reference"):
         raise ValueError(f"SVDQ_B200_ACT_LAYOUT must be 'native' or 'reference', got {v!r}")
-    return _lib.LAYOUT_REFERENCE if v == "reference" else _lib.LAYOUT_NATIVE
+    _layout_env = (raw, _lib.LAYOUT_REFERENCE if v == "reference" else _lib.LAYOUT_NATIVE)
+    return _layout_env[1]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -31,7 +40,23 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 
 def stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw cudaStream_t of torch's current stream on ``device`` (the entry points launch on it)."""
+    idx = device.index
+    if idx is None:
+        idx = torch._C._cuda_getDevice()
+    return torch._C._cuda_getCurrentRawStream(idx)
+
+
+_NULL_CTX = contextlib.nullcontext()
+
+
+def on_device(device: torch.device):
+    """Context that makes ``device`` the current CUDA device; free when it already is (the entry points act on the
+    current device, and switching through ``torch.cuda.device`` costs more than a launch)."""
+    idx = device.index
+    if idx is None or idx == torch._C._cuda_getDevice():
+        return _NULL_CTX
+    return torch.cuda.device(idx)
 
 
 def require_cuda_contiguous(name: str, t: torch.Tensor | None, dtypes=None) -> None:

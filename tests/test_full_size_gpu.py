@@ -1,0 +1,122 @@
+"""Full-size workloads against something that knows the right answer.
+
+* The FLUX MLP chain at full size (M = 4608, 3072 -> 12288 -> 3072, rank 32, both precisions) against the CPU oracle
+  chain ``ref_gemm -> ref_requantize -> ref_gemm`` on every 9th row (rows are independent, so a row sample of the oracle
+  is compared with the same rows of the full GPU call): relative L2 <= 1e-2 on the chain's output, and the 4-bit codes /
+  scales that fc1's epilogue hands to fc2 bit-exact given the kernel's own bf16 tile.
+* One joint and one single FLUX block at full geometry (hidden 3072, 24 heads, 4096 + 512 tokens) and a SANA block pair at
+  full width (2240 -> 2304, GLUMBConv 5600) against their bf16 twins built from the same master weights.
+"""
+import copy
+
+import pytest
+import torch
+
+import helpers as H
+from oracle import svdq_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _rows(q: R.QuantOut, rows) -> R.QuantOut:
+    return R.QuantOut(q.codes[rows], q.scales[:, rows].contiguous(), q.lora_act[rows], q.fp4, q.unsigned)
+
+
+@pytest.mark.parametrize("fp4", [True, False])
+def test_mlp_chain_full_size_against_oracle(fp4):
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops.gemm import svdq_gemm_w4a4_cuda
+
+    M, K, N1 = 4608, 3072, 12288
+    x = R.make_activations(M, K, seed=11)
+    fc1 = R.make_linear(K, N1, 32, fp4=fp4, x_absmax=x.float().abs().amax(0), seed=12, mode="svd")
+    rows = torch.arange(0, M, 9)
+    q1 = R.ref_quantize(x, fc1.smooth, fc1.lora_down, fp4=fp4)
+    h = R.ref_gemm(_rows(q1, rows), fc1, act="gelu")                              # [512, N1] fp32
+    fc2 = R.make_linear(N1, K, 32, fp4=fp4, x_absmax=(h.abs().amax(0) + (0.0 if fp4 else 0.171875)).clamp(min=1e-3), seed=13, mode="svd")
+    q2 = R.ref_requantize(h, fc2, M_pad=rows.numel(), unsigned=not fp4)
+    y = R.ref_gemm(q2, fc2)                                                       # oracle chain on the sampled rows
+
+    m1, m2 = H.to_module(fc1), H.to_module(fc2, act_unsigned=not fp4)
+    xq = m1.quantize(x.cuda())
+    M_pad = xq[0].shape[0]
+    out1 = torch.empty(M, N1, dtype=torch.bfloat16, device="cuda")
+    qout = torch.empty(M_pad, N1 // 2, dtype=torch.uint8, device="cuda")
+    osc = (torch.empty(N1 // 16, M_pad, dtype=torch.float8_e4m3fn, device="cuda") if fp4
+           else torch.empty(N1 // 64, M_pad, dtype=torch.bfloat16, device="cuda"))
+    la2 = torch.empty(M_pad, 32, dtype=torch.float32, device="cuda")
+    svdq_gemm_w4a4_cuda(act=xq[0], wgt=m1.qweight, out=out1, qout=qout, ascales=xq[1], wscales=m1.wscales, oscales=osc,
+                        lora_act_in=xq[2], lora_up=m1.proj_up, lora_down=m2.proj_down, lora_act_out=la2, bias=m1.bias,
+                        smooth_factor=m2.smooth_factor, fp4=fp4, alpha=m1.wtscale, wcscales=m1.wcscales,
+                        act_layout=_lib.LAYOUT_NATIVE, out_layout=_lib.LAYOUT_NATIVE)
+    got_y = m2.forward_quant(qout, osc, la2, torch.empty(M, K, dtype=torch.bfloat16, device="cuda"))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    # the first layer's quantiser: codes and scales of all rows bit-exact against the oracle
+    gq1 = H.unpack_quant_out(*xq, K, fp4, "native")
+    assert torch.equal(gq1.codes[:M], q1.codes[:M])
+    # the chain's output on the sampled rows
+    e = R.rel_l2(got_y.float().cpu()[rows], y)
+    assert e <= 1e-2, f"MLP chain vs oracle chain: relative L2 {e}"
+    # fc1's bf16 tile against the oracle, then its requantisation bit-exact given that very tile
+    assert R.rel_l2(out1.float().cpu()[rows], h) <= 4e-3
+    gq2 = H.unpack_quant_out(qout, osc, la2, N1, fp4, "native")
+    exp = R.ref_requantize(out1.float().cpu()[rows], fc2, M_pad=rows.numel(), unsigned=not fp4)
+    assert torch.equal(gq2.codes[rows], exp.codes), "requantised codes differ from quantising the kernel's own output"
+    view = torch.uint8 if fp4 else torch.int16
+    assert torch.equal(gq2.scales[:, rows].contiguous().view(view), exp.scales.view(view))
+    err = (gq2.lora_act[rows] - exp.lora_act).abs().max().item()
+    assert err <= 2e-5 * max(exp.lora_act.abs().max().item(), 1.0) + 1e-6
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+
+def test_flux_blocks_full_geometry_track_bf16():
+    """One joint + one single block with FLUX.1-dev's real sizes, one image (4096 + 512 tokens)."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.models.flux import FluxTransformer
+
+    torch.manual_seed(0)
+    ref = FluxTransformer(precision=None, n_joint=1, n_single=1)
+    q = copy.deepcopy(ref).quantize_(precision="nvfp4", rank=32)
+    assert len(q.w4a4_linears()) == 12
+    B, Hh, Ww, T = 1, 64, 64, 512
+    latents = torch.randn(B, Hh * Ww, 64, device="cuda", dtype=torch.bfloat16)
+    text = torch.randn(B, T, 4096, device="cuda", dtype=torch.bfloat16)
+    pooled = torch.randn(B, 768, device="cuda", dtype=torch.bfloat16)
+    t = torch.tensor([0.3], device="cuda")
+    g = torch.tensor([3.5], device="cuda")
+    with torch.no_grad():
+        y_ref = ref(latents, text, pooled, t, g, (Hh, Ww))
+        y_q = q(latents, text, pooled, t, g, (Hh, Ww))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert torch.isfinite(y_q).all()
+    assert _rel(y_q, y_ref) < 0.15, _rel(y_q, y_ref)
+
+
+@pytest.mark.parametrize("precision", ["int4", "nvfp4"])
+def test_sana_blocks_full_width_track_bf16(precision):
+    """Two SANA blocks at full width (hidden 2240 padded to 2304, 70 + 2 heads of 32, GLUMBConv 5600, 1024 tokens) against
+    the same model built from bf16 masters."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.models.sana import SanaTransformer
+
+    torch.manual_seed(0)
+    ref = SanaTransformer(n_blocks=2, precision=None)
+    q = copy.deepcopy(ref).quantize_(precision)
+    assert len(q.w4a4_linears()) == 12
+    B, Hh, Ww, T = 2, 32, 32, 300
+    lat = torch.randn(B, Hh * Ww, 32, device="cuda", dtype=torch.bfloat16)
+    cap = torch.randn(B, T, 2304, device="cuda", dtype=torch.bfloat16)
+    t = torch.tensor([0.2, 0.9], device="cuda")
+    with torch.no_grad():
+        y_ref = ref(lat, cap, t, (Hh, Ww))
+        y_q = q(lat, cap, t, (Hh, Ww))
+        y_q2 = q(lat, cap, t, (Hh, Ww))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert torch.isfinite(y_q).all() and torch.equal(y_q, y_q2)
+    assert _rel(y_q, y_ref) < 0.15, _rel(y_q, y_ref)

@@ -45,7 +45,7 @@ def test_quantize_matches_oracle(M, K, Rk, fp4, layout):
 
 @pytest.mark.parametrize("fp4", [True, False])
 def test_quantize_headline_shapes(fp4):
-    # BASELINE config 0 (M=4096, K=3072) and config 1 (M=4608, K=3072) activations
+    # the activations of the INT4 (M=4096, K=3072) and NVFP4 (M=4608, K=3072) workloads, and the MLP's second layer
     run_case(4096, 3072, 32, fp4, "native")
     run_case(4608, 3072, 32, fp4, "native")
     run_case(4608, 12288, 32, fp4, "native")
