@@ -199,12 +199,14 @@ typedef struct svdq_norm_rope_args {
      * out_q / out_k / out_v - write the three thirds head-major, bf16 [rows / seq_len, heads, tokens_pad, 128], instead
      *   of in place (the job of EpiloguePackQKV, epilogues.cuh:427-550; there the destination is the fragment order of
      *   the reference's own fp16 attention kernel with NaN-masked K padding, here it is plain row-major for a
-     *   TMA / library attention, and rows at or beyond attn_tokens, when attn_tokens > 0, are written as zeros). */
+     *   TMA / library attention, and rows at or beyond attn_tokens, when attn_tokens > 0, are written as zeros).
+     *   token_offset shifts the destination rows (two streams of a joint block writing one buffer); token_major = 1
+     *   selects [rows / seq_len, tokens_pad, heads, 128] instead (what flash-attention style kernels take). */
     const float* rotary_packed;
     void* out_q;
     void* out_k;
     void* out_v;
-    int32_t tokens_pad, attn_tokens;
+    int32_t tokens_pad, attn_tokens, token_offset, token_major;
 } svdq_norm_rope_args;
 int svdq_qk_norm_rope(const svdq_norm_rope_args* args, void* stream);
 

@@ -136,6 +136,8 @@ class NormRopeArgs(Structure):
         ("out_v", c_void_p),
         ("tokens_pad", c_int32),
         ("attn_tokens", c_int32),
+        ("token_offset", c_int32),
+        ("token_major", c_int32),
     ]
 
 

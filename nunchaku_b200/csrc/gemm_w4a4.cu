@@ -179,8 +179,13 @@ __device__ __forceinline__ void raise_abort(GemmShared* sh) {
 // Bounded wait.  BACKOFF > 0 puts the warp to sleep for that many nanoseconds between polls: a warp that spins on a
 // barrier is always eligible and takes issue slots from the working warps of its scheduler, so the roles with slack
 // (producers waiting for a free slot, epilogue warps waiting for an accumulator) back off; the MMA warp does not.
-template <int BACKOFF = 0>
+template <int BACKOFF_ = 0>
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, GemmShared* sh, int* status, int where) {
+#ifdef SVDQ_BACKOFF_OVERRIDE
+    constexpr int BACKOFF = BACKOFF_ ? SVDQ_BACKOFF_OVERRIDE : 0;   // timing experiments
+#else
+    constexpr int BACKOFF = BACKOFF_;
+#endif
 #pragma unroll 1
     for (int i = 0; i < (BACKOFF ? 2 : 512); ++i) {
         if (mbar_try_wait(bar, parity)) return true;

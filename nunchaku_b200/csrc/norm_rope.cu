@@ -31,13 +31,14 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
 // PACKED: the rotary table is the reference's fragment-packed fp32 tensor (pack_rotemb, nunchaku/models/embeddings.py:88-120):
 // for row m = 16 mb + 8 h + g and column pair p = 4 j + t, {sin, cos} sit at ((((mb*16 + j)*8 + g)*4 + t)*2 + h)*2.
 // SPLIT: instead of working in place, write q, k (normalised + rotated) and v (copied) head-major to
-// out_q / out_k / out_v [batch, heads, tokens_pad, 128]; rows at or beyond attn_tokens (when given) become zeros.
+// out_q / out_k / out_v [batch, heads, tokens_pad, 128] (token_major: [batch, tokens_pad, heads, 128]) from token
+// token_offset on; rows at or beyond attn_tokens (when given) become zeros.
 template <bool PACKED, bool SPLIT>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                     const float* __restrict__ cosp, const float* __restrict__ sinp, long long rows, int seq_len, int heads,
                     float eps, __nv_bfloat16* __restrict__ out_q, __nv_bfloat16* __restrict__ out_k,
-                    __nv_bfloat16* __restrict__ out_v, int tokens_pad, int attn_tokens) {
+                    __nv_bfloat16* __restrict__ out_v, int tokens_pad, int attn_tokens, int token_offset, int token_major) {
     const int lane = threadIdx.x & 31;
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -84,8 +85,9 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
         if constexpr (SPLIT) {
             if (attn_tokens > 0 && pos >= attn_tokens) o = make_uint2(0u, 0u);
             __nv_bfloat16* dst = which == 0 ? out_q : which == 1 ? out_k : out_v;
-            const long long b = row / seq_len;
-            *reinterpret_cast<uint2*>(dst + ((b * heads + head) * tokens_pad + pos) * 128 + lane * 4) = o;
+            const long long b = row / seq_len, tok = token_offset + pos;
+            const long long at = token_major ? (b * tokens_pad + tok) * heads + head : (b * heads + head) * tokens_pad + tok;
+            *reinterpret_cast<uint2*>(dst + at * 128 + lane * 4) = o;
         } else {
             *reinterpret_cast<uint2*>(p) = o;
         }
@@ -174,9 +176,10 @@ extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
                    "qk_norm_rope: misaligned tensor");
     SVDQ_CHECK_ARG(!a->rotary_packed || a->seq_len % 16 == 0, "qk_norm_rope: a packed rotary table has a multiple of 16 rows (got %d)", a->seq_len);
     const bool split = a->out_q || a->out_k || a->out_v;
-    SVDQ_CHECK_ARG(!split || (a->out_q && a->out_k && a->out_v && a->tokens_pad >= a->seq_len && a->attn_tokens >= 0 &&
-                              a->attn_tokens <= a->seq_len),
-                   "qk_norm_rope: out_q, out_k and out_v go together, with tokens_pad >= seq_len and 0 <= attn_tokens <= seq_len");
+    SVDQ_CHECK_ARG(!split || (a->out_q && a->out_k && a->out_v && a->token_offset >= 0 &&
+                              a->tokens_pad >= a->token_offset + a->seq_len && a->attn_tokens >= 0 && a->attn_tokens <= a->seq_len),
+                   "qk_norm_rope: out_q, out_k and out_v go together, with tokens_pad >= token_offset + seq_len and "
+                   "0 <= attn_tokens <= seq_len");
     if (int rc = check_arch()) return rc;
     const long long items = static_cast<long long>(a->rows) * a->heads * (split ? 3 : 2);
     const float* tab = a->rotary_packed ? a->rotary_packed : a->cos;
@@ -185,7 +188,7 @@ extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
             static_cast<__nv_bfloat16*>(a->qkv), static_cast<const __nv_bfloat16*>(a->weight_q),
             static_cast<const __nv_bfloat16*>(a->weight_k), tab, a->sin, a->rows, a->seq_len, a->heads, a->eps,
             static_cast<__nv_bfloat16*>(a->out_q), static_cast<__nv_bfloat16*>(a->out_k), static_cast<__nv_bfloat16*>(a->out_v),
-            a->tokens_pad, a->attn_tokens);
+            a->tokens_pad, a->attn_tokens, a->token_offset, a->token_major);
     };
     if (a->rotary_packed) {
         if (split) launch(qk_norm_rope_kernel<true, true>); else launch(qk_norm_rope_kernel<true, false>);

@@ -1,7 +1,8 @@
 // Device helpers shared by the activation quantiser and the GEMM's requantising epilogue.
 // Rounding follows the reference kernels (src/kernels/zgemm/gemm_w4a4.cuh:85-187,429-523 and
-// gemm_utils.cuh:206-264): bf16 round-to-nearest for every half_t step, E2M1 / E4M3 / s4 conversions with
-// saturation; a group whose absolute maximum is zero gets all-zero codes.
+// gemm_utils.cuh:206-264): bf16 round-to-nearest for every half_t step, the group scale's reciprocal with
+// rcp.approx.ftz, E2M1 / E4M3 / s4 conversions with saturation; a group whose absolute maximum is zero gets
+// all-zero codes.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -102,10 +103,20 @@ __device__ __forceinline__ float smooth16(const uint32_t (&xw)[8], const float4*
     return fmaxf(fabsf(m.x), fabsf(m.y));
 }
 
+// The reciprocal of a group scale as the reference computes it (cuda_frcp, gemm_utils.cuh:259-263): the hardware's
+// approximate reciprocal, not the IEEE one.  Scaled values that sit exactly on a rounding tie (frequent: bf16 values have
+// 8-bit mantissas) fall to one side or the other depending on the last bit of this reciprocal, so only the same
+// instruction reproduces the reference kernel's codes bit for bit.
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
 // NVFP4 group of 16: E4M3 scale byte and two words of E2M1 codes (lowest nibble = lowest column).
 __device__ __forceinline__ uint32_t nvfp4_encode16(const uint32_t (&q)[8], float amax, uint32_t (&cw)[2]) {
     const float scale = fminf(amax * (1.0f / 6.0f), 448.0f);
-    const float rs = scale == 0.f ? 0.f : __frcp_rn(scale);
+    const float rs = scale == 0.f ? 0.f : rcp_approx_ftz(scale);
     const float2 rs2 = make_float2(rs, rs);
 #pragma unroll
     for (int w = 0; w < 2; ++w)
@@ -118,7 +129,7 @@ __device__ __forceinline__ uint32_t nvfp4_encode16(const uint32_t (&q)[8], float
 template <bool UNSIGNED>
 __device__ __forceinline__ float int4_encode16(const uint32_t (&q)[8], float amax, uint32_t (&cw)[2]) {
     const float scale = amax * (UNSIGNED ? (1.0f / 15.0f) : (1.0f / 7.0f));
-    const float rs = scale == 0.f ? 0.f : __frcp_rn(scale);
+    const float rs = scale == 0.f ? 0.f : rcp_approx_ftz(scale);
     cw[0] = cw[1] = 0u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {

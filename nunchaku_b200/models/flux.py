@@ -126,14 +126,18 @@ class FluxJointBlock(nn.Module):
         self.mlp_txt = FluxMLP(dim, mlp_dim, precision, rank, device, dtype)
 
     @staticmethod
-    def _qkv(lin, norm: QKNorm, x, heads, cos=None, sin=None):
+    def _qkv(lin, norm: QKNorm, x, heads, cos=None, sin=None, out=None, token_offset=0):
         """Fused projection, then RMSNorm of q and k per head.  With (cos, sin) of this stream's rows and a W4A4
-        projection the norm and the rotary embedding run as one in-place kernel (and the caller skips its own)."""
+        projection the norm and the rotary embedding run as one kernel (and the caller skips its own); with ``out`` that
+        kernel writes q, k, v straight into the attention's [B, S_total, C] buffers at ``token_offset``."""
         B, S, C = x.shape
         qkv = _apply(lin, x)
         D = C // heads
         if cos is not None and isinstance(lin, SVDQW4A4Linear) and D == 128:
-            qkv = qk_norm_rope(qkv, norm.q.weight, norm.k.weight, cos.contiguous(), sin.contiguous(), heads, eps=1e-6)
+            qkv = qk_norm_rope(qkv, norm.q.weight, norm.k.weight, cos.contiguous(), sin.contiguous(), heads, eps=1e-6,
+                               out=out, token_offset=token_offset)
+            if out is not None:
+                return None, None, None, True
             q, k, v = qkv.chunk(3, dim=-1)
             return q, k, v, True
         q, k, v = qkv.chunk(3, dim=-1)
@@ -148,11 +152,20 @@ class FluxJointBlock(nn.Module):
         ni = _ln_mod(img, mi[1], mi[0], fused)
         nt = _ln_mod(txt, mt[1], mt[0], fused)
         T = txt.shape[1]
-        qi, ki, vi, ri = self._qkv(self.qkv_img, self.norm_img, ni, self.heads, cos[T:], sin[T:])
-        qt, kt, vt, rt = self._qkv(self.qkv_txt, self.norm_txt, nt, self.heads, cos[:T], sin[:T])
-        roped = ri and rt
-        attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads,
-                          None if roped else cos, None if roped else sin, None)
+        B, S, C = img.shape
+        if fused and C // self.heads == 128:
+            # both streams write their q, k, v (normalised, rotated) into one set of token-major buffers: no concatenation
+            qkv = torch.empty(3, B, T + S, C, dtype=img.dtype, device=img.device)
+            bufs = (qkv[0], qkv[1], qkv[2])
+            self._qkv(self.qkv_txt, self.norm_txt, nt, self.heads, cos[:T], sin[:T], bufs, 0)
+            self._qkv(self.qkv_img, self.norm_img, ni, self.heads, cos[T:], sin[T:], bufs, T)
+            attn = _attention(qkv[0], qkv[1], qkv[2], self.heads, None, None, None)
+        else:
+            qi, ki, vi, ri = self._qkv(self.qkv_img, self.norm_img, ni, self.heads, cos[T:], sin[T:])
+            qt, kt, vt, rt = self._qkv(self.qkv_txt, self.norm_txt, nt, self.heads, cos[:T], sin[:T])
+            roped = ri and rt
+            attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads,
+                              None if roped else cos, None if roped else sin, None)
         at, ai = attn[:, :T], attn[:, T:]
         img = img + mi[2].unsqueeze(1) * _apply(self.out_img, ai.contiguous())
         txt = txt + mt[2].unsqueeze(1) * _apply(self.out_txt, at.contiguous())

@@ -122,11 +122,15 @@ def linearattn_vk_mul_q(q: torch.Tensor, vk: torch.Tensor, eps: float = 1e-6) ->
 
 
 def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
-                 heads: int, eps: float = 1e-6) -> torch.Tensor:
+                 heads: int, eps: float = 1e-6, out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+                 token_offset: int = 0) -> torch.Tensor:
     """RMSNorm of q and k per 128-wide head and rotary embedding, in place on the output of a fused QKV projection
     (what ``fused_qkv_norm_rottary``, ``nunchaku/ops/fused.py:50-110``, gets from the GEMM epilogue).
 
     qkv: bf16 [B, S, 3*heads*128] (or [B*S, ...] with ``cos.shape[0]`` dividing the rows); cos, sin: fp32 [S, 64].
+    With ``out = (q, k, v)``, three bf16 [B, S_total, heads*128] buffers, the three thirds are written there instead
+    (token-major, rows ``token_offset .. token_offset + S``): the two streams of a joint block fill one set of buffers
+    that attention reads without any concatenation.
     """
     require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
     require_cuda_contiguous("weight_q", weight_q, (torch.bfloat16,))
@@ -138,6 +142,13 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
     rows = qkv.numel() // qkv.shape[-1]
     args = _lib.NormRopeArgs(qkv=ptr(qkv), weight_q=ptr(weight_q), weight_k=ptr(weight_k), cos=ptr(cos), sin=ptr(sin),
                              rows=rows, seq_len=cos.shape[0], heads=heads, eps=eps)
+    if out is not None:
+        for t in out:
+            require_cuda_contiguous("out", t, (torch.bfloat16,))
+            if t.dim() != 3 or t.shape[2] != heads * 128 or t.shape[0] * cos.shape[0] != rows:
+                raise ValueError("qk_norm_rope: out tensors must be [rows / S, S_total, heads*128]")
+        args.out_q, args.out_k, args.out_v = ptr(out[0]), ptr(out[1]), ptr(out[2])
+        args.tokens_pad, args.token_offset, args.token_major = out[0].shape[1], token_offset, 1
     with on_device(qkv.device):
         _lib.check(_lib.load().svdq_qk_norm_rope(ctypes.byref(args), stream_ptr(qkv.device)))
     return qkv

@@ -43,6 +43,7 @@ class QuantOut:
     lora_act: torch.Tensor   # fp32 [M_pad, R]
     fp4: bool
     unsigned: bool = False
+    tie: torch.Tensor | None = None   # bool [M_pad, K]: the scaled value sits on (or within 1e-5 of) a rounding tie
 
 
 def _silu_bf16(y: torch.Tensor) -> torch.Tensor:
@@ -62,7 +63,13 @@ def group_quantize(v: torch.Tensor, *, fp4: bool, unsigned: bool = False):
 
     Follows quantize_w4a4_fp4_from_fpsum_warp (gemm_w4a4.cuh:85-187) and
     quantize_w4a4_from_fpsum_warp (gemm_w4a4.cuh:429-523).
-    Returns (codes uint8 [rows, K], scales [K/G, rows]).
+    Returns (codes uint8 [rows, K], scales [K/G, rows], tie bool [rows, K]).
+
+    The reference takes the reciprocal of the group scale with ``rcp.approx.ftz`` (gemm_utils.cuh:259-263), which this
+    restatement models as the exact fp32 reciprocal.  The two differ by at most one unit in the last place, which can
+    change a code only where ``v * rscale`` lies on a rounding tie; since bf16 values have 8-bit mantissas such exact
+    ties are common (a few in 10^4 elements).  ``tie`` flags the elements within 1e-5 (relative) of a tie: there the
+    code is "either neighbour", everywhere else it is pinned.
     """
     assert v.dtype == BF16
     rows, K = v.shape
@@ -78,7 +85,13 @@ def group_quantize(v: torch.Tensor, *, fp4: bool, unsigned: bool = False):
     rscale = torch.where(scale == 0, torch.zeros_like(scale), 1.0 / scale)
     q = vf * rscale.unsqueeze(2)
     codes = fmt.e2m1_encode(q) if fp4 else fmt.int4_encode(q, unsigned)
-    return codes.reshape(rows, K), stored.t().contiguous()
+    aq = q.abs().to(torch.float64)
+    if fp4:   # midpoints of the E2M1 grid {0, .5, 1, 1.5, 2, 3, 4, 6}
+        mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=torch.float64)
+        tie = ((aq.unsqueeze(-1) - mids).abs() <= 1e-5 * mids).any(-1)
+    else:
+        tie = ((aq - aq.floor()) - 0.5).abs() <= 1e-5 * aq.clamp(min=1.0)
+    return codes.reshape(rows, K), stored.t().contiguous(), tie.reshape(rows, K)
 
 
 def ref_quantize(
@@ -114,8 +127,8 @@ def ref_quantize(
     # EpilogueQuantize (gemm_w4a4.cuh:930-1043) with shift_value = 0: bf16 add of +0, then h2div
     vs = (vp.to(F32) + 0.0).to(BF16)
     vs = (vs.to(F32) / smooth.to(F32).unsqueeze(0)).to(BF16)
-    codes, scales = group_quantize(vs, fp4=fp4, unsigned=False)
-    return QuantOut(codes, scales, lora_act, fp4)
+    codes, scales, tie = group_quantize(vs, fp4=fp4, unsigned=False)
+    return QuantOut(codes, scales, lora_act, fp4, False, tie)
 
 
 def dequant_act(q: QuantOut) -> torch.Tensor:
@@ -212,8 +225,8 @@ def ref_requantize(
     shift = INT4_UNSIGNED_SHIFT if unsigned else 0.0
     v = (yb.to(F32) + shift).to(BF16)
     v = (v.to(F32) / nxt.smooth.to(F32).unsqueeze(0)).to(BF16)
-    codes, scales = group_quantize(v, fp4=nxt.fp4, unsigned=unsigned)
-    return QuantOut(codes, scales, lora_act, nxt.fp4, unsigned)
+    codes, scales, tie = group_quantize(v, fp4=nxt.fp4, unsigned=unsigned)
+    return QuantOut(codes, scales, lora_act, nxt.fp4, unsigned, tie)
 
 
 # ---------------------------------------------------------------------------

@@ -69,3 +69,30 @@ def unpack_quant_out(codes, scales, lora, K: int, fp4: bool, layout: str) -> R.Q
         s = L.ref_unpack_amscales(scales.view(torch.uint8)) if fp4 else L.ref_unpack_ascales(scales)
         la = L.ref_unpack_lora_act(lora)
     return R.QuantOut(c, s, la, fp4)
+
+
+def assert_codes_match(got: torch.Tensor, exp: R.QuantOut, rows=None, what: str = "4-bit codes") -> None:
+    """``got`` (uint8 nibble values, same shape as ``exp.codes``) equals the oracle's codes, except that an element whose
+    scaled value sits on a rounding tie (``exp.tie``) may take either neighbouring code: the kernels take the group
+    scale's reciprocal with ``rcp.approx.ftz`` like the reference, the oracle with an exact division."""
+    e, t = exp.codes, exp.tie
+    if rows is not None:
+        got, e, t = got[rows], e[rows], (None if t is None else t[rows])
+    bad = got != e
+    if t is not None:
+        assert t.float().mean().item() <= 5e-2, "implausibly many rounding ties"
+        bad = bad & ~t
+    assert not bad.any(), f"{int(bad.sum())} {what} differ from the oracle away from rounding ties"
+    if t is not None:
+        d = (got.int() - e.int())[got != e]
+        if exp.fp4:
+            ok = ((got & 7).int() - (e & 7).int())[got != e].abs() <= 1
+        else:
+            ok = ((d + 8) % 16 - 8).abs() <= 1
+        assert bool(ok.all()), "a tie may only move a code to its neighbour"
+
+
+def module_quantize(m, x: torch.Tensor) -> "R.QuantOut":
+    """Run the module's own quantiser on the GPU and return its output as an oracle ``QuantOut`` (native layout)."""
+    codes, scales, lora = m.quantize(x)
+    return unpack_quant_out(codes, scales, lora, x.shape[-1], m.precision == "nvfp4", "native")

@@ -165,12 +165,14 @@ def test_prepared_weights_follow_the_parameters():
     y0 = m(x.view(1, M, K)).clone()
     first = m.qweight.__dict__[G._ATTR][0]
     assert m(x.view(1, M, K)) is not None and m.qweight.__dict__[G._ATTR][0] is first   # served from the cache
+    b0 = m.bias.detach().clone()
     with torch.no_grad():
         m.bias.add_(1.0)                                  # bumps the version counter
     y1 = m(x.view(1, M, K))
     assert m.qweight.__dict__[G._ATTR][0] is not first
     assert torch.allclose((y1 - y0).float().mean(), torch.tensor(1.0, device=dev), atol=2e-2)
-    m.bias.data.sub_(1.0)                                  # bypasses the counter: stale until told
+    m.bias.data.copy_(b0)                                  # bypasses the counter: stale until told
+    assert torch.equal(m(x.view(1, M, K)), y1)
     m.invalidate_prepared_weights()
     assert torch.equal(m(x.view(1, M, K)), y0)
     sd = {k: v.clone() for k, v in m.state_dict().items()}

@@ -31,7 +31,7 @@ def test_group_quantize_hand_case_nvfp4():
     # one group of 16: max 12 -> scale 2.0 exactly (12 * fp32(1/6) rounds to 2), codes = v / 2
     v = torch.zeros(1, 16, dtype=torch.bfloat16)
     v[0, :6] = torch.tensor([12.0, -6.0, 3.0, 1.0, 0.5, -0.4], dtype=torch.bfloat16)
-    codes, scales = R.group_quantize(v, fp4=True)
+    codes, scales, _ = R.group_quantize(v, fp4=True)
     assert scales.tolist() == [[0x40]]  # e4m3 2.0
     assert codes[0, :6].tolist() == [7, 8 | 5, 3, 1, 0, 8 | 0]   # 6, -3, 1.5, .5, .25->0 (tie to even), -.2->-0
     assert codes[0, 6:].tolist() == [0] * 10
@@ -40,7 +40,7 @@ def test_group_quantize_hand_case_nvfp4():
 def test_group_quantize_zero_group_and_scale_clamp():
     v = torch.zeros(2, 16, dtype=torch.bfloat16)
     v[1, 0] = 6000.0
-    codes, scales = R.group_quantize(v, fp4=True)
+    codes, scales, _ = R.group_quantize(v, fp4=True)
     assert scales[0, 0].item() == 0 and codes[0].sum().item() == 0
     assert scales[0, 1].item() == 0x7E          # 1000 clamps to 448
     assert codes[1, 0].item() == 7              # 6000 / 448 saturates to 6
@@ -49,7 +49,7 @@ def test_group_quantize_zero_group_and_scale_clamp():
 def test_group_quantize_hand_case_int4():
     v = torch.zeros(1, 64, dtype=torch.bfloat16)
     v[0, :4] = torch.tensor([7.0, -3.5, 0.5, -7.0], dtype=torch.bfloat16)
-    codes, scales = R.group_quantize(v, fp4=False)
+    codes, scales, _ = R.group_quantize(v, fp4=False)
     assert scales[0, 0].item() == 1.0
     assert fmt.int4_decode(codes[0, :4], False).tolist() == [7, -4, 0, -7]  # -3.5 -> -4 and .5 -> 0: ties to even
 
@@ -103,3 +103,19 @@ def test_ref_litela_against_explicit_loops():
                 o = ref_vk.float().double() @ q
                 exp = (o[:32].float() / (o[32].float() + 1e-6)).to(torch.bfloat16)
                 assert torch.equal(out[b, t, 32 * h: 32 * h + 32], exp)
+
+
+def test_group_quantize_flags_rounding_ties():
+    """An exact tie (7 * v / max = k + 0.5) is flagged: there the reference's approximate reciprocal decides the code."""
+    v = torch.zeros(1, 64)
+    v[0, 0] = 14.0            # group maximum: scale = 2
+    v[0, 1] = 3.0             # 3 / 2 = 1.5: a tie
+    v[0, 2] = 3.25            # 1.625: not a tie
+    codes, scales, tie = R.group_quantize(v.to(torch.bfloat16), fp4=False)
+    assert bool(tie[0, 1]) and not bool(tie[0, 2]) and not bool(tie[0, 0])
+    v = torch.zeros(1, 16)
+    v[0, 0] = 6.0             # scale = 1
+    v[0, 1] = 2.5             # midway between 2 and 3
+    v[0, 2] = 2.75
+    codes, scales, tie = R.group_quantize(v.to(torch.bfloat16), fp4=True)
+    assert bool(tie[0, 1]) and not bool(tie[0, 2])
