@@ -124,8 +124,20 @@ struct GemmParams {
 };
 #ifdef SVDQ_ABLATE
 #define ABLATE(p, bit) ((p).ablate & (1 << (bit)))
+// cycle accounting of pair 0 (timing experiments): [0..3] MMA warp total / wait full / wait tempty / stages,
+// [4..5] leader's A producer total / wait empty, [6..7] peer's A producer, [8..10] leader's epilogue warp 2 total / wait tfull / tiles,
+// [11] MMA warp: issue of cp + mma, [12] commit
+__device__ long long g_prof[16];
+#define PROF_T0(v) const long long v = clock64()
+#define PROF_ACC(v) long long v = 0
+#define PROF_ADD(acc, t0) acc += clock64() - (t0)
+#define PROF_OUT(cond, idx, acc) do { if (cond) g_prof[idx] += (acc); } while (0)
 #else
 #define ABLATE(p, bit) false
+#define PROF_T0(v)
+#define PROF_ACC(v)
+#define PROF_ADD(acc, t0)
+#define PROF_OUT(cond, idx, acc)
 #endif
 
 struct GemmShared {
@@ -476,13 +488,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int role = warp == 0 ? 0 : warp - 5;
         uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
         bool ok = true;
+        const bool prof_me = blockIdx.x < 2 && role == 0 && lane == 0;
+        PROF_T0(pt_all);
+        PROF_ACC(pa_wait);
         for (int ti = 0; ti < tr.count && ok; ++ti) {
             int m0, n0;
             tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
             const int nb0 = n0 + rank * G_BNH;   // this CTA's half of the tile's weight rows
             for (int ks = 0; ks < per_tile; ++ks, ++it) {
                 const int s = it % NS;
+                PROF_T0(pt_w);
                 ok = __all_sync(0xffffffffu, wait_or_abort<64>(&sh->empty[s], ((it / NS) & 1) ^ 1, sh, p.status, 10 + role));
+                PROF_ADD(pa_wait, pt_w);
                 if (!ok) break;
                 uint8_t* st = smem + s * G_STAGE_BYTES;
                 const uint32_t lfull = mapa_shared(smem_u32(&sh->full[s]), 0);   // the leader's barrier
@@ -510,6 +527,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 __syncwarp();
             }
         }
+        PROF_ACC(pa_all);
+        PROF_ADD(pa_all, pt_all);
+        PROF_OUT(prof_me, 4 + 2 * blockIdx.x, pa_all);
+        PROF_OUT(prof_me, 5 + 2 * blockIdx.x, pa_wait);
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and barrier
@@ -519,35 +540,53 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_F16 = idesc_f16(2 * G_BM, G_BN);
+            // This warp's instruction stream is the kernel's critical path: it is one warp, so every dependent instruction
+            // costs its full latency, and a stage's four MMAs only take ~470 cycles.  So the loop keeps the ring slot, its
+            // phase bit and the slot's descriptor offset as running values (no division), and builds each descriptor from a
+            // constant upper half and a lower half that moves by small immediates (the start-address field counts 16-byte
+            // units and cannot carry out of its 14 bits for addresses below 256 KB).
             const uint64_t adesc0 = smem_desc_sw128(smem_u32(smem));
             const uint64_t sfdesc0 = smem_desc_sf(smem_u32(smem) + G_A_BYTES + G_B_BYTES);
-            uint32_t it = 0, sq = 0;  // ring position, scale-factor stage count
+            const uint32_t sw_hi = static_cast<uint32_t>(adesc0 >> 32), sf_hi = static_cast<uint32_t>(sfdesc0 >> 32);
+            const uint32_t a_lo0 = static_cast<uint32_t>(adesc0), sf_lo0 = static_cast<uint32_t>(sfdesc0);
+            const uint32_t full0 = smem_u32(&sh->full[0]), empty0 = smem_u32(&sh->empty[0]);
+            uint32_t slot = 0, phase = 0, slot_off = 0, sq = 0;   // ring slot, its parity, its offset in 16-byte units, scale buffer
             bool ok = true;
+            const bool prof_me = blockIdx.x == 0 && lane == 0;
+            PROF_T0(pt_all);
+            PROF_ACC(pa_full); PROF_ACC(pa_te); PROF_ACC(pa_n); PROF_ACC(pa_issue); PROF_ACC(pa_commit);
             for (int ti = 0; ti < tr.count && ok; ++ti) {
                 const uint32_t as = ti & 1;
                 int m0_, n0_;
                 tile_coords(p, tr.first + ti * tr.stride, 0, m0_, n0_);
                 const uint32_t sfb_off = (n0_ & 127) ? 2 : 0;  // tile starts 64 rows into a 128-row scale atom
+                PROF_T0(pt_te);
                 ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
+                PROF_ADD(pa_te, pt_te);
                 if (!ok) break;
-                tc_fence_after_sync();
                 const uint32_t d_tmem = tmem + as * G_TM_ACC1;
                 uint32_t accumulate = 0;
-                for (int ks = 0; ks < per_tile; ++ks, ++it) {
-                    const int s = it % NS;
-                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->full[s], (it / NS) & 1, sh, p.status, 21));
+                for (int ks = 0; ks < per_tile; ++ks) {
+                    PROF_T0(pt_f);
+                    const uint32_t fbar = full0 + 8 * slot;
+                    if (!mbar_try_wait_addr(fbar, phase))   // usually there already
+                        ok = wait_or_abort(&sh->full[slot], phase, sh, p.status, 21);
+                    ok = __all_sync(0xffffffffu, ok);
+                    PROF_ADD(pa_full, pt_f);
+#ifdef SVDQ_ABLATE
+                    pa_n += 1;
+#endif
+                    PROF_T0(pt_i);
                     if (!ok) break;
-                    // descriptors of ring slot s: the start-address field counts 16-byte units
-                    const uint64_t adesc = adesc0 + static_cast<uint32_t>(s * (SB >> 4));
-                    const uint64_t bdesc = adesc + (G_A_BYTES >> 4);
+                    tc_fence_after_sync();
+                    const uint32_t a_lo = a_lo0 + slot_off, b_lo = a_lo + (G_A_BYTES >> 4);
                     if (I4 && ks < kstages) {
                         // INT4: four K=16 fp16 MMAs over the stage's 64 k (operands already carry their group scales)
-                        tc_fence_after_sync();
                         if (elect_one()) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                tc_mma_pair_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_F16, j == 0 ? accumulate : 1u);
-                            tc_commit_pair(&sh->empty[s], 3);
+                                tc_mma_pair_f16(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_F16, j == 0 ? accumulate : 1u);
+                            tc_commit_pair_addr(empty0 + 8 * slot, 3);
                         }
                     } else if (ks < kstages) {
                         const int nkb = min(4, KB - ks * 4);
@@ -555,45 +594,53 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         // reads them (the tensor pipe keeps the order).  Per k-block one 512-byte atom for the 128
                         // activation rows (4 columns) and two for the weight rows (8 columns; a tile that starts 64
                         // rows into an atom reads from column 2 on).  Two TMEM buffers alternate.
-                        const uint32_t t_sfa = tmem + G_TM_SF + (sq & 1) * G_TM_SF_STRIDE;
+                        const uint32_t t_sfa = tmem + G_TM_SF + sq * G_TM_SF_STRIDE;
                         const uint32_t t_sfb = t_sfa + 16;
-                        const uint64_t sfdesc = sfdesc0 + static_cast<uint32_t>(s * (SB >> 4));
-                        tc_fence_after_sync();
+                        const uint32_t sf_lo = sf_lo0 + slot_off;
                         if (elect_one()) {
                             if (nkb == 4) {
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     if (!ABLATE(p, 1)) {
-                                        tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
-                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
-                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
+                                        tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sf_lo + 32 * j, sf_hi);
+                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sf_lo + (G_SFA_BYTES >> 4) + 32 * j, sf_hi);
+                                        tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sf_lo + ((G_SFA_BYTES + 2048) >> 4) + 32 * j, sf_hi);
                                     }
                                     if (!ABLATE(p, 3))
-                                        tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
+                                        tc_mma_pair_nvfp4(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_FP4, t_sfa + 4 * j,
                                                           t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
                                 }
                             } else {
                                 for (int j = 0; j < nkb; ++j) {
-                                    tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sfdesc + 32 * j);
-                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sfdesc + (G_SFA_BYTES >> 4) + 32 * j);
-                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sfdesc + ((G_SFA_BYTES + 2048) >> 4) + 32 * j);
-                                    tc_mma_pair_nvfp4(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_FP4, t_sfa + 4 * j,
+                                    tc_cp_pair_32x128b_warpx4(t_sfa + 4 * j, sf_lo + 32 * j, sf_hi);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sf_lo + (G_SFA_BYTES >> 4) + 32 * j, sf_hi);
+                                    tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sf_lo + ((G_SFA_BYTES + 2048) >> 4) + 32 * j, sf_hi);
+                                    tc_mma_pair_nvfp4(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_FP4, t_sfa + 4 * j,
                                                       t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
                                 }
                             }
-                            tc_commit_pair(&sh->empty[s], 3);   // frees the stage in both CTAs
+                            PROF_ADD(pa_issue, pt_i);
+                            PROF_T0(pt_c);
+                            tc_commit_pair_addr(empty0 + 8 * slot, 3);   // frees the stage in both CTAs
+                            PROF_ADD(pa_commit, pt_c);
                         }
-                        ++sq;
+                        sq ^= 1;
                     } else {
-                        tc_fence_after_sync();
                         if (elect_one()) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                tc_mma_pair_tf32(d_tmem, adesc + 2 * j, bdesc + 2 * j, IDESC_TF32, j == 0 ? accumulate : 1u);
-                            tc_commit_pair(&sh->empty[s], 3);
+                                tc_mma_pair_tf32(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_TF32, j == 0 ? accumulate : 1u);
+                            tc_commit_pair_addr(empty0 + 8 * slot, 3);
                         }
                     }
                     accumulate = 1;
+                    if (++slot == NS) {
+                        slot = 0;
+                        slot_off = 0;
+                        phase ^= 1;
+                    } else {
+                        slot_off += SB >> 4;
+                    }
                     __syncwarp();
                 }
                 if (ok) {
@@ -601,6 +648,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     __syncwarp();
                 }
             }
+            PROF_ACC(pa_all);
+            PROF_ADD(pa_all, pt_all);
+            PROF_OUT(prof_me, 0, pa_all); PROF_OUT(prof_me, 1, pa_full); PROF_OUT(prof_me, 2, pa_te); PROF_OUT(prof_me, 3, pa_n);
+            PROF_OUT(prof_me, 11, pa_issue); PROF_OUT(prof_me, 12, pa_commit);
             if (sh->abort_flag) {  // let whatever was issued finish before TMEM is released
                 if (lane == 0) {
                     tc_commit_pair(&sh->drain, 1);
@@ -691,6 +742,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         };
         lacc_zero();
+        const bool prof_me = blockIdx.x == 0 && warp == 2 && lane == 0;
+        PROF_T0(pt_all);
+        PROF_ACC(pa_tf); PROF_ACC(pa_tiles);
 
         for (int ti = 0; ti < tr.count; ++ti) {
             int m0, n0;
@@ -725,7 +779,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
             __syncwarp();
+            PROF_T0(pt_tf);
             if (!wait_or_abort<64>(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
+            PROF_ADD(pa_tf, pt_tf);
+#ifdef SVDQ_ABLATE
+            pa_tiles += 1;
+#endif
             tc_fence_after_sync();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
             const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
@@ -846,6 +905,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if constexpr (RTN > 0) {
             if (cur_m0 >= 0) lacc_flush();
         }
+        PROF_ACC(pa_all);
+        PROF_ADD(pa_all, pt_all);
+        PROF_OUT(prof_me, 8, pa_all); PROF_OUT(prof_me, 9, pa_tf); PROF_OUT(prof_me, 10, pa_tiles);
         if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
     }
 
@@ -1275,3 +1337,15 @@ extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* s
 }
 
 
+
+#ifdef SVDQ_ABLATE
+// timing experiments: read and clear the cycle counters of pair 0
+extern "C" int svdq_debug_prof(long long* host16) {
+    using namespace svdq;
+    SVDQ_CUDA(cudaDeviceSynchronize());
+    SVDQ_CUDA(cudaMemcpyFromSymbol(host16, g_prof, sizeof(long long) * 16));
+    long long zero[16] = {};
+    SVDQ_CUDA(cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)));
+    return SVDQ_OK;
+}
+#endif

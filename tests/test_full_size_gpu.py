@@ -2,8 +2,9 @@
 
 * The FLUX MLP chain at full size (M = 4608, 3072 -> 12288 -> 3072, rank 32, both precisions) against the CPU oracle
   chain ``ref_gemm -> ref_requantize -> ref_gemm`` on every 9th row (rows are independent, so a row sample of the oracle
-  is compared with the same rows of the full GPU call): relative L2 <= 1e-2 on the chain's output, and the 4-bit codes /
-  scales that fc1's epilogue hands to fc2 bit-exact given the kernel's own bf16 tile.
+  is compared with the same rows of the full GPU call): fc1's bf16 tile and fc2's output (on the codes the GPU handed
+  over) within 4e-3, the 4-bit codes / scales that fc1's epilogue hands to fc2 bit-exact given the kernel's own bf16 tile,
+  and the whole chain against the all-oracle chain.
 * One joint and one single FLUX block at full geometry (hidden 3072, 24 heads, 4096 + 512 tokens) and a SANA block pair at
   full width (2240 -> 2304, GLUMBConv 5600) against their bf16 twins built from the same master weights.
 """
@@ -56,9 +57,12 @@ def test_mlp_chain_full_size_against_oracle(fp4):
     # the first layer's quantiser: codes and scales of all rows bit-exact against the oracle
     gq1 = H.unpack_quant_out(*xq, K, fp4, "native")
     H.assert_codes_match(gq1.codes, q1, rows=slice(0, M))
-    # the chain's output on the sampled rows
+    # the chain's output on the sampled rows against the all-oracle chain.  Two correct evaluations of fc1 differ in the
+    # last bf16 bit of some outputs (summation order), which moves those values across a 4-bit rounding boundary of fc2's
+    # input: a full quantisation step each, for a fraction of a percent of the codes.  That bounds how close two
+    # chains can be (measured 1.6-1.8e-2); the steps themselves are held to the path's 1e-2 / 4e-3 below.
     e = R.rel_l2(got_y.float().cpu()[rows], y)
-    assert e <= 1e-2, f"MLP chain vs oracle chain: relative L2 {e}"
+    assert e <= 2.5e-2, f"MLP chain vs oracle chain: relative L2 {e}"
     # fc1's bf16 tile against the oracle, then its requantisation bit-exact given that very tile
     assert R.rel_l2(out1.float().cpu()[rows], h) <= 4e-3
     gq2 = H.unpack_quant_out(qout, osc, la2, N1, fp4, "native")
@@ -68,6 +72,10 @@ def test_mlp_chain_full_size_against_oracle(fp4):
     assert torch.equal(gq2.scales[:, rows].contiguous().view(view), exp.scales.view(view))
     err = (gq2.lora_act[rows] - exp.lora_act).abs().max().item()
     assert err <= 2e-5 * max(exp.lora_act.abs().max().item(), 1.0) + 1e-6
+    # fc2 on the codes the GPU handed over: the second GEMM alone, tight
+    g2 = R.QuantOut(gq2.codes[rows], gq2.scales[:, rows].contiguous(), gq2.lora_act[rows], fp4, not fp4)
+    e2 = R.rel_l2(got_y.float().cpu()[rows], R.ref_gemm(g2, fc2))
+    assert e2 <= 4e-3, f"fc2 on the GPU's own 4-bit input vs oracle: relative L2 {e2}"
 
 
 def _rel(a, b):
