@@ -56,31 +56,31 @@
 namespace svdq {
 
 constexpr int G_BM = 128;
-constexpr int G_BN = 192;
+constexpr int G_BN = 256;
 constexpr int G_BNH = G_BN / 2;                 // weight rows each CTA of a pair loads
 constexpr int G_STAGES = 5;
 constexpr int G_A_BYTES = G_BM * 128;           // 16 KB
-constexpr int G_B_BYTES = G_BNH * 128;          // 12 KB
+constexpr int G_B_BYTES = G_BNH * 128;          // 16 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
-constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 34816 = 34 * 1024
+constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 38912 = 38 * 1024
 constexpr int G_THREADS = 9 * 32;              // warp 1 issues MMAs; 2..5 epilogue; 0, 6, 7, 8 produce (A, B, scales of A, scales of B)
 constexpr int G_THREADS_RQ = 13 * 32;          // requantising variants up to rank 32: warps 9..12 are a second epilogue set
 constexpr int G_SF_BUFS = 2;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
-constexpr int G_TM_ACC1 = G_BN;                 // second accumulator
-constexpr int G_TM_SF = 2 * G_BN;               // 384: scale-factor buffers of 40 columns each
-constexpr int G_TM_SF_STRIDE = 48;              // per buffer: 4 x 4 columns for A, 4 x 8 for B (two 128-row atoms per k-block)
+constexpr int G_TM_ACC1 = G_BN;                 // second accumulator: the two fill all 512 columns
+constexpr int G_TM_SF_STRIDE = 48;              // per scale-factor buffer: 4 x 4 columns for A, 4 x 8 for B (two 128-row atoms per k-block)
+constexpr int G_TM_SF_COLS = G_SF_BUFS * G_TM_SF_STRIDE;   // 96: they live in the first columns of the accumulator that is being drained
 constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
-constexpr int G_COLV_FLOATS = 3 * G_BN;                     // per epilogue warp: scale, bias, 1/smooth_next
-constexpr int G_COLV_BYTES = 8 * G_COLV_FLOATS * 4;           // up to 8 epilogue warps
+constexpr int G_COLV_FLOATS = 64;                           // per epilogue warp: 1/smooth_next of the chunk in hand
+constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;           // INT4: four epilogue warps; NVFP4: eight, see smem_bytes
 // INT4 variant (template parameter I4): a stage is 64 k of fp16 operands, the activation half converted from packed
 // codes by converter warps; the packed codes come through a small ring of their own.
 constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
-constexpr int H_B_BYTES = G_BNH * 128;          // 96 rows x 64 fp16
-constexpr int H_STAGE_BYTES = H_A_BYTES + H_B_BYTES;   // 28672 = 28 * 1024
-constexpr int H_STAGES = 6;                     // INT4 operand ring (28 KB stages)
+constexpr int H_B_BYTES = G_BNH * 128;          // 128 rows x 64 fp16
+constexpr int H_STAGE_BYTES = H_A_BYTES + H_B_BYTES;   // 32768
+constexpr int H_STAGES = 6;                     // INT4 operand ring (32 KB stages)
 constexpr int H_GROUPS = 5;                     // converter groups: stages in conversion at once
 constexpr int H_CONV_WARPS = 2 * H_GROUPS;
 constexpr int H_CONV_PER_STAGE = 2;             // converter warps that share one stage (64 rows each); four such groups take turns
@@ -89,8 +89,9 @@ template <bool I4>
 constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
 template <bool I4>
 constexpr size_t smem_bytes() {
-    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + G_COLV_BYTES + 512;
+    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + (I4 ? 1 : 2) * G_COLV_BYTES + 256;
 }
+static_assert(smem_bytes<false>() <= 227 * 1024 && smem_bytes<true>() <= 227 * 1024, "dynamic shared memory of a CTA on sm_100");
 
 struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
@@ -145,6 +146,7 @@ struct GemmShared {
     uint64_t empty[H_STAGES];       // each CTA: the MMAs of the stage are done (multicast tcgen05.commit)
     uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
+    uint64_t sfree[2];              // leader: the first G_TM_SF_COLS columns of the accumulator are in registers (all epilogue warps, both CTAs)
     uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
     uint64_t xempty[4];             // ... and has been added by the first
     uint64_t drain;
@@ -252,8 +254,8 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
         const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const float4 s4 = cs[2 * j + i];
-            const float4 b4 = cb[2 * j + i];
+            const float4 s4 = __ldg(cs + 2 * j + i);
+            const float4 b4 = __ldg(cb + 2 * j + i);
             float2 a01 = make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1]));
             float2 a23 = make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
             if constexpr (ROWSCALE) {   // exact: a power of two
@@ -276,7 +278,7 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
 // Requantising epilogues do about three times the work of the plain one per chunk; up to rank 32 (where a warp's
 // LoRA-down partial fits its 4 KB staging buffer) a second set of four epilogue warps takes every other 64-column chunk.
 template <int RTN, bool I4>
-constexpr int epi_sets() { return (!I4 && (RTN == 1 || RTN == 2)) ? 2 : 1; }
+constexpr int epi_sets() { return (!I4 && RTN <= 2) ? 2 : 1; }
 template <int RTN, bool I4>
 constexpr int cta_threads() { return I4 ? H_THREADS : (epi_sets<RTN, I4>() == 2 ? G_THREADS_RQ : G_THREADS); }
 
@@ -312,7 +314,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     constexpr int NS = I4 ? H_STAGES : G_STAGES;                              // depth of the operand ring
     uint8_t* epi_smem = smem + NS * SB;
     float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
-    GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + G_COLV_BYTES);
+    GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + (I4 ? 1 : 2) * G_COLV_BYTES);
+    static_assert(sizeof(GemmShared) <= 256, "barrier block");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -331,6 +334,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int i = 0; i < 2; ++i) {
             mbar_init(&sh->tfull[i], 1);
             mbar_init(&sh->tempty[i], 8 * epi_sets<RTN, I4>());
+            mbar_init(&sh->sfree[i], 8 * epi_sets<RTN, I4>());
         }
         for (int i = 0; i < 4; ++i) {
             mbar_init(&sh->xfull[i], 1);
@@ -557,14 +561,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             PROF_ACC(pa_full); PROF_ACC(pa_te); PROF_ACC(pa_n); PROF_ACC(pa_issue); PROF_ACC(pa_commit);
             for (int ti = 0; ti < tr.count && ok; ++ti) {
                 const uint32_t as = ti & 1;
-                int m0_, n0_;
-                tile_coords(p, tr.first + ti * tr.stride, 0, m0_, n0_);
-                const uint32_t sfb_off = (n0_ & 127) ? 2 : 0;  // tile starts 64 rows into a 128-row scale atom
                 PROF_T0(pt_te);
                 ok = __all_sync(0xffffffffu, wait_or_abort(&sh->tempty[as], ((ti >> 1) & 1) ^ 1, sh, p.status, 20));
+                // The two accumulators fill TMEM, so this tile's scale factors go to the first columns of the OTHER
+                // accumulator: the previous tile's, which its epilogue is draining.  They are free once every epilogue warp
+                // of both CTAs has its first chunk in registers (the very first tile finds them unused).
+                if (!I4 && ti > 0 && ok)
+                    ok = __all_sync(0xffffffffu, wait_or_abort(&sh->sfree[as ^ 1], ((ti - 1) >> 1) & 1, sh, p.status, 22));
                 PROF_ADD(pa_te, pt_te);
                 if (!ok) break;
                 const uint32_t d_tmem = tmem + as * G_TM_ACC1;
+                const uint32_t sf_tmem = tmem + (as ^ 1) * G_TM_ACC1;
                 uint32_t accumulate = 0;
                 for (int ks = 0; ks < per_tile; ++ks) {
                     PROF_T0(pt_f);
@@ -592,9 +599,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         const int nkb = min(4, KB - ks * 4);
                         // Scale factors: shared memory -> TMEM with tcgen05.cp, issued just ahead of the MMA that
                         // reads them (the tensor pipe keeps the order).  Per k-block one 512-byte atom for the 128
-                        // activation rows (4 columns) and two for the weight rows (8 columns; a tile that starts 64
-                        // rows into an atom reads from column 2 on).  Two TMEM buffers alternate.
-                        const uint32_t t_sfa = tmem + G_TM_SF + sq * G_TM_SF_STRIDE;
+                        // activation rows (4 columns) and two for the tile's 256 weight rows (8 columns).  Two TMEM
+                        // buffers alternate.
+                        const uint32_t t_sfa = sf_tmem + sq * G_TM_SF_STRIDE;
                         const uint32_t t_sfb = t_sfa + 16;
                         const uint32_t sf_lo = sf_lo0 + slot_off;
                         if (elect_one()) {
@@ -608,7 +615,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                     }
                                     if (!ABLATE(p, 3))
                                         tc_mma_pair_nvfp4(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_FP4, t_sfa + 4 * j,
-                                                          t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
+                                                          t_sfb + 8 * j, j == 0 ? accumulate : 1u);
                                 }
                             } else {
                                 for (int j = 0; j < nkb; ++j) {
@@ -616,7 +623,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                     tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j, sf_lo + (G_SFA_BYTES >> 4) + 32 * j, sf_hi);
                                     tc_cp_pair_32x128b_warpx4(t_sfb + 8 * j + 4, sf_lo + ((G_SFA_BYTES + 2048) >> 4) + 32 * j, sf_hi);
                                     tc_mma_pair_nvfp4(d_tmem, a_lo + 2 * j, b_lo + 2 * j, sw_hi, IDESC_FP4, t_sfa + 4 * j,
-                                                      t_sfb + 8 * j + sfb_off, j == 0 ? accumulate : 1u);
+                                                      t_sfb + 8 * j, j == 0 ? accumulate : 1u);
                                 }
                             }
                             PROF_ADD(pa_issue, pt_i);
@@ -759,26 +766,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     cur_m0 = m0;
                 }
             }
-            // per-column constants of this tile -> this warp's shared-memory copy (issued before the
-            // accumulator is needed, so the latency hides behind the wait)
-#pragma unroll
-            for (int i = 0; i < 3; ++i) {
-                const int e = lane + 32 * i;            // 0..95: 48 float4 of scale, then 48 of bias
-                const int which = e / 48, c4 = (e % 48) * 4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (n0 + c4 < p.N) v = __ldg(reinterpret_cast<const float4*>((which ? p.col_bias : p.col_scale) + n0 + c4));
-                *reinterpret_cast<float4*>(cvs + which * G_BN + c4) = v;
-            }
-            if constexpr (RTN > 0) {
-#pragma unroll
-                for (int i = 0; i < G_BN / 32; ++i) {
-                    const int n = n0 + lane + 32 * i;
-                    float r = 0.f;
-                    if (n < p.N) r = __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)]));
-                    cvs[2 * G_BN + lane + 32 * i] = r;
-                }
-            }
-            __syncwarp();
             PROF_T0(pt_tf);
             if (!wait_or_abort<64>(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
             PROF_ADD(pa_tf, pt_tf);
@@ -790,6 +777,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
             float rowsc = 1.0f;
             if constexpr (I4) rowsc = __ldg(p.row_scale + grow);
+            bool sf_cols_free = I4;   // NVFP4: the accumulator's first columns become the next tile's scale-factor buffers
 #pragma unroll 1
             for (int h = 0; h < G_BN / 64; ++h) {
                 if (n0 + h * 64 >= p.N || ABLATE(p, 0)) break;
@@ -797,14 +785,31 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t r0[32], r1[32];
                 tc_ld_32x32b_x32(taddr + h * 64, r0);
                 tc_ld_32x32b_x32(taddr + h * 64 + 32, r1);
+                if constexpr (RTN > 0) {   // reciprocal smoothing factors of the chunk's 64 columns (next layer), un-permuted
+                    __syncwarp();          // every lane is done with the previous chunk's factors
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int n = n0 + h * 64 + lane + 32 * i;
+                        cvs[lane + 32 * i] = __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)]));
+                    }
+                }
                 uint8_t* buf = SETS == 2 ? my_buf : my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
                 if (lane == 0) {   // the store that last used this buffer has been read
                     if (SETS == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
                 }
                 __syncwarp();
                 tc_wait_ld();
-                const float4* cs = reinterpret_cast<const float4*>(cvs + h * 64);
-                const float4* cb = reinterpret_cast<const float4*>(cvs + G_BN + h * 64);
+                if (!sf_cols_free && h >= G_TM_SF_COLS / 64 - (SETS == 2 ? 1 : 0)) {
+                    // columns [0, G_TM_SF_COLS) of this accumulator are in registers (this warp's share of them): the MMA
+                    // warp may overwrite them with the next tile's scale factors
+                    sf_cols_free = true;
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
+                }
+                // per-column scale and bias straight from global memory (the same address in every lane: one L1 line per load)
+                const float4* cs = reinterpret_cast<const float4*>(p.col_scale + n0 + h * 64);
+                const float4* cb = reinterpret_cast<const float4*>(p.col_bias + n0 + h * 64);
                 uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
                 if constexpr (RTN > 0) {
                     // the reference's requantising branch always applies GELU (gemm_w4a4_launch_impl.cuh:282-309)
@@ -844,7 +849,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             }
                         }
                     }
-                    const float4* rcn = reinterpret_cast<const float4*>(cvs + 2 * G_BN + h * 64);
+                    const float4* rcn = reinterpret_cast<const float4*>(cvs);
                     uint4* qdst = reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(grow) * (p.N >> 1) + ((n0 + h * 64) >> 1));
                     if constexpr (I4) {
                         // ---- INT4 group quantisation: this thread's 64 values are exactly one group of the next layer;
@@ -900,7 +905,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tempty[as]), 0));
+            if (lane == 0) {
+                if (!sf_cols_free) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
+                mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tempty[as]), 0));
+            }
         }
         if constexpr (RTN > 0) {
             if (cur_m0 >= 0) lacc_flush();
