@@ -248,6 +248,36 @@ def int4_config0(dev, peaks):
             "launches_timed": 50}
 
 
+def mlp_chain_config2(dev, peaks, fp4_peak, reps=30):
+    """The FLUX MLP chain (M=4608, 3072 -> 12288 with GELU + next-layer requantisation + LoRA-down fused into fc1's GEMM,
+    then 12288 -> 3072), rank 32, NVFP4, random packed weights: time of the whole chain and of fc1 / fc2 as plain GEMMs."""
+    from nunchaku_b200.models.random_init import random_w4a4_linear
+    from nunchaku_b200.ops import fused_gelu_mlp
+
+    Mm, Hd = 4608, 3072
+    g = torch.Generator(device=dev).manual_seed(11)
+    fc1 = random_w4a4_linear(Hd, 4 * Hd, R, "nvfp4", True, g, dev, bias_std=0.02)
+    fc2 = random_w4a4_linear(4 * Hd, Hd, R, "nvfp4", True, g, dev, bias_std=0.02)
+    x = torch.randn(1, Mm, Hd, generator=g, device=dev).to(torch.bfloat16)
+    for _ in range(3):
+        fused_gelu_mlp(x, fc1, fc2)
+    chain = event_times([lambda: fused_gelu_mlp(x, fc1, fc2)], reps)[0]
+    q1 = fc1.quantize(x.view(Mm, Hd))
+    o1 = torch.empty(Mm, 4 * Hd, dtype=torch.bfloat16, device=dev)
+    fc1.forward_quant(*q1, o1)
+    t1 = event_times([lambda: fc1.forward_quant(*q1, o1)], reps)[0]
+    q2 = fc2.quantize(o1)
+    o2 = torch.empty(Mm, Hd, dtype=torch.bfloat16, device=dev)
+    fc2.forward_quant(*q2, o2)
+    t2 = event_times([lambda: fc2.forward_quant(*q2, o2)], reps)[0]
+    tq = event_times([lambda: fc1.quantize(x.view(Mm, Hd))], reps)[0]
+    flop = 2.0 * Mm * Hd * 4 * Hd * 2 + 2.0 * Mm * R * 5 * Hd
+    return {"workload": f"FLUX MLP chain M={Mm}, {Hd} -> {4 * Hd} (GELU + NVFP4 requantisation + LoRA-down in the epilogue) -> {Hd}, R={R}",
+            "chain_us": chain * 1e3, "chain_tflops": flop / (chain * 1e-3) / 1e12, "chain_frac_of_fp4_peak": flop / (chain * 1e-3) / 1e12 / fp4_peak,
+            "quantizer_us": tq * 1e3, "fc1_plain_gemm_us": t1 * 1e3, "fc2_plain_gemm_us": t2 * 1e3,
+            "fc1_requant_gemm_us_est": (chain - tq - t2) * 1e3, "launches_timed": reps}
+
+
 def reference_int4_kernels(dev):
     """The reference's own INT4 kernels (compiled from the reference tree into oracle/_ref, mma.sync, no sm_100 tuning)
     timed on this GPU on the same case as ``int4_config0``: a baseline beside the CPU port, not the product path."""
@@ -287,6 +317,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model-steps", action="store_true", help="skip the FLUX / SANA transformer-step legs and the INT4 case")
+    ap.add_argument("--only", default=None, choices=["mlp", "int4"],
+                    help="profiler captures: run just this leg (a few launches of it) and print its record")
     ap.add_argument("--shape", default=None, help="M,K,N override: a smaller case of the same path for profiler captures "
                     "(the default is the benchmark workload); implies --no-model-steps")
     args = ap.parse_args()
@@ -312,6 +344,11 @@ def main():
     dev = torch.device("cuda", local)
     from nunchaku_b200 import _lib
     _lib.load()
+    if args.only:
+        peaks, _ = load_peaks()
+        rec = mlp_chain_config2(dev, peaks, 8500.0, reps=max(2, args.steps)) if args.only == "mlp" else int4_config0(dev, peaks)
+        print(json.dumps(rec), flush=True)
+        return
 
     x = make_inputs(dev, rank)
     m = build_layer(dev, 0, x)
@@ -448,6 +485,7 @@ def main():
         torch.cuda.empty_cache()
         if rank == 0:
             line["int4_config0"] = int4_config0(dev, peaks)
+            line["mlp_chain_config2"] = mlp_chain_config2(dev, peaks, fp4_peak)
         D.barrier()
         from nunchaku_b200.models import flux_bench, sana_bench
         line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2)

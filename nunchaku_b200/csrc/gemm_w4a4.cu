@@ -766,6 +766,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     cur_m0 = m0;
                 }
             }
+            // next layer's smoothing factors of the chunks this warp will take: fetched now, so that the loads fly while the
+            // warp waits for the accumulator (lane l: columns l and l + 32 of each 64-column chunk)
+            __nv_bfloat16 nsm[G_BN / 64][2];
+            if constexpr (RTN > 0) {
+#pragma unroll
+                for (int h = 0; h < G_BN / 64; ++h)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int n = n0 + h * 64 + lane + 32 * i;
+                        nsm[h][i] = n < p.N ? p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)] : __nv_bfloat16(1.0f);
+                    }
+            }
             PROF_T0(pt_tf);
             if (!wait_or_abort<64>(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
             PROF_ADD(pa_tf, pt_tf);
@@ -789,8 +801,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     __syncwarp();          // every lane is done with the previous chunk's factors
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
-                        const int n = n0 + h * 64 + lane + 32 * i;
-                        cvs[lane + 32 * i] = __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)]));
+                        __nv_bfloat16 v = nsm[0][i];
+#pragma unroll
+                        for (int hh = 1; hh < G_BN / 64; ++hh) v = h == hh ? nsm[hh][i] : v;   // registers: no dynamic indexing
+                        cvs[lane + 32 * i] = __frcp_rn(__bfloat162float(v));
                     }
                 }
                 uint8_t* buf = SETS == 2 ? my_buf : my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
