@@ -64,8 +64,13 @@ constexpr int G_B_BYTES = G_BNH * 128;          // 16 KB
 constexpr int G_SFA_BYTES = 4 * 512;            // 4 k-blocks x one 128-row atom
 constexpr int G_SFB_BYTES = 2 * 4 * 512;        // 4 k-blocks x two 128-row atoms
 constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;  // 38912 = 38 * 1024
-constexpr int G_THREADS = 9 * 32;              // warp 1 issues MMAs; 2..5 epilogue; 0, 6, 7, 8 produce (A, B, scales of A, scales of B)
-constexpr int G_THREADS_RQ = 13 * 32;          // requantising variants up to rank 32: warps 9..12 are a second epilogue set
+// NVFP4 warp map, by warpgroup (four warps; registers are re-divided between warpgroups, see reg_dealloc):
+//   warps 0..3   producers (A tile, B tile, scale atoms of A, scale atoms of B)
+//   warps 4..7   epilogue set 0 (TMEM lane quadrant = warp & 3);  warps 8..11  epilogue set 1 (when there are two sets)
+//   first warp of the last warpgroup: MMA issuer; the other three warps of that group only take part in the barriers
+constexpr int G_THREADS = 12 * 32;             // one epilogue set
+constexpr int G_THREADS_RQ = 16 * 32;          // two epilogue sets
+constexpr int G_REGS_PRODUCER = 48, G_REGS_MMA = 48, G_REGS_EPILOGUE = 200;   // per thread after the re-division (two sets)
 constexpr int G_SF_BUFS = 2;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator: the two fill all 512 columns
@@ -281,6 +286,8 @@ template <int RTN, bool I4>
 constexpr int epi_sets() { return (!I4 && RTN <= 2) ? 2 : 1; }
 template <int RTN, bool I4>
 constexpr int cta_threads() { return I4 ? H_THREADS : (epi_sets<RTN, I4>() == 2 ? G_THREADS_RQ : G_THREADS); }
+template <int RTN, bool I4>
+constexpr int mma_warp() { return I4 ? 1 : 4 + 4 * epi_sets<RTN, I4>(); }
 
 // Eight packed s4 / u4 codes -> eight fp16 values code * scale, in the order (0, 4, 1, 5, 2, 6, 3, 7).
 // (x & 0x000f000f) | 0x6400 is the fp16 number 1024 + code, (x & 0x00f000f0) | 0x6400 is 1024 + 16 * code; one exact
@@ -355,7 +362,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             prefetch_tmap(&tm_lu);
         }
     }
-    if (warp == 1) {
+    constexpr int MMA_WARP = mma_warp<RTN, I4>();
+    if (warp == MMA_WARP) {
         tmem_alloc_pair(&sh->tmem_base, G_TMEM_COLS);
         tmem_relinquish_pair();
     }
@@ -365,6 +373,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     pdl_launch_dependents();
     pdl_wait();           // nothing above touches global memory; the quantiser's output is this kernel's input
     const uint32_t tmem = sh->tmem_base;
+    // 16 warps at 128 registers each fill the register file; the epilogue needs ~180 and the other roles ~50: each role's
+    // branch starts by giving registers back or asking for more (inside the branch, so that the compiler can tell which
+    // budget applies to which code)
+    constexpr bool REGCTL = !I4 && epi_sets<RTN, I4>() == 2;
 
     if (I4 && (warp == 0 || warp >= 6)) {
         // ------------------------------------------------------------------ INT4 producers and converter warps
@@ -482,14 +494,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
             }
         }
-    } else if (!I4 && (warp == 0 || (warp >= 6 && warp < 9))) {
+    } else if (!I4 && warp < 4) {
+        if constexpr (REGCTL) reg_dealloc<G_REGS_PRODUCER>();
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
         // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
         // 1 = weight tile, 2 = scale atoms of the activation rows, 3 = scale atoms of the 192 weight rows (whole
         // 128-row atoms: two of them).  All are counted on the leader's barrier; a tile past the end of a
         // tensor is filled with zeros by the hardware and still counts its full size.
-        const int role = warp == 0 ? 0 : warp - 5;
+        const int role = warp;
         uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
         bool ok = true;
         const bool prof_me = blockIdx.x < 2 && role == 0 && lane == 0;
@@ -535,12 +548,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         PROF_ADD(pa_all, pt_all);
         PROF_OUT(prof_me, 4 + 2 * blockIdx.x, pa_all);
         PROF_OUT(prof_me, 5 + 2 * blockIdx.x, pa_wait);
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    } else if (warp >= MMA_WARP && (I4 ? warp == MMA_WARP : true)) {
+        if constexpr (REGCTL) reg_dealloc<G_REGS_MMA>();
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only; NVFP4: the other
+        // warps of its warpgroup only give their registers back)
         // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and barrier
         // addresses then stay warp-uniform.  (With the loop inside `if (lane == 0)` every operand is a
         // per-thread value and the issue rate, not the tensor pipe, bounds the kernel.)
-        if (rank == 0) {
+        if (rank == 0 && warp == MMA_WARP) {
             constexpr uint32_t IDESC_FP4 = idesc_nvfp4(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_TF32 = idesc_tf32(2 * G_BM, G_BN);
             constexpr uint32_t IDESC_F16 = idesc_f16(2 * G_BM, G_BN);
@@ -667,14 +682,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 __syncwarp();
             }
         }
-    } else if ((warp >= 2 && warp < 6) || (!I4 && warp >= 9)) {
-        // ------------------------------------------------------------------ epilogue (warps 2..5, and 9..12 when requantising)
+    } else if (I4 ? (warp >= 2 && warp < 6) : (warp >= 4 && warp < MMA_WARP)) {
+        if constexpr (REGCTL) reg_alloc<G_REGS_EPILOGUE>();
+        // ------------------------------------------------------------------ epilogue (INT4: warps 2..5; NVFP4: 4..7 and 8..11)
         // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
         // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
         // hardware clips rows >= M and columns >= N).  Two staging buffers per warp keep a store in flight.
         constexpr int SETS = epi_sets<RTN, I4>();
         const int q = warp & 3;  // TMEM lane quadrant this warp may read
-        const int eset = warp >= 9 ? 1 : 0;
+        const int eset = I4 ? 0 : (warp - 4) >> 2;
         // one set: two staging buffers per warp (a store stays in flight); two sets: one buffer per warp
         uint8_t* my_buf = epi_smem + (q * 2 + (SETS == 2 ? eset : 0)) * G_EPI_BUF_BYTES;
         float* cvs = colv + (eset * 4 + q) * G_COLV_FLOATS;
@@ -749,7 +765,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         };
         lacc_zero();
-        const bool prof_me = blockIdx.x == 0 && warp == 2 && lane == 0;
+        const bool prof_me = blockIdx.x == 0 && (warp == (I4 ? 2 : 4)) && lane == 0;
         PROF_T0(pt_all);
         PROF_ACC(pa_tf); PROF_ACC(pa_tiles);
 
@@ -938,7 +954,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();
-    if (warp == 1) {
+    if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem, G_TMEM_COLS);
     }

@@ -40,6 +40,20 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- register reallocation between warpgroups
+// The register file is split evenly between the threads of a CTA at launch; a warpgroup (four consecutive warps, all of
+// which must execute the instruction) can hand registers back or ask for more.  Roles that only issue copies or MMAs give
+// theirs to the epilogue warps, which would otherwise spill.  The increase waits until the registers are free, so the
+// decreases must be reached unconditionally.
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
