@@ -38,8 +38,8 @@ FLOP_STEP = FLOP_GEMM                                   # the metric counts GEMM
 QUANT_BYTES = 2 * M * K + M * K // 2 + M * K // 16 + 4 * M * R + 2 * K * R + 2 * K
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size gemm_w4a4_kernel (NVFP4) launch (48.7 MB + 144.6 MB)
-GEMM_DRAM_TRAFFIC = 48716544 + 144581632
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size gemm_w4a4_kernel (NVFP4) launch (49.2 MB + 146.2 MB)
+GEMM_DRAM_TRAFFIC = 49225472 + 146244608
 
 
 def load_peaks():
@@ -278,6 +278,36 @@ def mlp_chain_config2(dev, peaks, fp4_peak, reps=30):
             "fc1_requant_gemm_us_est": (chain - tq - t2) * 1e3, "launches_timed": reps}
 
 
+def rowwise_kernels(dev, peaks, reps=20):
+    """The row-wise kernels either side of the W4A4 linears against their algorithmic HBM bytes: RMSNorm + RoPE on a FLUX QKV
+    output [4608, 9216], LayerNorm + modulation on [4608, 3072], ReLU linear attention on a SANA QKV output [4, 1024, 6912]."""
+    from nunchaku_b200.ops import layernorm_modulate, litela_attention, qk_norm_rope
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    res = {}
+
+    def add(name, fn, byt, shape):
+        for _ in range(3):
+            fn()
+        us = event_times([fn], reps)[0] * 1e3
+        res[name] = {"us": us, "GBps": byt / us / 1e3, "frac_hbm": byt / us / 1e3 / peaks["hbm_gbs"], "shape": shape}
+
+    S, heads = 4608, 24
+    qkv = torch.randn(1, S, 3 * heads * 128, generator=g, **bf)
+    w = torch.ones(128, **bf)
+    ang = torch.rand(S, 64, device=dev, generator=g) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    add("qk_norm_rope", lambda: qk_norm_rope(qkv, w, w, cos, sin, heads), S * (8 * heads * 128 + 512), [S, 3 * heads * 128])
+    x = torch.randn(1, S, 3072, generator=g, **bf)
+    sc, sh = torch.randn(1, 3072, generator=g, **bf) * 0.1, torch.randn(1, 3072, generator=g, **bf) * 0.1
+    add("layernorm_modulate", lambda: layernorm_modulate(x, sc, sh), S * 3072 * 4, [S, 3072])
+    B, T, lh = 4, 1024, 72
+    q = torch.randn(B, T, 3 * lh * 32, generator=g, **bf)
+    add("litela_attention", lambda: litela_attention(q, lh), B * T * lh * 32 * 8, [B, T, 3 * lh * 32])
+    return res
+
+
 def reference_int4_kernels(dev):
     """The reference's own INT4 kernels (compiled from the reference tree into oracle/_ref, mma.sync, no sm_100 tuning)
     timed on this GPU on the same case as ``int4_config0``: a baseline beside the CPU port, not the product path."""
@@ -317,7 +347,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model-steps", action="store_true", help="skip the FLUX / SANA transformer-step legs and the INT4 case")
-    ap.add_argument("--only", default=None, choices=["mlp", "int4"],
+    ap.add_argument("--only", default=None, choices=["mlp", "int4", "rowwise"],
                     help="profiler captures: run just this leg (a few launches of it) and print its record")
     ap.add_argument("--shape", default=None, help="M,K,N override: a smaller case of the same path for profiler captures "
                     "(the default is the benchmark workload); implies --no-model-steps")
@@ -346,7 +376,12 @@ def main():
     _lib.load()
     if args.only:
         peaks, _ = load_peaks()
-        rec = mlp_chain_config2(dev, peaks, 8500.0, reps=max(2, args.steps)) if args.only == "mlp" else int4_config0(dev, peaks)
+        if args.only == "mlp":
+            rec = mlp_chain_config2(dev, peaks, 8500.0, reps=max(2, args.steps))
+        elif args.only == "rowwise":
+            rec = rowwise_kernels(dev, peaks, reps=max(2, args.steps))
+        else:
+            rec = int4_config0(dev, peaks)
         print(json.dumps(rec), flush=True)
         return
 
@@ -486,6 +521,7 @@ def main():
         if rank == 0:
             line["int4_config0"] = int4_config0(dev, peaks)
             line["mlp_chain_config2"] = mlp_chain_config2(dev, peaks, fp4_peak)
+            line["rowwise_kernels"] = rowwise_kernels(dev, peaks)
         D.barrier()
         from nunchaku_b200.models import flux_bench, sana_bench
         line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2)
