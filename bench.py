@@ -238,7 +238,7 @@ def int4_config0(dev, peaks):
     tq, tg = event_times([q, gm], 50)
     flop = 2.0 * M0 * N0 * K0 + 2.0 * M0 * N0 * R
     tf = flop / (tg * 1e-3) / 1e12
-    f16 = mma_rate_pair("f16", 192, iters=2000)["tflops"]
+    f16 = mma_rate_pair("f16", 256, iters=2000)["tflops"]
     i8 = mma_rate("i8", 256, iters=2000)["tflops"]
     qbytes = 2 * M0 * K0 + M0 * K0 // 2 + M0 * (K0 // 64) * 2 + 4 * M0 * R + 2 * K0 * R + 2 * K0
     return {"workload": f"INT4 W4A4+LoRA linear M={M0} K={K0} N={N0} R={R}", "gemm_us": tg * 1e3, "gemm_tflops": tf,

@@ -12,29 +12,35 @@
 // The INT4 variant (template parameter I4; what it computes is stated above gemm_int4_impl) differs only in how the
 // operands reach the tensor core and in the group format of the requantised output.
 //
-// How it maps to a B200.  The two SMs of a CTA pair (cluster of 2) walk 256 x 192 output tiles together with
-// tcgen05 cta_group::2: each CTA holds 128 rows of A, 128 rows of the accumulator (its own TMEM) and 96 of the
-// tile's 192 weight rows; the even CTA ("leader") issues one 256-row MMA for both.  Per byte loaded the pair
-// does 1.4x the math of two independent 128 x 192 CTAs.  Five-stage operand ring.  In each CTA (NVFP4):
-//   warps 0, 6, 7, 8  producers, one TMA stream each (the TMA unit retires the copies of one issuing warp one
-//               after the other): per stage (256 codes of K) the 128B-swizzled 128 x 128 B box of A, the 96 x 128 B
+// How it maps to a B200.  The two SMs of a CTA pair (cluster of 2) walk 256 x 256 output tiles together with
+// tcgen05 cta_group::2: each CTA holds 128 rows of A, 128 rows of the accumulator (its own TMEM) and 128 of the
+// tile's 256 weight rows; the even CTA ("leader") issues one 256-row MMA for both.  Per byte loaded the pair
+// does 1.5x the math of two independent 128 x 256 CTAs.  Five-stage operand ring.  In each CTA (NVFP4), by warpgroup:
+//   warps 0..3  producers, one TMA stream each (the TMA unit retires the copies of one issuing warp one
+//               after the other): per stage (256 codes of K) the 128B-swizzled 128 x 128 B box of A, the 128 x 128 B
 //               box of B, the 2 KB of scale atoms of the CTA's activation rows and the 4 KB of the two 128-row
 //               weight scale atoms; the cta_group::2 form of the load counts all of them on the leader's barrier
-//   warp 1      leader only: MMA issuer.  Per k-block three tcgen05.cp (scale atoms, shared memory -> TMEM) and one
-//               tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N192 K64); the low-rank branch is fed
-//               through the same ring as fp32 tiles and issued as kind::tf32 into the same accumulator; one
-//               multicast tcgen05.commit per stage releases the stage in both CTAs, one per tile publishes the
-//               accumulator
-//   warps 2..5  epilogue: tcgen05.ld (one row per thread), scale + bias + activation, bf16 into a swizzled
-//               staging buffer, TMA store (coalesced, clipped at M and N by the hardware); when requantising,
-//               the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix + mma.sync) and the
-//               thread's own row chunk is group-quantised in registers
-//   warps 9..12 (NVFP4 requantising variants up to rank 32) a second epilogue set; the two warps of a lane quadrant
-//               take alternate 64-column chunks
-// INT4 (16 warps, six-stage ring of 28 KB): warp 6 brings the fp16 weights, warps 0 and 7..15 read the packed activation
-// codes from global memory and convert them to fp16(code * group scale) into the operand ring; the MMAs are kind::f16.
-// TMEM per CTA: two 192-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1)
-// plus two 48-column scale-factor buffers (16 for A, 32 for B) = 480 of 512 columns.
+//   warps 4..7  epilogue set 0 (TMEM lane quadrant = warp & 3): tcgen05.ld (one row per thread), scale + bias +
+//               activation, bf16 into a swizzled staging buffer, TMA store (coalesced, clipped at M and N by the
+//               hardware); when requantising, the staged bf16 tile also feeds the next layer's LoRA-down (ldmatrix +
+//               mma.sync) and the thread's own row chunk is group-quantised in registers
+//   warps 8..11 epilogue set 1 (all variants but next rank 64): the two warps of a lane quadrant take alternate
+//               64-column chunks
+//   warp 12     (first warp after the epilogue sets) leader only: MMA issuer.  Per k-block three tcgen05.cp (scale
+//               atoms, shared memory -> TMEM) and one tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale (M256 N256
+//               K64); the low-rank branch is fed through the same ring as fp32 tiles and issued as kind::tf32 into the
+//               same accumulator; one multicast tcgen05.commit per stage releases the stage in both CTAs, one per tile
+//               publishes the accumulator.  Its loop carries no division and no descriptor rebuild: this one warp's
+//               instruction stream, not bandwidth, is what bounds the kernel
+//   warps 13..15 take part in the barriers only (registers are re-divided per warpgroup: producers and this group 48,
+//               epilogue 200 per thread)
+// INT4 (16 warps, six-stage ring of 32 KB): warp 1 issues, warps 2..5 are the epilogue, warp 6 brings the fp16 weights,
+// warps 0 and 7..15 read the packed activation codes from global memory and convert them to fp16(code * group scale)
+// into the operand ring; the MMAs are kind::f16.
+// TMEM per CTA: two 256-column fp32 accumulators (the epilogue of tile i overlaps the main loop of tile i+1) fill all
+// 512 columns.  The two 48-column scale-factor buffers of a tile (16 columns for A, 32 for B) therefore live in the first
+// 96 columns of the OTHER accumulator, the one being drained: the epilogue warps arrive on `sfree` once those columns are
+// in registers and the MMA warp waits for that before the tile's first tcgen05.cp.
 // Every loop that issues tcgen05 / TMA instructions is run by a whole warp with one elected lane issuing, so
 // that descriptors and coordinates stay warp-uniform.  Every wait is bounded; a wait that runs out raises the
 // abort flag of both CTAs, all roles leave their loops, and the status words tell the host.
@@ -110,7 +116,7 @@ struct GemmParams {
     int* status;
     int M, M_pad, N, K;
     int lora_chunks;          // number of 32-rank chunks of the low-rank branch (0 = none)
-    int tiles_m, tiles_n;     // in 256 x 192 pair tiles
+    int tiles_m, tiles_n;     // in 256 x 256 pair tiles
     int activation;
     int store_out;            // bf16 `out` is wanted
     // tile schedule: 0: m-fastest, strided by gridDim; 1: n-fastest, each CTA a contiguous run of `run` tiles
@@ -499,7 +505,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
         // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
-        // 1 = weight tile, 2 = scale atoms of the activation rows, 3 = scale atoms of the 192 weight rows (whole
+        // 1 = weight tile, 2 = scale atoms of the activation rows, 3 = scale atoms of the 256 weight rows (whole
         // 128-row atoms: two of them).  All are counted on the leader's barrier; a tile past the end of a
         // tensor is filled with zeros by the hardware and still counts its full size.
         const int role = warp;
@@ -1013,7 +1019,7 @@ int4_row_norm_kernel(const __nv_bfloat16* __restrict__ ascales, int KB, int M_pa
 }
 
 struct NvfpPlan {
-    int requant, tiles_m, tiles_n, npairs, run, slots, rn;   // tiles are 256 x 192 pair tiles
+    int requant, tiles_m, tiles_n, npairs, run, slots, rn;   // tiles are 256 x 256 pair tiles
     size_t workspace;
 };
 
