@@ -41,6 +41,9 @@ extern "C" {
 #define SVDQ_LAYOUT_NATIVE 0    /* row-major codes, 512-byte scale atoms, row-major fp32 low-rank */
 #define SVDQ_LAYOUT_REFERENCE 1 /* the reference's mma.sync fragment order (gemm_base.cuh:265-340) */
 
+/* Largest LoRA rank of any low-rank tensor (src/kernels/zgemm/lora.cuh:22); ranks are multiples of 16. */
+#define SVDQ_MAX_LORA_RANK 1024
+
 #define SVDQ_ACT_NONE 0
 #define SVDQ_ACT_SILU 1 /* fuse_silu  (gemm_w4a4_launch_impl.cuh:407-420) */
 #define SVDQ_ACT_GELU 2 /* GELU before next-layer requantisation (launch_impl.cuh:282-309) */
@@ -62,7 +65,7 @@ typedef struct svdq_quantize_args {
     int32_t M;             /* valid rows                                                      */
     int32_t M_pad;         /* multiple of 256 (nunchaku/ops/quantize.py:40)                   */
     int32_t K;             /* multiple of 128                                                 */
-    int32_t R;             /* multiple of 16, 16..128                                         */
+    int32_t R;             /* multiple of 16, 16..SVDQ_MAX_LORA_RANK (above 128: extra passes)   */
     int32_t fp4;           /* 1: NVFP4 group 16, 0: INT4 group 64                             */
     int32_t fuse_glu;      /* 1: input holds (value, gate) pairs, quantise value*silu(gate)   */
     int32_t layout;        /* SVDQ_LAYOUT_* of codes / scales / lora_act                      */
@@ -130,7 +133,9 @@ typedef struct svdq_gemm_args {
                                  requantising epilogue (per-CTA LoRA-down partials) and by every INT4 GEMM
                                  (per-row power-of-two normalisation of the activation scales); else may be NULL */
     size_t workspace_bytes;
-    int32_t M, M_pad, N, K, R, R_next;
+    int32_t M, M_pad, N, K, R, R_next; /* R, R_next: multiples of 16 up to SVDQ_MAX_LORA_RANK.  The epilogue computes the
+                                 first 64 (32, 16) ranks of the next layer's LoRA-down itself; further ranks are follow-up
+                                 launches over the bf16 output (`out`, or a copy of it in the workspace)        */
     int32_t fp4;              /* precision of act / weights                                  */
     int32_t act_unsigned;     /* INT4 only: activations are u4 codes                         */
     int32_t activation;       /* SVDQ_ACT_*; must be SVDQ_ACT_GELU when qout is given        */

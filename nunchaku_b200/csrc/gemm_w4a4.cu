@@ -61,6 +61,10 @@
 
 namespace svdq {
 
+// quantize.cu: lora_act[:, 16 rt_first :] = input @ lora_down[:, 16 rt_first :] for a bf16 [M, K] input
+int lora_down_rank_tiles(const void* input, int M, int M_pad, int K, const void* smooth, const void* lora_down, int RT_total,
+                         int rt_first, float* lora_act, cudaStream_t stream);
+
 constexpr int G_BM = 128;
 constexpr int G_BN = 256;
 constexpr int G_BNH = G_BN / 2;                 // weight rows each CTA of a pair loads
@@ -127,6 +131,7 @@ struct GemmParams {
     uint8_t* oscales;                   // scale atoms [M_pad/128][N/64][512]
     const __nv_bfloat16* next_smooth;   // [N] reference-packed
     const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
+    int next_rt_total;                  // Rn/16 of that tensor (the epilogue takes its first RTN rank tiles)
     float* lora_partial;                // scratch [CTA][slots][128][Rn]
     int slots;
 #ifdef SVDQ_ABLATE
@@ -872,7 +877,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         uint4 bfrag[RTA];
 #pragma unroll
                         for (int rt = 0; rt < RTN; ++rt)
-                            bfrag[rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * RTN + rt) * 32 + lane);
+                            bfrag[rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
 #pragma unroll
                         for (int mt = 0; mt < 2; ++mt) {
                             const int arow = mt * 16 + (lane & 15);
@@ -970,7 +975,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 // of the CTA that owns the row's half.  Row block mb2 (256 rows) holds pair tiles [mb2*tiles_n, (mb2+1)*tiles_n);
 // pair c owns tiles [c*run, (c+1)*run); CTA 2c + h of the pair owns rows h*128.. of each tile.
 __global__ void __launch_bounds__(256)
-lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int tiles_n, int run, int slots,
+lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict__ out, int rn, int ld, int tiles_n, int run, int slots,
                            int npairs) {
     const int mb = blockIdx.x;   // 128-row block
     const int mb2 = mb >> 1, h = mb & 1;
@@ -985,7 +990,8 @@ lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict_
                                        partial + (static_cast<size_t>(2 * c + h) * slots + (mb2 - first_mb2)) * (G_BM * rn)) + i);
             s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
         }
-        reinterpret_cast<float4*>(out + static_cast<size_t>(mb) * G_BM * rn)[i] = s;
+        const int e = 4 * i;   // element (row, rank) of the block; `out` rows are `ld` floats apart
+        *reinterpret_cast<float4*>(out + (static_cast<size_t>(mb) * G_BM + e / rn) * ld + e % rn) = s;
     }
 }
 
@@ -1019,9 +1025,15 @@ int4_row_norm_kernel(const __nv_bfloat16* __restrict__ ascales, int KB, int M_pa
 }
 
 struct NvfpPlan {
-    int requant, tiles_m, tiles_n, npairs, run, slots, rn;   // tiles are 256 x 256 pair tiles
-    size_t workspace;
+    int requant, tiles_m, tiles_n, npairs, run, slots;   // tiles are 256 x 256 pair tiles
+    int rn;              // ranks of the next layer's LoRA-down that the epilogue computes: the first 16, 32 or 64
+    size_t partials;     // bytes of the per-CTA partials
+    size_t workspace;    // partials + (when further ranks are left and the caller wants no `out`) a bf16 copy of the output
 };
+
+// The epilogue holds the next layer's LoRA-down accumulators in registers: 16, 32 or 64 ranks.  Any further ranks
+// (lora.cuh:22 allows up to 1024) are computed from the bf16 output by follow-up launches of the quantiser's LoRA-down.
+static inline int fused_next_rank(int r_next) { return r_next >= 64 ? 64 : r_next >= 32 ? 32 : 16; }
 
 static void plan_nvfp4(const svdq_gemm_args* a, int sms, NvfpPlan* pl) {
     pl->requant = a->qout != nullptr;
@@ -1033,9 +1045,18 @@ static void plan_nvfp4(const svdq_gemm_args* a, int sms, NvfpPlan* pl) {
     pl->run = (num_tiles + pl->npairs - 1) / pl->npairs;
     if (pl->requant) pl->npairs = (num_tiles + pl->run - 1) / pl->run;
     pl->slots = (pl->run + pl->tiles_n - 2) / pl->tiles_n + 1;
-    pl->rn = a->R_next;
-    pl->workspace = pl->requant ? static_cast<size_t>(2 * pl->npairs) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
+    pl->rn = fused_next_rank(a->R_next);
+    pl->partials = pl->requant ? static_cast<size_t>(2 * pl->npairs) * pl->slots * G_BM * pl->rn * sizeof(float) : 0;
+    const bool out_copy = pl->requant && a->R_next > pl->rn && a->out == nullptr;
+    pl->workspace = pl->partials + (out_copy ? ((static_cast<size_t>(a->M) * a->N * 2 + 255) & ~static_cast<size_t>(255)) : 0);
 }
+
+// Launch the fused kernel for the plan's rank count, add up the partials, then the ranks the epilogue did not take.
+template <bool I4>
+static int launch_requant(const svdq_gemm_args* a, const NvfpPlan& pl, cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
+                          const CUtensorMap& tm_la, const CUtensorMap& tm_lu, const CUtensorMap& tm_out, const CUtensorMap& tm_sfa,
+                          const CUtensorMap& tm_sfb, const GemmParams& p, const void* out_bf16);
+
 
 // real column count of `out`: the store's tensor map ends there, so the hardware drops the padded columns
 static inline int n_out(const svdq_gemm_args* a) { return a->N_out ? a->N_out : a->N; }
@@ -1082,7 +1103,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                          "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(!a->act_unsigned, "gemm(nvfp4): act_unsigned is INT4 only (gemm_w4a4_launch_impl.cuh:127)");
-    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= SVDQ_MAX_LORA_RANK, "gemm: R (%d) must be a multiple of 16, at most %d", a->R, SVDQ_MAX_LORA_RANK);
     SVDQ_CHECK_ARG(n_out_ok(a), "gemm: N_out (%d) must be a multiple of 8 with N - 128 < N_out <= N (%d)", a->N_out, a->N);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
     if (requant) {
@@ -1095,8 +1116,9 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
                            aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
                        "gemm(nvfp4): requantisation tensors must be 16-byte aligned (workspace: 256)");
-        if (a->R_next != 16 && a->R_next != 32 && a->R_next != 64)
-            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
+        SVDQ_CHECK_ARG(a->R_next >= 16 && a->R_next % 16 == 0 && a->R_next <= SVDQ_MAX_LORA_RANK,
+                       "gemm(nvfp4): R_next (%d) must be a multiple of 16 in [16, %d]", a->R_next, SVDQ_MAX_LORA_RANK);
+        SVDQ_CHECK_ARG(a->R_next <= 64 || n_out(a) == a->N, "gemm(nvfp4): next-layer ranks above 64 need an unpadded output (N_out == N)");
     }
 
     int sms = 0;
@@ -1119,13 +1141,16 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
     p.activation = a->activation;
-    p.store_out = a->out != nullptr;
+    // the bf16 output: the caller's, or (ranks left for the follow-up LoRA-down and no `out` wanted) a copy in the workspace
+    void* const out_bf16 = a->out ? a->out : (pl.workspace > pl.partials ? static_cast<uint8_t*>(a->workspace) + pl.partials : nullptr);
+    p.store_out = out_bf16 != nullptr;
     p.contiguous = requant;
     p.run = pl.run;
     p.qout = static_cast<uint8_t*>(a->qout);
     p.oscales = static_cast<uint8_t*>(a->oscales);
     p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
+    p.next_rt_total = a->R_next / 16;
     p.lora_partial = static_cast<float*>(a->workspace);
     p.slots = pl.slots;
 #ifdef SVDQ_ABLATE
@@ -1148,8 +1173,8 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_la = tm_a;
         tm_lu = tm_b;
     }
-    if (a->out) {
-        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
+    if (out_bf16) {
+        if (int rc = make_tmap_2d(&tm_out, out_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_a;
@@ -1163,16 +1188,25 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
             return rc;
     }
     int rc;
-    if (!requant) rc = launch_pair<0, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else if (a->R_next == 16) rc = launch_pair<1, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else if (a->R_next == 32) rc = launch_pair<2, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
-    else rc = launch_pair<4, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    if (!requant) return launch_pair<0, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    return launch_requant<false>(a, pl, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p, out_bf16);
+}
+
+template <bool I4>
+static int launch_requant(const svdq_gemm_args* a, const NvfpPlan& pl, cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
+                          const CUtensorMap& tm_la, const CUtensorMap& tm_lu, const CUtensorMap& tm_out, const CUtensorMap& tm_sfa,
+                          const CUtensorMap& tm_sfb, const GemmParams& p, const void* out_bf16) {
+    int rc;
+    if (pl.rn == 16) rc = launch_pair<1, I4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else if (pl.rn == 32) rc = launch_pair<2, I4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
+    else rc = launch_pair<4, I4>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
     if (rc) return rc;
-    if (requant) {
-        lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run,
-                                                                      pl.slots, pl.npairs);
-        SVDQ_CUDA(cudaGetLastError());
-    }
+    lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(
+        p.lora_partial, a->lora_act_out, pl.rn, a->R_next, pl.tiles_n, pl.run, pl.slots, pl.npairs);
+    SVDQ_CUDA(cudaGetLastError());
+    if (a->R_next > pl.rn)
+        return lora_down_rank_tiles(out_bf16, a->M, a->M_pad, a->N, a->next_smooth, a->next_lora_down, a->R_next / 16, pl.rn / 16,
+                                    a->lora_act_out, stream);
     return SVDQ_OK;
 }
 
@@ -1218,12 +1252,13 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         SVDQ_CHECK_ARG(aligned(a->qout, 16) && aligned(a->oscales, 16) && aligned(a->lora_act_out, 16) &&
                            aligned(a->next_smooth, 16) && aligned(a->next_lora_down, 16) && aligned(a->workspace, 256),
                        "gemm(int4): requantisation tensors must be 16-byte aligned (workspace: 256)");
-        if (a->R_next != 16 && a->R_next != 32 && a->R_next != 64)
-            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): fused next-layer LoRA-down is built for rank 16, 32, 64 (got %d)", a->R_next);
+        SVDQ_CHECK_ARG(a->R_next >= 16 && a->R_next % 16 == 0 && a->R_next <= SVDQ_MAX_LORA_RANK,
+                       "gemm(int4): R_next (%d) must be a multiple of 16 in [16, %d]", a->R_next, SVDQ_MAX_LORA_RANK);
+        SVDQ_CHECK_ARG(a->R_next <= 64 || n_out(a) == a->N, "gemm(int4): next-layer ranks above 64 need an unpadded output (N_out == N)");
     }
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(int4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                         "(convert with svdq_w4a4_relayout_act)");
-    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= 128, "gemm: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R % 16 == 0 && a->R >= 0 && a->R <= SVDQ_MAX_LORA_RANK, "gemm: R (%d) must be a multiple of 16, at most %d", a->R, SVDQ_MAX_LORA_RANK);
     SVDQ_CHECK_ARG(n_out_ok(a), "gemm: N_out (%d) must be a multiple of 8 with N - 128 < N_out <= N (%d)", a->N_out, a->N);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_act_in && a->w.lora_up), "gemm: low-rank tensors missing");
 
@@ -1253,13 +1288,15 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.tiles_m = pl.tiles_m;
     p.tiles_n = pl.tiles_n;
     p.activation = a->activation;
-    p.store_out = a->out != nullptr;
+    void* const out_bf16 = a->out ? a->out : (pl.workspace > pl.partials ? reinterpret_cast<uint8_t*>(partials) + pl.partials : nullptr);
+    p.store_out = out_bf16 != nullptr;
     p.contiguous = requant;
     p.run = pl.run;
     p.qout = static_cast<uint8_t*>(a->qout);
     p.oscales = static_cast<uint8_t*>(a->oscales);
     p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
+    p.next_rt_total = a->R_next / 16;
     p.lora_partial = partials;
     p.slots = pl.slots;
     if (int rc = status_words(&p.status)) return rc;
@@ -1281,8 +1318,8 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_la = tm_b;
         tm_lu = tm_b;
     }
-    if (a->out) {
-        if (int rc = make_tmap_2d(&tm_out, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
+    if (out_bf16) {
+        if (int rc = make_tmap_2d(&tm_out, out_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_b;
@@ -1300,18 +1337,8 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         SVDQ_CUDA(cudaLaunchKernelEx(&cfg, int4_row_norm_kernel, p.ascales_i4, a->K / 64, a->M_pad,
                                      a->R > 0 ? a->lora_act_in : static_cast<const float*>(nullptr), a->R, row_scale, lora_scaled));
     }
-    int rc;
-    if (!requant) rc = launch_pair<0, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
-    else if (a->R_next == 16) rc = launch_pair<1, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
-    else if (a->R_next == 32) rc = launch_pair<2, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
-    else rc = launch_pair<4, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
-    if (rc) return rc;
-    if (requant) {
-        lora_partial_reduce_kernel<<<dim3(2 * pl.tiles_m, (G_BM * pl.rn / 4 + 255) / 256), 256, 0, stream>>>(
-            p.lora_partial, a->lora_act_out, pl.rn, pl.tiles_n, pl.run, pl.slots, pl.npairs);
-        SVDQ_CUDA(cudaGetLastError());
-    }
-    return SVDQ_OK;
+    if (!requant) return launch_pair<0, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p);
+    return launch_requant<true>(a, pl, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p, out_bf16);
 }
 
 }  // namespace svdq

@@ -124,7 +124,7 @@ __global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, 
 // Reference order of Wu (packer.py:362-398): [N/16][R/16][g 8][t 4][nh 2][kh 2][e 2],
 // n = cp*16 + nh*8 + g, r = rp*16 + kh*8 + 2t + e.
 struct LoraScales {
-    float v[8];
+    float v[SVDQ_MAX_LORA_RANK / 16];
 };
 
 __global__ void prepare_columns_kernel(const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ wcscales,
@@ -264,7 +264,7 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
     SVDQ_CHECK_ARG(a->qweight && a->wscales && o->wgt && o->wscales && o->col_scale && o->col_bias,
                    "prepare_weights: null tensor pointer");
     SVDQ_CHECK_ARG(a->N > 0 && a->N % 128 == 0 && a->K > 0 && a->K % 128 == 0, "prepare_weights: need N%%128==0 and K%%128==0");
-    SVDQ_CHECK_ARG(a->R >= 0 && a->R % 16 == 0 && a->R <= 128, "prepare_weights: R (%d) must be a multiple of 16, at most 128", a->R);
+    SVDQ_CHECK_ARG(a->R >= 0 && a->R % 16 == 0 && a->R <= SVDQ_MAX_LORA_RANK, "prepare_weights: R (%d) must be a multiple of 16, at most %d", a->R, SVDQ_MAX_LORA_RANK);
     SVDQ_CHECK_ARG(a->R == 0 || (a->lora_up && o->lora_up), "prepare_weights: lora_up missing");
     SVDQ_CHECK_ARG(a->fp4 || a->alpha == 1.0f, "prepare_weights: alpha must be 1 for INT4 (gemm_w4a4_launch_impl.cuh:107)");
     SVDQ_CHECK_ARG(aligned(a->qweight, 16) && aligned(a->wscales, 16) && aligned(o->wgt, 16) && aligned(o->wscales, 16),
@@ -288,7 +288,7 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
                                                                         static_cast<uint4*>(o->wgt), a->N, a->K);
     }
     LoraScales ls;
-    for (int i = 0; i < 8; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
+    for (int i = 0; i < SVDQ_MAX_LORA_RANK / 16; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
     const int R32 = (a->R + 31) / 32 * 32;
     prepare_columns_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(a->bias), static_cast<const __nv_bfloat16*>(a->wcscales),

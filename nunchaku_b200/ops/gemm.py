@@ -289,7 +289,7 @@ def svdq_gemm_w4a4_cuda(
         a.qout = a.oscales = a.lora_act_out = a.next_smooth = a.next_lora_down = None
         a.R_next = 0
     lib = _lib.load()
-    wkey = (M_pad, a.R_next, int(requant))
+    wkey = (M_pad, a.R_next, int(requant), out is None)
     need = prepared.workspace_bytes.get(wkey)
     if need is None:
         n = ctypes.c_size_t(0)

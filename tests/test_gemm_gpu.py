@@ -61,11 +61,13 @@ def test_nvfp4_exact_small_integers():
 @pytest.mark.parametrize("M,K,N,Rk,use_lora", [
     (256, 128, 128, 32, False),
     (256, 256, 384, 32, True),
-    (300, 512, 640, 32, True),      # ragged M, N not a multiple of the 192-column tile
+    (300, 512, 640, 32, True),      # ragged M, N not a multiple of the 256-column tile
     (1, 128, 128, 16, True),
     (256, 384, 128, 64, True),
     (512, 640, 1280, 128, True),
     (1024, 3072, 3072, 32, True),
+    (300, 256, 384, 80, True),      # ranks that are not a multiple of 32, and above 128
+    (256, 256, 256, 272, True),
 ])
 def test_nvfp4_gemm_matches_oracle(M, K, N, Rk, use_lora):
     x, lin, q = problem(M, K, N, Rk, True, seed=M + N)
@@ -279,7 +281,8 @@ def _requant_case(M, K, N, R1, R2, seed, with_out=True):
     return x, fc1, fc2, q, out, got, M_pad
 
 
-@pytest.mark.parametrize("M,K,N,R1,R2", [(256, 256, 384, 32, 32), (300, 512, 640, 32, 16), (1024, 1024, 3072, 32, 32), (256, 128, 256, 16, 64)])
+@pytest.mark.parametrize("M,K,N,R1,R2", [(256, 256, 384, 32, 32), (300, 512, 640, 32, 16), (1024, 1024, 3072, 32, 32), (256, 128, 256, 16, 64),
+                                         (300, 256, 384, 32, 48), (256, 256, 640, 32, 128), (256, 128, 256, 16, 208)])
 def test_nvfp4_gemm_gelu_requant(M, K, N, R1, R2):
     x, fc1, fc2, q, out, got, M_pad = _requant_case(M, K, N, R1, R2, seed=M + N)
     # (1) the bf16 activated output matches the oracle
@@ -296,8 +299,9 @@ def test_nvfp4_gemm_gelu_requant(M, K, N, R1, R2):
     assert R.rel_l2(R.dequant_act(got)[:M], R.dequant_act(exp2)[:M]) <= 2e-2
 
 
-def test_nvfp4_gemm_requant_without_out_and_padding_rows():
-    x, fc1, fc2, q, out, got, M_pad = _requant_case(300, 256, 384, 32, 32, seed=3, with_out=False)
+@pytest.mark.parametrize("R2", [32, 96])     # 96: the ranks above 64 come from a bf16 copy of the output in the workspace
+def test_nvfp4_gemm_requant_without_out_and_padding_rows(R2):
+    x, fc1, fc2, q, out, got, M_pad = _requant_case(300, 256, 384, 32, R2, seed=3, with_out=False)
     y = R.ref_gemm(q, fc1, act="gelu")                     # all M_pad rows: padding rows are bias-only
     exp = R.ref_requantize(y, fc2, M_pad=M_pad, unsigned=False)
     assert R.rel_l2(R.dequant_act(got), R.dequant_act(exp)) <= 2e-2
@@ -351,7 +355,8 @@ def _int4_requant_case(M, K, N, R1, R2, seed, with_out=True):
     return x, fc1, fc2, q, out, got, M_pad
 
 
-@pytest.mark.parametrize("M,K,N,R1,R2", [(256, 256, 384, 32, 32), (300, 512, 640, 32, 16), (1024, 1024, 3072, 32, 32), (256, 128, 256, 16, 64)])
+@pytest.mark.parametrize("M,K,N,R1,R2", [(256, 256, 384, 32, 32), (300, 512, 640, 32, 16), (1024, 1024, 3072, 32, 32), (256, 128, 256, 16, 64),
+                                         (300, 256, 384, 32, 96), (256, 128, 256, 160, 144)])
 def test_int4_gemm_gelu_requant(M, K, N, R1, R2):
     """INT4 chain of the reference (gemm_w4a4_launch_impl.cuh:282-309): GELU, LoRA-down of the next layer on the activated
     value, then u4 codes of (y + 0.171875) / smooth with bf16 group-64 scales."""

@@ -41,7 +41,8 @@ def run_case(M, K, Rk, fp4, layout, x=None, seed=0):
 
 @pytest.mark.parametrize("fp4", [True, False])
 @pytest.mark.parametrize("layout", ["native", "reference"])
-@pytest.mark.parametrize("M,K,Rk", [(256, 128, 32), (300, 512, 32), (520, 256, 16), (256, 1024, 64), (1, 384, 48), (256, 256, 128)])
+@pytest.mark.parametrize("M,K,Rk", [(256, 128, 32), (300, 512, 32), (520, 256, 16), (256, 1024, 64), (1, 384, 48), (256, 256, 128),
+                                     (300, 256, 80), (256, 384, 112), (300, 512, 160), (256, 256, 256), (70, 128, 1024)])
 def test_quantize_matches_oracle(M, K, Rk, fp4, layout):
     run_case(M, K, Rk, fp4, layout)
 
