@@ -88,8 +88,10 @@ constexpr int G_TM_SF_STRIDE = 48;              // per scale-factor buffer: 4 x 
 constexpr int G_TM_SF_COLS = G_SF_BUFS * G_TM_SF_STRIDE;   // 96: they live in the first columns of the accumulator that is being drained
 constexpr int G_EPI_BUF_BYTES = 32 * 128;       // one warp's 32 rows x 64 bf16 columns, 128B-swizzled
 constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffers
-constexpr int G_COLV_FLOATS = 64;                           // per epilogue warp: 1/smooth_next of the chunk in hand
-constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;           // INT4: four epilogue warps; NVFP4: eight, see smem_bytes
+constexpr int G_COLV_FLOATS = 64;                           // INT4, per epilogue warp: 1/smooth_next of the chunk in hand
+constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;           // INT4: four epilogue warps
+// NVFP4: the tile's per-column constants, staged once per tile by a warp of its own: [scale | bias | 1/smooth_next] x G_BN floats
+constexpr int G_TILEC_BYTES = 3 * G_BN * 4;
 // INT4 variant (template parameter I4): a stage is 64 k of fp16 operands, the activation half converted from packed
 // codes by converter warps; the packed codes come through a small ring of their own.
 constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
@@ -104,7 +106,7 @@ template <bool I4>
 constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
 template <bool I4>
 constexpr size_t smem_bytes() {
-    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + (I4 ? 1 : 2) * G_COLV_BYTES + 256;
+    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + (I4 ? G_COLV_BYTES : G_TILEC_BYTES) + 256;
 }
 static_assert(smem_bytes<false>() <= 227 * 1024 && smem_bytes<true>() <= 227 * 1024, "dynamic shared memory of a CTA on sm_100");
 
@@ -136,14 +138,16 @@ struct GemmParams {
     int slots;
 #ifdef SVDQ_ABLATE
     int ablate;   // timing experiments only (results are wrong): bit 0 no epilogue work, 1 no tcgen05.cp, 2 no scale loads,
-                  // 3 no MMAs, 4 no operand loads
+                  // 3 no MMAs, 4 no operand loads, 5 next layer's LoRA-down without its weight loads, 6 without its mma.sync,
+                  // 7 per-column constants always from the same (cached) addresses
 #endif
 };
 #ifdef SVDQ_ABLATE
 #define ABLATE(p, bit) ((p).ablate & (1 << (bit)))
 // cycle accounting of pair 0 (timing experiments): [0..3] MMA warp total / wait full / wait tempty / stages,
 // [4..5] leader's A producer total / wait empty, [6..7] peer's A producer, [8..10] leader's epilogue warp 2 total / wait tfull / tiles,
-// [11] MMA warp: issue of cp + mma, [12] commit
+// [11] MMA warp: issue of cp + mma, [12] commit, [13..15] that epilogue warp: activation + staging / next layer's LoRA-down /
+// smoothing + group quantisation
 __device__ long long g_prof[16];
 #define PROF_T0(v) const long long v = clock64()
 #define PROF_ACC(v) long long v = 0
@@ -165,6 +169,7 @@ struct GemmShared {
     uint64_t sfree[2];              // leader: the first G_TM_SF_COLS columns of the accumulator are in registers (all epilogue warps, both CTAs)
     uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
     uint64_t xempty[4];             // ... and has been added by the first
+    uint64_t cfull, cempty;         // NVFP4, each CTA: the tile's per-column constants are in shared memory / have been read by all epilogue warps
     uint64_t drain;
     uint32_t tmem_base;
     volatile int abort_flag;
@@ -262,7 +267,8 @@ __device__ __forceinline__ float2 act2(float2 v) {
 // 128B-swizzled staging tile.  The activation is a template parameter: selected per element at run time it put a
 // branch between every two values and kept the compiler from interleaving them.
 // ROWSCALE: the accumulator is first multiplied by this row's power of two `rs` (INT4 operands are normalised per row).
-template <int ACT, bool ROWSCALE = false>
+// SMEMC: the per-column constants are in shared memory (plain loads) instead of global memory (read-only path).
+template <int ACT, bool ROWSCALE = false, bool SMEMC = false>
 __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const float4* cs, const float4* cb,
                                             uint32_t (&ow)[32], uint8_t* buf, int lane, float rs = 1.0f) {
 #pragma unroll
@@ -270,8 +276,8 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
         const uint32_t* r = j < 4 ? &r0[8 * j] : &r1[8 * (j - 4)];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const float4 s4 = __ldg(cs + 2 * j + i);
-            const float4 b4 = __ldg(cb + 2 * j + i);
+            const float4 s4 = SMEMC ? cs[2 * j + i] : __ldg(cs + 2 * j + i);
+            const float4 b4 = SMEMC ? cb[2 * j + i] : __ldg(cb + 2 * j + i);
             float2 a01 = make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1]));
             float2 a23 = make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
             if constexpr (ROWSCALE) {   // exact: a power of two
@@ -332,7 +338,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     constexpr int NS = I4 ? H_STAGES : G_STAGES;                              // depth of the operand ring
     uint8_t* epi_smem = smem + NS * SB;
     float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
-    GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + (I4 ? 1 : 2) * G_COLV_BYTES);
+    GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + (I4 ? G_COLV_BYTES : G_TILEC_BYTES));
     static_assert(sizeof(GemmShared) <= 256, "barrier block");
 
     const int warp = threadIdx.x >> 5;
@@ -358,6 +364,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(&sh->xfull[i], 1);
             mbar_init(&sh->xempty[i], 1);
         }
+        mbar_init(&sh->cfull, 1);
+        mbar_init(&sh->cempty, 4 * epi_sets<RTN, I4>());
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         fence_mbar_init();
@@ -692,6 +700,35 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
                 __syncwarp();
             }
+        } else if (!I4 && warp == MMA_WARP + 1) {
+            // ------------------------------------------------------------------ per-column constants of every tile (NVFP4)
+            // alpha * wcscale, bias and the next layer's reciprocal smoothing factors of the tile's G_BN columns go to shared
+            // memory once per tile and CTA; the epilogue warps read them from there (from global memory every 64-column
+            // chunk of every warp paid an L2 round trip: the L1 left beside 227 KB of shared memory does not hold them).
+            // The values of the next tile wait in registers until all epilogue warps are done with the current ones.
+            for (int ti = 0; ti < tr.count; ++ti) {
+                int m0, n0;
+                tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+                float cst[3][G_BN / 32];
+#pragma unroll
+                for (int i = 0; i < G_BN / 32; ++i) {
+                    const int n = n0 + lane + 32 * i;
+                    const bool in = n < p.N;
+                    cst[0][i] = in ? __ldg(p.col_scale + n) : 1.0f;
+                    cst[1][i] = in ? __ldg(p.col_bias + n) : 0.0f;
+                    if constexpr (RTN > 0)
+                        cst[2][i] = in ? __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)])) : 1.0f;
+                }
+                if (ti > 0 && !wait_or_abort<32>(&sh->cempty, (ti - 1) & 1, sh, p.status, 60)) break;
+#pragma unroll
+                for (int i = 0; i < G_BN / 32; ++i) {
+                    colv[lane + 32 * i] = cst[0][i];
+                    colv[G_BN + lane + 32 * i] = cst[1][i];
+                    if constexpr (RTN > 0) colv[2 * G_BN + lane + 32 * i] = cst[2][i];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->cfull);
+            }
         }
     } else if (I4 ? (warp >= 2 && warp < 6) : (warp >= 4 && warp < MMA_WARP)) {
         if constexpr (REGCTL) reg_alloc<G_REGS_EPILOGUE>();
@@ -704,7 +741,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int eset = I4 ? 0 : (warp - 4) >> 2;
         // one set: two staging buffers per warp (a store stays in flight); two sets: one buffer per warp
         uint8_t* my_buf = epi_smem + (q * 2 + (SETS == 2 ? eset : 0)) * G_EPI_BUF_BYTES;
-        float* cvs = colv + (eset * 4 + q) * G_COLV_FLOATS;
+        float* cvs = colv + q * G_COLV_FLOATS;   // INT4 only
         uint32_t nstore = 0, nflush = 0;
         // next layer's LoRA-down partial of this warp's 32 rows: [m-tile 2][rank tile][8]
         constexpr int RTA = RTN > 0 ? RTN : 1;
@@ -778,7 +815,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         lacc_zero();
         const bool prof_me = blockIdx.x == 0 && (warp == (I4 ? 2 : 4)) && lane == 0;
         PROF_T0(pt_all);
-        PROF_ACC(pa_tf); PROF_ACC(pa_tiles);
+        PROF_ACC(pa_tf); PROF_ACC(pa_tiles); PROF_ACC(pa_stage); PROF_ACC(pa_lora); PROF_ACC(pa_quant);
 
         for (int ti = 0; ti < tr.count; ++ti) {
             int m0, n0;
@@ -796,7 +833,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // next layer's smoothing factors of the chunks this warp will take: fetched now, so that the loads fly while the
             // warp waits for the accumulator (lane l: columns l and l + 32 of each 64-column chunk)
             __nv_bfloat16 nsm[G_BN / 64][2];
-            if constexpr (RTN > 0) {
+            if constexpr (RTN > 0 && I4) {
 #pragma unroll
                 for (int h = 0; h < G_BN / 64; ++h)
 #pragma unroll
@@ -812,6 +849,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             pa_tiles += 1;
 #endif
             tc_fence_after_sync();
+            if constexpr (!I4) {   // the tile's per-column constants are in shared memory
+                if (!wait_or_abort<32>(&sh->cfull, ti & 1, sh, p.status, 31)) break;
+            }
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + as * G_TM_ACC1;
             const int grow = m0 + q * 32 + lane;   // this thread's row (< M_pad)
             float rowsc = 1.0f;
@@ -824,7 +864,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t r0[32], r1[32];
                 tc_ld_32x32b_x32(taddr + h * 64, r0);
                 tc_ld_32x32b_x32(taddr + h * 64 + 32, r1);
-                if constexpr (RTN > 0) {   // reciprocal smoothing factors of the chunk's 64 columns (next layer), un-permuted
+                if constexpr (RTN > 0 && I4) {   // reciprocal smoothing factors of the chunk's 64 columns (next layer), un-permuted
                     __syncwarp();          // every lane is done with the previous chunk's factors
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
@@ -848,20 +888,29 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
                 }
-                // per-column scale and bias straight from global memory (the same address in every lane: one L1 line per load)
-                const float4* cs = reinterpret_cast<const float4*>(p.col_scale + n0 + h * 64);
-                const float4* cb = reinterpret_cast<const float4*>(p.col_bias + n0 + h * 64);
+                // per-column scale and bias (the same address in every lane).  NVFP4: staged in shared memory per tile; INT4
+                // (every warp has a job there): straight from global memory
+                const float4* cs = reinterpret_cast<const float4*>(I4 ? p.col_scale + n0 + h * 64 : colv + h * 64);
+                const float4* cb = reinterpret_cast<const float4*>(I4 ? p.col_bias + n0 + h * 64 : colv + G_BN + h * 64);
+#ifdef SVDQ_ABLATE
+                if (I4 && ABLATE(p, 7)) {   // always the same 256 bytes of per-column constants: they stay in L1
+                    cs = reinterpret_cast<const float4*>(p.col_scale);
+                    cb = reinterpret_cast<const float4*>(p.col_bias);
+                }
+#endif
                 uint32_t ow[32];   // this thread's 64 bf16 outputs, packed (kept for the requantisation)
+                PROF_T0(pt_stage);
                 if constexpr (RTN > 0) {
                     // the reference's requantising branch always applies GELU (gemm_w4a4_launch_impl.cuh:282-309)
-                    stage_chunk<SVDQ_ACT_GELU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    stage_chunk<SVDQ_ACT_GELU, I4, !I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
                 } else {
-                    if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
-                    else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
-                    else stage_chunk<SVDQ_ACT_NONE, I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    if (p.activation == SVDQ_ACT_GELU) stage_chunk<SVDQ_ACT_GELU, I4, !I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    else if (p.activation == SVDQ_ACT_SILU) stage_chunk<SVDQ_ACT_SILU, I4, !I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
+                    else stage_chunk<SVDQ_ACT_NONE, I4, !I4>(r0, r1, cs, cb, ow, buf, lane, rowsc);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
+                PROF_ADD(pa_stage, pt_stage);
                 if (lane == 0) {
                     if (p.store_out && m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, n0 + h * 64, m0 + q * 32);
                     bulk_commit_group();
@@ -869,28 +918,24 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 ++nstore;
 
                 if constexpr (RTN > 0) {
-                    // ---- next layer's LoRA-down on the staged bf16 tile: [32 x 64] x Wd_next[64 x Rn]
+                    // The chunk's slice of the next layer's LoRA-down weight (B fragments, from L2) is asked for now and used after
+                    // the quantisation below, whose work covers the latency.  Rank 64: half now, half before the products.
                     const int ch_tile0 = (n0 + h * 64) >> 4;           // 16-channel tile index of the chunk
-                    const uint32_t bufa = smem_u32(buf);
+                    constexpr int KPRE = RTN <= 2 ? 4 : 2;
+                    uint4 bfrag[4][RTA];
+                    auto load_bfrag = [&](int kk) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        uint4 bfrag[RTA];
-#pragma unroll
-                        for (int rt = 0; rt < RTN; ++rt)
-                            bfrag[rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
-#pragma unroll
-                        for (int mt = 0; mt < 2; ++mt) {
-                            const int arow = mt * 16 + (lane & 15);
-                            uint32_t a[4];
-                            ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
-#pragma unroll
-                            for (int rt = 0; rt < RTN; ++rt) {
-                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[rt].x, bfrag[rt].y);
-                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[rt].z, bfrag[rt].w);
-                            }
+                        for (int rt = 0; rt < RTN; ++rt) {
+#ifdef SVDQ_ABLATE
+                            if (ABLATE(p, 5)) { bfrag[kk][rt] = make_uint4(kk, rt, lane, 0); continue; }
+#endif
+                            bfrag[kk][rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
                         }
-                    }
-                    const float4* rcn = reinterpret_cast<const float4*>(cvs);
+                    };
+#pragma unroll
+                    for (int kk = 0; kk < KPRE; ++kk) load_bfrag(kk);
+                    PROF_T0(pt_quant);
+                    const float4* rcn = reinterpret_cast<const float4*>(I4 ? cvs : colv + 2 * G_BN + h * 64);
                     uint4* qdst = reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(grow) * (p.N >> 1) + ((n0 + h * 64) >> 1));
                     if constexpr (I4) {
                         // ---- INT4 group quantisation: this thread's 64 values are exactly one group of the next layer;
@@ -942,6 +987,35 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                             (grow & 31) * 16 + ((grow >> 5) & 3) * 4;
                         *reinterpret_cast<uint32_t*>(p.oscales + soff) = sw;
                     }
+                    PROF_ADD(pa_quant, pt_quant);
+                    // ---- next layer's LoRA-down on the staged bf16 tile: [32 x 64] x Wd_next[64 x Rn]
+                    PROF_T0(pt_lora);
+#pragma unroll
+                    for (int kk = KPRE; kk < 4; ++kk) load_bfrag(kk);
+                    const uint32_t bufa = smem_u32(buf);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+#ifdef SVDQ_ABLATE
+                        if (ABLATE(p, 6)) {
+#pragma unroll
+                            for (int rt = 0; rt < RTN; ++rt)
+                                lacc[0][rt][0] += __uint_as_float(bfrag[kk][rt].x ^ bfrag[kk][rt].y ^ bfrag[kk][rt].z ^ bfrag[kk][rt].w);
+                            continue;
+                        }
+#endif
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            const int arow = mt * 16 + (lane & 15);
+                            uint32_t a[4];
+                            ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
+#pragma unroll
+                            for (int rt = 0; rt < RTN; ++rt) {
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
+                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
+                            }
+                        }
+                    }
+                    PROF_ADD(pa_lora, pt_lora);
                 }
             }
             tc_fence_before_sync();
@@ -949,6 +1023,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (lane == 0) {
                 if (!sf_cols_free) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
                 mbar_arrive_cluster(mapa_shared(smem_u32(&sh->tempty[as]), 0));
+                if constexpr (!I4) mbar_arrive(&sh->cempty);   // this warp is done with the tile's constants
             }
         }
         if constexpr (RTN > 0) {
@@ -957,6 +1032,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         PROF_ACC(pa_all);
         PROF_ADD(pa_all, pt_all);
         PROF_OUT(prof_me, 8, pa_all); PROF_OUT(prof_me, 9, pa_tf); PROF_OUT(prof_me, 10, pa_tiles);
+        PROF_OUT(prof_me, 13, pa_stage); PROF_OUT(prof_me, 14, pa_lora); PROF_OUT(prof_me, 15, pa_quant);
         if (lane == 0) bulk_wait_group<0>();  // all stores of this warp have landed
     }
 
