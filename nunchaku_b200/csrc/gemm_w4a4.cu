@@ -78,9 +78,14 @@ constexpr int G_STAGE_BYTES = G_A_BYTES + G_B_BYTES + G_SFA_BYTES + G_SFB_BYTES;
 //   warps 0..3   producers (A tile, B tile, scale atoms of A, scale atoms of B)
 //   warps 4..7   epilogue set 0 (TMEM lane quadrant = warp & 3);  warps 8..11  epilogue set 1 (when there are two sets)
 //   first warp of the last warpgroup: MMA issuer; the other three warps of that group only take part in the barriers
+//   requantising variants with two epilogue sets: a fifth warpgroup, warps 16..19 = LoRA-down warp of TMEM lane quadrant 0..3
 constexpr int G_THREADS = 12 * 32;             // one epilogue set
 constexpr int G_THREADS_RQ = 16 * 32;          // two epilogue sets
-constexpr int G_REGS_PRODUCER = 48, G_REGS_MMA = 48, G_REGS_EPILOGUE = 200;   // per thread after the re-division (two sets)
+constexpr int G_THREADS_LW = 20 * 32;          // two epilogue sets and the LoRA-down warpgroup
+constexpr int G_REGS_PRODUCER = 48, G_REGS_MMA = 48, G_REGS_EPILOGUE = 200;   // per thread after the re-division (16 warps, 128 at launch)
+// 20 warps start with 96 registers each; what the producers, the MMA group and the LoRA-down warps give back
+// (2 x 128 x 56 + 128 x 16 = 16384) is exactly what the eight epilogue warps take (256 x 64)
+constexpr int L_REGS_PRODUCER = 40, L_REGS_MMA = 40, L_REGS_LORA = 80, L_REGS_EPILOGUE = 160;
 constexpr int G_SF_BUFS = 2;                    // scale-factor buffers in TMEM
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_ACC1 = G_BN;                 // second accumulator: the two fill all 512 columns
@@ -92,6 +97,7 @@ constexpr int G_COLV_FLOATS = 64;                           // INT4, per epilogu
 constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;           // INT4: four epilogue warps
 // NVFP4: the tile's per-column constants, staged once per tile by a warp of its own: [scale | bias | 1/smooth_next] x G_BN floats
 constexpr int G_TILEC_BYTES = 3 * G_BN * 4;
+constexpr int G_SHARED_BYTES = 384;                           // barriers and flags (GemmShared)
 // INT4 variant (template parameter I4): a stage is 64 k of fp16 operands, the activation half converted from packed
 // codes by converter warps; the packed codes come through a small ring of their own.
 constexpr int H_A_BYTES = G_BM * 128;           // 128 rows x 64 fp16
@@ -106,7 +112,7 @@ template <bool I4>
 constexpr int stage_bytes() { return I4 ? H_STAGE_BYTES : G_STAGE_BYTES; }
 template <bool I4>
 constexpr size_t smem_bytes() {
-    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + (I4 ? G_COLV_BYTES : G_TILEC_BYTES) + 256;
+    return 1024 + static_cast<size_t>(I4 ? H_STAGES : G_STAGES) * stage_bytes<I4>() + G_EPI_BYTES + (I4 ? G_COLV_BYTES : G_TILEC_BYTES) + G_SHARED_BYTES;
 }
 static_assert(smem_bytes<false>() <= 227 * 1024 && smem_bytes<true>() <= 227 * 1024, "dynamic shared memory of a CTA on sm_100");
 
@@ -167,8 +173,7 @@ struct GemmShared {
     uint64_t tfull[2];              // each CTA: accumulator complete (multicast commit)
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
     uint64_t sfree[2];              // leader: the first G_TM_SF_COLS columns of the accumulator are in registers (all epilogue warps, both CTAs)
-    uint64_t xfull[4];              // per lane quadrant: the second epilogue warp's LoRA-down partial is in its staging buffer
-    uint64_t xempty[4];             // ... and has been added by the first
+    uint64_t lfull[4][2], lempty[4][2];   // LoRA-down warps: staging buffer of (quadrant, epilogue set) holds a chunk / has been read
     uint64_t cfull, cempty;         // NVFP4, each CTA: the tile's per-column constants are in shared memory / have been read by all epilogue warps
     uint64_t drain;
     uint32_t tmem_base;
@@ -296,13 +301,42 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
     }
 }
 
+// One warp's LoRA-down partial (32 rows of lane quadrant q x RT rank tiles, mma.sync C-fragment order) of a 128-row block
+// -> scratch[CTA][slot][128][16 RT].
+template <int RT>
+__device__ __forceinline__ void store_lora_partial(const GemmParams& p, const float (&lacc)[2][RT][8], int slot, int q, int lane) {
+    constexpr int RN = RT * 16;
+    float* dst = p.lora_partial + (static_cast<size_t>(blockIdx.x) * p.slots + slot) * (G_BM * RN);
+    const int gq = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+            for (int nh = 0; nh < 2; ++nh)
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int row = q * 32 + mt * 16 + gq + half * 8;
+                    const int rank = rt * 16 + nh * 8 + 2 * t;
+                    *reinterpret_cast<float2*>(dst + row * RN + rank) =
+                        make_float2(lacc[mt][rt][nh * 4 + half * 2], lacc[mt][rt][nh * 4 + half * 2 + 1]);
+                }
+}
+
 // RTN: rank tiles (of 16) of the next layer's LoRA-down; 0 = plain epilogue (no requantisation).
 // Requantising epilogues do about three times the work of the plain one per chunk; up to rank 32 (where a warp's
 // LoRA-down partial fits its 4 KB staging buffer) a second set of four epilogue warps takes every other 64-column chunk.
 template <int RTN, bool I4>
 constexpr int epi_sets() { return (!I4 && RTN <= 2) ? 2 : 1; }
+// The tensor pipe serves mma.sync poorly while tcgen05.mma keeps it busy (a warp stalls ~80 cycles per instruction): in the
+// two-set requantising variants the next layer's LoRA-down therefore runs in four warps of its own, fed from the staged bf16
+// tiles, so that those stalls no longer delay the activation and quantisation work of the epilogue warps.
 template <int RTN, bool I4>
-constexpr int cta_threads() { return I4 ? H_THREADS : (epi_sets<RTN, I4>() == 2 ? G_THREADS_RQ : G_THREADS); }
+constexpr bool lora_warps() { return !I4 && RTN > 0 && epi_sets<RTN, I4>() == 2; }
+template <int RTN, bool I4>
+constexpr int cta_threads() {
+    return I4 ? H_THREADS : lora_warps<RTN, I4>() ? G_THREADS_LW : (epi_sets<RTN, I4>() == 2 ? G_THREADS_RQ : G_THREADS);
+}
 template <int RTN, bool I4>
 constexpr int mma_warp() { return I4 ? 1 : 4 + 4 * epi_sets<RTN, I4>(); }
 
@@ -339,7 +373,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint8_t* epi_smem = smem + NS * SB;
     float* colv = reinterpret_cast<float*>(epi_smem + G_EPI_BYTES);
     GemmShared* sh = reinterpret_cast<GemmShared*>(epi_smem + G_EPI_BYTES + (I4 ? G_COLV_BYTES : G_TILEC_BYTES));
-    static_assert(sizeof(GemmShared) <= 256, "barrier block");
+    static_assert(sizeof(GemmShared) <= G_SHARED_BYTES, "barrier block");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -360,9 +394,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             mbar_init(&sh->tempty[i], 8 * epi_sets<RTN, I4>());
             mbar_init(&sh->sfree[i], 8 * epi_sets<RTN, I4>());
         }
-        for (int i = 0; i < 4; ++i) {
-            mbar_init(&sh->xfull[i], 1);
-            mbar_init(&sh->xempty[i], 1);
+        for (int i = 0; i < 8; ++i) {
+            mbar_init(&sh->lfull[i >> 1][i & 1], 1);
+            mbar_init(&sh->lempty[i >> 1][i & 1], 1);
         }
         mbar_init(&sh->cfull, 1);
         mbar_init(&sh->cempty, 4 * epi_sets<RTN, I4>());
@@ -396,6 +430,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // branch starts by giving registers back or asking for more (inside the branch, so that the compiler can tell which
     // budget applies to which code)
     constexpr bool REGCTL = !I4 && epi_sets<RTN, I4>() == 2;
+    constexpr bool LW = lora_warps<RTN, I4>();
+    constexpr int REGS_P = LW ? L_REGS_PRODUCER : G_REGS_PRODUCER, REGS_M = LW ? L_REGS_MMA : G_REGS_MMA,
+                  REGS_E = LW ? L_REGS_EPILOGUE : G_REGS_EPILOGUE;
 
     if (I4 && (warp == 0 || warp >= 6)) {
         // ------------------------------------------------------------------ INT4 producers and converter warps
@@ -514,7 +551,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         }
     } else if (!I4 && warp < 4) {
-        if constexpr (REGCTL) reg_dealloc<G_REGS_PRODUCER>();
+        if constexpr (REGCTL) reg_dealloc<REGS_P>();
         // ------------------------------------------------------------------ producers (whole warp, elected lane issues)
         // The TMA unit retires the copies of one issuing warp one after the other (about 500 cycles each,
         // almost independent of size), so each stream of a stage has its own warp: 0 = activation tile,
@@ -567,8 +604,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         PROF_ADD(pa_all, pt_all);
         PROF_OUT(prof_me, 4 + 2 * blockIdx.x, pa_all);
         PROF_OUT(prof_me, 5 + 2 * blockIdx.x, pa_wait);
-    } else if (warp >= MMA_WARP && (I4 ? warp == MMA_WARP : true)) {
-        if constexpr (REGCTL) reg_dealloc<G_REGS_MMA>();
+    } else if (warp >= MMA_WARP && (I4 ? warp == MMA_WARP : warp < MMA_WARP + 4)) {
+        if constexpr (REGCTL) reg_dealloc<REGS_M>();
         // ------------------------------------------------------------------ MMA issuer (leader CTA only; NVFP4: the other
         // warps of its warpgroup only give their registers back)
         // The whole warp runs the loop and one elected lane issues: descriptors, TMEM addresses and barrier
@@ -730,8 +767,75 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (lane == 0) mbar_arrive(&sh->cfull);
             }
         }
+    } else if (LW && warp >= MMA_WARP + 4) {
+        if constexpr (REGCTL) reg_dealloc<L_REGS_LORA>();
+        // ------------------------------------------------------------------ next layer's LoRA-down (two-set requantising variants)
+        // Warp q of this group takes every chunk of lane quadrant q, from whichever epilogue set staged it, in tile
+        // order: [32 rows x 64 columns] of bf16 from the staging buffer times Wd_next[64 x Rn] (B fragments straight from
+        // global memory, asked for before the wait for the tile), accumulated over the tiles of one 128-row block.
+        constexpr int RTL = RTN > 0 ? RTN : 1;
+        const int q = warp & 3;
+        float lacc[2][RTL][8];
+        auto lacc_zero = [&]() {
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int b = 0; b < RTL; ++b)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) lacc[a][b][c] = 0.f;
+        };
+        lacc_zero();
+        int cur_m0 = -1, slot = 0;
+        uint32_t cnt[2] = {0u, 0u};   // chunks taken from each epilogue set's buffer
+        bool ok = true;
+        for (int ti = 0; ti < tr.count && ok; ++ti) {
+            int m0, n0;
+            tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
+            if (m0 != cur_m0) {
+                if (cur_m0 >= 0) {
+                    store_lora_partial<RTL>(p, lacc, slot++, q, lane);
+                    lacc_zero();
+                }
+                cur_m0 = m0;
+            }
+#pragma unroll 1
+            for (int h = 0; h < G_BN / 64; ++h) {
+                if (n0 + h * 64 >= p.N) break;
+                const int e = (h + ti) & 1;
+                const int ch_tile0 = (n0 + h * 64) >> 4;
+                uint4 bfrag[4][RTL];
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                    for (int rt = 0; rt < RTL; ++rt)
+                        bfrag[kk][rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
+                const uint32_t par = e ? cnt[1] : cnt[0];
+                if (!wait_or_abort<32>(&sh->lfull[q][e], par & 1, sh, p.status, 70)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t bufa = smem_u32(epi_smem + (q * 2 + e) * G_EPI_BUF_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        const int arow = mt * 16 + (lane & 15);
+                        uint32_t a[4];
+                        ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
+#pragma unroll
+                        for (int rt = 0; rt < RTL; ++rt) {
+                            mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
+                            mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
+                        }
+                    }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->lempty[q][e]);   // the epilogue warp may stage its next chunk
+                if (e) ++cnt[1]; else ++cnt[0];
+            }
+        }
+        if (ok && cur_m0 >= 0) store_lora_partial<RTL>(p, lacc, slot, q, lane);
     } else if (I4 ? (warp >= 2 && warp < 6) : (warp >= 4 && warp < MMA_WARP)) {
-        if constexpr (REGCTL) reg_alloc<G_REGS_EPILOGUE>();
+        if constexpr (REGCTL) reg_alloc<REGS_E>();
         // ------------------------------------------------------------------ epilogue (INT4: warps 2..5; NVFP4: 4..7 and 8..11)
         // One row per thread.  Per 64-column chunk: two tcgen05.ld, scale + bias + activation, bf16 into a
         // 128B-swizzled [32 rows x 128 B] staging buffer of this warp, then one TMA store of that box (the
@@ -742,9 +846,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // one set: two staging buffers per warp (a store stays in flight); two sets: one buffer per warp
         uint8_t* my_buf = epi_smem + (q * 2 + (SETS == 2 ? eset : 0)) * G_EPI_BUF_BYTES;
         float* cvs = colv + q * G_COLV_FLOATS;   // INT4 only
-        uint32_t nstore = 0, nflush = 0;
-        // next layer's LoRA-down partial of this warp's 32 rows: [m-tile 2][rank tile][8]
-        constexpr int RTA = RTN > 0 ? RTN : 1;
+        uint32_t nstore = 0;
+        // Next layer's LoRA-down partial of this warp's 32 rows: [m-tile 2][rank tile][8].  ELORA: this warp computes it (one
+        // epilogue set); otherwise the LoRA-down warps do, from the staged tiles.
+        constexpr bool ELORA = RTN > 0 && !LW;
+        constexpr int RTA = ELORA ? RTN : 1;
         float lacc[2][RTA][8];
         int cur_m0 = -1, slot = 0;
         auto lacc_zero = [&]() {
@@ -756,61 +862,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int c = 0; c < 8; ++c) lacc[a][b][c] = 0.f;
         };
         auto lacc_flush = [&]() {   // partial of row block cur_m0 -> scratch[blockIdx][slot][128][Rn]
-            if constexpr (RTN > 0) {
-                constexpr int RN = RTN * 16;
-                if constexpr (SETS == 2) {
-                    // The second warp of the quadrant hands its partial over through its staging buffer (bounded
-                    // mbarrier hand-shake, fixed order of addition), the first adds it and writes the sum.
-                    float* xb = reinterpret_cast<float*>(epi_smem + (q * 2 + 1) * G_EPI_BUF_BYTES);
-                    if (eset == 1) {
-                        if (lane == 0) bulk_wait_group_read<0>();   // the buffer's last TMA store has been read
-                        __syncwarp();
-#pragma unroll
-                        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                            for (int rt = 0; rt < RTN; ++rt)
-#pragma unroll
-                                for (int c = 0; c < 8; c += 4)
-                                    *reinterpret_cast<float4*>(xb + (((mt * RTN + rt) * 2 + (c >> 2)) * 32 + lane) * 4) =
-                                        make_float4(lacc[mt][rt][c], lacc[mt][rt][c + 1], lacc[mt][rt][c + 2], lacc[mt][rt][c + 3]);
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&sh->xfull[q]);
-                        // the buffer goes back to staging only after the first warp has read it
-                        (void)wait_or_abort(&sh->xempty[q], nflush & 1, sh, p.status, 50);
-                        ++nflush;
-                        return;
-                    }
-                    if (!wait_or_abort(&sh->xfull[q], nflush & 1, sh, p.status, 51)) return;
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                        for (int rt = 0; rt < RTN; ++rt)
-#pragma unroll
-                            for (int c = 0; c < 8; c += 4) {
-                                const float4 v = *reinterpret_cast<const float4*>(xb + (((mt * RTN + rt) * 2 + (c >> 2)) * 32 + lane) * 4);
-                                lacc[mt][rt][c] += v.x; lacc[mt][rt][c + 1] += v.y; lacc[mt][rt][c + 2] += v.z; lacc[mt][rt][c + 3] += v.w;
-                            }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->xempty[q]);
-                    ++nflush;
-                }
-                float* dst = p.lora_partial + (static_cast<size_t>(blockIdx.x) * p.slots + slot) * (G_BM * RN);
-                const int gq = lane >> 2, t = lane & 3;
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int rt = 0; rt < RTN; ++rt)
-#pragma unroll
-                        for (int nh = 0; nh < 2; ++nh)
-#pragma unroll
-                            for (int half = 0; half < 2; ++half) {
-                                const int row = q * 32 + mt * 16 + gq + half * 8;
-                                const int rank = rt * 16 + nh * 8 + 2 * t;
-                                *reinterpret_cast<float2*>(dst + row * RN + rank) =
-                                    make_float2(lacc[mt][rt][nh * 4 + half * 2], lacc[mt][rt][nh * 4 + half * 2 + 1]);
-                            }
-                ++slot;
-            }
+            if constexpr (ELORA) store_lora_partial<RTN>(p, lacc, slot++, q, lane);
         };
         lacc_zero();
         const bool prof_me = blockIdx.x == 0 && (warp == (I4 ? 2 : 4)) && lane == 0;
@@ -821,7 +873,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int m0, n0;
             tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
             const uint32_t as = ti & 1;
-            if constexpr (RTN > 0) {
+            if constexpr (ELORA) {
                 if (m0 != cur_m0) {
                     if (cur_m0 >= 0) {
                         lacc_flush();
@@ -857,6 +909,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             float rowsc = 1.0f;
             if constexpr (I4) rowsc = __ldg(p.row_scale + grow);
             bool sf_cols_free = I4;   // NVFP4: the accumulator's first columns become the next tile's scale-factor buffers
+            bool epi_ok = true;
 #pragma unroll 1
             for (int h = 0; h < G_BN / 64; ++h) {
                 if (n0 + h * 64 >= p.N || ABLATE(p, 0)) break;
@@ -877,6 +930,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint8_t* buf = SETS == 2 ? my_buf : my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
                 if (lane == 0) {   // the store that last used this buffer has been read
                     if (SETS == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
+                }
+                if constexpr (LW) {   // ... and so has the LoRA-down warp of this quadrant
+                    if (nstore > 0 && !wait_or_abort<32>(&sh->lempty[q][eset], (nstore - 1) & 1, sh, p.status, 32)) {
+                        epi_ok = false;
+                        break;
+                    }
                 }
                 __syncwarp();
                 tc_wait_ld();
@@ -912,6 +971,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 __syncwarp();
                 PROF_ADD(pa_stage, pt_stage);
                 if (lane == 0) {
+                    if constexpr (LW) mbar_arrive(&sh->lfull[q][eset]);   // the staged tile is complete: the LoRA-down warp may read it
                     if (p.store_out && m0 + q * 32 < p.M) tma_store_2d(&tm_out, buf, n0 + h * 64, m0 + q * 32);
                     bulk_commit_group();
                 }
@@ -924,12 +984,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     constexpr int KPRE = RTN <= 2 ? 4 : 2;
                     uint4 bfrag[4][RTA];
                     auto load_bfrag = [&](int kk) {
+                        if constexpr (ELORA) {
 #pragma unroll
                         for (int rt = 0; rt < RTN; ++rt) {
 #ifdef SVDQ_ABLATE
                             if (ABLATE(p, 5)) { bfrag[kk][rt] = make_uint4(kk, rt, lane, 0); continue; }
 #endif
                             bfrag[kk][rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
+                        }
                         }
                     };
 #pragma unroll
@@ -994,7 +1056,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int kk = KPRE; kk < 4; ++kk) load_bfrag(kk);
                     const uint32_t bufa = smem_u32(buf);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
+                    for (int kk = 0; kk < (ELORA ? 4 : 0); ++kk) {
 #ifdef SVDQ_ABLATE
                         if (ABLATE(p, 6)) {
 #pragma unroll
@@ -1018,6 +1080,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     PROF_ADD(pa_lora, pt_lora);
                 }
             }
+            if (!epi_ok) break;
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -1026,7 +1089,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if constexpr (!I4) mbar_arrive(&sh->cempty);   // this warp is done with the tile's constants
             }
         }
-        if constexpr (RTN > 0) {
+        if constexpr (ELORA) {
             if (cur_m0 >= 0) lacc_flush();
         }
         PROF_ACC(pa_all);
