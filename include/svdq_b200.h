@@ -44,6 +44,11 @@ extern "C" {
 /* Largest LoRA rank of any low-rank tensor (src/kernels/zgemm/lora.cuh:22); ranks are multiples of 16. */
 #define SVDQ_MAX_LORA_RANK 1024
 
+/* The 16-bit floating-point type of activations, smoothing factors, LoRA weights, biases, INT4 group scales and
+ * outputs ("bf16" in the comments below): the reference's GEMMConfig_W4A4_BF16 / _FP16 (gemm_w4a4.cu:17-31).   */
+#define SVDQ_DTYPE_BF16 0
+#define SVDQ_DTYPE_FP16 1
+
 #define SVDQ_ACT_NONE 0
 #define SVDQ_ACT_SILU 1 /* fuse_silu  (gemm_w4a4_launch_impl.cuh:407-420) */
 #define SVDQ_ACT_GELU 2 /* GELU before next-layer requantisation (launch_impl.cuh:282-309) */
@@ -73,6 +78,7 @@ typedef struct svdq_quantize_args {
                               the input is [M, K_in] ([M, 2 K_in] when fuse_glu), columns [K_in, K) read as
                               zero (the reference's in_features / in_features_pad, src/Linear.cpp:92,452);
                               K - 128 < K_in <= K, multiple of 8                                  */
+    int32_t dtype;         /* SVDQ_DTYPE_* of input, smooth, lora_down and the INT4 scales        */
 } svdq_quantize_args;
 
 int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* stream);
@@ -104,6 +110,7 @@ typedef struct svdq_weights_args {
     const float* lora_scales; /* host array, one per 16 ranks, may be NULL (all 1.0)        */
     float alpha;          /* NVFP4 per-tensor weight scale (wtscale); must be 1 for INT4    */
     int32_t N, K, R, fp4;
+    int32_t dtype;        /* SVDQ_DTYPE_* of wscales (INT4), lora_up, bias, wcscales        */
 } svdq_weights_args;
 
 /* bytes[0..4] = sizes of wgt, wscales, lora_up, col_scale, col_bias */
@@ -145,6 +152,8 @@ typedef struct svdq_gemm_args {
     int32_t N_out;            /* 0, or the real column count of `out` when N is its padding to 128: out is
                                  [M, N_out] and columns [N_out, N) are dropped (the reference's actualN,
                                  gemm_base.cuh:544-548); N - 128 < N_out <= N, multiple of 8      */
+    int32_t dtype;            /* SVDQ_DTYPE_* of out, ascales / oscales (INT4), next_smooth, next_lora_down;
+                                 the prepared weights do not depend on it beyond what prepare_weights read   */
 } svdq_gemm_args;
 
 int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes);

@@ -43,6 +43,7 @@ class QuantizeArgs(Structure):
         ("fuse_glu", c_int32),
         ("layout", c_int32),
         ("K_in", c_int32),
+        ("dtype", c_int32),
     ]
 
 
@@ -69,6 +70,7 @@ class WeightsArgs(Structure):
         ("K", c_int32),
         ("R", c_int32),
         ("fp4", c_int32),
+        ("dtype", c_int32),
     ]
 
 
@@ -99,6 +101,7 @@ class GemmArgs(Structure):
         ("out_layout", c_int32),
         ("next_fp4", c_int32),
         ("N_out", c_int32),
+        ("dtype", c_int32),
     ]
 
 

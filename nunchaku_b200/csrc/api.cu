@@ -8,14 +8,19 @@
 
 namespace svdq {
 
-int quantize_impl(const svdq_quantize_args* a, cudaStream_t stream);
+#define SVDQ_DECLARE_TYPED(ns)                                                        \
+    namespace ns {                                                                    \
+    int quantize_impl(const svdq_quantize_args* a, cudaStream_t stream);              \
+    int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream);                \
+    int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);           \
+    int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);            \
+    int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream);                 \
+    }
+SVDQ_DECLARE_TYPED(bf)   // kernels compiled for bf16 tensors
+SVDQ_DECLARE_TYPED(hf)   // ... and for fp16 (the *_f16.cu translation units)
 int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]);
 int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights* o, cudaStream_t stream);
 int relayout_impl(const svdq_relayout_args* a, cudaStream_t stream);
-int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream);
-int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);
-int gemm_int4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes);
-int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream);
 
 std::string& last_error() {
     static thread_local std::string s;
@@ -188,6 +193,7 @@ int check_gemm_common(const svdq_gemm_args* a) {
                        aligned(a->w.col_scale, 16) && aligned(a->w.col_bias, 16),
                    "gemm: tensors must be 16-byte aligned");
     SVDQ_CHECK_ARG(a->activation >= SVDQ_ACT_NONE && a->activation <= SVDQ_ACT_GELU, "gemm: bad activation %d", a->activation);
+    SVDQ_CHECK_ARG(a->dtype == SVDQ_DTYPE_BF16 || a->dtype == SVDQ_DTYPE_FP16, "gemm: bad dtype %d", a->dtype);
     return check_arch();
 }
 
@@ -196,7 +202,9 @@ int check_gemm_common(const svdq_gemm_args* a) {
 extern "C" {
 
 int svdq_quantize_w4a4_act_fuse_lora(const svdq_quantize_args* args, void* stream) {
-    return svdq::quantize_impl(args, static_cast<cudaStream_t>(stream));
+    if (args && args->dtype == SVDQ_DTYPE_FP16) return svdq::hf::quantize_impl(args, static_cast<cudaStream_t>(stream));
+    if (args && args->dtype != SVDQ_DTYPE_BF16) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, "quantize: bad dtype %d", args->dtype);
+    return svdq::bf::quantize_impl(args, static_cast<cudaStream_t>(stream));
 }
 
 int svdq_w4a4_prepared_bytes(int32_t N, int32_t K, int32_t R, int32_t fp4, size_t bytes[5]) {
@@ -211,15 +219,17 @@ int svdq_w4a4_prepare_weights(const svdq_weights_args* args, const svdq_prepared
 int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes) {
     if (!args || !bytes) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, "workspace_bytes: null argument");
     *bytes = 0;
-    if (args->fp4 && args->qout) return svdq::gemm_nvfp4_workspace_bytes(args, bytes);
-    if (!args->fp4) return svdq::gemm_int4_workspace_bytes(args, bytes);   // always: per-row normalisation scratch
+    // (the scratch does not depend on the 16-bit type)
+    if (args->fp4 && args->qout) return svdq::bf::gemm_nvfp4_workspace_bytes(args, bytes);
+    if (!args->fp4) return svdq::bf::gemm_int4_workspace_bytes(args, bytes);   // always: per-row normalisation scratch
     return SVDQ_OK;
 }
 
 int svdq_gemm_w4a4(const svdq_gemm_args* args, void* stream) {
     if (int rc = svdq::check_gemm_common(args)) return rc;
-    if (args->fp4) return svdq::gemm_nvfp4_impl(args, static_cast<cudaStream_t>(stream));
-    return svdq::gemm_int4_impl(args, static_cast<cudaStream_t>(stream));
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (args->dtype == SVDQ_DTYPE_FP16) return args->fp4 ? svdq::hf::gemm_nvfp4_impl(args, st) : svdq::hf::gemm_int4_impl(args, st);
+    return args->fp4 ? svdq::bf::gemm_nvfp4_impl(args, st) : svdq::bf::gemm_int4_impl(args, st);
 }
 
 int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream) {

@@ -11,7 +11,10 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["api.cu", "quantize.cu", "prepare.cu", "gemm_w4a4.cu", "norm_rope.cu", "litela.cu", "peak_probe.cu"]
+SOURCES = ["api.cu", "quantize.cu", "quantize_f16.cu", "prepare.cu", "gemm_w4a4.cu", "gemm_w4a4_f16.cu", "norm_rope.cu", "litela.cu",
+           "peak_probe.cu"]
+# the fp16 builds are the bf16 sources compiled again with the 16-bit type switched
+INCLUDES = {"quantize_f16.cu": "quantize.cu", "gemm_w4a4_f16.cu": "gemm_w4a4.cu"}
 LIB = os.path.join(PKG, "libsvdq_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
@@ -36,7 +39,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
         s = os.path.join(HERE, src)
         o = os.path.join(HERE, src.replace(".cu", ".o"))
         objs.append(o)
-        if force or _stale(o, [s] + headers):
+        deps = [s] + headers + ([os.path.join(HERE, INCLUDES[src])] if src in INCLUDES else [])
+        if force or _stale(o, deps):
             cmd = [NVCC, *FLAGS, "-c", s, "-o", o] + (["-Xptxas", "-v"] if verbose else [])
             jobs.append(cmd)
 

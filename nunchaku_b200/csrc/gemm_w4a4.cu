@@ -49,8 +49,6 @@
 // deterministic: in requantising mode every pair owns a contiguous run of tiles in n-fastest order, each CTA
 // adds up its tiles of one 128-row block in registers, writes one partial per row block it touches to caller
 // scratch, and a second small kernel adds the partials in pair order.
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
 
 #include <cstdlib>
 #include <mutex>
@@ -60,6 +58,7 @@
 #include "quant_common.cuh"
 
 namespace svdq {
+namespace SVDQ_DT {
 
 // quantize.cu: lora_act[:, 16 rt_first :] = input @ lora_down[:, 16 rt_first :] for a bf16 [M, K] input
 int lora_down_rank_tiles(const void* input, int M, int M_pad, int K, const void* smooth, const void* lora_down, int RT_total,
@@ -119,7 +118,7 @@ static_assert(smem_bytes<false>() <= 227 * 1024 && smem_bytes<true>() <= 227 * 1
 struct GemmParams {
     const uint8_t* sfa;       // activation scale atoms [M_pad/128][K/64][512]
     const uint8_t* sfb;       // weight scale atoms     [N/128][K/64][512]
-    const __nv_bfloat16* ascales_i4;   // INT4: activation group scales [K/64][M_pad]
+    const h16* ascales_i4;   // INT4: activation group scales [K/64][M_pad]
     const uint8_t* act_i4;             // INT4: packed activation codes [M_pad][K/2], read directly by the converter warps
     const float* row_scale;            // INT4: power of two taken out of each row's group scales [M_pad] (see int4_row_norm_kernel)
     int act_unsigned;                  // INT4: activation codes are u4
@@ -137,7 +136,7 @@ struct GemmParams {
     // requantising epilogue
     uint8_t* qout;                      // [M_pad][N/2]
     uint8_t* oscales;                   // scale atoms [M_pad/128][N/64][512]
-    const __nv_bfloat16* next_smooth;   // [N] reference-packed
+    const h16* next_smooth;   // [N] reference-packed
     const uint4* next_lora_down;        // reference-packed [N/16][Rn/16][32] x 16 bytes
     int next_rt_total;                  // Rn/16 of that tensor (the epilogue takes its first RTN rank tiles)
     float* lora_partial;                // scratch [CTA][slots][128][Rn]
@@ -291,10 +290,8 @@ __device__ __forceinline__ void stage_chunk(const uint32_t (&r0)[32], const uint
             }
             const float2 v01 = act2<ACT>(__ffma2_rn(a01, make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
             const float2 v23 = act2<ACT>(__ffma2_rn(a23, make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(v01.x, v01.y);
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(v23.x, v23.y);
-            ow[4 * j + 2 * i] = *reinterpret_cast<uint32_t*>(&p0);
-            ow[4 * j + 2 * i + 1] = *reinterpret_cast<uint32_t*>(&p1);
+            ow[4 * j + 2 * i] = pack2(v01);
+            ow[4 * j + 2 * i + 1] = pack2(v23);
         }
         *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
             make_uint4(ow[4 * j], ow[4 * j + 1], ow[4 * j + 2], ow[4 * j + 3]);
@@ -462,19 +459,19 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 for (int ti = 0; ti < tr.count && ok; ++ti) {
                     int m0, n0;
                     tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
-                    const __nv_bfloat16* asp = p.ascales_i4 + m0 + r0;
+                    const h16* asp = p.ascales_i4 + m0 + r0;
                     int ks = (grp + H_GROUPS - static_cast<int>(it_base % H_GROUPS)) % H_GROUPS;   // first stage of this tile that is ours
                     // the lane's 16 bytes (32 codes) of row r0 + 16 i in k-block ks sit at apk + 16 i * pitch + 32 ks
                     const size_t pitch = static_cast<size_t>(p.K) >> 1;
                     const uint8_t* apk = p.act_i4 + static_cast<size_t>(m0 + r0) * pitch + hh * 16;
-                    __nv_bfloat16 nxt[4];
+                    h16 nxt[4];
                     uint4 wnxt[4];
                     float inv[4];   // 1 / (this row's power-of-two normalisation): exact
 #pragma unroll
                     for (int i = 0; i < 4; ++i) inv[i] = __frcp_rn(__ldg(p.row_scale + m0 + r0 + 16 * i));
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : __nv_bfloat16(0.f);
+                        nxt[i] = ks < kstages ? __ldg(asp + static_cast<size_t>(ks) * p.M_pad + 16 * i) : f2h(0.f);
                         wnxt[i] = ks < kstages ? __ldg(reinterpret_cast<const uint4*>(apk + 16 * i * pitch + 32 * ks)) : make_uint4(0, 0, 0, 0);
                     }
                     for (; ks < per_tile; ks += H_GROUPS) {
@@ -489,7 +486,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             __syncwarp();
                             continue;
                         }
-                        __nv_bfloat16 cur[4];
+                        h16 cur[4];
                         uint4 w[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -503,7 +500,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             // the row's largest group scale is in [1, 2) after normalisation, so |code * scale| < 30 in fp16
-                            const __half2 s2 = __float2half2_rn(__bfloat162float(cur[i]) * inv[i]);
+                            const __half2 s2 = __float2half2_rn(h2f(cur[i]) * inv[i]);
                             const int row = r0 + 16 * i;
                             uint8_t* dst = st + row * 128;
                             const int sw = row & 7;
@@ -561,7 +558,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int role = warp;
         uint32_t it = 0;  // ring position, counted over every stage this CTA ever fills
         bool ok = true;
-        const bool prof_me = blockIdx.x < 2 && role == 0 && lane == 0;
+        const bool prof_me = blockIdx.x < (LW ? 1 : 2) && role == 0 && lane == 0;   // with LoRA-down warps their counters take the peer's slots
         PROF_T0(pt_all);
         PROF_ACC(pa_wait);
         for (int ti = 0; ti < tr.count && ok; ++ti) {
@@ -754,7 +751,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     cst[0][i] = in ? __ldg(p.col_scale + n) : 1.0f;
                     cst[1][i] = in ? __ldg(p.col_bias + n) : 0.0f;
                     if constexpr (RTN > 0)
-                        cst[2][i] = in ? __frcp_rn(__bfloat162float(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)])) : 1.0f;
+                        cst[2][i] = in ? __frcp_rn(h2f(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)])) : 1.0f;
                 }
                 if (ti > 0 && !wait_or_abort<32>(&sh->cempty, (ti - 1) & 1, sh, p.status, 60)) break;
 #pragma unroll
@@ -788,6 +785,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int cur_m0 = -1, slot = 0;
         uint32_t cnt[2] = {0u, 0u};   // chunks taken from each epilogue set's buffer
         bool ok = true;
+        const bool prof_me = blockIdx.x == 0 && q == 0 && lane == 0;
+        PROF_T0(pt_all);
+        PROF_ACC(pa_wait);
         for (int ti = 0; ti < tr.count && ok; ++ti) {
             int m0, n0;
             tile_coords(p, tr.first + ti * tr.stride, rank, m0, n0);
@@ -810,10 +810,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     for (int rt = 0; rt < RTL; ++rt)
                         bfrag[kk][rt] = __ldg(p.next_lora_down + (static_cast<size_t>(ch_tile0 + kk) * p.next_rt_total + rt) * 32 + lane);
                 const uint32_t par = e ? cnt[1] : cnt[0];
+                PROF_T0(pt_w);
                 if (!wait_or_abort<32>(&sh->lfull[q][e], par & 1, sh, p.status, 70)) {
                     ok = false;
                     break;
                 }
+                PROF_ADD(pa_wait, pt_w);
                 const uint32_t bufa = smem_u32(epi_smem + (q * 2 + e) * G_EPI_BUF_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)
@@ -824,8 +826,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
 #pragma unroll
                         for (int rt = 0; rt < RTL; ++rt) {
-                            mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
-                            mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
+                            mma_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
+                            mma_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
                         }
                     }
                 __syncwarp();
@@ -834,6 +836,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         }
         if (ok && cur_m0 >= 0) store_lora_partial<RTL>(p, lacc, slot, q, lane);
+        PROF_ACC(pa_all);
+        PROF_ADD(pa_all, pt_all);
+        PROF_OUT(prof_me, 6, pa_all); PROF_OUT(prof_me, 7, pa_wait);
     } else if (I4 ? (warp >= 2 && warp < 6) : (warp >= 4 && warp < MMA_WARP)) {
         if constexpr (REGCTL) reg_alloc<REGS_E>();
         // ------------------------------------------------------------------ epilogue (INT4: warps 2..5; NVFP4: 4..7 and 8..11)
@@ -884,14 +889,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
             // next layer's smoothing factors of the chunks this warp will take: fetched now, so that the loads fly while the
             // warp waits for the accumulator (lane l: columns l and l + 32 of each 64-column chunk)
-            __nv_bfloat16 nsm[G_BN / 64][2];
+            h16 nsm[G_BN / 64][2];
             if constexpr (RTN > 0 && I4) {
 #pragma unroll
                 for (int h = 0; h < G_BN / 64; ++h)
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const int n = n0 + h * 64 + lane + 32 * i;
-                        nsm[h][i] = n < p.N ? p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)] : __nv_bfloat16(1.0f);
+                        nsm[h][i] = n < p.N ? p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)] : f2h(1.0f);
                     }
             }
             PROF_T0(pt_tf);
@@ -921,10 +926,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     __syncwarp();          // every lane is done with the previous chunk's factors
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
-                        __nv_bfloat16 v = nsm[0][i];
+                        h16 v = nsm[0][i];
 #pragma unroll
                         for (int hh = 1; hh < G_BN / 64; ++hh) v = h == hh ? nsm[hh][i] : v;   // registers: no dynamic indexing
-                        cvs[lane + 32 * i] = __frcp_rn(__bfloat162float(v));
+                        cvs[lane + 32 * i] = __frcp_rn(h2f(v));
                     }
                 }
                 uint8_t* buf = SETS == 2 ? my_buf : my_buf + (nstore & 1) * G_EPI_BUF_BYTES;
@@ -932,10 +937,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (SETS == 2) bulk_wait_group_read<0>(); else bulk_wait_group_read<1>();
                 }
                 if constexpr (LW) {   // ... and so has the LoRA-down warp of this quadrant
+                    PROF_T0(pt_le);
                     if (nstore > 0 && !wait_or_abort<32>(&sh->lempty[q][eset], (nstore - 1) & 1, sh, p.status, 32)) {
                         epi_ok = false;
                         break;
                     }
+                    PROF_ADD(pa_lora, pt_le);
                 }
                 __syncwarp();
                 tc_wait_ld();
@@ -1009,9 +1016,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             uint32_t xw[8];
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
-                                const float2 f = bf16x2_to_float2(ow[8 * g + i]);
-                                const __nv_bfloat162 sft = __floats2bfloat162_rn(f.x + 0.171875f, f.y + 0.171875f);
-                                xw[i] = *reinterpret_cast<const uint32_t*>(&sft);
+                                const float2 f = unpack2(ow[8 * g + i]);
+                                xw[i] = pack2(make_float2(f.x + 0.171875f, f.y + 0.171875f));
                             }
                             amax = fmaxf(amax, smooth16(xw, rcn + 4 * g, qv[g]));
                         }
@@ -1026,8 +1032,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         }
                         qdst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
                         qdst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-                        reinterpret_cast<__nv_bfloat16*>(p.oscales)[static_cast<size_t>((n0 + h * 64) >> 6) * p.M_pad + grow] =
-                            __float2bfloat16_rn(scale);
+                        reinterpret_cast<h16*>(p.oscales)[static_cast<size_t>((n0 + h * 64) >> 6) * p.M_pad + grow] = f2h(scale);
                     } else {
                         // ---- NVFP4 group quantisation of this thread's 64 values (4 groups of 16)
                         uint32_t codes[8];
@@ -1072,8 +1077,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             ldmatrix_x4(a, bufa + arow * 128 + (((2 * kk + (lane >> 4)) ^ (arow & 7)) << 4));
 #pragma unroll
                             for (int rt = 0; rt < RTN; ++rt) {
-                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
-                                mma_bf16_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
+                                mma_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][0]), a, bfrag[kk][rt].x, bfrag[kk][rt].y);
+                                mma_16816(*reinterpret_cast<float(*)[4]>(&lacc[mt][rt][4]), a, bfrag[kk][rt].z, bfrag[kk][rt].w);
                             }
                         }
                     }
@@ -1140,14 +1145,14 @@ lora_partial_reduce_kernel(const float* __restrict__ partial, float* __restrict_
 // largest lose bits.  The low-rank activations share the accumulator and are divided by the same factor (into scratch).
 // One CTA per 128 rows: thread = row for the maximum, then all threads copy the block's low-rank rows.
 __global__ void __launch_bounds__(128)
-int4_row_norm_kernel(const __nv_bfloat16* __restrict__ ascales, int KB, int M_pad, const float* __restrict__ lora_in, int R,
+int4_row_norm_kernel(const h16* __restrict__ ascales, int KB, int M_pad, const float* __restrict__ lora_in, int R,
                      float* __restrict__ row_scale, float* __restrict__ lora_out) {
     __shared__ float inv[128];
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x * 128 + threadIdx.x;
     float mx = 0.f;
-    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(__bfloat162float(ascales[static_cast<size_t>(g) * M_pad + row])));
+    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(h2f(ascales[static_cast<size_t>(g) * M_pad + row])));
     int e = 0;
     if (mx > 0.f && mx < 3.0e38f) {
         (void)frexpf(mx, &e);   // mx = f * 2^e, f in [0.5, 1)
@@ -1287,7 +1292,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.run = pl.run;
     p.qout = static_cast<uint8_t*>(a->qout);
     p.oscales = static_cast<uint8_t*>(a->oscales);
-    p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
+    p.next_smooth = static_cast<const h16*>(a->next_smooth);
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
     p.next_rt_total = a->R_next / 16;
     p.lora_partial = static_cast<float*>(a->workspace);
@@ -1313,7 +1318,7 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_lu = tm_b;
     }
     if (out_bf16) {
-        if (int rc = make_tmap_2d(&tm_out, out_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
+        if (int rc = make_tmap_2d(&tm_out, out_bf16, SVDQ_TMAP_16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_a;
@@ -1413,7 +1418,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     float* partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + int4_rows_bytes(a) + int4_lora_bytes(a));
 
     GemmParams p = {};
-    p.ascales_i4 = static_cast<const __nv_bfloat16*>(a->ascales);
+    p.ascales_i4 = static_cast<const h16*>(a->ascales);
     p.row_scale = row_scale;
     p.act_i4 = static_cast<const uint8_t*>(a->act);
     p.act_unsigned = a->act_unsigned;
@@ -1433,7 +1438,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     p.run = pl.run;
     p.qout = static_cast<uint8_t*>(a->qout);
     p.oscales = static_cast<uint8_t*>(a->oscales);
-    p.next_smooth = static_cast<const __nv_bfloat16*>(a->next_smooth);
+    p.next_smooth = static_cast<const h16*>(a->next_smooth);
     p.next_lora_down = static_cast<const uint4*>(a->next_lora_down);
     p.next_rt_total = a->R_next / 16;
     p.lora_partial = partials;
@@ -1458,7 +1463,7 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         tm_lu = tm_b;
     }
     if (out_bf16) {
-        if (int rc = make_tmap_2d(&tm_out, out_bf16, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
+        if (int rc = make_tmap_2d(&tm_out, out_bf16, SVDQ_TMAP_16, n_out(a), a->M, static_cast<uint64_t>(n_out(a)) * 2, 64, 32))
             return rc;
     } else {
         tm_out = tm_b;
@@ -1480,6 +1485,15 @@ int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     return launch_requant<true>(a, pl, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_a, tm_a, p, out_bf16);
 }
 
+}  // namespace SVDQ_DT
+}  // namespace svdq
+
+#ifndef SVDQ_F16   // what follows exists once, in the bf16 build of this file
+namespace svdq {
+namespace hf {
+int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream);
+int gemm_int4_impl(const svdq_gemm_args* a, cudaStream_t stream);
+}  // namespace hf
 }  // namespace svdq
 
 // ---------------------------------------------------------------------------------------------------
@@ -1526,11 +1540,11 @@ static int static_scratch_ptr(void** out) {
 extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* stream) {
     using namespace svdq;
     if (int rc = check_gemm_common(args)) return rc;
-    size_t need = 0;
+    size_t need = 0;   // the scratch does not depend on the 16-bit type
     if (!args->fp4) {
-        if (int rc = gemm_int4_workspace_bytes(args, &need)) return rc;
+        if (int rc = bf::gemm_int4_workspace_bytes(args, &need)) return rc;
     } else if (args->qout) {
-        if (int rc = gemm_nvfp4_workspace_bytes(args, &need)) return rc;
+        if (int rc = bf::gemm_nvfp4_workspace_bytes(args, &need)) return rc;
     }
     if (need > SVDQ_STATIC_SCRATCH_BYTES)
         return fail(SVDQ_ERR_INVALID_ARGUMENT,
@@ -1542,8 +1556,9 @@ extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* s
     svdq_gemm_args local = *args;
     local.workspace = scratch;
     local.workspace_bytes = SVDQ_STATIC_SCRATCH_BYTES;
-    if (local.fp4) return gemm_nvfp4_impl(&local, static_cast<cudaStream_t>(stream));
-    return gemm_int4_impl(&local, static_cast<cudaStream_t>(stream));
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (local.dtype == SVDQ_DTYPE_FP16) return local.fp4 ? hf::gemm_nvfp4_impl(&local, st) : hf::gemm_int4_impl(&local, st);
+    return local.fp4 ? bf::gemm_nvfp4_impl(&local, st) : bf::gemm_int4_impl(&local, st);
 }
 
 
@@ -1553,9 +1568,10 @@ extern "C" int svdq_gemm_w4a4_static_scratch(const svdq_gemm_args* args, void* s
 extern "C" int svdq_debug_prof(long long* host16) {
     using namespace svdq;
     SVDQ_CUDA(cudaDeviceSynchronize());
-    SVDQ_CUDA(cudaMemcpyFromSymbol(host16, g_prof, sizeof(long long) * 16));
+    SVDQ_CUDA(cudaMemcpyFromSymbol(host16, bf::g_prof, sizeof(long long) * 16));
     long long zero[16] = {};
-    SVDQ_CUDA(cudaMemcpyToSymbol(g_prof, zero, sizeof(zero)));
+    SVDQ_CUDA(cudaMemcpyToSymbol(bf::g_prof, zero, sizeof(zero)));
     return SVDQ_OK;
 }
 #endif
+#endif   // !SVDQ_F16

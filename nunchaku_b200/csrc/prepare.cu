@@ -9,6 +9,10 @@
 
 namespace svdq {
 
+// the 16-bit type of the checkpoint's scales, biases and LoRA weights: bf16 or fp16 (svdq_weights_args.dtype)
+__device__ __forceinline__ float tf(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float tf(__half v) { return __half2float(v); }
+
 __device__ __forceinline__ int packed_vec_pos128(int n) {
     return (n & ~15) | (((n >> 1) & 3) << 2) | (((n >> 3) & 1) << 1) | (n & 1);
 }
@@ -43,11 +47,12 @@ __global__ void retile_wgt_codes_kernel(const uint32_t* __restrict__ src, uint32
 // below it lose bits, and is applied again in the GEMM epilogue.  Within each block of 8 k the order is
 // (0, 4, 1, 5, 2, 6, 3, 7): the order in which the GEMM's converter warps produce the activations of a packed word
 // (a dot product does not care about the order as long as both operands agree).  Row-major [N][K].
-__global__ void int4_col_scale_kernel(const __nv_bfloat16* __restrict__ ws, float* __restrict__ col_scale, int N, int KB) {
+template <typename T>
+__global__ void int4_col_scale_kernel(const T* __restrict__ ws, float* __restrict__ col_scale, int N, int KB) {
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N) return;
     float mx = 0.f;
-    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(__bfloat162float(ws[static_cast<size_t>(g) * N + n])));
+    for (int g = 0; g < KB; ++g) mx = fmaxf(mx, fabsf(tf(ws[static_cast<size_t>(g) * N + n])));
     int e = 0;
     if (mx > 0.f && mx < 3.0e38f) {
         (void)frexpf(mx, &e);   // mx = f * 2^e, f in [0.5, 1)
@@ -57,7 +62,8 @@ __global__ void int4_col_scale_kernel(const __nv_bfloat16* __restrict__ ws, floa
     col_scale[n] = ldexpf(1.0f, e);
 }
 
-__global__ void retile_wgt_codes_f16_kernel(const uint32_t* __restrict__ src, const __nv_bfloat16* __restrict__ ws,
+template <typename T>
+__global__ void retile_wgt_codes_f16_kernel(const uint32_t* __restrict__ src, const T* __restrict__ ws,
                                             const float* __restrict__ col_scale, uint4* __restrict__ dst, int N, int K) {
     const size_t total = static_cast<size_t>(N) * K / 8;
     const int KB = K / 64;
@@ -74,7 +80,7 @@ __global__ void retile_wgt_codes_f16_kernel(const uint32_t* __restrict__ src, co
         const int n = bn * 128 + nt * 16 + half * 8 + g;
         const int k = bk * 64 + kh * 32 + t * 8;
         const uint32_t w = src[i];
-        const float s = __bfloat162float(ws[static_cast<size_t>(bk) * N + n]) / col_scale[n];
+        const float s = tf(ws[static_cast<size_t>(bk) * N + n]) / col_scale[n];
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {   // output pair j = codes j and j + 4
@@ -103,7 +109,7 @@ __global__ void retile_wgt_mscales_kernel(const uint32_t* __restrict__ src, uint
 
 // INT4 weight scales.  Reference (packer.py:241-301): [N/128][K/64][a 8][c 4][b 2][d 2] bf16,
 // n = a*16 + b*8 + c*2 + d.  Native: bf16 [K/64][N] (the values are bf16 in the checkpoint; alpha is 1 for INT4).
-__global__ void retile_wgt_scales_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int N, int K) {
+__global__ void retile_wgt_scales_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int N, int K) {
     const int KB = K / 64;
     const size_t total = static_cast<size_t>(N) * KB;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -127,17 +133,18 @@ struct LoraScales {
     float v[SVDQ_MAX_LORA_RANK / 16];
 };
 
-__global__ void prepare_columns_kernel(const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ wcscales,
-                                       const __nv_bfloat16* __restrict__ lora_up, float* __restrict__ col_scale,
+template <typename T>
+__global__ void prepare_columns_kernel(const T* __restrict__ bias, const T* __restrict__ wcscales,
+                                       const T* __restrict__ lora_up, float* __restrict__ col_scale,
                                        float* __restrict__ col_bias, float* __restrict__ lora_out, float alpha, int N,
                                        int R, int R32, LoraScales ls, bool col_scale_given) {
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N) return;
     const int pos = (n & ~127) + packed_vec_pos128(n & 127);
-    const float wc = wcscales ? __bfloat162float(wcscales[pos]) : 1.0f;
+    const float wc = wcscales ? tf(wcscales[pos]) : 1.0f;
     const float cs = (col_scale_given ? col_scale[n] : 1.0f) * alpha * wc;   // INT4: times the power of two taken out of the weights
     col_scale[n] = cs;
-    col_bias[n] = bias ? __bfloat162float(bias[pos]) : 0.0f;
+    col_bias[n] = bias ? tf(bias[pos]) : 0.0f;
     if (lora_out == nullptr) return;
     const float inv = cs != 0.0f ? 1.0f / cs : 0.0f;
     const int cp = n >> 4, nh = (n >> 3) & 1, g = n & 7;
@@ -146,7 +153,7 @@ __global__ void prepare_columns_kernel(const __nv_bfloat16* __restrict__ bias, c
         if (r < R) {
             const int rp = r >> 4, kh = (r >> 3) & 1, t = (r >> 1) & 3, e = r & 1;
             const size_t idx = ((((static_cast<size_t>(cp) * (R / 16) + rp) * 8 + g) * 4 + t) * 2 + nh) * 4 + kh * 2 + e;
-            v = __bfloat162float(lora_up[idx]) * ls.v[rp] * inv;
+            v = tf(lora_up[idx]) * ls.v[rp] * inv;
             uint32_t u;
             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
             v = __uint_as_float(u);
@@ -259,6 +266,34 @@ int prepared_bytes_impl(int N, int K, int R, int fp4, size_t bytes[5]) {
     return SVDQ_OK;
 }
 
+template <typename T>
+static void prepare_typed(const svdq_weights_args* a, const svdq_prepared_weights* o, cudaStream_t stream) {
+    const size_t words = static_cast<size_t>(a->N) * a->K / 8;
+    if (a->fp4) {
+        retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                    static_cast<uint32_t*>(o->wgt), a->N, a->K);
+        const size_t sw = static_cast<size_t>(a->N) * a->K / 64;
+        retile_wgt_mscales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint32_t*>(a->wscales),
+                                                                   static_cast<uint32_t*>(o->wscales), a->N, a->K);
+    } else {
+        const size_t sw = static_cast<size_t>(a->N) * (a->K / 64);
+        retile_wgt_scales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint16_t*>(a->wscales),
+                                                                  static_cast<uint16_t*>(o->wscales), a->N, a->K);
+        int4_col_scale_kernel<T><<<(a->N + 127) / 128, 128, 0, stream>>>(static_cast<const T*>(o->wscales), o->col_scale,
+                                                                     a->N, a->K / 64);
+        retile_wgt_codes_f16_kernel<T><<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
+                                                                        static_cast<const T*>(o->wscales), o->col_scale,
+                                                                        static_cast<uint4*>(o->wgt), a->N, a->K);
+    }
+    LoraScales ls;
+    for (int i = 0; i < SVDQ_MAX_LORA_RANK / 16; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
+    const int R32 = (a->R + 31) / 32 * 32;
+    prepare_columns_kernel<T><<<(a->N + 127) / 128, 128, 0, stream>>>(
+        static_cast<const T*>(a->bias), static_cast<const T*>(a->wcscales),
+        static_cast<const T*>(a->lora_up), o->col_scale, o->col_bias, a->R ? o->lora_up : nullptr, a->alpha,
+        a->N, a->R, R32, ls, !a->fp4);
+}
+
 int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights* o, cudaStream_t stream) {
     SVDQ_CHECK_ARG(a && o, "prepare_weights: null args");
     SVDQ_CHECK_ARG(a->qweight && a->wscales && o->wgt && o->wscales && o->col_scale && o->col_bias,
@@ -270,30 +305,9 @@ int prepare_weights_impl(const svdq_weights_args* a, const svdq_prepared_weights
     SVDQ_CHECK_ARG(aligned(a->qweight, 16) && aligned(a->wscales, 16) && aligned(o->wgt, 16) && aligned(o->wscales, 16),
                    "prepare_weights: tensors must be 16-byte aligned");
     if (int rc = check_arch()) return rc;
-    const size_t words = static_cast<size_t>(a->N) * a->K / 8;
-    if (a->fp4) {
-        retile_wgt_codes_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
-                                                                    static_cast<uint32_t*>(o->wgt), a->N, a->K);
-        const size_t sw = static_cast<size_t>(a->N) * a->K / 64;
-        retile_wgt_mscales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const uint32_t*>(a->wscales),
-                                                                   static_cast<uint32_t*>(o->wscales), a->N, a->K);
-    } else {
-        const size_t sw = static_cast<size_t>(a->N) * (a->K / 64);
-        retile_wgt_scales_kernel<<<grid_for(sw), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a->wscales),
-                                                                  static_cast<__nv_bfloat16*>(o->wscales), a->N, a->K);
-        int4_col_scale_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(o->wscales), o->col_scale,
-                                                                     a->N, a->K / 64);
-        retile_wgt_codes_f16_kernel<<<grid_for(words), 256, 0, stream>>>(static_cast<const uint32_t*>(a->qweight),
-                                                                        static_cast<const __nv_bfloat16*>(o->wscales), o->col_scale,
-                                                                        static_cast<uint4*>(o->wgt), a->N, a->K);
-    }
-    LoraScales ls;
-    for (int i = 0; i < SVDQ_MAX_LORA_RANK / 16; ++i) ls.v[i] = (a->lora_scales && i < a->R / 16) ? a->lora_scales[i] : 1.0f;
-    const int R32 = (a->R + 31) / 32 * 32;
-    prepare_columns_kernel<<<(a->N + 127) / 128, 128, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(a->bias), static_cast<const __nv_bfloat16*>(a->wcscales),
-        static_cast<const __nv_bfloat16*>(a->lora_up), o->col_scale, o->col_bias, a->R ? o->lora_up : nullptr, a->alpha,
-        a->N, a->R, R32, ls, !a->fp4);
+    SVDQ_CHECK_ARG(a->dtype == SVDQ_DTYPE_BF16 || a->dtype == SVDQ_DTYPE_FP16, "prepare_weights: bad dtype %d", a->dtype);
+    if (a->dtype == SVDQ_DTYPE_FP16) prepare_typed<__half>(a, o, stream);
+    else prepare_typed<__nv_bfloat16>(a, o, stream);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }

@@ -4,12 +4,14 @@
 // rcp.approx.ftz, E2M1 / E4M3 / s4 conversions with saturation; a group whose absolute maximum is zero gets
 // all-zero codes.
 #pragma once
-#include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 #include <cstdint>
 
+#include "dtype.cuh"
+
 namespace svdq {
+namespace SVDQ_DT {
 
 __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
     uint32_t r;
@@ -17,13 +19,6 @@ __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
         : "=r"(r)
         : "f"(hi), "f"(lo));
     return r;
-}
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
@@ -36,17 +31,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
 // (gemm_base.cuh:612-623, gemm_utils.cuh:291-327): s = bf16(g * sigmoid(g)), sigmoid(g) = rcp.approx(1 + ex2.approx(-log2(e) g)),
 // result = bf16(v * s); words hold the value in the low half and the gate in the high half.
 __device__ __forceinline__ float glu_one(uint32_t w) {
-    const float v = __uint_as_float(w << 16);
-    const float g = __uint_as_float(w & 0xffff0000u);
+    const float2 vg = unpack2(w);
+    const float v = vg.x, g = vg.y;
     float e, r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.442695041f * g));
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
-    const float s = __bfloat162float(__float2bfloat16_rn(g * r));
+    const float s = h2f(f2h(g * r));
     return v * s;
 }
 __device__ __forceinline__ uint32_t glu_pair2(uint32_t w0, uint32_t w1) {
-    const __nv_bfloat162 o = __floats2bfloat162_rn(glu_one(w0), glu_one(w1));
-    return *reinterpret_cast<const uint32_t*>(&o);
+    return pack2(make_float2(glu_one(w0), glu_one(w1)));
 }
 
 // position of channel n (0..127) inside a 128-block of a reference-packed vector
@@ -69,18 +63,6 @@ __device__ __forceinline__ uint32_t e2m1x8(float2 a, float2 b, float2 c, float2 
     return r;
 }
 
-// |result| = max(|a|, |b|) per bf16 lane (the sign of the result is meaningless): one instruction per
-// pair instead of two abs and a max.
-__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-
-__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-
 // 16 bf16 values (8 packed words, low half = lower column) times their 16 reciprocal smoothing factors
 // (fp32, 16-byte aligned), rounded to bf16: q[] and the group's absolute maximum.
 // "x * rcp + 0.0f" as one FMA: the reference adds a bf16 zero shift before dividing, which turns -0 into +0.
@@ -91,15 +73,14 @@ __device__ __forceinline__ float smooth16(const uint32_t (&xw)[8], const float4*
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float4 r4 = rc[i];
-        const float2 a = __ffma2_rn(bf16x2_to_float2(xw[2 * i]), make_float2(r4.x, r4.y), zero);
-        const float2 b = __ffma2_rn(bf16x2_to_float2(xw[2 * i + 1]), make_float2(r4.z, r4.w), zero);
-        __nv_bfloat162 qa = __float22bfloat162_rn(a), qb = __float22bfloat162_rn(b);
-        q[2 * i] = *reinterpret_cast<uint32_t*>(&qa);
-        q[2 * i + 1] = *reinterpret_cast<uint32_t*>(&qb);
-        mx = absmax_bf16x2(mx, q[2 * i]);
-        mx = absmax_bf16x2(mx, q[2 * i + 1]);
+        const float2 a = __ffma2_rn(unpack2(xw[2 * i]), make_float2(r4.x, r4.y), zero);
+        const float2 b = __ffma2_rn(unpack2(xw[2 * i + 1]), make_float2(r4.z, r4.w), zero);
+        q[2 * i] = pack2(a);
+        q[2 * i + 1] = pack2(b);
+        mx = absmax2(mx, q[2 * i]);
+        mx = absmax2(mx, q[2 * i + 1]);
     }
-    const float2 m = bf16x2_to_float2(mx);
+    const float2 m = unpack2(mx);
     return fmaxf(fabsf(m.x), fabsf(m.y));
 }
 
@@ -120,8 +101,8 @@ __device__ __forceinline__ uint32_t nvfp4_encode16(const uint32_t (&q)[8], float
     const float2 rs2 = make_float2(rs, rs);
 #pragma unroll
     for (int w = 0; w < 2; ++w)
-        cw[w] = e2m1x8(__fmul2_rn(bf16x2_to_float2(q[4 * w]), rs2), __fmul2_rn(bf16x2_to_float2(q[4 * w + 1]), rs2),
-                       __fmul2_rn(bf16x2_to_float2(q[4 * w + 2]), rs2), __fmul2_rn(bf16x2_to_float2(q[4 * w + 3]), rs2));
+        cw[w] = e2m1x8(__fmul2_rn(unpack2(q[4 * w]), rs2), __fmul2_rn(unpack2(q[4 * w + 1]), rs2),
+                       __fmul2_rn(unpack2(q[4 * w + 2]), rs2), __fmul2_rn(unpack2(q[4 * w + 3]), rs2));
     return static_cast<uint32_t>(__nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E4M3));
 }
 
@@ -133,7 +114,7 @@ __device__ __forceinline__ float int4_encode16(const uint32_t (&q)[8], float ama
     cw[0] = cw[1] = 0u;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float2 f = bf16x2_to_float2(q[i]);
+        const float2 f = unpack2(q[i]);
         int c0 = __float2int_rn(f.x * rs), c1 = __float2int_rn(f.y * rs);
         if (UNSIGNED) {
             c0 = max(0, min(15, c0));
@@ -147,4 +128,5 @@ __device__ __forceinline__ float int4_encode16(const uint32_t (&q)[8], float ama
     return scale;
 }
 
+}  // namespace SVDQ_DT
 }  // namespace svdq

@@ -18,7 +18,7 @@ import threading
 import torch
 
 from .. import _lib
-from ..utils import default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr
+from ..utils import default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr, HALF_DTYPES, dtype_code, require_same_half_dtype
 
 _ATTR = "_svdq_b200_prepared"
 _lock = threading.Lock()   # guards creation / replacement of a layer's prepared weights (the C entry points are re-entrant)
@@ -68,10 +68,11 @@ def prepare_weights(
     fp4: bool,
 ) -> PreparedWeights:
     require_cuda_contiguous("wgt", wgt, (torch.int8, torch.uint8))
-    require_cuda_contiguous("wscales", wscales, (torch.float8_e4m3fn,) if fp4 else (torch.bfloat16,))
-    require_cuda_contiguous("lora_up", lora_up, (torch.bfloat16,))
-    require_cuda_contiguous("bias", bias, (torch.bfloat16,))
-    require_cuda_contiguous("wcscales", wcscales, (torch.bfloat16,))
+    require_cuda_contiguous("wscales", wscales, (torch.float8_e4m3fn,) if fp4 else HALF_DTYPES)
+    require_cuda_contiguous("lora_up", lora_up)
+    require_cuda_contiguous("bias", bias)
+    require_cuda_contiguous("wcscales", wcscales)
+    half = require_same_half_dtype(wscales=None if fp4 else wscales, lora_up=lora_up, bias=bias, wcscales=wcscales) or torch.bfloat16
     N, K = wgt.shape[0], wgt.shape[1] * 2
     R = 0 if lora_up is None else lora_up.shape[1]
     out = PreparedWeights(N, K, R, fp4, wgt.device)
@@ -80,8 +81,9 @@ def prepare_weights(
         ls = (ctypes.c_float * len(lora_scales))(*lora_scales)
     args = _lib.WeightsArgs(
         qweight=ptr(wgt), wscales=ptr(wscales), lora_up=ptr(lora_up), bias=ptr(bias), wcscales=ptr(wcscales),
-        lora_scales=ls, alpha=float(alpha), N=N, K=K, R=R, fp4=int(fp4),
+        lora_scales=ls, alpha=float(alpha), N=N, K=K, R=R, fp4=int(fp4), dtype=dtype_code(half),
     )
+    out.half_dtype = half
     st = out.as_struct()
     with on_device(wgt.device):
         _lib.check(_lib.load().svdq_w4a4_prepare_weights(ctypes.byref(args), ctypes.byref(st), stream_ptr(wgt.device)))
@@ -215,9 +217,9 @@ def svdq_gemm_w4a4_cuda(
     if ascales is None or wscales is None:
         raise ValueError("ascales and wscales are required")
     require_cuda_contiguous("act", act, (torch.uint8, torch.int8))
-    require_cuda_contiguous("ascales", ascales, (torch.float8_e4m3fn,) if fp4 else (torch.bfloat16,))
+    require_cuda_contiguous("ascales", ascales, (torch.float8_e4m3fn,) if fp4 else HALF_DTYPES)
     require_cuda_contiguous("lora_act_in", lora_act_in, (torch.float32,))
-    require_cuda_contiguous("out", out, (torch.bfloat16,))
+    require_cuda_contiguous("out", out, HALF_DTYPES)
     if (lora_act_in is None) != (lora_up is None):
         raise ValueError("lora_act_in and lora_up must be given together")
     if lora_scales is None and lora_up is not None:
@@ -252,7 +254,7 @@ def svdq_gemm_w4a4_cuda(
             raise ValueError("out_linearattn needs out_vk (gemm_w4a4_launch_impl.cuh:313)")
         activation = _lib.ACT_NONE
         M = M_pad
-        tmp_out = out = torch.empty(M_pad, N, dtype=torch.bfloat16, device=dev)
+        tmp_out = out = torch.empty(M_pad, N, dtype=torch.bfloat16, device=dev)   # the row-wise kernels are bf16 only
     else:
         if out is None:
             raise ValueError("either `out` or (`qout`, `oscales`) must be given")
@@ -263,7 +265,16 @@ def svdq_gemm_w4a4_cuda(
     if next_fp4 is None:
         next_fp4 = fp4
 
+    # one 16-bit type per call: the weights' (as prepared), the output's, the INT4 scales' and the next layer's
+    half = require_same_half_dtype(out=out, ascales=None if fp4 else ascales, smooth_factor=smooth_factor, lora_down=lora_down,
+                                   oscales=None if (oscales is None or oscales.dtype == torch.float8_e4m3fn) else oscales)
+    if half is None:
+        half = prepared.half_dtype
+    if half != prepared.half_dtype and (lora_up is not None or bias is not None or wcscales is not None or not fp4):
+        raise ValueError(f"the call's tensors are {half} but the layer's parameters are {prepared.half_dtype}")
+
     a = prepared.args()
+    a.dtype = dtype_code(half)
     a.act = act.data_ptr()
     a.ascales = ascales.data_ptr()
     a.lora_act_in = ptr(lora_act_in)

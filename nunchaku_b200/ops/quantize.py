@@ -7,7 +7,7 @@ import ctypes
 import torch
 
 from .. import _lib
-from ..utils import ceil_divide, default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr
+from ..utils import ceil_divide, default_act_layout, on_device, ptr, require_cuda_contiguous, stream_ptr, HALF_DTYPES, dtype_code, require_same_half_dtype
 
 
 def svdq_quantize_w4a4_act_fuse_lora_cuda(
@@ -33,9 +33,10 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
     """
     if lora_down is None or smooth is None:
         raise ValueError("lora_down and smooth are required (the reference dereferences both)")
-    require_cuda_contiguous("input", input, (torch.bfloat16,))
-    require_cuda_contiguous("lora_down", lora_down, (torch.bfloat16,))
-    require_cuda_contiguous("smooth", smooth, (torch.bfloat16,))
+    require_cuda_contiguous("input", input, HALF_DTYPES)
+    require_cuda_contiguous("lora_down", lora_down, HALF_DTYPES)
+    require_cuda_contiguous("smooth", smooth, HALF_DTYPES)
+    half = require_same_half_dtype(input=input, lora_down=lora_down, smooth=smooth)
     if input.dim() != 2:
         raise ValueError("input must be 2-D [M, K]")
     batch_size, channels = input.shape
@@ -63,7 +64,7 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
     if lora_act_out is None:
         lora_act_out = torch.empty(batch_size_pad, rank, dtype=torch.float32, device=dev)
     require_cuda_contiguous("output", output, (torch.uint8, torch.int8))
-    require_cuda_contiguous("oscales", oscales, (torch.float8_e4m3fn,) if fp4 else (torch.bfloat16,))
+    require_cuda_contiguous("oscales", oscales, (torch.float8_e4m3fn,) if fp4 else (half,))
     require_cuda_contiguous("lora_act_out", lora_act_out, (torch.float32,))
     if output.numel() != batch_size_pad * channels // 2 or lora_act_out.numel() != batch_size_pad * rank:
         raise ValueError("output / lora_act_out have the wrong number of elements")
@@ -75,7 +76,7 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
         smooth=ptr(smooth), lora_down=ptr(lora_down),
         M=batch_size, M_pad=batch_size_pad, K=channels, R=rank,
         fp4=int(fp4), fuse_glu=int(fuse_glu),
-        layout=default_act_layout() if layout is None else layout, K_in=k_in,
+        layout=default_act_layout() if layout is None else layout, K_in=k_in, dtype=dtype_code(half),
     )
     with on_device(dev):
         _lib.check(_lib.load().svdq_quantize_w4a4_act_fuse_lora(ctypes.byref(args), stream_ptr(dev)))

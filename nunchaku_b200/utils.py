@@ -59,6 +59,32 @@ def on_device(device: torch.device):
     return torch.cuda.device(idx)
 
 
+# The 16-bit floating-point types of the path (the reference's GEMMConfig_W4A4_BF16 / _FP16) and their C-ABI codes.
+HALF_DTYPES = (torch.bfloat16, torch.float16)
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 0
+    if dtype == torch.float16:
+        return 1
+    raise ValueError(f"dtype {dtype}: the W4A4 path computes with bf16 or fp16 tensors")
+
+
+def require_same_half_dtype(**tensors) -> torch.dtype | None:
+    """All given (non-None) tensors share one of the two 16-bit types; returns it (None when there is no tensor)."""
+    found = None
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if t.dtype not in HALF_DTYPES:
+            raise ValueError(f"{name} has dtype {t.dtype}, expected one of {HALF_DTYPES}")
+        if found is not None and t.dtype != found:
+            raise ValueError(f"{name} has dtype {t.dtype} but other tensors of the call are {found}")
+        found = t.dtype
+    return found
+
+
 def require_cuda_contiguous(name: str, t: torch.Tensor | None, dtypes=None) -> None:
     if t is None:
         return

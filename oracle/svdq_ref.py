@@ -24,6 +24,8 @@ from . import fmt
 
 F32 = torch.float32
 BF16 = torch.bfloat16
+F16 = torch.float16
+HALF_TYPES = (BF16, F16)   # the reference's half_t: GEMMConfig_W4A4_BF16 / _FP16 (gemm_base.cuh:29-54)
 
 # fp32 compile-time constants of the reference (gemm_w4a4.cuh:91-93,435-441)
 RCP6 = torch.tensor(1.0, dtype=F32) / torch.tensor(6.0, dtype=F32)
@@ -49,7 +51,7 @@ class QuantOut:
 def _silu_bf16(y: torch.Tensor) -> torch.Tensor:
     """gemm_utils.cuh:321-327: (T)(float(x) * sigmoid(float(x)))."""
     yf = y.to(F32)
-    return (yf * torch.sigmoid(yf)).to(BF16)
+    return (yf * torch.sigmoid(yf)).to(y.dtype)
 
 
 def gelu_f32(x: torch.Tensor) -> torch.Tensor:
@@ -71,7 +73,7 @@ def group_quantize(v: torch.Tensor, *, fp4: bool, unsigned: bool = False):
     ties are common (a few in 10^4 elements).  ``tie`` flags the elements within 1e-5 (relative) of a tie: there the
     code is "either neighbour", everywhere else it is pinned.
     """
-    assert v.dtype == BF16
+    assert v.dtype in HALF_TYPES
     rows, K = v.shape
     G = 16 if fp4 else 64
     vf = v.to(F32).reshape(rows, K // G, G)
@@ -81,7 +83,7 @@ def group_quantize(v: torch.Tensor, *, fp4: bool, unsigned: bool = False):
         stored = fmt.e4m3_encode(scale)
     else:
         scale = amax * (RCP15 if unsigned else RCP7)
-        stored = scale.to(BF16)
+        stored = scale.to(v.dtype)
     rscale = torch.where(scale == 0, torch.zeros_like(scale), 1.0 / scale)
     q = vf * rscale.unsqueeze(2)
     codes = fmt.e2m1_encode(q) if fp4 else fmt.int4_encode(q, unsigned)
@@ -109,15 +111,16 @@ def ref_quantize(
     smooth    bf16 [K]     logical order
     lora_down bf16 [R, K]  logical order (the unpacked ``proj_down``)
     """
-    assert x.dtype == BF16 and smooth.dtype == BF16
+    assert x.dtype in HALF_TYPES and smooth.dtype == x.dtype
+    HT = x.dtype
     M = x.shape[0]
     if fuse_glu:  # gemm_base.cuh:612-623: pack[j] = raw[j].x * silu(raw[j].y), both in bf16
-        v = (x[:, 0::2].to(F32) * _silu_bf16(x[:, 1::2]).to(F32)).to(BF16)
+        v = (x[:, 0::2].to(F32) * _silu_bf16(x[:, 1::2]).to(F32)).to(HT)
     else:
         v = x
     K = v.shape[1]
     M_pad = ceil_to(M, pad_size)
-    vp = torch.zeros(M_pad, K, dtype=BF16)
+    vp = torch.zeros(M_pad, K, dtype=HT)
     vp[:M] = v
     # LoRA down on the un-smoothed tile (lora.cuh:243-353), fp32 accumulation
     if lora_down is not None:
@@ -125,8 +128,10 @@ def ref_quantize(
     else:
         lora_act = torch.zeros(M_pad, 0, dtype=F32)
     # EpilogueQuantize (gemm_w4a4.cuh:930-1043) with shift_value = 0: bf16 add of +0, then h2div
-    vs = (vp.to(F32) + 0.0).to(BF16)
-    vs = (vs.to(F32) / smooth.to(F32).unsqueeze(0)).to(BF16)
+    # (fp16: the reference's half division is rcp.approx(b) * a rounded once, cuda_fp16.hpp __hdiv; the exact quotient used
+    # here can differ from it only within 2^-23 of a rounding boundary of the result)
+    vs = (vp.to(F32) + 0.0).to(HT)
+    vs = (vs.to(F32) / smooth.to(F32).unsqueeze(0)).to(HT)
     codes, scales, tie = group_quantize(vs, fp4=fp4, unsigned=False)
     return QuantOut(codes, scales, lora_act, fp4, False, tie)
 
@@ -219,12 +224,13 @@ def ref_requantize(
     ``y`` is the activated GEMM output in fp32 [M, N]; it is rounded to bf16 first,
     as the reference's accumulator tile is bf16 at that point."""
     M, N = y.shape
-    yb = torch.zeros(M_pad, N, dtype=BF16)
-    yb[:M] = y.to(BF16)
+    HT = nxt.smooth.dtype
+    yb = torch.zeros(M_pad, N, dtype=HT)
+    yb[:M] = y.to(F32).clamp(-65504.0, 65504.0).to(HT) if HT == F16 else y.to(HT)
     lora_act = (yb.to(torch.float64) @ nxt.lora_down.to(torch.float64).t()).to(F32)
     shift = INT4_UNSIGNED_SHIFT if unsigned else 0.0
-    v = (yb.to(F32) + shift).to(BF16)
-    v = (v.to(F32) / nxt.smooth.to(F32).unsqueeze(0)).to(BF16)
+    v = (yb.to(F32) + shift).to(HT)
+    v = (v.to(F32) / nxt.smooth.to(F32).unsqueeze(0)).to(HT)
     codes, scales, tie = group_quantize(v, fp4=nxt.fp4, unsigned=unsigned)
     return QuantOut(codes, scales, lora_act, nxt.fp4, unsigned, tie)
 
@@ -233,22 +239,22 @@ def ref_requantize(
 # Synthetic SVDQuant problems (the reference has no quantiser; its checkpoints
 # come from the external DeepCompressor project).
 # ---------------------------------------------------------------------------
-def make_activations(M: int, K: int, seed: int = 0, outlier_frac: float = 0.01, outlier_mul: float = 20.0):
+def make_activations(M: int, K: int, seed: int = 0, outlier_frac: float = 0.01, outlier_mul: float = 20.0, dtype=BF16):
     """bf16 [M, K] ~ N(0,1) with a fraction of channels scaled up (outliers)."""
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(M, K, generator=g, dtype=F32)
     n_out = max(1, math.ceil(outlier_frac * K))
     cols = torch.randperm(K, generator=g)[:n_out]
     x[:, cols] *= outlier_mul
-    return x.to(BF16)
+    return x.to(dtype)
 
 
-def quantize_weight(res: torch.Tensor, fp4: bool):
+def quantize_weight(res: torch.Tensor, fp4: bool, dtype=BF16):
     """Residual fp32 [N, K] -> (codes uint8 [N,K], scales [K/G, N], wtscale)."""
     N, K = res.shape
     if fp4:
         amax_t = res.abs().max().item()
-        wtscale = float(torch.tensor(max(amax_t / (6.0 * 448.0), 1e-12), dtype=BF16).item())  # module stores bf16
+        wtscale = float(torch.tensor(max(amax_t / (6.0 * 448.0), 1e-12), dtype=dtype).item())  # the module stores it in its 16-bit type
         g = res.reshape(N, K // 16, 16)
         s = g.abs().amax(dim=2) / (6.0 * wtscale)
         sb = fmt.e4m3_encode(s)
@@ -257,7 +263,7 @@ def quantize_weight(res: torch.Tensor, fp4: bool):
         codes = fmt.e2m1_encode(q).reshape(N, K)
         return codes, sb.t().contiguous(), wtscale
     g = res.reshape(N, K // 64, 64)
-    s = (g.abs().amax(dim=2) / 7.0).to(BF16)
+    s = (g.abs().amax(dim=2) / 7.0).to(dtype)
     sf = s.to(F32)
     q = g / torch.where(sf == 0, torch.ones_like(sf), sf).unsqueeze(2)
     codes = fmt.int4_encode(q, False).reshape(N, K)
@@ -276,6 +282,7 @@ def make_linear(
     bias: bool = True,
     w_std: float = 0.02,
     wcscales: bool = False,
+    dtype=BF16,
 ) -> Linear:
     """Random-init SVDQuant linear.
 
@@ -289,7 +296,7 @@ def make_linear(
     if x_absmax is None:
         x_absmax = torch.ones(K)
     w_absmax = W.abs().amax(dim=0).clamp(min=1e-8)
-    smooth = torch.sqrt(x_absmax.to(F32).clamp(min=1e-8) / w_absmax).clamp(min=1e-4).to(BF16)
+    smooth = torch.sqrt(x_absmax.to(F32).clamp(min=1e-8) / w_absmax).clamp(min=1e-4).to(dtype)
     What = W * smooth.to(F32).unsqueeze(0)
     if R > 0:
         if min(N, K) <= 1024:
@@ -303,17 +310,17 @@ def make_linear(
     else:
         low = torch.zeros_like(What)
     res = What - low
-    wcodes, wscales, wtscale = quantize_weight(res, fp4)
+    wcodes, wscales, wtscale = quantize_weight(res, fp4, dtype)
     if mode == "literal":
-        lora_down = (torch.randn(R, K, generator=g) * 0.02).to(BF16)
-        lora_up = (torch.randn(N, R, generator=g) * 0.02).to(BF16)
+        lora_down = (torch.randn(R, K, generator=g) * 0.02).to(dtype)
+        lora_up = (torch.randn(N, R, generator=g) * 0.02).to(dtype)
     else:
-        lora_up = (U * S).to(BF16)
-        lora_down = (V.t() / smooth.to(F32).unsqueeze(0)).to(BF16)
-    b = (torch.randn(N, generator=g) * 0.02).to(BF16) if bias else None
+        lora_up = (U * S).to(dtype)
+        lora_down = (V.t() / smooth.to(F32).unsqueeze(0)).to(dtype)
+    b = (torch.randn(N, generator=g) * 0.02).to(dtype) if bias else None
     wc = None
     if fp4:
-        wc = (1.0 + 0.25 * torch.rand(N, generator=g)).to(BF16) if wcscales else torch.ones(N, dtype=BF16)
+        wc = (1.0 + 0.25 * torch.rand(N, generator=g)).to(dtype) if wcscales else torch.ones(N, dtype=dtype)
     lin = Linear(K, N, R, fp4, wcodes, wscales, smooth, lora_down, lora_up, b, wtscale, wc)
     lin.master = W  # type: ignore[attr-defined]
     return lin

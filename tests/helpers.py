@@ -22,7 +22,7 @@ def packed_params(lin: R.Linear) -> dict[str, torch.Tensor]:
     }
     if lin.fp4:
         d["wscales"] = fp8(L.ref_pack_wmscales(lin.wscales))
-        d["wtscale"] = torch.tensor([lin.wtscale], dtype=torch.bfloat16)
+        d["wtscale"] = torch.tensor([lin.wtscale], dtype=lin.smooth.dtype)
         d["wcscales"] = L.ref_pack_vector(lin.wcscales)
     else:
         d["wscales"] = L.ref_pack_wscales(lin.wscales)
@@ -36,7 +36,7 @@ def to_module(lin: R.Linear, device="cuda", act_unsigned: bool = False):
 
     m = SVDQW4A4Linear(
         lin.K, lin.N, rank=lin.R, bias=lin.bias is not None, precision="nvfp4" if lin.fp4 else "int4",
-        act_unsigned=act_unsigned, device=device,
+        act_unsigned=act_unsigned, device=device, torch_dtype=lin.smooth.dtype,
     )
     sd = packed_params(lin)
     with torch.no_grad():
