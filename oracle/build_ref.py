@@ -2,11 +2,12 @@
 
     python -m oracle.build_ref [--force]
 
-Two translation units, compiled with nvcc for sm_100a straight from where they lie in the reference tree (nothing is
+Three translation units, compiled with nvcc for sm_100a straight from where they lie in the reference tree (nothing is
 copied, the reference's own build system is not run):
 
   * ``src/kernels/zgemm/gemm_w4a4_launch_bf16_int4.cu``: the explicit instantiation of
     ``GEMM_W4A4_Launch<GEMMConfig_W4A4_BF16, false>`` (quantiser, GEMM with every epilogue, ``vk_mul_q``);
+  * ``src/kernels/zgemm/gemm_w4a4_launch_fp16_int4.cu``: the same for ``GEMMConfig_W4A4_FP16``;
   * ``oracle/ref_int4_shim.cu``: a C-ABI wrapper around it (raw device pointers -> the reference's ``Tensor``).
 
 The reference's ``common.h`` includes spdlog, an un-vendored submodule of the reference; a header-only copy of spdlog
@@ -57,7 +58,8 @@ def build(force: bool = False, verbose: bool = False) -> str | None:
     ]
     jobs = []
     objs = []
-    for src, name in ((launch, "launch_bf16_int4.o"), (shim, "shim.o")):
+    launch_f16 = os.path.join(REFERENCE, "src", "kernels", "zgemm", "gemm_w4a4_launch_fp16_int4.cu")
+    for src, name in ((launch, "launch_bf16_int4.o"), (launch_f16, "launch_fp16_int4.o"), (shim, "shim.o")):
         obj = os.path.join(OUT_DIR, name)
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < os.path.getmtime(src):
@@ -66,7 +68,7 @@ def build(force: bool = False, verbose: bool = False) -> str | None:
     def run(cmd):
         return cmd, subprocess.run(cmd, capture_output=True, text=True)
 
-    with ThreadPoolExecutor(max_workers=2) as ex:
+    with ThreadPoolExecutor(max_workers=3) as ex:
         for cmd, r in ex.map(run, jobs):
             if verbose or r.returncode != 0:
                 sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

@@ -1,4 +1,4 @@
-// TEST INFRASTRUCTURE, not part of the product: a C-ABI door onto the reference's OWN INT4 (bf16) W4A4 kernels,
+// TEST INFRASTRUCTURE, not part of the product: a C-ABI door onto the reference's OWN INT4 (bf16 and fp16) W4A4 kernels,
 // compiled from the reference sources where they lie (nothing of them is copied here).  Only tests, the smoke check
 // and bench.py's reference leg may load the resulting library; the package never does.
 //
@@ -9,7 +9,9 @@
 //   GEMM_W4A4_Launch<GEMMConfig_W4A4_BF16, false>::quantize_w4a4_act_fuse_lora   (gemm_w4a4_launch_impl.cuh:451-521)
 //   GEMM_W4A4_Launch<GEMMConfig_W4A4_BF16, false>::gemm_w4a4                     (gemm_w4a4_launch_impl.cuh:7-424)
 //   GEMM_W4A4_Launch<GEMMConfig_W4A4_BF16, false>::linearattn_vk_mul_q           (gemm_w4a4_launch_impl.cuh:426-448)
-// whose explicit instantiation lives in src/kernels/zgemm/gemm_w4a4_launch_bf16_int4.cu (compiled next to this file).
+// whose explicit instantiation lives in src/kernels/zgemm/gemm_w4a4_launch_bf16_int4.cu (compiled next to this file), and
+// the same three members of GEMM_W4A4_Launch<GEMMConfig_W4A4_FP16, false> (gemm_w4a4_launch_fp16_int4.cu) when a call's
+// `fp16` flag is set.
 // Entry points never pass fp4 = true.  Shape violations hit the reference's live asserts (abort), so callers
 // validate shapes first; CUDA errors surface as the reference's exceptions, turned into -1 here.
 #include "kernels/zgemm/zgemm.h"
@@ -36,7 +38,8 @@ Tensor wrap(const void *p, std::vector<int> shape, Tensor::ScalarType type, int 
     return t;
 }
 
-using Launch = nunchaku::kernels::GEMM_W4A4_Launch<nunchaku::kernels::GEMMConfig_W4A4_BF16, false>;
+using LaunchBF16 = nunchaku::kernels::GEMM_W4A4_Launch<nunchaku::kernels::GEMMConfig_W4A4_BF16, false>;
+using LaunchFP16 = nunchaku::kernels::GEMM_W4A4_Launch<nunchaku::kernels::GEMMConfig_W4A4_FP16, false>;
 
 thread_local std::string g_error;
 
@@ -52,16 +55,27 @@ struct ref_int4_quantize_args {
     float *lora_act_out;     // fp32 [M_pad, R] fragment order (zeroed by the reference launcher)
     const void *smooth;      // bf16 [K_pad] packed
     int M, in_cols, M_pad, K_pad, R, fuse_glu, device;
+    int fp16;            // the 16-bit tensors are fp16 instead of bf16
 };
+
+}  // extern "C"
+
+template <typename Launch>
+static void quantize_typed(const ref_int4_quantize_args *a, Tensor::ScalarType H) {
+    Launch::quantize_w4a4_act_fuse_lora(
+        wrap(a->input, {a->M, a->in_cols}, H, a->device), wrap(a->output, {a->M_pad, a->K_pad / 2}, Tensor::INT8, a->device),
+        wrap(a->oscales, {a->K_pad / 64, a->M_pad}, H, a->device), wrap(a->lora_down, {a->K_pad, a->R}, H, a->device),
+        wrap(a->lora_act_out, {a->M_pad, a->R}, Tensor::FP32, a->device), wrap(a->smooth, {a->K_pad}, H, a->device),
+        a->fuse_glu != 0, false);
+}
+
+extern "C" {
 
 int ref_int4_quantize(const ref_int4_quantize_args *a, void *stream) {
     try {
         CUDAStreamContext ctx(static_cast<cudaStream_t>(stream));
-        Launch::quantize_w4a4_act_fuse_lora(
-            wrap(a->input, {a->M, a->in_cols}, Tensor::BF16, a->device), wrap(a->output, {a->M_pad, a->K_pad / 2}, Tensor::INT8, a->device),
-            wrap(a->oscales, {a->K_pad / 64, a->M_pad}, Tensor::BF16, a->device), wrap(a->lora_down, {a->K_pad, a->R}, Tensor::BF16, a->device),
-            wrap(a->lora_act_out, {a->M_pad, a->R}, Tensor::FP32, a->device), wrap(a->smooth, {a->K_pad}, Tensor::BF16, a->device),
-            a->fuse_glu != 0, false);
+        if (a->fp16) quantize_typed<LaunchFP16>(a, Tensor::FP16);
+        else quantize_typed<LaunchBF16>(a, Tensor::BF16);
         return 0;
     } catch (const std::exception &e) {
         g_error = e.what();
@@ -88,27 +102,38 @@ struct ref_int4_gemm_args {
     const float *lora_scales;         // host, n_lora_scales entries
     int M, M_pad, N, N_out, K, R_up, R_down, act_unsigned, fuse_silu, n_lora_scales;
     int batch, heads, tokens, tokens_pad, attn_tokens, device;
+    int fp16;                         // the 16-bit tensors are fp16 instead of bf16
 };
 
-int ref_int4_gemm(const ref_int4_gemm_args *a, void *stream) {
-    try {
-        CUDAStreamContext ctx(static_cast<cudaStream_t>(stream));
+}  // extern "C"
+
+template <typename Launch>
+static void gemm_typed(const ref_int4_gemm_args *a, Tensor::ScalarType H) {
         const int d = a->device;
         std::vector<float> ls(a->lora_scales, a->lora_scales + a->n_lora_scales);
         Launch::gemm_w4a4(
             wrap(a->act, {a->M_pad, a->K / 2}, Tensor::INT8, d), wrap(a->wgt, {a->N, a->K / 2}, Tensor::INT8, d),
-            wrap(a->out, {a->M, a->N_out}, Tensor::BF16, d), wrap(a->qout, {a->M_pad, a->N / 2}, Tensor::INT8, d),
-            wrap(a->ascales, {a->K / 64, a->M_pad}, Tensor::BF16, d), wrap(a->wscales, {a->K / 64, a->N}, Tensor::BF16, d),
-            wrap(a->oscales, {a->N / 64, a->M_pad}, Tensor::BF16, d), Tensor{},
-            wrap(a->lora_act_in, {a->M_pad, a->R_up}, Tensor::FP32, d), wrap(a->lora_up, {a->N, a->R_up}, Tensor::BF16, d),
-            wrap(a->lora_down, {a->N, a->R_down}, Tensor::BF16, d), wrap(a->lora_act_out, {a->M_pad, a->R_down}, Tensor::FP32, d),
-            wrap(a->norm_q, {128}, Tensor::BF16, d), wrap(a->norm_k, {128}, Tensor::BF16, d),
-            wrap(a->rotary_emb, {1, a->M_pad, 128}, Tensor::FP32, d), wrap(a->bias, {a->N}, Tensor::BF16, d),
-            wrap(a->smooth_factor, {a->N}, Tensor::BF16, d), wrap(a->out_vk, {a->batch, a->heads, 33, 32}, Tensor::FP32, d),
-            wrap(a->out_linearattn, {a->batch, a->tokens, a->N / 3}, Tensor::BF16, d), a->act_unsigned != 0, ls, a->fuse_silu != 0,
-            false, 1.0f, Tensor{}, wrap(a->out_q, {a->batch, a->heads, a->tokens_pad, 128}, Tensor::BF16, d),
-            wrap(a->out_k, {a->batch, a->heads, a->tokens_pad, 128}, Tensor::BF16, d),
-            wrap(a->out_v, {a->batch, a->heads, a->tokens_pad, 128}, Tensor::BF16, d), a->attn_tokens);
+            wrap(a->out, {a->M, a->N_out}, H, d), wrap(a->qout, {a->M_pad, a->N / 2}, Tensor::INT8, d),
+            wrap(a->ascales, {a->K / 64, a->M_pad}, H, d), wrap(a->wscales, {a->K / 64, a->N}, H, d),
+            wrap(a->oscales, {a->N / 64, a->M_pad}, H, d), Tensor{},
+            wrap(a->lora_act_in, {a->M_pad, a->R_up}, Tensor::FP32, d), wrap(a->lora_up, {a->N, a->R_up}, H, d),
+            wrap(a->lora_down, {a->N, a->R_down}, H, d), wrap(a->lora_act_out, {a->M_pad, a->R_down}, Tensor::FP32, d),
+            wrap(a->norm_q, {128}, H, d), wrap(a->norm_k, {128}, H, d),
+            wrap(a->rotary_emb, {1, a->M_pad, 128}, Tensor::FP32, d), wrap(a->bias, {a->N}, H, d),
+            wrap(a->smooth_factor, {a->N}, H, d), wrap(a->out_vk, {a->batch, a->heads, 33, 32}, Tensor::FP32, d),
+            wrap(a->out_linearattn, {a->batch, a->tokens, a->N / 3}, H, d), a->act_unsigned != 0, ls, a->fuse_silu != 0,
+            false, 1.0f, Tensor{}, wrap(a->out_q, {a->batch, a->heads, a->tokens_pad, 128}, H, d),
+            wrap(a->out_k, {a->batch, a->heads, a->tokens_pad, 128}, H, d),
+            wrap(a->out_v, {a->batch, a->heads, a->tokens_pad, 128}, H, d), a->attn_tokens);
+}
+
+extern "C" {
+
+int ref_int4_gemm(const ref_int4_gemm_args *a, void *stream) {
+    try {
+        CUDAStreamContext ctx(static_cast<cudaStream_t>(stream));
+        if (a->fp16) gemm_typed<LaunchFP16>(a, Tensor::FP16);
+        else gemm_typed<LaunchBF16>(a, Tensor::BF16);
         return 0;
     } catch (const std::exception &e) {
         g_error = e.what();
@@ -120,7 +145,7 @@ int ref_int4_gemm(const ref_int4_gemm_args *a, void *stream) {
 int ref_int4_vk_mul_q(void *q, float *vk, int batch, int tokens, int heads, int device, void *stream) {
     try {
         CUDAStreamContext ctx(static_cast<cudaStream_t>(stream));
-        Launch::linearattn_vk_mul_q(wrap(q, {batch, tokens, heads * 32}, Tensor::BF16, device),
+        LaunchBF16::linearattn_vk_mul_q(wrap(q, {batch, tokens, heads * 32}, Tensor::BF16, device),
                                     wrap(vk, {batch, heads, 33, 32}, Tensor::FP32, device));
         return 0;
     } catch (const std::exception &e) {

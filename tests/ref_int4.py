@@ -1,4 +1,4 @@
-"""ctypes binding of ``oracle/_ref/libnunchaku_ref_int4.so``: the reference's own INT4 (bf16) W4A4 kernels, built by
+"""ctypes binding of ``oracle/_ref/libnunchaku_ref_int4.so``: the reference's own INT4 (bf16 and fp16) W4A4 kernels, built by
 ``python -m oracle.build_ref`` from the reference tree (test infrastructure; see ``oracle/ref_int4_shim.cu``).
 All tensors are in the reference's packed orders; helpers below convert from the oracle's logical tensors."""
 from __future__ import annotations
@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(ROOT, "oracle", "_ref", "libnunchaku_ref_int4.so")
 class QuantArgs(Structure):
     _fields_ = [("input", c_void_p), ("output", c_void_p), ("oscales", c_void_p), ("lora_down", c_void_p),
                 ("lora_act_out", c_void_p), ("smooth", c_void_p), ("M", c_int), ("in_cols", c_int), ("M_pad", c_int),
-                ("K_pad", c_int), ("R", c_int), ("fuse_glu", c_int), ("device", c_int)]
+                ("K_pad", c_int), ("R", c_int), ("fuse_glu", c_int), ("device", c_int), ("fp16", c_int)]
 
 
 class GemmArgs(Structure):
@@ -25,7 +25,7 @@ class GemmArgs(Structure):
         "norm_q", "norm_k", "rotary_emb", "bias", "smooth_factor", "out_vk", "out_linearattn", "out_q", "out_k", "out_v")] + [
         ("lora_scales", POINTER(c_float))] + [(n, c_int) for n in (
             "M", "M_pad", "N", "N_out", "K", "R_up", "R_down", "act_unsigned", "fuse_silu", "n_lora_scales", "batch", "heads",
-            "tokens", "tokens_pad", "attn_tokens", "device")]
+            "tokens", "tokens_pad", "attn_tokens", "device", "fp16")]
 
 
 _lib = None
@@ -71,10 +71,10 @@ def quantize(x: torch.Tensor, smooth_packed: torch.Tensor, lora_down_packed: tor
     R = lora_down_packed.shape[1]
     assert smooth_packed.numel() == K_pad and lora_down_packed.shape[0] == K_pad
     codes = torch.empty(M_pad, K_pad // 2, dtype=torch.int8, device=dev)
-    scales = torch.empty(K_pad // 64, M_pad, dtype=torch.bfloat16, device=dev)
+    scales = torch.empty(K_pad // 64, M_pad, dtype=x.dtype, device=dev)
     lora = torch.empty(M_pad, R, dtype=torch.float32, device=dev)
     a = QuantArgs(_p(x), _p(codes), _p(scales), _p(lora_down_packed), _p(lora), _p(smooth_packed), M, cols, M_pad, K_pad, R,
-                  int(fuse_glu), dev.index or 0)
+                  int(fuse_glu), dev.index or 0, int(x.dtype == torch.float16))
     _check(load().ref_int4_quantize(ctypes.byref(a), _stream(dev)))
     return codes, scales, lora
 
@@ -106,6 +106,7 @@ def gemm(act, wgt, ascales, wscales, *, out=None, qout=None, oscales=None, lora_
         a.batch, a.heads, a.tokens_pad = out_q.shape[0], out_q.shape[1], out_q.shape[2]
     a.attn_tokens = attn_tokens
     a.device = dev.index or 0
+    a.fp16 = int(wscales.dtype == torch.float16)
     _check(load().ref_int4_gemm(ctypes.byref(a), _stream(dev)))
 
 
