@@ -102,6 +102,19 @@ class GemmArgs(Structure):
         ("next_fp4", c_int32),
         ("N_out", c_int32),
         ("dtype", c_int32),
+        ("rope_norm_q", c_void_p),
+        ("rope_norm_k", c_void_p),
+        ("rope_cos", c_void_p),
+        ("rope_sin", c_void_p),
+        ("rope_out_q", c_void_p),
+        ("rope_out_k", c_void_p),
+        ("rope_out_v", c_void_p),
+        ("rope_eps", c_float),
+        ("rope_seq_len", c_int32),
+        ("rope_heads", c_int32),
+        ("rope_tokens_pad", c_int32),
+        ("rope_token_offset", c_int32),
+        ("rope_attn_tokens", c_int32),
     ]
 
 

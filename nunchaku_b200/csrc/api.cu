@@ -227,6 +227,8 @@ int svdq_gemm_w4a4_workspace_bytes(const svdq_gemm_args* args, size_t* bytes) {
 
 int svdq_gemm_w4a4(const svdq_gemm_args* args, void* stream) {
     if (int rc = svdq::check_gemm_common(args)) return rc;
+    if (args->rope_cos && !args->fp4)
+        return svdq::fail(SVDQ_ERR_UNSUPPORTED, "gemm(int4): the fused RMSNorm + RoPE epilogue is built for NVFP4");
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (args->dtype == SVDQ_DTYPE_FP16) return args->fp4 ? svdq::hf::gemm_nvfp4_impl(args, st) : svdq::hf::gemm_int4_impl(args, st);
     return args->fp4 ? svdq::bf::gemm_nvfp4_impl(args, st) : svdq::bf::gemm_int4_impl(args, st);

@@ -141,6 +141,16 @@ struct GemmParams {
     int next_rt_total;                  // Rn/16 of that tensor (the epilogue takes its first RTN rank tiles)
     float* lora_partial;                // scratch [CTA][slots][128][Rn]
     int slots;
+    // RMSNorm + rotary embedding of a fused QKV projection in the epilogue (ROPE variants)
+    const h16* rope_wq;                 // RMSNorm weights of q and k [128]
+    const h16* rope_wk;
+    const float* rope_cos;              // [rope_seq_len][64]
+    const float* rope_sin;
+    float rope_eps;
+    int rope_seq_len;                   // rows per batch element (row % rope_seq_len = token position)
+    int rope_dim;                       // heads * 128: columns of each of q, k, v
+    int rope_split;                     // 1: q, k, v go to three token-major tensors [batch * tokens_pad, rope_dim]
+    int rope_tokens_pad, rope_token_offset, rope_attn_tokens;
 #ifdef SVDQ_ABLATE
     int ablate;   // timing experiments only (results are wrong): bit 0 no epilogue work, 1 no tcgen05.cp, 2 no scale loads,
                   // 3 no MMAs, 4 no operand loads, 5 next layer's LoRA-down without its weight loads, 6 without its mma.sync,
@@ -357,12 +367,19 @@ __device__ __forceinline__ uint4 int4x8_to_f16(uint32_t x, uint32_t flip, __half
                       *reinterpret_cast<const uint32_t*>(&v2), *reinterpret_cast<const uint32_t*>(&v3));
 }
 
-template <int RTN, bool I4>
+struct RopeMaps {
+    CUtensorMap q, k, v;   // token-major outputs of the ROPE variant in split mode; unused otherwise
+};
+
+// ROPE (plain NVFP4 epilogue only): the GEMM is a fused QKV projection [.., 3 * heads * 128]; RMSNorm of every 128-column
+// head of q and k and the rotary embedding are applied to the tile before it is stored (EpilogueRMSNormRope,
+// src/kernels/zgemm/epilogues.cuh:269-425).
+template <int RTN, bool I4, bool ROPE = false>
 __global__ void __launch_bounds__(cta_threads<RTN, I4>(), 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_la, const __grid_constant__ CUtensorMap tm_lu,
                   const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_sfa,
-                  const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tm_sfb, const __grid_constant__ RopeMaps tm_rope, const GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int SB = stage_bytes<I4>();
@@ -754,6 +771,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         cst[2][i] = in ? __frcp_rn(h2f(p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)])) : 1.0f;
                 }
                 if (ti > 0 && !wait_or_abort<32>(&sh->cempty, (ti - 1) & 1, sh, p.status, 60)) break;
+                if constexpr (ROPE) {   // RMSNorm weights of q and k: the same for every tile
+                    if (ti == 0) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            colv[2 * G_BN + lane + 32 * i] = h2f(p.rope_wq[lane + 32 * i]);
+                            colv[2 * G_BN + 128 + lane + 32 * i] = h2f(p.rope_wk[lane + 32 * i]);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < G_BN / 32; ++i) {
                     colv[lane + 32 * i] = cst[0][i];
@@ -899,6 +925,19 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         nsm[h][i] = n < p.N ? p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)] : f2h(1.0f);
                     }
             }
+            // ROPE: the rotary table entries of this thread's row (L2, one 512-byte line set per row) are asked for before the
+            // wait for the accumulator: first half of the head now, second half while the first is being stored
+            float4 rc[8], rs[8];
+            if constexpr (ROPE) {
+                const int pos = (m0 + q * 32 + lane) % p.rope_seq_len;
+                if (n0 + eset * 128 < 2 * p.rope_dim) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        rc[j] = __ldg(reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64) + j);
+                        rs[j] = __ldg(reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64) + j);
+                    }
+                }
+            }
             PROF_T0(pt_tf);
             if (!wait_or_abort<64>(&sh->tfull[as], (ti >> 1) & 1, sh, p.status, 30)) break;
             PROF_ADD(pa_tf, pt_tf);
@@ -915,8 +954,111 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if constexpr (I4) rowsc = __ldg(p.row_scale + grow);
             bool sf_cols_free = I4;   // NVFP4: the accumulator's first columns become the next tile's scale-factor buffers
             bool epi_ok = true;
+            if constexpr (ROPE) {
+                // This warp takes head `eset` of the tile (128 columns = two chunks) for its 32 rows: one row per thread, so
+                // the sum of squares needs no shuffle.  Values are rounded to the 16-bit type first and the norm and the
+                // rotation computed from those, exactly as a separate pass over the stored tile would.
+                const int col0 = n0 + eset * 128;               // first column of the head
+                const int which = col0 / p.rope_dim;            // 0: q, 1: k, 2: v
+                const int hcol = col0 - which * p.rope_dim;     // column inside q / k / v
+                const int pos = grow % p.rope_seq_len;          // token position of this thread's row
+                const float4* cosr = reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64);
+                const float4* sinr = reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64);
+                uint32_t y[64];   // the head's 128 values of this row, packed
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t r0[32], r1[32];
+                    tc_ld_32x32b_x32(taddr + eset * 128 + hh * 64, r0);
+                    tc_ld_32x32b_x32(taddr + eset * 128 + hh * 64 + 32, r1);
+                    tc_wait_ld();
+                    const float4* cs = reinterpret_cast<const float4*>(colv + eset * 128 + hh * 64);
+                    const float4* cb = reinterpret_cast<const float4*>(colv + G_BN + eset * 128 + hh * 64);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const uint32_t* r = j < 8 ? &r0[4 * j] : &r1[4 * (j - 8)];
+                        const float4 s4 = cs[j], b4 = cb[j];
+                        y[hh * 32 + 2 * j] = pack2(__ffma2_rn(make_float2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                                                              make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
+                        y[hh * 32 + 2 * j + 1] = pack2(__ffma2_rn(make_float2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                                                                  make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
+                    }
+                }
+                // the accumulator's first columns (this tile's share of them) are in registers: the next tile's scale factors
+                // may go there
+                sf_cols_free = true;
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
+                float coef = 0.f;
+                if (which < 2) {
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const float2 f = unpack2(y[i]);
+                        ss = fmaf(f.x, f.x, ss);
+                        ss = fmaf(f.y, f.y, ss);
+                    }
+                    coef = rsqrtf(ss * (1.0f / 128.0f) + p.rope_eps);
+                }
+                const float* wn = colv + 2 * G_BN + which * 128;   // RMSNorm weights of q or k
+                const bool zero_row = p.rope_split && p.rope_attn_tokens > 0 && pos >= p.rope_attn_tokens;
+                const CUtensorMap* omap = !p.rope_split ? &tm_out : which == 0 ? &tm_rope.q : which == 1 ? &tm_rope.k : &tm_rope.v;
+                // rows of the slab in the output: in place, or (batch, token offset + position) of a token-major tensor
+                const int srow = m0 + q * 32;
+                const int orow = !p.rope_split ? srow
+                                               : (srow / p.rope_seq_len) * p.rope_tokens_pad + p.rope_token_offset + srow % p.rope_seq_len;
+                const int ocol = p.rope_split ? hcol : col0;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t o[32];
+                    if (which < 2) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {   // four pairs = 8 columns per step
+                            const float4 c4a = rc[j], s4a = rs[j];
+                            const float4 w0 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j);
+                            const float4 w1 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j + 4);
+                            const float2 p0 = unpack2(y[hh * 32 + 4 * j]), p1 = unpack2(y[hh * 32 + 4 * j + 1]);
+                            const float2 p2 = unpack2(y[hh * 32 + 4 * j + 2]), p3 = unpack2(y[hh * 32 + 4 * j + 3]);
+                            const float a0 = p0.x * (coef * w0.x), b0 = p0.y * (coef * w0.y);
+                            const float a1 = p1.x * (coef * w0.z), b1 = p1.y * (coef * w0.w);
+                            const float a2 = p2.x * (coef * w1.x), b2 = p2.y * (coef * w1.y);
+                            const float a3 = p3.x * (coef * w1.z), b3 = p3.y * (coef * w1.w);
+                            o[4 * j] = pack2(make_float2(a0 * c4a.x - b0 * s4a.x, a0 * s4a.x + b0 * c4a.x));
+                            o[4 * j + 1] = pack2(make_float2(a1 * c4a.y - b1 * s4a.y, a1 * s4a.y + b1 * c4a.y));
+                            o[4 * j + 2] = pack2(make_float2(a2 * c4a.z - b2 * s4a.z, a2 * s4a.z + b2 * c4a.z));
+                            o[4 * j + 3] = pack2(make_float2(a3 * c4a.w - b3 * s4a.w, a3 * s4a.w + b3 * c4a.w));
+                        }
+                        if (hh == 0) {   // the second half's table entries: in flight while this half is staged and stored
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                rc[j] = __ldg(cosr + 8 + j);
+                                rs[j] = __ldg(sinr + 8 + j);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = y[hh * 32 + i];
+                    }
+                    if (zero_row) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = 0u;
+                    }
+                    if (lane == 0) bulk_wait_group_read<0>();   // the store that last used this buffer has been read
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(my_buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                            make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (srow < p.M) tma_store_2d(omap, my_buf, ocol + hh * 64, orow);
+                        bulk_commit_group();
+                    }
+                }
+            }
 #pragma unroll 1
-            for (int h = 0; h < G_BN / 64; ++h) {
+            for (int h = 0; h < (ROPE ? 0 : G_BN / 64); ++h) {
                 if (n0 + h * 64 >= p.N || ABLATE(p, 0)) break;
                 if (SETS == 2 && ((h + ti) & 1) != eset) continue;   // the other warp of this quadrant takes it
                 uint32_t r0[32], r1[32];
@@ -1217,12 +1359,15 @@ int gemm_nvfp4_workspace_bytes(const svdq_gemm_args* a, size_t* bytes) {
     return SVDQ_OK;
 }
 
-template <int RTN, bool I4>
+template <int RTN, bool I4, bool ROPE = false>
 static int launch_pair(int grid, cudaStream_t stream, const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& la,
                         const CUtensorMap& lu, const CUtensorMap& o, const CUtensorMap& sfa, const CUtensorMap& sfb,
-                        const GemmParams& p) {
+                        const GemmParams& p, const RopeMaps* rope = nullptr) {
     static std::atomic<uint64_t> attr_done{0};
-    if (int rc = ensure_dynamic_smem(gemm_w4a4_kernel<RTN, I4>, smem_bytes<I4>(), attr_done)) return rc;
+    if (int rc = ensure_dynamic_smem(gemm_w4a4_kernel<RTN, I4, ROPE>, smem_bytes<I4>(), attr_done)) return rc;
+    RopeMaps rm;
+    if (rope) rm = *rope;
+    else rm.q = rm.k = rm.v = a;   // unused: any valid map
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);   // 2 CTAs per pair
     cfg.blockDim = dim3(cta_threads<RTN, I4>(), 1, 1);
@@ -1237,13 +1382,13 @@ static int launch_pair(int grid, cudaStream_t stream, const CUtensorMap& a, cons
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<RTN, I4>, a, b, la, lu, o, sfa, sfb, p));
+    SVDQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_w4a4_kernel<RTN, I4, ROPE>, a, b, la, lu, o, sfa, sfb, rm, p));
     return SVDQ_OK;
 }
 
 int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
     const bool requant = a->qout != nullptr;
-    SVDQ_CHECK_ARG(a->out != nullptr || requant, "gemm(nvfp4): neither `out` nor `qout` given");
+    SVDQ_CHECK_ARG(a->out != nullptr || requant || (a->rope_cos && a->rope_out_q), "gemm(nvfp4): neither `out` nor `qout` given");
     SVDQ_CHECK_ARG(a->act_layout == SVDQ_LAYOUT_NATIVE, "gemm(nvfp4): activations must be in SVDQ_LAYOUT_NATIVE "
                                                          "(convert with svdq_w4a4_relayout_act)");
     SVDQ_CHECK_ARG(!a->act_unsigned, "gemm(nvfp4): act_unsigned is INT4 only (gemm_w4a4_launch_impl.cuh:127)");
@@ -1332,6 +1477,42 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
             return rc;
     }
     int rc;
+    if (a->rope_cos != nullptr) {
+        // RMSNorm + rotary embedding of a fused QKV projection inside the epilogue
+        const int dim = a->rope_heads * 128;
+        const bool split = a->rope_out_q != nullptr;
+        if (kF16 || requant || a->activation != SVDQ_ACT_NONE || a->N != 3 * dim || n_out(a) != a->N || dim % G_BN != 0 ||
+            a->rope_seq_len <= 0 || a->rope_seq_len % 32 != 0 || a->M % a->rope_seq_len != 0 || (!split && a->out == nullptr))
+            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): this fused RMSNorm + RoPE epilogue is built for bf16, a plain QKV projection "
+                                              "with N = 3 * heads * 128 (heads even), rows = batch * seq_len and seq_len a multiple of 32");
+        SVDQ_CHECK_ARG(a->rope_sin && a->rope_norm_q && a->rope_norm_k && aligned(a->rope_cos, 16) && aligned(a->rope_sin, 16),
+                       "gemm(nvfp4): rope_sin, rope_norm_q, rope_norm_k are required; the tables must be 16-byte aligned");
+        p.rope_wq = static_cast<const h16*>(a->rope_norm_q);
+        p.rope_wk = static_cast<const h16*>(a->rope_norm_k);
+        p.rope_cos = a->rope_cos;
+        p.rope_sin = a->rope_sin;
+        p.rope_eps = a->rope_eps;
+        p.rope_seq_len = a->rope_seq_len;
+        p.rope_dim = dim;
+        p.rope_split = split ? 1 : 0;
+        p.rope_tokens_pad = a->rope_tokens_pad;
+        p.rope_token_offset = a->rope_token_offset;
+        p.rope_attn_tokens = a->rope_attn_tokens;
+        RopeMaps rm;
+        rm.q = rm.k = rm.v = tm_a;
+        if (split) {
+            SVDQ_CHECK_ARG(a->rope_out_k && a->rope_out_v && a->rope_tokens_pad >= a->rope_token_offset + a->rope_seq_len &&
+                               a->rope_token_offset >= 0,
+                           "gemm(nvfp4): split q / k / v outputs need all three tensors and tokens_pad >= token_offset + seq_len");
+            const uint64_t rows = static_cast<uint64_t>(a->M / a->rope_seq_len) * a->rope_tokens_pad;
+            void* outs[3] = {a->rope_out_q, a->rope_out_k, a->rope_out_v};
+            CUtensorMap* maps[3] = {&rm.q, &rm.k, &rm.v};
+            for (int i = 0; i < 3; ++i)
+                if (int rc = make_tmap_2d(maps[i], outs[i], SVDQ_TMAP_16, dim, rows, static_cast<uint64_t>(dim) * 2, 64, 32)) return rc;
+            p.store_out = 1;
+        }
+        return launch_pair<0, false, true>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p, &rm);
+    }
     if (!requant) return launch_pair<0, false>(2 * pl.npairs, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p);
     return launch_requant<false>(a, pl, stream, tm_a, tm_b, tm_la, tm_lu, tm_out, tm_sfa, tm_sfb, p, out_bf16);
 }

@@ -23,7 +23,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ..ops.fused import fused_gelu_mlp, layernorm_modulate, qk_norm_rope
+from ..ops.fused import fused_gelu_mlp, layernorm_modulate, qkv_proj_norm_rope
 from ..weights import quantize_linear
 from .linear import SVDQW4A4Linear
 from .random_init import random_w4a4_linear
@@ -128,18 +128,18 @@ class FluxJointBlock(nn.Module):
     @staticmethod
     def _qkv(lin, norm: QKNorm, x, heads, cos=None, sin=None, out=None, token_offset=0):
         """Fused projection, then RMSNorm of q and k per head.  With (cos, sin) of this stream's rows and a W4A4
-        projection the norm and the rotary embedding run as one kernel (and the caller skips its own); with ``out`` that
+        projection the norm and the rotary embedding run inside the projection's GEMM (and the caller skips its own); with ``out`` that
         kernel writes q, k, v straight into the attention's [B, S_total, C] buffers at ``token_offset``."""
         B, S, C = x.shape
-        qkv = _apply(lin, x)
         D = C // heads
         if cos is not None and isinstance(lin, SVDQW4A4Linear) and D == 128:
-            qkv = qk_norm_rope(qkv, norm.q.weight, norm.k.weight, cos.contiguous(), sin.contiguous(), heads, eps=1e-6,
-                               out=out, token_offset=token_offset)
+            qkv = qkv_proj_norm_rope(x, lin, norm.q.weight, norm.k.weight, cos.contiguous(), sin.contiguous(), heads, eps=1e-6,
+                                     out=out, token_offset=token_offset)
             if out is not None:
                 return None, None, None, True
             q, k, v = qkv.chunk(3, dim=-1)
             return q, k, v, True
+        qkv = _apply(lin, x)
         q, k, v = qkv.chunk(3, dim=-1)
         q = norm.q(q.reshape(B, S, heads, D)).reshape(B, S, C)
         k = norm.k(k.reshape(B, S, heads, D)).reshape(B, S, C)
@@ -167,12 +167,13 @@ class FluxJointBlock(nn.Module):
             attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads,
                               None if roped else cos, None if roped else sin, None)
         at, ai = attn[:, :T], attn[:, T:]
-        img = img + mi[2].unsqueeze(1) * _apply(self.out_img, ai.contiguous())
-        txt = txt + mt[2].unsqueeze(1) * _apply(self.out_txt, at.contiguous())
+        # gated residuals as one fused multiply-add pass each
+        img = torch.addcmul(img, mi[2].unsqueeze(1), _apply(self.out_img, ai.contiguous()))
+        txt = torch.addcmul(txt, mt[2].unsqueeze(1), _apply(self.out_txt, at.contiguous()))
         ni = _ln_mod(img, mi[4], mi[3], fused)
         nt = _ln_mod(txt, mt[4], mt[3], fused)
-        img = img + mi[5].unsqueeze(1) * self.mlp_img(ni)
-        txt = txt + mt[5].unsqueeze(1) * self.mlp_txt(nt)
+        img = torch.addcmul(img, mi[5].unsqueeze(1), self.mlp_img(ni))
+        txt = torch.addcmul(txt, mt[5].unsqueeze(1), self.mlp_txt(nt))
         return img, txt
 
 
@@ -194,7 +195,7 @@ class FluxSingleBlock(nn.Module):
         n = _ln_mod(x, m[1], m[0], fused)
         q, k, v, roped = FluxJointBlock._qkv(self.qkv, self.norm, n, self.heads, cos, sin)
         a = _attention(q, k, v, self.heads, None if roped else cos, None if roped else sin, None)
-        return x + m[2].unsqueeze(1) * (_apply(self.attn_out, a.contiguous()) + self.mlp(n))
+        return torch.addcmul(x, m[2].unsqueeze(1), _apply(self.attn_out, a.contiguous()).add_(self.mlp(n)))
 
 
 class FluxTransformer(nn.Module):

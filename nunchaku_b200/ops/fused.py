@@ -62,6 +62,37 @@ def fused_qkv_norm_rottary(x: torch.Tensor, proj, norm_q, norm_k, rotary_emb: to
     return output.view(batch_size, seq_len, -1)
 
 
+def qkv_proj_norm_rope(x: torch.Tensor, proj, weight_q: torch.Tensor, weight_k: torch.Tensor, cos: torch.Tensor,
+                       sin: torch.Tensor, heads: int, eps: float = 1e-6,
+                       out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None, token_offset: int = 0):
+    """Fused QKV projection of ``x`` [B, S, C] through the W4A4 layer ``proj`` with RMSNorm of q / k per 128-wide head and the
+    rotary embedding from plain tables (cos, sin fp32 [S, 64]): one quantiser launch and one GEMM whose epilogue does the
+    rest (a second row-wise kernel only for shapes the fused epilogue is not built for).  Returns the [B, S, 3*C'] tensor,
+    or None when ``out = (q, k, v)`` (token-major [B, S_total, heads*128] buffers filled from ``token_offset`` on)."""
+    B, S, C = x.shape
+    quantized_x, ascales, lora_act = proj.quantize(x.reshape(B * S, C))
+    tile = None if out is not None else torch.empty(B * S, proj.out_features, dtype=x.dtype, device=x.device)
+    svdq_gemm_w4a4_cuda(act=quantized_x, wgt=proj.qweight, out=tile, ascales=ascales, wscales=proj.wscales, lora_act_in=lora_act,
+                        lora_up=proj.proj_up, bias=proj.bias, fp4=proj.precision == "nvfp4", alpha=proj.wtscale,
+                        wcscales=proj.wcscales, norm_q=weight_q, norm_k=weight_k, rope_cos=cos, rope_sin=sin, rope_heads=heads,
+                        rope_eps=eps, rope_out=out, rope_token_offset=token_offset)
+    return None if tile is None else tile.view(B, S, -1)
+
+
+def unpack_rotemb(rotary_emb: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The reference's fragment-packed rotary tensor (``pack_rotemb``, nunchaku/models/embeddings.py:88-120) as plain
+    (cos, sin) tables fp32 [rows, 64]: for row m = 16 mb + 8 h + g and pair p = 4 j + t, {sin, cos} sit at
+    ((((mb*16 + j)*8 + g)*4 + t)*2 + h)*2.  Cached on the tensor (per version)."""
+    cached = rotary_emb.__dict__.get("_svdq_b200_tables")
+    if cached is not None and cached[0] == rotary_emb._version:
+        return cached[1], cached[2]
+    rows = rotary_emb.shape[0] * rotary_emb.shape[1]
+    t = rotary_emb.reshape(rows // 16, 16, 8, 4, 2, 2).permute(0, 4, 2, 1, 3, 5).reshape(rows, 64, 2)
+    sin, cos = t[..., 0].contiguous(), t[..., 1].contiguous()
+    rotary_emb.__dict__["_svdq_b200_tables"] = (rotary_emb._version, cos, sin)
+    return cos, sin
+
+
 def _norm_rope_packed(qkv, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn_tokens: int) -> None:
     """The RMSNorm + RoPE (+ head-major split) step of the QKV epilogue on the projection's bf16 tile ``qkv`` [rows, 3*dim],
     with the reference's packed rotary tensor [B_r, M_r, 128] (B_r * M_r rows; the table repeats over ``qkv``'s rows)."""

@@ -160,6 +160,54 @@ def relayout_act(codes, scales, lora_act, K: int, fp4: bool, from_layout: int, t
     return co, so, lo
 
 
+def _gemm_rope_tables(a, lib, prepared, dev, out, norm_q, norm_k, cos, sin, heads, eps, rope_out, token_offset, M_pad, N) -> bool:
+    """The QKV projection with RMSNorm + rotary embedding from plain (cos, sin) tables.  Returns True when done: either
+    inside the GEMM's epilogue, or (shapes the fused epilogue is not built for) by the GEMM into a tile followed by the
+    row-wise kernel."""
+    from .fused import qk_norm_rope
+
+    if norm_q is None or norm_k is None or sin is None or heads <= 0:
+        raise ValueError("rope_cos needs rope_sin, norm_q, norm_k and rope_heads")
+    require_cuda_contiguous("rope_cos", cos, (torch.float32,))
+    require_cuda_contiguous("rope_sin", sin, (torch.float32,))
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != 64 or N != 3 * heads * 128:
+        raise ValueError("rope tables must be fp32 [S, 64] and N = 3 * heads * 128")
+    S = cos.shape[0]
+    rows = a.M
+    if rope_out is not None:
+        for t in rope_out:
+            require_cuda_contiguous("rope_out", t, HALF_DTYPES)
+            if t.dim() != 3 or t.shape[2] != heads * 128 or t.shape[0] * S != rows or t.shape[1] < token_offset + S:
+                raise ValueError("rope_out tensors must be [rows / S, S_total >= token_offset + S, heads*128]")
+    elif out is None:
+        raise ValueError("rope_cos needs `out` or `rope_out`")
+    a.rope_norm_q, a.rope_norm_k = norm_q.data_ptr(), norm_k.data_ptr()
+    a.rope_cos, a.rope_sin = cos.data_ptr(), sin.data_ptr()
+    a.rope_eps, a.rope_seq_len, a.rope_heads = eps, S, heads
+    a.rope_attn_tokens = 0
+    if rope_out is not None:
+        a.rope_out_q, a.rope_out_k, a.rope_out_v = (t.data_ptr() for t in rope_out)
+        a.rope_tokens_pad, a.rope_token_offset = rope_out[0].shape[1], token_offset
+    else:
+        a.rope_out_q = a.rope_out_k = a.rope_out_v = None
+        a.rope_tokens_pad = a.rope_token_offset = 0
+    with on_device(dev):
+        try:
+            _lib.check(lib.svdq_gemm_w4a4(prepared.tls.ref, stream_ptr(dev)))
+            return True
+        except NotImplementedError:
+            pass
+        # not a shape of the fused epilogue: plain projection, then the row-wise kernel on its tile
+        a.rope_cos = None
+        tile = out
+        if tile is None:
+            tile = torch.empty(rows, N, dtype=rope_out[0].dtype, device=dev)
+            a.out = tile.data_ptr()
+        _lib.check(lib.svdq_gemm_w4a4(prepared.tls.ref, stream_ptr(dev)))
+        qk_norm_rope(tile, norm_q, norm_k, cos, sin, heads, eps=eps, out=rope_out, token_offset=token_offset)
+    return True
+
+
 def svdq_gemm_w4a4_cuda(
     act: torch.Tensor,
     wgt: torch.Tensor,
@@ -193,6 +241,12 @@ def svdq_gemm_w4a4_cuda(
     act_layout: int | None = None,
     out_layout: int | None = None,
     next_fp4: bool | None = None,
+    rope_cos: torch.Tensor | None = None,
+    rope_sin: torch.Tensor | None = None,
+    rope_heads: int = 0,
+    rope_eps: float = 1e-6,
+    rope_out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+    rope_token_offset: int = 0,
 ) -> None:
     """W4A4 GEMM with the fused SVDQuant epilogue; results are written in place.
 
@@ -211,6 +265,11 @@ def svdq_gemm_w4a4_cuda(
     * otherwise ``out`` with optional SiLU.
 
     ``act_layout`` / ``out_layout`` give the memory order of the incoming / produced activation tensors.
+
+    ``rope_cos`` / ``rope_sin`` (fp32 [S, 64], with ``norm_q`` / ``norm_k`` and ``rope_heads``) ask for the same RMSNorm +
+    rotary embedding from plain tables, computed inside the GEMM's epilogue when the shape allows (else by a second
+    kernel): into ``out`` [rows, 3*heads*128], or with ``rope_out = (q, k, v)`` into three token-major tensors
+    [rows / S, S_total, heads*128] from token ``rope_token_offset`` on.
     """
     if poolout is not None:
         raise NotImplementedError("poolout is unused by the reference launcher as well")
@@ -256,10 +315,10 @@ def svdq_gemm_w4a4_cuda(
         M = M_pad
         tmp_out = out = torch.empty(M_pad, N, dtype=torch.bfloat16, device=dev)   # the row-wise kernels are bf16 only
     else:
-        if out is None:
+        if out is None and rope_out is None:
             raise ValueError("either `out` or (`qout`, `oscales`) must be given")
         activation = _lib.ACT_SILU if fuse_silu else _lib.ACT_NONE
-        M = out.numel() // out.shape[-1]
+        M = out.numel() // out.shape[-1] if out is not None else rope_out[0].shape[0] * rope_cos.shape[0]
     if rope and (norm_q is None or norm_k is None):
         raise ValueError("rotary_emb needs norm_q and norm_k (gemm_w4a4_launch_impl.cuh:348-349)")
     if next_fp4 is None:
@@ -274,6 +333,7 @@ def svdq_gemm_w4a4_cuda(
         raise ValueError(f"the call's tensors are {half} but the layer's parameters are {prepared.half_dtype}")
 
     a = prepared.args()
+    a.rope_cos = None   # the struct is reused between calls
     a.dtype = dtype_code(half)
     a.act = act.data_ptr()
     a.ascales = ascales.data_ptr()
@@ -315,6 +375,15 @@ def svdq_gemm_w4a4_cuda(
     else:
         a.workspace = None
         a.workspace_bytes = 0
+    if rope and not packqkv and rope_cos is None and rotary_emb.dim() == 3 and rotary_emb.shape[2] == 128:
+        # the reference's packed rotary tensor, in place on `out`: same epilogue, tables unpacked once per tensor
+        from .fused import unpack_rotemb
+        rope_cos, rope_sin = unpack_rotemb(rotary_emb)
+        rope_heads, rope_eps, rope_out, rope_token_offset, rope = N // 384, 1e-6, None, 0, False
+    if rope_cos is not None:
+        if _gemm_rope_tables(a, lib, prepared, dev, out, norm_q, norm_k, rope_cos, rope_sin, rope_heads, rope_eps, rope_out,
+                             rope_token_offset, M_pad, N):
+            return
     with on_device(dev):
         _lib.check(lib.svdq_gemm_w4a4(prepared.tls.ref, stream_ptr(dev)))
         if requant and want_layout == _lib.LAYOUT_REFERENCE:

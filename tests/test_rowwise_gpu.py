@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+import helpers as H
 from nunchaku_b200 import _lib
 from oracle import svdq_ref as R
 
@@ -65,3 +66,45 @@ def test_litela_matches_oracle(B, S, heads):
     g32, e32 = got.float().cpu(), exp.float()
     assert R.rel_l2(g32, e32) <= 3e-3
     assert ((g32 - e32).abs() <= 2.0 ** -7 * e32.abs() + 1e-6).all()
+
+
+@pytest.mark.parametrize("B,S,heads,split", [(2, 64, 2, False), (1, 320, 4, True), (3, 96, 2, True),
+                                                 (2, 50, 2, True)])   # the last: not a shape of the fused epilogue (second kernel)
+def test_qkv_projection_with_norm_rope_in_the_gemm_epilogue(B, S, heads, split):
+    """RMSNorm + rotary embedding inside the QKV GEMM's epilogue (svdq_gemm_args.rope_*) against (a) the same projection
+    followed by the row-wise kernel and (b) the oracle on the GEMM's own bf16 tile.  The two GPU paths differ only in the
+    order of the 128 additions of the sum of squares, which can move a result by one bf16 ulp now and then."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops import qk_norm_rope, qkv_proj_norm_rope
+
+    C = heads * 128
+    torch.manual_seed(S + heads)
+    x = R.make_activations(B * S, C, seed=S)
+    lin = R.make_linear(C, 3 * C, 32, fp4=True, x_absmax=x.float().abs().amax(0), seed=S + 1, mode="svd", wcscales=True)
+    m = H.to_module(lin)
+    wq = (1.0 + 0.1 * torch.randn(128)).to(torch.bfloat16).cuda()
+    wk = (1.0 + 0.1 * torch.randn(128)).to(torch.bfloat16).cuda()
+    ang = torch.rand(S, 64) * 6.28
+    cos, sin = ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous()
+    xg = x.cuda().view(B, S, C)
+    tile = m(xg)                                                   # plain projection: the bf16 tile
+    off, S_total = 32, S + 64
+    if split:
+        outs = tuple(torch.full((B, S_total, C), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+        ref = tuple(torch.full((B, S_total, C), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+        assert qkv_proj_norm_rope(xg, m, wq, wk, cos, sin, heads, out=outs, token_offset=off) is None
+        qk_norm_rope(tile.clone(), wq, wk, cos, sin, heads, out=ref, token_offset=off)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0, 0)
+        for g, e in zip(outs, ref):
+            assert torch.isnan(g[:, :off].float()).all() and torch.isnan(g[:, off + S:].float()).all()   # nothing else written
+            _bf16_close(g[:, off:off + S].float().cpu(), e[:, off:off + S].float().cpu(), ulps=1.0, frac=0.9995)
+        got = torch.cat([t[:, off:off + S] for t in outs], dim=-1)
+    else:
+        got = qkv_proj_norm_rope(xg, m, wq, wk, cos, sin, heads)
+        ref = qk_norm_rope(tile.clone(), wq, wk, cos, sin, heads)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0, 0)
+        _bf16_close(got.float().cpu(), ref.float().cpu(), ulps=1.0, frac=0.9995)
+    exp = R.ref_qk_norm_rope(tile.cpu().view(B * S, 3 * C), wq.cpu(), wk.cpu(), cos.cpu(), sin.cpu(), heads)
+    _bf16_close(got.float().cpu().view(B * S, 3 * C), exp.float(), ulps=1.0, frac=0.999)
