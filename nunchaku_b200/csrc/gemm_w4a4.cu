@@ -965,41 +965,40 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const float4* cosr = reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64);
                 const float4* sinr = reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64);
                 uint32_t y[64];   // the head's 128 values of this row, packed
+                {
+                    uint32_t r[4][32];
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    uint32_t r0[32], r1[32];
-                    tc_ld_32x32b_x32(taddr + eset * 128 + hh * 64, r0);
-                    tc_ld_32x32b_x32(taddr + eset * 128 + hh * 64 + 32, r1);
+                    for (int i = 0; i < 4; ++i) tc_ld_32x32b_x32(taddr + eset * 128 + i * 32, r[i]);
                     tc_wait_ld();
-                    const float4* cs = reinterpret_cast<const float4*>(colv + eset * 128 + hh * 64);
-                    const float4* cb = reinterpret_cast<const float4*>(colv + G_BN + eset * 128 + hh * 64);
+                    // the accumulator's first columns (this warp's share of them) are in registers: the next tile's scale
+                    // factors may go there - said as early as possible, the MMA warp waits for it
+                    sf_cols_free = true;
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
+                    const float4* cs = reinterpret_cast<const float4*>(colv + eset * 128);
+                    const float4* cb = reinterpret_cast<const float4*>(colv + G_BN + eset * 128);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const uint32_t* r = j < 8 ? &r0[4 * j] : &r1[4 * (j - 8)];
+                    for (int j = 0; j < 32; ++j) {   // columns 4j .. 4j+3 of the head
+                        const uint32_t* rr = &r[j >> 3][4 * (j & 7)];
                         const float4 s4 = cs[j], b4 = cb[j];
-                        y[hh * 32 + 2 * j] = pack2(__ffma2_rn(make_float2(__uint_as_float(r[0]), __uint_as_float(r[1])),
-                                                              make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
-                        y[hh * 32 + 2 * j + 1] = pack2(__ffma2_rn(make_float2(__uint_as_float(r[2]), __uint_as_float(r[3])),
-                                                                  make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
+                        y[2 * j] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[0]), __uint_as_float(rr[1])),
+                                                    make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
+                        y[2 * j + 1] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[2]), __uint_as_float(rr[3])),
+                                                        make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
                     }
                 }
-                // the accumulator's first columns (this tile's share of them) are in registers: the next tile's scale factors
-                // may go there
-                sf_cols_free = true;
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
                 float coef = 0.f;
                 if (which < 2) {
-                    float ss = 0.f;
+                    float2 ss = make_float2(0.f, 0.f);   // even and odd columns apart (packed fp32 arithmetic)
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const float2 f = unpack2(y[i]);
-                        ss = fmaf(f.x, f.x, ss);
-                        ss = fmaf(f.y, f.y, ss);
+                        ss = __ffma2_rn(f, f, ss);
                     }
-                    coef = rsqrtf(ss * (1.0f / 128.0f) + p.rope_eps);
+                    coef = rsqrtf((ss.x + ss.y) * (1.0f / 128.0f) + p.rope_eps);
                 }
+                const float2 coef2 = make_float2(coef, coef);
                 const float* wn = colv + 2 * G_BN + which * 128;   // RMSNorm weights of q or k
                 const bool zero_row = p.rope_split && p.rope_attn_tokens > 0 && pos >= p.rope_attn_tokens;
                 const CUtensorMap* omap = !p.rope_split ? &tm_out : which == 0 ? &tm_rope.q : which == 1 ? &tm_rope.k : &tm_rope.v;
@@ -1017,16 +1016,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             const float4 c4a = rc[j], s4a = rs[j];
                             const float4 w0 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j);
                             const float4 w1 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j + 4);
-                            const float2 p0 = unpack2(y[hh * 32 + 4 * j]), p1 = unpack2(y[hh * 32 + 4 * j + 1]);
-                            const float2 p2 = unpack2(y[hh * 32 + 4 * j + 2]), p3 = unpack2(y[hh * 32 + 4 * j + 3]);
-                            const float a0 = p0.x * (coef * w0.x), b0 = p0.y * (coef * w0.y);
-                            const float a1 = p1.x * (coef * w0.z), b1 = p1.y * (coef * w0.w);
-                            const float a2 = p2.x * (coef * w1.x), b2 = p2.y * (coef * w1.y);
-                            const float a3 = p3.x * (coef * w1.z), b3 = p3.y * (coef * w1.w);
-                            o[4 * j] = pack2(make_float2(a0 * c4a.x - b0 * s4a.x, a0 * s4a.x + b0 * c4a.x));
-                            o[4 * j + 1] = pack2(make_float2(a1 * c4a.y - b1 * s4a.y, a1 * s4a.y + b1 * c4a.y));
-                            o[4 * j + 2] = pack2(make_float2(a2 * c4a.z - b2 * s4a.z, a2 * s4a.z + b2 * c4a.z));
-                            o[4 * j + 3] = pack2(make_float2(a3 * c4a.w - b3 * s4a.w, a3 * s4a.w + b3 * c4a.w));
+                            // (a, b) = y * (coef * w) as packed pairs; (a c - b s, a s + b c) = (a, b) * c + (-b s, a s)
+                            const float2 ab0 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j]), __fmul2_rn(coef2, make_float2(w0.x, w0.y)));
+                            const float2 ab1 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 1]), __fmul2_rn(coef2, make_float2(w0.z, w0.w)));
+                            const float2 ab2 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 2]), __fmul2_rn(coef2, make_float2(w1.x, w1.y)));
+                            const float2 ab3 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 3]), __fmul2_rn(coef2, make_float2(w1.z, w1.w)));
+                            const float2 t0 = __fmul2_rn(ab0, make_float2(c4a.x, c4a.x)), t1 = __fmul2_rn(ab1, make_float2(c4a.y, c4a.y));
+                            const float2 t2 = __fmul2_rn(ab2, make_float2(c4a.z, c4a.z)), t3 = __fmul2_rn(ab3, make_float2(c4a.w, c4a.w));
+                            o[4 * j] = pack2(make_float2(fmaf(-ab0.y, s4a.x, t0.x), fmaf(ab0.x, s4a.x, t0.y)));
+                            o[4 * j + 1] = pack2(make_float2(fmaf(-ab1.y, s4a.y, t1.x), fmaf(ab1.x, s4a.y, t1.y)));
+                            o[4 * j + 2] = pack2(make_float2(fmaf(-ab2.y, s4a.z, t2.x), fmaf(ab2.x, s4a.z, t2.y)));
+                            o[4 * j + 3] = pack2(make_float2(fmaf(-ab3.y, s4a.w, t3.x), fmaf(ab3.x, s4a.w, t3.y)));
                         }
                         if (hh == 0) {   // the second half's table entries: in flight while this half is staged and stored
 #pragma unroll
