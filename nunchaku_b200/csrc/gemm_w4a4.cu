@@ -95,7 +95,7 @@ constexpr int G_EPI_BYTES = 4 * 2 * G_EPI_BUF_BYTES;        // 4 warps x 2 buffe
 constexpr int G_COLV_FLOATS = 64;                           // INT4, per epilogue warp: 1/smooth_next of the chunk in hand
 constexpr int G_COLV_BYTES = 4 * G_COLV_FLOATS * 4;           // INT4: four epilogue warps
 // NVFP4: the tile's per-column constants, staged once per tile by a warp of its own: [scale | bias | 1/smooth_next] x G_BN floats
-constexpr int G_TILEC_BYTES = 3 * G_BN * 4;
+constexpr int G_TILEC_BYTES = 3 * G_BN * 4 + 512;   // ROPE variant: [scale | bias | RMSNorm weights of q, k (16-bit) | sums of squares]
 constexpr int G_SHARED_BYTES = 384;                           // barriers and flags (GemmShared)
 // INT4 variant (template parameter I4): a stage is 64 k of fp16 operands, the activation half converted from packed
 // codes by converter warps; the packed codes come through a small ring of their own.
@@ -183,6 +183,7 @@ struct GemmShared {
     uint64_t tempty[2];             // leader: accumulator drained (4 epilogue warps x 2 CTAs)
     uint64_t sfree[2];              // leader: the first G_TM_SF_COLS columns of the accumulator are in registers (all epilogue warps, both CTAs)
     uint64_t lfull[4][2], lempty[4][2];   // LoRA-down warps: staging buffer of (quadrant, epilogue set) holds a chunk / has been read
+    uint64_t xsum[4], xread[4];     // ROPE, per lane quadrant: both epilogue warps have written / read their sums of squares
     uint64_t cfull, cempty;         // NVFP4, each CTA: the tile's per-column constants are in shared memory / have been read by all epilogue warps
     uint64_t drain;
     uint32_t tmem_base;
@@ -411,6 +412,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         for (int i = 0; i < 8; ++i) {
             mbar_init(&sh->lfull[i >> 1][i & 1], 1);
             mbar_init(&sh->lempty[i >> 1][i & 1], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&sh->xsum[i], 2);
+            mbar_init(&sh->xread[i], 2);
         }
         mbar_init(&sh->cfull, 1);
         mbar_init(&sh->cempty, 4 * epi_sets<RTN, I4>());
@@ -775,8 +780,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (ti == 0) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            colv[2 * G_BN + lane + 32 * i] = h2f(p.rope_wq[lane + 32 * i]);
-                            colv[2 * G_BN + 128 + lane + 32 * i] = h2f(p.rope_wk[lane + 32 * i]);
+                            reinterpret_cast<h16*>(colv + 2 * G_BN)[lane + 32 * i] = p.rope_wq[lane + 32 * i];
+                            reinterpret_cast<h16*>(colv + 2 * G_BN)[128 + lane + 32 * i] = p.rope_wk[lane + 32 * i];
                         }
                     }
                 }
@@ -896,6 +901,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if constexpr (ELORA) store_lora_partial<RTN>(p, lacc, slot++, q, lane);
         };
         lacc_zero();
+        float4 rc[8], rs[8];   // ROPE: rotary table entries of this thread's row and this warp's 32 column pairs
+        int rope_m0 = -1;
+        uint32_t nx = 0;       // ROPE: exchanges of sums of squares so far
         const bool prof_me = blockIdx.x == 0 && (warp == (I4 ? 2 : 4)) && lane == 0;
         PROF_T0(pt_all);
         PROF_ACC(pa_tf); PROF_ACC(pa_tiles); PROF_ACC(pa_stage); PROF_ACC(pa_lora); PROF_ACC(pa_quant);
@@ -925,16 +933,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         nsm[h][i] = n < p.N ? p.next_smooth[(n & ~127) + packed_vec_pos(n & 127)] : f2h(1.0f);
                     }
             }
-            // ROPE: the rotary table entries of this thread's row (L2, one 512-byte line set per row) are asked for before the
-            // wait for the accumulator: first half of the head now, second half while the first is being stored
-            float4 rc[8], rs[8];
+            // ROPE: this warp takes columns [64 eset, 64 eset + 64) of both heads of every tile, i.e. always the same 32 column
+            // pairs of its rows: their rotary table entries (32 x (cos, sin) per thread, each lane another table row: 32
+            // cache lines per load instruction) are fetched once per row block and stay in registers for all its tiles.
             if constexpr (ROPE) {
-                const int pos = (m0 + q * 32 + lane) % p.rope_seq_len;
-                if (n0 + eset * 128 < 2 * p.rope_dim) {
+                if (m0 != rope_m0) {
+                    rope_m0 = m0;
+                    const int pos = (m0 + q * 32 + lane) % p.rope_seq_len;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        rc[j] = __ldg(reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64) + j);
-                        rs[j] = __ldg(reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64) + j);
+                        rc[j] = __ldg(reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64) + 8 * eset + j);
+                        rs[j] = __ldg(reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64) + 8 * eset + j);
                     }
                 }
             }
@@ -955,72 +964,82 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             bool sf_cols_free = I4;   // NVFP4: the accumulator's first columns become the next tile's scale-factor buffers
             bool epi_ok = true;
             if constexpr (ROPE) {
-                // This warp takes head `eset` of the tile (128 columns = two chunks) for its 32 rows: one row per thread, so
-                // the sum of squares needs no shuffle.  Values are rounded to the 16-bit type first and the norm and the
-                // rotation computed from those, exactly as a separate pass over the stored tile would.
-                const int col0 = n0 + eset * 128;               // first column of the head
-                const int which = col0 / p.rope_dim;            // 0: q, 1: k, 2: v
-                const int hcol = col0 - which * p.rope_dim;     // column inside q / k / v
+                // Both heads of the tile, one after the other; of each, this warp takes 64 columns (chunk `eset`) of its 32 rows,
+                // one row per thread.  Values are rounded to the 16-bit type first and the norm and the rotation computed from
+                // those, exactly as a separate pass over the stored tile would.  The two warps of a lane quadrant exchange their
+                // halves of the row's sum of squares through shared memory (named barrier of the pair).
                 const int pos = grow % p.rope_seq_len;          // token position of this thread's row
-                const float4* cosr = reinterpret_cast<const float4*>(p.rope_cos + static_cast<size_t>(pos) * 64);
-                const float4* sinr = reinterpret_cast<const float4*>(p.rope_sin + static_cast<size_t>(pos) * 64);
-                uint32_t y[64];   // the head's 128 values of this row, packed
-                {
-                    uint32_t r[4][32];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) tc_ld_32x32b_x32(taddr + eset * 128 + i * 32, r[i]);
-                    tc_wait_ld();
-                    // the accumulator's first columns (this warp's share of them) are in registers: the next tile's scale
-                    // factors may go there - said as early as possible, the MMA warp waits for it
-                    sf_cols_free = true;
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
-                    const float4* cs = reinterpret_cast<const float4*>(colv + eset * 128);
-                    const float4* cb = reinterpret_cast<const float4*>(colv + G_BN + eset * 128);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {   // columns 4j .. 4j+3 of the head
-                        const uint32_t* rr = &r[j >> 3][4 * (j & 7)];
-                        const float4 s4 = cs[j], b4 = cb[j];
-                        y[2 * j] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[0]), __uint_as_float(rr[1])),
-                                                    make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
-                        y[2 * j + 1] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[2]), __uint_as_float(rr[3])),
-                                                        make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
-                    }
-                }
-                float coef = 0.f;
-                if (which < 2) {
-                    float2 ss = make_float2(0.f, 0.f);   // even and odd columns apart (packed fp32 arithmetic)
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const float2 f = unpack2(y[i]);
-                        ss = __ffma2_rn(f, f, ss);
-                    }
-                    coef = rsqrtf((ss.x + ss.y) * (1.0f / 128.0f) + p.rope_eps);
-                }
-                const float2 coef2 = make_float2(coef, coef);
-                const float* wn = colv + 2 * G_BN + which * 128;   // RMSNorm weights of q or k
                 const bool zero_row = p.rope_split && p.rope_attn_tokens > 0 && pos >= p.rope_attn_tokens;
-                const CUtensorMap* omap = !p.rope_split ? &tm_out : which == 0 ? &tm_rope.q : which == 1 ? &tm_rope.k : &tm_rope.v;
-                // rows of the slab in the output: in place, or (batch, token offset + position) of a token-major tensor
-                const int srow = m0 + q * 32;
+                const int srow = m0 + q * 32;                   // first row of the warp's slab
                 const int orow = !p.rope_split ? srow
                                                : (srow / p.rope_seq_len) * p.rope_tokens_pad + p.rope_token_offset + srow % p.rope_seq_len;
-                const int ocol = p.rope_split ? hcol : col0;
+                float* xss = colv + 2 * G_BN + 128 + q * 64;   // [set 2][lane 32] of this quadrant
+#pragma unroll 1
+                for (int hd = 0; hd < 2; ++hd) {
+                    const int hb = n0 + hd * 128;                   // first column of the head
+                    const int which = hb / p.rope_dim;              // 0: q, 1: k, 2: v
+                    const int ccol = hb - (p.rope_split ? which * p.rope_dim : 0) + eset * 64;   // output column of the chunk
+                    uint32_t y[32];   // the chunk's 64 values of this row, packed
+                    {
+                        uint32_t r0[32], r1[32];
+                        tc_ld_32x32b_x32(taddr + hd * 128 + eset * 64, r0);
+                        tc_ld_32x32b_x32(taddr + hd * 128 + eset * 64 + 32, r1);
+                        tc_wait_ld();
+                        if (hd == 0) {
+                            // columns [0, G_TM_SF_COLS) of this accumulator are in registers (this warp's share of them): the
+                            // MMA warp may overwrite them with the next tile's scale factors
+                            sf_cols_free = true;
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&sh->sfree[as]), 0));
+                        }
+                        const float4* cs = reinterpret_cast<const float4*>(colv + hd * 128 + eset * 64);
+                        const float4* cb = reinterpret_cast<const float4*>(colv + G_BN + hd * 128 + eset * 64);
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
+                        for (int j = 0; j < 16; ++j) {   // columns 4j .. 4j+3 of the chunk
+                            const uint32_t* rr = j < 8 ? &r0[4 * j] : &r1[4 * (j - 8)];
+                            const float4 s4 = cs[j], b4 = cb[j];
+                            y[2 * j] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[0]), __uint_as_float(rr[1])),
+                                                        make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
+                            y[2 * j + 1] = pack2(__ffma2_rn(make_float2(__uint_as_float(rr[2]), __uint_as_float(rr[3])),
+                                                            make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
+                        }
+                    }
                     uint32_t o[32];
-                    if (which < 2) {
+                    if (which < 2) {   // (uniform over the CTA: a tile lies inside q, k or v)
+                        float2 ss = make_float2(0.f, 0.f);   // even and odd columns apart (packed fp32 arithmetic)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float2 f = unpack2(y[i]);
+                            ss = __ffma2_rn(f, f, ss);
+                        }
+                        // the two warps of the quadrant exchange their halves of the sum (bounded waits, like everywhere else)
+                        if (nx > 0 && !wait_or_abort(&sh->xread[q], (nx - 1) & 1, sh, p.status, 33)) {   // last exchange's values have been read
+                            epi_ok = false;
+                            break;
+                        }
+                        xss[eset * 32 + lane] = ss.x + ss.y;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sh->xsum[q]);
+                        if (!wait_or_abort(&sh->xsum[q], nx & 1, sh, p.status, 34)) {
+                            epi_ok = false;
+                            break;
+                        }
+                        const float coef = rsqrtf((xss[lane] + xss[32 + lane]) * (1.0f / 128.0f) + p.rope_eps);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sh->xread[q]);
+                        ++nx;
+                        const float2 coef2 = make_float2(coef, coef);
+                        const uint32_t* wn = reinterpret_cast<const uint32_t*>(colv + 2 * G_BN) + which * 64 + eset * 32;   // 16-bit pairs
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {   // four pairs = 8 columns per step
                             const float4 c4a = rc[j], s4a = rs[j];
-                            const float4 w0 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j);
-                            const float4 w1 = *reinterpret_cast<const float4*>(wn + hh * 64 + 8 * j + 4);
+                            const uint4 w4 = *reinterpret_cast<const uint4*>(wn + 4 * j);
                             // (a, b) = y * (coef * w) as packed pairs; (a c - b s, a s + b c) = (a, b) * c + (-b s, a s)
-                            const float2 ab0 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j]), __fmul2_rn(coef2, make_float2(w0.x, w0.y)));
-                            const float2 ab1 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 1]), __fmul2_rn(coef2, make_float2(w0.z, w0.w)));
-                            const float2 ab2 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 2]), __fmul2_rn(coef2, make_float2(w1.x, w1.y)));
-                            const float2 ab3 = __fmul2_rn(unpack2(y[hh * 32 + 4 * j + 3]), __fmul2_rn(coef2, make_float2(w1.z, w1.w)));
+                            const float2 ab0 = __fmul2_rn(unpack2(y[4 * j]), __fmul2_rn(coef2, unpack2(w4.x)));
+                            const float2 ab1 = __fmul2_rn(unpack2(y[4 * j + 1]), __fmul2_rn(coef2, unpack2(w4.y)));
+                            const float2 ab2 = __fmul2_rn(unpack2(y[4 * j + 2]), __fmul2_rn(coef2, unpack2(w4.z)));
+                            const float2 ab3 = __fmul2_rn(unpack2(y[4 * j + 3]), __fmul2_rn(coef2, unpack2(w4.w)));
                             const float2 t0 = __fmul2_rn(ab0, make_float2(c4a.x, c4a.x)), t1 = __fmul2_rn(ab1, make_float2(c4a.y, c4a.y));
                             const float2 t2 = __fmul2_rn(ab2, make_float2(c4a.z, c4a.z)), t3 = __fmul2_rn(ab3, make_float2(c4a.w, c4a.w));
                             o[4 * j] = pack2(make_float2(fmaf(-ab0.y, s4a.x, t0.x), fmaf(ab0.x, s4a.x, t0.y)));
@@ -1028,16 +1047,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             o[4 * j + 2] = pack2(make_float2(fmaf(-ab2.y, s4a.z, t2.x), fmaf(ab2.x, s4a.z, t2.y)));
                             o[4 * j + 3] = pack2(make_float2(fmaf(-ab3.y, s4a.w, t3.x), fmaf(ab3.x, s4a.w, t3.y)));
                         }
-                        if (hh == 0) {   // the second half's table entries: in flight while this half is staged and stored
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                rc[j] = __ldg(cosr + 8 + j);
-                                rs[j] = __ldg(sinr + 8 + j);
-                            }
-                        }
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = y[hh * 32 + i];
+                        for (int i = 0; i < 32; ++i) o[i] = y[i];
                     }
                     if (zero_row) {
 #pragma unroll
@@ -1052,7 +1064,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (srow < p.M) tma_store_2d(omap, my_buf, ocol + hh * 64, orow);
+                        const CUtensorMap* omap = !p.rope_split ? &tm_out : which == 0 ? &tm_rope.q : which == 1 ? &tm_rope.k : &tm_rope.v;
+                        if (srow < p.M) tma_store_2d(omap, my_buf, ccol, orow);
                         bulk_commit_group();
                     }
                 }
@@ -1498,6 +1511,10 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         p.rope_tokens_pad = a->rope_tokens_pad;
         p.rope_token_offset = a->rope_token_offset;
         p.rope_attn_tokens = a->rope_attn_tokens;
+        // n-fastest tile order in contiguous runs: a pair stays on one row block for many tiles, whose rotary table entries
+        // its epilogue warps keep in registers
+        p.contiguous = 1;
+        p.run = pl.run;
         RopeMaps rm;
         rm.q = rm.k = rm.v = tm_a;
         if (split) {
