@@ -21,19 +21,55 @@ namespace svdq {
 
 constexpr int LA_HD = 32;
 constexpr int LA_WARPS = 8;
-constexpr int LA_U = 16;                         // tokens a warp has in flight
+constexpr int LA_SLAB = 16;                      // tokens per warp step = the k (phase 1) / m (phase 2) extent of one mma
 
+__device__ __forceinline__ void la_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void la_ldsm(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void la_ldsm_t(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+// max(x, 0) on two packed bf16 values
+__device__ __forceinline__ uint32_t la_relu2(uint32_t w) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&w), __floats2bfloat162_rn(0.f, 0.f));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint4 la_relu8(uint4 w) { return make_uint4(la_relu2(w.x), la_relu2(w.y), la_relu2(w.z), la_relu2(w.w)); }
+__device__ __forceinline__ uint32_t la_pack(float a, float b) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Both contractions run on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulation):
+//   phase 1  vk[r, c] = sum_tok Vx[tok, r] * relu(K)[tok, c]: M = r (Vx = V with a 33rd column of ones, which makes row 32 the
+//            column sums of relu(K)), N = c, K = tokens.  A warp walks slabs of 16 tokens; the [K_h | V_h] lines of a slab
+//            go through a 128B-swizzled tile of shared memory (relu applied on the way) and come back as fragments with
+//            transposed ldmatrix (both operands have the contraction index as their slow one).  Products of bf16 values are
+//            exact in fp32, so only the order of additions differs from the scalar formulation.
+//   phase 2  o[tok, j] = sum_i relu(Q)[tok, i] * vk[j, i]: M = tokens, N = j (33 -> five 8-column tiles), K = i.  vk is fp32:
+//            it enters as a bf16 high part plus a bf16 low part (two mma per tile; the split is exact to 2^-17).
 __global__ void __launch_bounds__(LA_WARPS * 32)
 litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, float* __restrict__ vk_out,
               int tokens, int heads, float eps, int mode) {
-    __shared__ __align__(16) float part[LA_WARPS][LA_HD + 1][LA_HD];   // 33.8 KB
+    __shared__ __align__(128) float part[LA_WARPS][LA_HD + 1][LA_HD];   // 33.8 KB; a warp's slice doubles as its staging tile
     __shared__ __align__(16) float vk[LA_HD + 1][LA_HD];
     const int h = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
     const int D = heads * LA_HD;
     const size_t pitch = static_cast<size_t>(3) * D;
     const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * tokens * pitch;
     const __nv_bfloat16* kv = base + D + 64 * h;
+    uint8_t* tile = reinterpret_cast<uint8_t*>(&part[warp][0][0]);   // 16 tokens x 128 B ([K | V]) or 16 x 64 B (Q)
+    const uint32_t tile_s = static_cast<uint32_t>(__cvta_generic_to_shared(tile));
     // mode 0: everything.  The reference does it in two launches, and the two halves exist on their own for callers
     // that follow it: mode 1 = what its GEMM epilogue leaves behind (vk, and relu(Q) as bf16 in `out`), mode 2 = its
     // vk_mul_q_kernel (reads relu(Q) from `out` and vk from `vk_out`, finishes `out` in place; qkv is not read).
@@ -42,137 +78,172 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
             vk[i >> 5][i & 31] = vk_out[(static_cast<size_t>(b) * heads + h) * (LA_HD + 1) * LA_HD + i];
         __syncthreads();
     } else {
-
-    // phase 1: a warp takes runs of LA_U consecutive tokens; lane = column c of K;
-    // acc[r] = sum over the warp's tokens of V[tok, r] * relu(K[tok, c]).  V goes through a warp-private fp32 slab of
-    // shared memory (it aliases the warp's slice of `part`, which is only written after the loop) and comes back as
-    // 16-byte broadcasts, four rows per load; LA_U loads per lane are in flight before the first use.
-    float acc[LA_HD + 1];
+        // ---------------------------------------------------------------- phase 1
+        float acc[3][4][4];   // [m-tile: r 0-15, 16-31, row 32 (+ padding)][n-tile: 8 columns c][fragment]
 #pragma unroll
-    for (int r = 0; r <= LA_HD; ++r) acc[r] = 0.f;
-    float (*vs)[LA_HD] = part[warp];   // [LA_U][32]
-    for (int t0 = warp * LA_U; t0 < tokens; t0 += LA_WARPS * LA_U) {
-        float kk[LA_U];
-        __nv_bfloat16 kraw[LA_U], vraw[LA_U];
+        for (int i = 0; i < 3; ++i)
 #pragma unroll
-        for (int u = 0; u < LA_U; ++u) {
-            const int t = t0 + u;
-            const __nv_bfloat16* p = kv + static_cast<size_t>(t < tokens ? t : t0) * pitch;
-            kraw[u] = p[lane];
-            vraw[u] = p[LA_HD + lane];
-        }
+            for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int u = 0; u < LA_U; ++u) {
-            const bool in = t0 + u < tokens;
-            kk[u] = in ? fmaxf(__bfloat162float(kraw[u]), 0.f) : 0.f;
-            vs[u][lane] = in ? __bfloat162float(vraw[u]) : 0.f;
-        }
-        __syncwarp();
+                for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+        // A fragment of the ones row: row g = 0 of the third m-tile is 1 for every token of the slab
+        const uint32_t one2 = g == 0 ? 0x3f803f80u : 0u;
+        const uint32_t ones[4] = {one2, 0u, one2, 0u};
+        // a lane brings 16-byte chunk (lane & 7) of the lines of tokens (lane >> 3) + 4 i
+        auto load_slab = [&](int t0, uint4 (&w)[4]) {
 #pragma unroll
-        for (int u = 0; u < LA_U; ++u) {
-#pragma unroll
-            for (int r4 = 0; r4 < LA_HD / 4; ++r4) {
-                const float4 v4 = *reinterpret_cast<const float4*>(&vs[u][4 * r4]);   // same address in every lane
-                acc[4 * r4 + 0] = fmaf(v4.x, kk[u], acc[4 * r4 + 0]);
-                acc[4 * r4 + 1] = fmaf(v4.y, kk[u], acc[4 * r4 + 1]);
-                acc[4 * r4 + 2] = fmaf(v4.z, kk[u], acc[4 * r4 + 2]);
-                acc[4 * r4 + 3] = fmaf(v4.w, kk[u], acc[4 * r4 + 3]);
+            for (int i = 0; i < 4; ++i) {
+                const int t = t0 + (lane >> 3) + 4 * i;
+                w[i] = t < tokens ? *reinterpret_cast<const uint4*>(kv + static_cast<size_t>(t) * pitch + (lane & 7) * 8) : make_uint4(0, 0, 0, 0);
             }
-            acc[LA_HD] += kk[u];
+        };
+        uint4 cur[4], nxt[4];
+        int t0 = warp * LA_SLAB;
+        if (t0 < tokens) load_slab(t0, cur);
+        for (; t0 < tokens; t0 += LA_WARPS * LA_SLAB) {
+            const int t1 = t0 + LA_WARPS * LA_SLAB;
+            if (t1 < tokens) load_slab(t1, nxt);   // in flight while this slab is multiplied
+            __syncwarp();                          // the previous slab's fragments have been read
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int tok = (lane >> 3) + 4 * i, c = lane & 7;   // chunks 0-3: K (relu), 4-7: V
+                *reinterpret_cast<uint4*>(tile + tok * 128 + ((c ^ (tok & 7)) << 4)) = c < 4 ? la_relu8(cur[i]) : cur[i];
+            }
+            __syncwarp();
+            // B fragments: relu(K) [tok][c], transposed loads: matrices (tok 0-7 | 8-15) x (c 8n..8n+7) for two n-tiles each
+            uint32_t bk[2][4];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int tok = (lane & 7) + ((lane >> 3) & 1) * 8, chunk = 2 * half + (lane >> 4);
+                la_ldsm_t(bk[half], tile_s + tok * 128 + ((chunk ^ (tok & 7)) << 4));
+            }
+            // A fragments: V [tok][r], transposed loads: matrices (tok 0-7, r lo) (tok 0-7, r hi) (tok 8-15, r lo) (tok 8-15, r hi)
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                uint32_t av[4];
+                const int tok = (lane & 7) + (lane >> 4) * 8, chunk = 4 + 2 * mt + ((lane >> 3) & 1);
+                la_ldsm_t(av, tile_s + tok * 128 + ((chunk ^ (tok & 7)) << 4));
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) la_mma(acc[mt][nt], av, bk[nt >> 1][2 * (nt & 1)], bk[nt >> 1][2 * (nt & 1) + 1]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) la_mma(acc[2][nt], ones, bk[nt >> 1][2 * (nt & 1)], bk[nt >> 1][2 * (nt & 1) + 1]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
         }
-        __syncwarp();
-    }
+        __syncwarp();   // the staging tile is about to become this warp's partial
 #pragma unroll
-    for (int r = 0; r <= LA_HD; ++r) part[warp][r][lane] = acc[r];
-    __syncthreads();
-    for (int i = threadIdx.x; i < (LA_HD + 1) * LA_HD; i += LA_WARPS * 32) {
-        const int r = i >> 5, c = i & 31;
-        float s = part[0][r][c];
+        for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int w = 1; w < LA_WARPS; ++w) s += part[w][r][c];   // fixed order
-        vk[r][c] = s;
-        if (vk_out) vk_out[(static_cast<size_t>(b) * heads + h) * (LA_HD + 1) * LA_HD + i] = s;
-    }
-    __syncthreads();
+            for (int nt = 0; nt < 4; ++nt) {
+                *reinterpret_cast<float2*>(&part[warp][16 * mt + g][8 * nt + 2 * t4]) = make_float2(acc[mt][nt][0], acc[mt][nt][1]);
+                *reinterpret_cast<float2*>(&part[warp][16 * mt + g + 8][8 * nt + 2 * t4]) = make_float2(acc[mt][nt][2], acc[mt][nt][3]);
+            }
+        if (g == 0) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                *reinterpret_cast<float2*>(&part[warp][LA_HD][8 * nt + 2 * t4]) = make_float2(acc[2][nt][0], acc[2][nt][1]);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < (LA_HD + 1) * LA_HD; i += LA_WARPS * 32) {
+            const int r = i >> 5, c = i & 31;
+            float s = part[0][r][c];
+#pragma unroll
+            for (int w = 1; w < LA_WARPS; ++w) s += part[w][r][c];   // fixed order
+            vk[r][c] = s;
+            if (vk_out) vk_out[(static_cast<size_t>(b) * heads + h) * (LA_HD + 1) * LA_HD + i] = s;
+        }
+        __syncthreads();
     }
     if (mode == 1) {   // relu(Q) of this head -> out, 16 bytes per thread and step
         for (int i = threadIdx.x; i < tokens * 4; i += LA_WARPS * 32) {
             const int t = i >> 2, j = i & 3;
             const uint4 w = reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h)[j];
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 r = __floats2bfloat162_rn(fmaxf(__uint_as_float(ww[e] << 16), 0.f),
-                                                               fmaxf(__uint_as_float(ww[e] & 0xffff0000u), 0.f));
-                o[e] = *reinterpret_cast<const uint32_t*>(&r);
-            }
-            reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)[j] = make_uint4(o[0], o[1], o[2], o[3]);
+            reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)[j] = la_relu8(w);
         }
         return;
     }
 
-    // phase 2: two tokens per thread (t and t + 256); q stays in registers, every vk row comes once as 16-byte
-    // broadcasts from shared memory and serves both tokens
-    auto load_q = [&](int t, float* q) {
-        const uint4* qp = mode == 2 ? reinterpret_cast<const uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)
-                                    : reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h);
+    // -------------------------------------------------------------------- phase 2
+    // B fragments of vk^T (column j = 8 n + g, rows i = 16 s + 2 t4 .. and + 8), high and low bf16 parts; the fifth n-tile
+    // holds row 32 (the denominator) in its column 0
+    uint32_t bh[5][2][2], bl[5][2][2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint4 w = qp[j];
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    for (int nt = 0; nt < 5; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                q[8 * j + 2 * i] = fmaxf(__uint_as_float(ww[i] << 16), 0.f);
-                q[8 * j + 2 * i + 1] = fmaxf(__uint_as_float(ww[i] & 0xffff0000u), 0.f);
+        for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int j = 8 * nt + g, i = 16 * ks + 8 * hh + 2 * t4;
+                float v0 = 0.f, v1 = 0.f;
+                if (j <= LA_HD) {
+                    v0 = vk[j][i];
+                    v1 = vk[j][i + 1];
+                }
+                const float h0 = __bfloat162float(__float2bfloat16_rn(v0)), h1 = __bfloat162float(__float2bfloat16_rn(v1));
+                bh[nt][ks][hh] = la_pack(h0, h1);
+                bl[nt][ks][hh] = la_pack(v0 - h0, v1 - h1);
+            }
+    for (int t0 = warp * LA_SLAB; t0 < tokens; t0 += LA_WARPS * LA_SLAB) {
+        // relu(Q) of 16 tokens -> 64-byte rows of the staging tile (16-byte chunk c of token tok at c ^ ((tok >> 1) & 3))
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int tok = (lane >> 2) + 8 * i, c = lane & 3, t = t0 + tok;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (t < tokens)
+                w = mode == 2 ? reinterpret_cast<const uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h)[c]
+                              : reinterpret_cast<const uint4*>(base + static_cast<size_t>(t) * pitch + LA_HD * h)[c];
+            *reinterpret_cast<uint4*>(tile + tok * 64 + ((c ^ ((tok >> 1) & 3)) << 4)) = la_relu8(w);
+        }
+        __syncwarp();
+        float o[5][4];
+#pragma unroll
+        for (int nt = 0; nt < 5; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t aq[4];   // matrices (tok 0-7, i lo) (tok 8-15, i lo) (tok 0-7, i hi) (tok 8-15, i hi) of this k-step
+            const int tok = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
+            la_ldsm(aq, tile_s + tok * 64 + ((c ^ ((tok >> 1) & 3)) << 4));
+#pragma unroll
+            for (int nt = 0; nt < 5; ++nt) {
+                la_mma(o[nt], aq, bh[nt][ks][0], bh[nt][ks][1]);
+                la_mma(o[nt], aq, bl[nt][ks][0], bl[nt][ks][1]);
             }
         }
-    };
-    for (int t = threadIdx.x; t < tokens; t += 2 * LA_WARPS * 32) {
-        const int t1 = t + LA_WARPS * 32;
-        const bool has1 = t1 < tokens;
-        float q0[LA_HD], q1[LA_HD];
-        load_q(t, q0);
-        load_q(has1 ? t1 : t, q1);
-        auto dot2 = [&](int row, float& s0, float& s1) {
-            const float4* vr = reinterpret_cast<const float4*>(vk[row]);
-            s0 = 0.f;
-            s1 = 0.f;
+        // the denominators of rows g and g + 8 sit in column 0 of the fifth tile: lanes with t4 == 0
+        const float den0 = __shfl_sync(0xffffffffu, o[4][0], lane & ~3) + eps;
+        const float den1 = __shfl_sync(0xffffffffu, o[4][2], lane & ~3) + eps;
+        const int ta = t0 + g, tb = t0 + g + 8;
+        // lane t4 of a quad holds columns 8 n + 2 t4 (+1) of every n-tile n; a 4 x 4 transpose of words inside the quad gives
+        // it the eight columns of n-tile t4 instead: one 16-byte store per row, 64 contiguous bytes per quad
+        uint32_t wa[4], wb[4];
 #pragma unroll
-            for (int i = 0; i < LA_HD / 4; ++i) {
-                const float4 v4 = vr[i];
-                s0 = fmaf(q0[4 * i], v4.x, s0);
-                s1 = fmaf(q1[4 * i], v4.x, s1);
-                s0 = fmaf(q0[4 * i + 1], v4.y, s0);
-                s1 = fmaf(q1[4 * i + 1], v4.y, s1);
-                s0 = fmaf(q0[4 * i + 2], v4.z, s0);
-                s1 = fmaf(q1[4 * i + 2], v4.z, s1);
-                s0 = fmaf(q0[4 * i + 3], v4.w, s0);
-                s1 = fmaf(q1[4 * i + 3], v4.w, s1);
+        for (int nt = 0; nt < 4; ++nt) {
+            wa[nt] = la_pack(__fdividef(o[nt][0], den0), __fdividef(o[nt][1], den0));
+            wb[nt] = la_pack(__fdividef(o[nt][2], den1), __fdividef(o[nt][3], den1));
+        }
+        auto quad_transpose = [&](uint32_t (&w)[4]) {
+#pragma unroll
+            for (int d = 1; d <= 2; d <<= 1) {          // exchange across lane bit d
+                const bool up = (t4 & d) != 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (i & d) continue;                 // pairs (i, i + d)
+                    const uint32_t send = up ? w[i] : w[i + d];
+                    const uint32_t got = __shfl_xor_sync(0xffffffffu, send, d);
+                    if (up) w[i] = got; else w[i + d] = got;
+                }
             }
         };
-        float den0, den1;
-        dot2(LA_HD, den0, den1);
-        den0 += eps;
-        den1 += eps;
-        uint4* op0 = reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + t) * D + LA_HD * h);
-        uint4* op1 = reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + (has1 ? t1 : t)) * D + LA_HD * h);
-#pragma unroll 1
-        for (int j = 0; j < 4; ++j) {
-            uint32_t o0[4], o1[4];
-#pragma unroll
-            for (int i2 = 0; i2 < 4; ++i2) {
-                float a0, a1, b0, b1;
-                dot2(8 * j + 2 * i2, a0, a1);
-                dot2(8 * j + 2 * i2 + 1, b0, b1);
-                const __nv_bfloat162 p0 = __floats2bfloat162_rn(__fdividef(a0, den0), __fdividef(b0, den0));
-                const __nv_bfloat162 p1 = __floats2bfloat162_rn(__fdividef(a1, den1), __fdividef(b1, den1));
-                o0[i2] = *reinterpret_cast<const uint32_t*>(&p0);
-                o1[i2] = *reinterpret_cast<const uint32_t*>(&p1);
-            }
-            op0[j] = make_uint4(o0[0], o0[1], o0[2], o0[3]);
-            if (has1) op1[j] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-        }
+        quad_transpose(wa);
+        quad_transpose(wb);
+        if (ta < tokens)
+            *reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + ta) * D + LA_HD * h + 8 * t4) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+        if (tb < tokens)
+            *reinterpret_cast<uint4*>(out + (static_cast<size_t>(b) * tokens + tb) * D + LA_HD * h + 8 * t4) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
     }
 }
 
