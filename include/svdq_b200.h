@@ -256,6 +256,22 @@ typedef struct svdq_ln_modulate_args {
 int svdq_layernorm_modulate(const svdq_ln_modulate_args* args, void* stream);
 
 /*
+ * Gated residual of a DiT block: out = x + gate[batch] * (y (+ z)), bf16, one pass (x, y, z, out: [rows, cols]; gate
+ * [batches, gate_stride] with its first `cols` entries used, or NULL for 1; out may be x).  Like svdq_layernorm_modulate
+ * it has no counterpart in the reference's W4A4 path; provided for the block harness.
+ */
+typedef struct svdq_gate_residual_args {
+    const void* x;
+    const void* gate;         /* bf16 or NULL */
+    const void* y;
+    const void* z;            /* bf16 or NULL: a second addend inside the gate */
+    void* out;
+    int64_t rows, rows_per_batch, gate_stride;
+    int32_t cols;             /* multiple of 8 */
+} svdq_gate_residual_args;
+int svdq_gate_residual(const svdq_gate_residual_args* args, void* stream);
+
+/*
  * ReLU linear attention of SANA on the bf16 output of the fused QKV projection: per (batch, head)
  * vk = [V | 1]^T relu(K) over the tokens (fp32), then out = (relu(Q) vk^T)[:32] / ((relu(Q) vk^T)[32] + eps).
  * What the reference does in the QKV GEMM's epilogue plus a second kernel: EpilogueLiteLA and vk_mul_q_kernel,

@@ -171,6 +171,20 @@ class LnModulateArgs(Structure):
     ]
 
 
+class GateResidualArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p),
+        ("gate", c_void_p),
+        ("y", c_void_p),
+        ("z", c_void_p),
+        ("out", c_void_p),
+        ("rows", ctypes.c_int64),
+        ("rows_per_batch", ctypes.c_int64),
+        ("gate_stride", ctypes.c_int64),
+        ("cols", c_int32),
+    ]
+
+
 class LiteLAArgs(Structure):
     _fields_ = [
         ("qkv", c_void_p),
@@ -195,6 +209,7 @@ EXPORTS = {
     "svdq_w4a4_relayout_act": (c_int32, [POINTER(RelayoutArgs), c_void_p]),
     "svdq_qk_norm_rope": (c_int32, [POINTER(NormRopeArgs), c_void_p]),
     "svdq_layernorm_modulate": (c_int32, [POINTER(LnModulateArgs), c_void_p]),
+    "svdq_gate_residual": (c_int32, [POINTER(GateResidualArgs), c_void_p]),
     "svdq_litela": (c_int32, [POINTER(LiteLAArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),

@@ -23,7 +23,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ..ops.fused import fused_gelu_mlp, layernorm_modulate, qkv_proj_norm_rope
+from ..ops.fused import fused_gelu_mlp, gate_residual, layernorm_modulate, qkv_proj_norm_rope
 from ..weights import quantize_linear
 from .linear import SVDQW4A4Linear
 from .random_init import random_w4a4_linear
@@ -42,6 +42,13 @@ def _make_linear(in_f: int, out_f: int, precision: str | None, rank: int, device
 def _apply(lin, x: torch.Tensor) -> torch.Tensor:
     """x: [B, S, C] through either kind of linear."""
     return lin(x)
+
+
+def _gated(x, gate, y, z, fused: bool):
+    """x + gate[:, None] * (y (+ z)): one row-wise kernel on the W4A4 path, library ops for the bf16 twin."""
+    if fused and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return gate_residual(x.contiguous(), gate, y.contiguous(), None if z is None else z.contiguous())
+    return torch.addcmul(x, gate.unsqueeze(1), y if z is None else y + z)
 
 
 def rope_table(ids: torch.Tensor, axes_dim=(16, 56, 56), theta: float = 10000.0):
@@ -167,13 +174,13 @@ class FluxJointBlock(nn.Module):
             attn = _attention(torch.cat([qt, qi], 1), torch.cat([kt, ki], 1), torch.cat([vt, vi], 1), self.heads,
                               None if roped else cos, None if roped else sin, None)
         at, ai = attn[:, :T], attn[:, T:]
-        # gated residuals as one fused multiply-add pass each
-        img = torch.addcmul(img, mi[2].unsqueeze(1), _apply(self.out_img, ai.contiguous()))
-        txt = torch.addcmul(txt, mt[2].unsqueeze(1), _apply(self.out_txt, at.contiguous()))
+        # gated residuals: one pass each
+        img = _gated(img, mi[2], _apply(self.out_img, ai.contiguous()), None, fused)
+        txt = _gated(txt, mt[2], _apply(self.out_txt, at.contiguous()), None, fused)
         ni = _ln_mod(img, mi[4], mi[3], fused)
         nt = _ln_mod(txt, mt[4], mt[3], fused)
-        img = torch.addcmul(img, mi[5].unsqueeze(1), self.mlp_img(ni))
-        txt = torch.addcmul(txt, mt[5].unsqueeze(1), self.mlp_txt(nt))
+        img = _gated(img, mi[5], self.mlp_img(ni), None, fused)
+        txt = _gated(txt, mt[5], self.mlp_txt(nt), None, fused)
         return img, txt
 
 
@@ -195,7 +202,7 @@ class FluxSingleBlock(nn.Module):
         n = _ln_mod(x, m[1], m[0], fused)
         q, k, v, roped = FluxJointBlock._qkv(self.qkv, self.norm, n, self.heads, cos, sin)
         a = _attention(q, k, v, self.heads, None if roped else cos, None if roped else sin, None)
-        return torch.addcmul(x, m[2].unsqueeze(1), _apply(self.attn_out, a.contiguous()).add_(self.mlp(n)))
+        return _gated(x, m[2], _apply(self.attn_out, a.contiguous()), self.mlp(n), fused)
 
 
 class FluxTransformer(nn.Module):

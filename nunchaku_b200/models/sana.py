@@ -24,7 +24,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from ..ops.fused import layernorm_modulate, litela_attention
+from ..ops.fused import gate_residual, layernorm_modulate, litela_attention
 from ..ops.gemm import svdq_gemm_w4a4_cuda
 from ..ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda
 from .linear import SVDQW4A4Linear
@@ -167,6 +167,13 @@ def _ln_mod(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, fused: bo
     return F.layer_norm(x, x.shape[-1:], eps=1e-6) * (1 + scale.unsqueeze(1)) + shift.unsqueeze(1)
 
 
+def _gated(x, gate, y, fused: bool):
+    """x + gate[:, None] * y (gate None = 1): one row-wise kernel on the W4A4 path, library ops for the bf16 twin."""
+    if fused and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return gate_residual(x.contiguous(), gate, y.contiguous())
+    return x + y if gate is None else x + gate.unsqueeze(1) * y
+
+
 class SanaBlock(nn.Module):
     """SanaModel.cpp:215-320."""
 
@@ -182,10 +189,10 @@ class SanaBlock(nn.Module):
         m = (self.scale_shift_table[None] + t6.view(B, 6, C)).unbind(1)   # shift, scale, gate (attention), shift, scale, gate (MLP)
         fused = self.attn.qkv_proj.master is None
         n = _ln_mod(x, m[1], m[0], fused)
-        x = x + m[2].unsqueeze(1) * self.attn(n)
-        x = x + self.cross_attn(x, cond)
+        x = _gated(x, m[2], self.attn(n), fused)
+        x = _gated(x, None, self.cross_attn(x, cond), fused)
         n = _ln_mod(x, m[4], m[3], fused)
-        return x + m[5].unsqueeze(1) * self.ff(n, H, W)
+        return _gated(x, m[5], self.ff(n, H, W), fused)
 
 
 class SanaTransformer(nn.Module):

@@ -8,7 +8,7 @@ import torch
 CLASSES = (
     ("w4a4_gemm", ("gemm_w4a4_kernel", "lora_partial_reduce")),
     ("quantiser", ("quantize_fuse_lora",)),
-    ("rowwise", ("qk_norm_rope", "layernorm_modulate", "litela", "relayout", "retile")),
+    ("rowwise", ("qk_norm_rope", "layernorm_modulate", "litela", "gate_residual", "relayout", "retile", "int4_row_norm")),
     ("attention", ("flash", "fmha", "attention", "sdpa", "cudnn", "mha")),
 )
 

@@ -202,6 +202,31 @@ def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor
     return out
 
 
+def gate_residual(x: torch.Tensor, gate: torch.Tensor | None, y: torch.Tensor, z: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x + gate[:, None, :] * (y (+ z))`` for bf16 x, y, z [B, S, C] and a per-batch gate bf16 [B, C] (a view with unit column
+    stride is fine; None = 1): the gated residual after a projection, in one pass.  ``out`` defaults to a new tensor and may
+    be ``x``."""
+    require_cuda_contiguous("x", x, (torch.bfloat16,))
+    require_cuda_contiguous("y", y, (torch.bfloat16,))
+    require_cuda_contiguous("z", z, (torch.bfloat16,))
+    B, S, C = x.shape
+    if y.shape != x.shape or (z is not None and z.shape != x.shape) or C % 8:
+        raise ValueError("gate_residual: x, y, z must be [B, S, C] with C a multiple of 8")
+    stride = 0
+    if gate is not None:
+        if gate.shape != (B, C) or gate.stride(1) != 1 or gate.dtype != torch.bfloat16 or not gate.is_cuda:
+            raise ValueError("gate_residual: gate must be a bf16 [B, C] view with unit column stride")
+        stride = gate.stride(0) if B > 1 else max(gate.stride(0), C)
+    if out is None:
+        out = torch.empty_like(x)
+    args = _lib.GateResidualArgs(x=ptr(x), gate=None if gate is None else gate.data_ptr(), y=ptr(y), z=ptr(z), out=ptr(out),
+                                 rows=B * S, rows_per_batch=S, gate_stride=stride, cols=C)
+    with on_device(x.device):
+        _lib.check(_lib.load().svdq_gate_residual(ctypes.byref(args), stream_ptr(x.device)))
+    return out
+
+
 def litela_attention(qkv: torch.Tensor, heads: int, eps: float = 1e-6, return_vk: bool = False):
     """ReLU linear attention of SANA on the bf16 output of the fused QKV projection (what ``EpilogueLiteLA`` in the QKV
     GEMM plus ``linearattn_vk_mul_q`` compute for ``SanaLinearAttention::forward``, ``src/SanaModel.cpp:25-106``).

@@ -47,6 +47,7 @@ def test_struct_layout_matches_c(lib, tmp_path):
         "svdq_relayout_args": lib.RelayoutArgs,
         "svdq_norm_rope_args": lib.NormRopeArgs,
         "svdq_ln_modulate_args": lib.LnModulateArgs,
+        "svdq_gate_residual_args": lib.GateResidualArgs,
         "svdq_litela_args": lib.LiteLAArgs,
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]

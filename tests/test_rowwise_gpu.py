@@ -108,3 +108,21 @@ def test_qkv_projection_with_norm_rope_in_the_gemm_epilogue(B, S, heads, split):
         _bf16_close(got.float().cpu(), ref.float().cpu(), ulps=1.0, frac=0.9995)
     exp = R.ref_qk_norm_rope(tile.cpu().view(B * S, 3 * C), wq.cpu(), wk.cpu(), cos.cpu(), sin.cpu(), heads)
     _bf16_close(got.float().cpu().view(B * S, 3 * C), exp.float(), ulps=1.0, frac=0.999)
+
+
+@pytest.mark.parametrize("B,S,C,with_z,with_gate", [(2, 70, 256, False, True), (3, 50, 2240, True, True), (1, 333, 3072, False, False)])
+def test_gate_residual_matches_torch(B, S, C, with_z, with_gate):
+    from nunchaku_b200.ops import gate_residual
+
+    g = torch.Generator().manual_seed(C + S)
+    x, y, z = (torch.randn(B, S, C, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    mod = torch.randn(B, 6 * C, generator=g).to(torch.bfloat16).cuda()
+    gate = mod.chunk(6, dim=-1)[2] if with_gate else None          # a strided view, as the blocks pass it
+    got = gate_residual(x, gate, y, z if with_z else None)
+    gf = gate.float().unsqueeze(1) if with_gate else 1.0
+    exp = x.float() + gf * (y.float() + (z.float() if with_z else 0.0))
+    assert _lib.device_status() == (0, 0)
+    _bf16_close(got.float().cpu(), exp.cpu(), ulps=0.51, frac=1.0)     # fp32 arithmetic, one rounding
+    # in place on x
+    x2 = x.clone()
+    assert gate_residual(x2, gate, y, z if with_z else None, out=x2) is x2 and torch.equal(x2, got)
