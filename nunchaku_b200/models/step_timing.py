@@ -6,9 +6,9 @@ from __future__ import annotations
 import torch
 
 CLASSES = (
-    ("w4a4_gemm", ("gemm_w4a4_kernel", "lora_partial_reduce")),
+    ("w4a4_gemm", ("gemm_w4a4_kernel", "lora_partial_reduce", "int4_row_norm")),
     ("quantiser", ("quantize_fuse_lora",)),
-    ("rowwise", ("qk_norm_rope", "layernorm_modulate", "litela", "gate_residual", "relayout", "retile", "int4_row_norm")),
+    ("rowwise", ("qk_norm_rope", "layernorm_modulate", "litela", "gate_residual", "relayout", "retile")),
     ("attention", ("flash", "fmha", "attention", "sdpa", "cudnn", "mha")),
 )
 
