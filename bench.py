@@ -201,9 +201,14 @@ def run_reference(args, rank):
 
 def event_times(fn_list, reps):
     """Average device time (ms) of each callable in ``fn_list`` run back to back ``reps`` times, one CUDA event between
-    every two launches (on torch's current stream, where the library launches)."""
+    every two launches (on torch's current stream, where the library launches).  ``reps`` launches are enqueued while the
+    stream is still busy with a delay kernel."""
     n = len(fn_list)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(reps)]
+    # The stream first gets some milliseconds of idle spinning, so that the host is many launches ahead when the timed kernels
+    # start: an interval between two events then never contains a wait for the next launch (on a busy host the enqueue of
+    # one pass, with its events, can take longer than the quantiser runs).
+    torch.cuda._sleep(int(2.5e7))
     for r in range(reps):
         ev[r][0].record()
         for i, fn in enumerate(fn_list):
@@ -280,8 +285,11 @@ def mlp_chain_config2(dev, peaks, fp4_peak, reps=30):
 
 def rowwise_kernels(dev, peaks, reps=20):
     """The row-wise kernels either side of the W4A4 linears against their algorithmic HBM bytes: RMSNorm + RoPE on a FLUX QKV
-    output [4608, 9216], LayerNorm + modulation on [4608, 3072], ReLU linear attention on a SANA QKV output [4, 1024, 6912]."""
-    from nunchaku_b200.ops import layernorm_modulate, litela_attention, qk_norm_rope
+    output [4608, 9216], LayerNorm + modulation and the gated residual on [4608, 3072], ReLU linear attention on a SANA QKV output
+    [4, 1024, 6912]; and the FLUX QKV projection (3072 -> 9216, NVFP4) with RMSNorm + RoPE inside the GEMM's epilogue against the
+    plain projection followed by the row-wise kernel."""
+    from nunchaku_b200.models.random_init import random_w4a4_linear
+    from nunchaku_b200.ops import gate_residual, layernorm_modulate, litela_attention, qk_norm_rope, qkv_proj_norm_rope
 
     g = torch.Generator(device=dev).manual_seed(0)
     bf = dict(device=dev, dtype=torch.bfloat16)
@@ -302,6 +310,16 @@ def rowwise_kernels(dev, peaks, reps=20):
     x = torch.randn(1, S, 3072, generator=g, **bf)
     sc, sh = torch.randn(1, 3072, generator=g, **bf) * 0.1, torch.randn(1, 3072, generator=g, **bf) * 0.1
     add("layernorm_modulate", lambda: layernorm_modulate(x, sc, sh), S * 3072 * 4, [S, 3072])
+    y = torch.randn(1, S, 3072, generator=g, **bf)
+    add("gate_residual", lambda: gate_residual(x, sc, y), S * 3072 * 6, [S, 3072])
+    proj = random_w4a4_linear(3072, 3 * heads * 128, R, "nvfp4", True, g, dev)
+    outs = tuple(torch.empty(1, S, heads * 128, **bf) for _ in range(3))
+    for _ in range(3):
+        qkv_proj_norm_rope(x, proj, w, w, cos, sin, heads, out=outs)
+    t_fused = event_times([lambda: qkv_proj_norm_rope(x, proj, w, w, cos, sin, heads, out=outs)], reps)[0] * 1e3
+    t_plain = event_times([lambda: proj(x)], reps)[0] * 1e3
+    res["qkv_projection_M4608"] = {"quantise_gemm_with_norm_rope_in_epilogue_us": t_fused, "quantise_gemm_plain_us": t_plain,
+                                   "separate_norm_rope_kernel_us": res["qk_norm_rope"]["us"]}
     B, T, lh = 4, 1024, 72
     q = torch.randn(B, T, 3 * lh * 32, generator=g, **bf)
     add("litela_attention", lambda: litela_attention(q, lh), B * T * lh * 32 * 8, [B, T, 3 * lh * 32])
