@@ -438,6 +438,9 @@ def main():
         sampler.start()
     D.barrier()
     torch.cuda.synchronize()
+    # a few milliseconds of idle spinning on the stream in front of the first event: the host is launches ahead when the
+    # clock starts, so its start-up latency (eight ranks share one host) is not in the interval
+    torch.cuda._sleep(int(1.0e7))
     t_host = time.perf_counter()
     e0.record()
     for _ in range(args.steps * inner):
