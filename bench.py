@@ -508,7 +508,12 @@ def main():
     # FP4 has no entry in MEASURED_PEAKS.json: measure the tensor-pipe peak here, on this GPU, with the
     # library's operand-resident tcgen05.mma loop (kind::mxf4nvf4, M128 N256 K64 per instruction).
     from nunchaku_b200.peak_probe import mma_rate
-    fp4_peak = mma_rate("mxf4nvf4", 256, iters=4000)["tflops"]
+    probe = mma_rate("mxf4nvf4", 256, iters=4000)
+    fp4_peak = probe["tflops"]
+    # The probe moves no data and runs near the maximum clock; the GEMM runs under the power cap (clocks.sm_mhz).  The same
+    # peak scaled to the clock the GEMM saw says how well the kernel uses the cycles it gets.
+    gemm_mhz = clocks["sm_mhz"] if clocks and clocks.get("sm_mhz") else None
+    peak_at_gemm_clock = fp4_peak * gemm_mhz / probe["sm_mhz"] if gemm_mhz else None
     gemm_tflops = FLOP_GEMM / (gemm_ms * 1e-3) / 1e12
     line = {
         "metric": METRIC, "value": world * FLOP_STEP / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
@@ -523,6 +528,8 @@ def main():
             "traffic_unit": "bytes per launch (dram read + write, one ncu capture of this workload)",
             "peak_source": "measured live: operand-resident tcgen05.mma kind::mxf4nvf4 M128 N256 K64 loop on all SMs "
                            "(burst; MEASURED_PEAKS.json has no FP4 entry); nominal dense FP4 is 9000",
+            "peak_probe_sm_mhz": probe["sm_mhz"], "peak_at_gemm_clock": peak_at_gemm_clock,
+            "frac_at_equal_clock": gemm_tflops / peak_at_gemm_clock if peak_at_gemm_clock else None,
             "frac_of_4x_bf16_measured": gemm_tflops / (4.0 * peaks["bf16_tflops"]), "bf16_peak_kind": peak_kind,
             "avg_launch_us": gemm_ms * 1e3, "launches_timed": launches,
             "quantizer": {"bound": "hbm", "achieved": QUANT_BYTES / (quant_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
@@ -545,9 +552,9 @@ def main():
             line["rowwise_kernels"] = rowwise_kernels(dev, peaks)
         D.barrier()
         from nunchaku_b200.models import flux_bench, sana_bench
-        line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2)
+        line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2, graph=True)
         torch.cuda.empty_cache()
-        line["sana_step"] = sana_bench.run(global_batch=32, reps=10, warmup=2)
+        line["sana_step"] = sana_bench.run(global_batch=32, reps=10, warmup=2, graph=True)
         torch.cuda.empty_cache()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1

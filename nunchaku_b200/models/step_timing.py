@@ -13,18 +13,22 @@ CLASSES = (
 )
 
 
-def timed_steps(step, reps: int, warmup: int) -> tuple[float, list[float]]:
+def timed_steps(step, reps: int, warmup: int, host: dict | None = None) -> tuple[float, list[float]]:
     """Runs ``step`` ``warmup`` + ``reps`` times; returns (trimmed mean ms: the 20 % fastest and slowest of the timed runs
     dropped, as the reference's script does, and the per-run times).  Every run is bracketed by its own pair of events;
-    nothing synchronises inside the timed sequence."""
+    nothing synchronises inside the timed sequence.  ``host``, when given, receives the host's enqueue time per step."""
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    import time
+    t0 = time.perf_counter()
     for a, b in ev:
         a.record()
         step()
         b.record()
+    if host is not None:   # how long the host needs to enqueue one step (the device lags behind while it does)
+        host["enqueue_ms_per_step"] = (time.perf_counter() - t0) * 1e3 / reps
     torch.cuda.synchronize()
     ts = sorted(a.elapsed_time(b) for a, b in ev)
     drop = int(len(ts) * 0.2)

@@ -26,10 +26,13 @@ def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_bu
     cyc = torch.zeros(grid * 2, dtype=torch.int64, device=dev)
     code, k = KINDS[kind]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for rep in range(2):
-        e0.record()
+    def launch():
         _lib.check(lib.svdq_probe_mma_rate(code, n, iters, cps_per_group, sf_buffers, grid, cyc.data_ptr(),
                                            torch.cuda.current_stream(dev).cuda_stream, sfb_step, int(commit_every), poll_warps))
+
+    for rep in range(2):
+        e0.record()
+        launch()
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
@@ -40,6 +43,7 @@ def mma_rate(kind: str, n: int, iters: int = 2000, cps_per_group: int = 0, sf_bu
         "commit_every": commit_every, "poll_warps": poll_warps,
         "cycles_per_mma_issue": c[0].item() / (4 * iters), "cycles_per_mma": c[1].item() / (4 * iters),
         "tflops": flops / (ms * 1e-3) / 1e12, "ms": ms,
+        "sm_mhz": c[1].item() / (ms * 1e3),   # SM clock during the loop: its cycles over its duration
     }
 
 
