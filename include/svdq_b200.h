@@ -292,6 +292,28 @@ typedef struct svdq_litela_args {
 int svdq_litela(const svdq_litela_args* args, void* stream);
 
 /*
+ * Softmax attention forward, 128-wide heads: out = softmax(scale * Q K^T) V per (batch, head), fp32 accumulation, the
+ * probabilities rounded to the 16-bit type before the second product.  Replaces attention_fp16
+ * (src/kernels/zgemm/attention.cu:10-96, bound at nunchaku/csrc/pybind.cpp:111, called from
+ * nunchaku/models/attention_processors/flux.py:167 and src/FluxModel.cpp:367,618,1063).  Every tensor is addressed as
+ * element (b, h, t, c) at b*stride[0] + h*stride[1] + t*stride[2] + c (strides in elements, multiples of 8): the
+ * reference's head-major [B, H, T, 128] inputs with its [B, T, H*128] output, or token-major buffers throughout.
+ * Token counts need not be multiples of the tile: rows past q_len are not written, keys past kv_len are masked.
+ */
+typedef struct svdq_attention_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];   /* batch, head, token */
+    int32_t batch, heads, q_len, kv_len;
+    int32_t head_dim;         /* 128 */
+    float scale;              /* head_dim ** -0.5 in the reference's callers */
+    int32_t dtype;            /* SVDQ_DTYPE_BF16 / SVDQ_DTYPE_FP16: q, k, v and out */
+} svdq_attention_args;
+int svdq_attention(const svdq_attention_args* args, void* stream);
+
+/*
  * Device-side status word of the current device: 0, or the SVDQ_ERR_TIMEOUT code a
  * kernel recorded when one of its bounded waits ran out.  Synchronises the device.
  * `detail` (may be NULL) receives a kernel-specific location code.  Reading clears it.

@@ -19,6 +19,7 @@ import types
 
 import torch
 
+from .ops.attention import attention_fp16 as _attention_fp16
 from .ops.gemm import svdq_gemm_w4a4_cuda as _gemm
 from .ops.quantize import svdq_quantize_w4a4_act_fuse_lora_cuda as _quantize
 
@@ -71,7 +72,8 @@ def _set_faster_i2f_mode(mode: str) -> None:
     _state["faster_i2f"] = str(mode)
 
 
-ops = types.SimpleNamespace(gemm_w4a4=_gemm_w4a4, quantize_w4a4_act_fuse_lora=_quantize_w4a4_act_fuse_lora)
+ops = types.SimpleNamespace(gemm_w4a4=_gemm_w4a4, quantize_w4a4_act_fuse_lora=_quantize_w4a4_act_fuse_lora,
+                            attention_fp16=_attention_fp16)
 utils = types.SimpleNamespace(set_log_level=_set_log_level, set_cuda_stack_limit=_set_cuda_stack_limit,
                               disable_memory_auto_release=_disable_memory_auto_release, trim_memory=_trim_memory,
                               set_faster_i2f_mode=_set_faster_i2f_mode)

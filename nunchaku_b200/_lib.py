@@ -185,6 +185,26 @@ class GateResidualArgs(Structure):
     ]
 
 
+class AttentionArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p),
+        ("k", c_void_p),
+        ("v", c_void_p),
+        ("out", c_void_p),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("k_stride", ctypes.c_int64 * 3),
+        ("v_stride", ctypes.c_int64 * 3),
+        ("o_stride", ctypes.c_int64 * 3),
+        ("batch", c_int32),
+        ("heads", c_int32),
+        ("q_len", c_int32),
+        ("kv_len", c_int32),
+        ("head_dim", c_int32),
+        ("scale", ctypes.c_float),
+        ("dtype", c_int32),
+    ]
+
+
 class LiteLAArgs(Structure):
     _fields_ = [
         ("qkv", c_void_p),
@@ -211,6 +231,7 @@ EXPORTS = {
     "svdq_layernorm_modulate": (c_int32, [POINTER(LnModulateArgs), c_void_p]),
     "svdq_gate_residual": (c_int32, [POINTER(GateResidualArgs), c_void_p]),
     "svdq_litela": (c_int32, [POINTER(LiteLAArgs), c_void_p]),
+    "svdq_attention": (c_int32, [POINTER(AttentionArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),
     "svdq_version": (c_int32, []),

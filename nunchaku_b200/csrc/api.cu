@@ -114,8 +114,8 @@ static EncodeTiledFn encode_tiled_fn() {
 // allocator hands back the same addresses) costs a hash and a compare instead of a driver call per map.
 struct TmapKey {
     const void* base;
-    uint64_t dims[3], strides[2];
-    uint32_t box[3];
+    uint64_t dims[4], strides[3];
+    uint32_t box[4];
     int32_t elem, rank, swizzle;
 };
 struct alignas(64) TmapEntry {
@@ -130,7 +130,8 @@ static int cached_tmap(CUtensorMap* out, const TmapKey& k) {
     if (!table) table = new TmapEntry[TMAP_CACHE_ENTRIES]();
     uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
     h ^= (k.dims[0] * 0xC2B2AE3D27D4EB4Full) ^ (k.dims[1] * 0x165667B19E3779F9ull) ^ (k.dims[2] << 17) ^ (k.strides[0] * 31) ^
-         (static_cast<uint64_t>(k.box[0]) << 40) ^ (static_cast<uint64_t>(k.box[1]) << 48) ^ (static_cast<uint64_t>(k.elem) << 56);
+         (static_cast<uint64_t>(k.box[0]) << 40) ^ (static_cast<uint64_t>(k.box[1]) << 48) ^ (static_cast<uint64_t>(k.elem) << 56) ^
+         (k.dims[3] << 29) ^ (k.strides[1] * 131) ^ (k.strides[2] * 8191);
     TmapEntry& e = table[(h >> 20) & (TMAP_CACHE_ENTRIES - 1)];
     if (e.valid && std::memcmp(&e.key, &k, sizeof(TmapKey)) == 0) {
         *out = e.map;
@@ -138,7 +139,7 @@ static int cached_tmap(CUtensorMap* out, const TmapKey& k) {
     }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SVDQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(&e.map, static_cast<CUtensorMapDataType>(k.elem), static_cast<cuuint32_t>(k.rank), const_cast<void*>(k.base),
                           k.dims, k.strides, k.box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           k.swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -177,6 +178,24 @@ int make_tmap_3d(CUtensorMap* map, const void* base, int elem, uint64_t d0, uint
     k.strides[0] = stride1_bytes; k.strides[1] = stride2_bytes;
     k.box[0] = box0; k.box[1] = box1; k.box[2] = box2;
     k.elem = elem; k.rank = 3; k.swizzle = 0;
+    return cached_tmap(map, k);
+}
+
+int make_tmap_nd(CUtensorMap* map, const void* base, int elem, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                 const uint32_t* box, bool swizzle128) {
+    SVDQ_CHECK_ARG(rank >= 2 && rank <= 4 && aligned(base, 16), "tensor map: rank 2..4 and a 16-byte aligned base");
+    TmapKey k;
+    std::memset(&k, 0, sizeof(k));
+    k.base = base;
+    for (int i = 0; i < rank; ++i) {
+        k.dims[i] = dims[i];
+        k.box[i] = box[i];
+        if (i + 1 < rank) {
+            SVDQ_CHECK_ARG(strides_bytes[i] % 16 == 0 && strides_bytes[i] > 0, "tensor map: strides must be positive multiples of 16 bytes");
+            k.strides[i] = strides_bytes[i];
+        }
+    }
+    k.elem = elem; k.rank = rank; k.swizzle = swizzle128 ? 1 : 0;
     return cached_tmap(map, k);
 }
 

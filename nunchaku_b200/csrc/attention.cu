@@ -1,0 +1,437 @@
+// Softmax attention forward for 128-wide heads on the tcgen05 tensor cores, sm_100a.
+//
+// What it computes (reference: attention_fp16, src/kernels/zgemm/attention.cu:10-96 and attention.cuh:226-330; called
+// from nunchaku/models/attention_processors/flux.py:160-185): per (batch, head)
+//   S = Q K^T,  P = exp2(S * scale*log2(e) - rowmax),  O = (P V) / rowsum(P)
+// with Q, K, V in a 16-bit type, S and O accumulated in fp32, P rounded to the 16-bit type before the second
+// product, as the reference does (it runs both products with mma.sync on fp16 fragments).  No mask, no dropout.
+// Q / K / V / O are addressed through (batch, head, token) strides with the 128 head channels contiguous, so the
+// reference's head-major [B, H, T, 128] inputs with its token-major [B, T, H*128] output and this library's all-token-major
+// buffers (written by the QKV projection's epilogue) are both plain cases.
+//
+// How it is laid out on a B200.  One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks
+// the keys in blocks of 128:
+//   warp 8      producer: TMA loads of Q (once) and of the K / V blocks into a 3-slot ring of 32 KB (128B swizzle);
+//   warp 9      MMA issuer: per tile and block S_t = Q_t K_j^T (8 x tcgen05.mma kind::f16 M128 N128 K16, both operands
+//               K-major) into TMEM, then O_t += P_t V_j (A = P_t from shared memory, B = V_j as it lies in memory, i.e.
+//               MN-major: no transposed copy of V is ever made);
+//   warps 0-7   (232 registers each, the others give theirs back) two softmax warpgroups, one per tile, one query row per thread: tcgen05.ld of the row of S, running
+//               maximum, exp2, row sum, P_t as 16-bit into a swizzled shared-memory tile, arrive.
+// The two tiles alternate on the tensor pipe: while one warpgroup is in its exponentials the issuer runs the other
+// tile's P V and the next Q K^T.  TMEM: S_0, S_1, O_0, O_1, 128 columns each (all 512).
+// Running maximum: O lives in TMEM and is only rescaled (tcgen05.ld / multiply / tcgen05.st by the tile's own
+// warpgroup, between two P V products) when some row's maximum has grown by more than 8 in the exponent since the
+// last rescale; until then the stale maximum is used for P and the row sum alike, which is exact algebra (the final
+// division cancels it) and keeps P <= 2^8.
+// Per key block and CTA: 4 x 8 MMAs = 2048 tensor-pipe cycles against 32768 exponentials on the 16-per-cycle
+// special-function unit = 2048 cycles: the kernel is balanced between the two when everything overlaps.
+//
+// Every wait is bounded; a role whose wait runs out records SVDQ_ERR_TIMEOUT and leaves its loop.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace svdq {
+
+constexpr int AT_D = 128;                  // head channels
+constexpr int AT_BM = 128;                 // query rows per tile (TMEM lanes)
+constexpr int AT_TILES = 2;                // tiles per CTA
+constexpr int AT_BN = 128;                 // keys per block
+constexpr int AT_HALF_BYTES = 128 * 128;   // one [128 rows x 64 x 16-bit] swizzled box
+constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;
+constexpr int AT_SLOTS = 3;                // K / V ring
+constexpr int AT_PRODUCER_WARP = 8, AT_MMA_WARP = 9;   // warps 10 and 11 only complete the third warpgroup
+constexpr int AT_THREADS = 12 * 32;
+constexpr int AT_REGS_SOFTMAX = 232, AT_REGS_OTHER = 40;   // 8 x 32 x 232 + 4 x 32 x 40 = 64512 of 65536 registers
+constexpr int AT_SMEM = 1024 + (2 * AT_TILES + AT_SLOTS) * AT_TILE_BYTES + 256;
+constexpr long long AT_WAIT_CYCLES = 600000000ll;   // ~0.3 s
+constexpr float AT_RESCALE_STEP = 8.f;
+
+struct AttnShared {
+    uint64_t q_full, kv_full[AT_SLOTS], kv_empty[AT_SLOTS], s_full[AT_TILES], p_full[AT_TILES], pv_done[AT_TILES];
+    uint32_t tmem_base;
+};
+
+struct AttnParams {
+    void* out;
+    long long o_stride_b, o_stride_h, o_stride_t;   // elements
+    int q_len, kv_len;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_t* bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], 16-bit operands, fp32 accumulation, one CTA.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulator, A and B of one 16-bit format (0 = fp16, 1 = bf16), A K-major,
+// B K-major or MN-major (bit 16).
+__host__ __device__ constexpr uint32_t idesc_h16(int M, int N, bool f16, bool b_mn_major) {
+    return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Shared-memory descriptor of an MN-major operand under the 128-byte swizzle: 64 consecutive MN elements (128 bytes)
+// per row, one row per K index, 8-row groups `sbo` bytes apart (stride byte offset), the next 64 MN elements `lbo`
+// bytes on (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(lbo >> 4) << 16;
+    d |= static_cast<uint64_t>(sbo >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_h16(float lo, float hi) {
+    uint32_t r;
+    if constexpr (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t at_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_s = smem;                                   // [tile][half]
+    uint8_t* p_s = q_s + AT_TILES * AT_TILE_BYTES;         // [tile][key half]
+    uint8_t* kv_s = p_s + AT_TILES * AT_TILE_BYTES;        // [slot][half]
+    AttnShared* sh = reinterpret_cast<AttnShared*>(kv_s + AT_SLOTS * AT_TILE_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int q0 = blockIdx.x * (AT_TILES * AT_BM);
+    const int head = blockIdx.y, batch = blockIdx.z;
+    const int nblocks = (p.kv_len + AT_BN - 1) / AT_BN;
+
+    if (tid == 0) {
+        mbar_init(&sh->q_full, 1);
+        for (int i = 0; i < AT_SLOTS; ++i) {
+            mbar_init(&sh->kv_full[i], 1);
+            mbar_init(&sh->kv_empty[i], 1);
+        }
+        for (int t = 0; t < AT_TILES; ++t) {
+            mbar_init(&sh->s_full[t], 1);
+            mbar_init(&sh->p_full[t], 4);
+            mbar_init(&sh->pv_done[t], 1);
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tm_q);
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+    }
+    if (warp == AT_MMA_WARP) {
+        tmem_alloc(&sh->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == AT_PRODUCER_WARP) {
+        reg_dealloc<AT_REGS_OTHER>();
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&sh->q_full, AT_TILES * AT_TILE_BYTES);
+            for (int t = 0; t < AT_TILES; ++t)
+                for (int h = 0; h < 2; ++h)
+                    tma_load_4d(q_s + t * AT_TILE_BYTES + h * AT_HALF_BYTES, &tm_q, &sh->q_full, h * 64, q0 + t * AT_BM, head, batch);
+            for (int i = 0; i < 2 * nblocks; ++i) {   // K_0, V_0, K_1, V_1, ...
+                const int slot = i % AT_SLOTS, use = i / AT_SLOTS;
+                if (!mbar_wait(&sh->kv_empty[slot], (use & 1) ^ 1, AT_WAIT_CYCLES)) {
+                    atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                    atomicExch(&p.status[1], 700 + slot);
+                    break;
+                }
+                mbar_arrive_expect_tx(&sh->kv_full[slot], AT_TILE_BYTES);
+                const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+                for (int h = 0; h < 2; ++h)
+                    tma_load_4d(kv_s + slot * AT_TILE_BYTES + h * AT_HALF_BYTES, tm, &sh->kv_full[slot], h * 64, (i >> 1) * AT_BN, head, batch);
+            }
+        }
+    } else if (warp == AT_MMA_WARP) {
+        reg_dealloc<AT_REGS_OTHER>();
+        // ------------------------------------------------------------------ MMA issuer (the whole warp walks the loop, lane 0 issues)
+        constexpr uint32_t IDESC_QK = idesc_h16(AT_BM, AT_BN, F16, false);
+        constexpr uint32_t IDESC_PV = idesc_h16(AT_BM, AT_D, F16, true);
+        const uint32_t q_u32 = smem_u32(q_s), p_u32 = smem_u32(p_s), kv_u32 = smem_u32(kv_s);
+        bool ok = true;
+        // S_t = Q_t K^T from ring slot `slot`: 8 k-steps of 16 channels, 32 bytes apart inside the swizzled 128-byte rows
+        auto issue_qk = [&](int t, int slot) {
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t off = (kk >> 2) * AT_HALF_BYTES + (kk & 3) * 32;
+                tc_mma_f16(tmem + t * AT_BN, smem_desc_sw128(q_u32 + t * AT_TILE_BYTES + off),
+                           smem_desc_sw128(kv_u32 + slot * AT_TILE_BYTES + off), IDESC_QK, kk > 0);
+            }
+        };
+        // O_t (+)= P_t V: 8 k-steps of 16 keys; V rows are keys, so a k-step is 16 rows = 2048 bytes further on
+        auto issue_pv = [&](int t, int slot, bool acc) {
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t aoff = (kk >> 2) * AT_HALF_BYTES + (kk & 3) * 32;
+                tc_mma_f16(tmem + 2 * AT_BN + t * AT_D, smem_desc_sw128(p_u32 + t * AT_TILE_BYTES + aoff),
+                           smem_desc_sw128_mn(kv_u32 + slot * AT_TILE_BYTES + kk * 2048, AT_HALF_BYTES, 1024), IDESC_PV,
+
+                           acc || kk > 0);
+            }
+        };
+        auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
+            if (!ok) return false;
+            if (!mbar_wait(bar, parity, AT_WAIT_CYCLES)) {
+                if (lane == 0) {
+                    atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                    atomicExch(&p.status[1], code);
+                }
+                ok = false;
+            }
+            return ok;
+        };
+        // ring item i (K_j: 2j, V_j: 2j + 1): slot i % 3, parity (i / 3) & 1
+        if (wait(&sh->q_full, 0, 710) && wait(&sh->kv_full[0], 0, 711)) {
+            tc_fence_after_sync();
+            if (lane == 0) {
+                issue_qk(0, 0);
+                tc_commit(&sh->s_full[0]);
+                issue_qk(1, 0);
+                tc_commit(&sh->s_full[1]);
+                tc_commit(&sh->kv_empty[0]);
+            }
+            __syncwarp();
+        }
+        for (int j = 0; j < nblocks && ok; ++j) {
+            const int iv = 2 * j + 1, ik = 2 * j + 2;
+            const int vslot = iv % AT_SLOTS, kslot = ik % AT_SLOTS;
+            const bool more = j + 1 < nblocks;
+            if (!wait(&sh->kv_full[vslot], (iv / AT_SLOTS) & 1, 720)) break;
+            for (int t = 0; t < AT_TILES; ++t) {
+                if (!wait(&sh->p_full[t], j & 1, 730 + t)) break;
+                if (more && t == 0 && !wait(&sh->kv_full[kslot], (ik / AT_SLOTS) & 1, 740)) break;
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    issue_pv(t, vslot, j > 0);
+                    tc_commit(&sh->pv_done[t]);
+                    if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[vslot]);
+                    if (more) {
+                        issue_qk(t, kslot);
+                        tc_commit(&sh->s_full[t]);
+                        if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[kslot]);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp > AT_MMA_WARP) {
+        reg_dealloc<AT_REGS_OTHER>();
+    } else {
+        reg_alloc<AT_REGS_SOFTMAX>();
+        // ------------------------------------------------------------------ softmax warpgroups: thread = one query row of tile t
+        const int t = warp >> 2, quad = warp & 3;
+        const int row = quad * 32 + lane;                       // row of the tile = TMEM lane
+        const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_addr + t * AT_BN;
+        const uint32_t o_tmem = tmem + lane_addr + 2 * AT_BN + t * AT_D;
+        uint8_t* p_row = p_s + t * AT_TILE_BYTES + row * 128;
+        const int rsw = row & 7;
+        float m_used = 0.f, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nblocks; ++j) {
+            if (!mbar_wait(&sh->s_full[t], j & 1, AT_WAIT_CYCLES)) {
+                if (lane == 0) {
+                    atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                    atomicExch(&p.status[1], 750 + t);
+                }
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            uint32_t s[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(s_tmem + c * 32, s[c]);
+            tc_wait_ld();
+            const int valid = p.kv_len - j * AT_BN;   // keys of this block that exist
+            if (valid < AT_BN) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i >= valid) s[c][i] = 0xff800000u;   // -inf
+            }
+            float mx = __uint_as_float(s[0][0]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            const float ms = mx * p.scale_log2;
+            if (j == 0) {
+                m_used = ms;
+            } else {
+                // P_t and O_t are read by the previous P V product until it has completed
+                if (!mbar_wait(&sh->pv_done[t], (j - 1) & 1, AT_WAIT_CYCLES)) {
+                    if (lane == 0) {
+                        atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                        atomicExch(&p.status[1], 760 + t);
+                    }
+                    ok = false;
+                    break;
+                }
+                const bool grow = ms > m_used + AT_RESCALE_STEP;
+                if (__any_sync(0xffffffffu, grow)) {
+                    tc_fence_after_sync();
+                    const float alpha = grow ? ex2(m_used - ms) : 1.f;
+                    if (grow) m_used = ms;
+                    l *= alpha;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tc_ld_32x32b_x32(o_tmem + c * 32, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tc_st_32x32b_x32(o_tmem + c * 32, o);
+                    }
+                    tc_wait_st();
+                }
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint8_t* dst = p_row + (c >> 1) * AT_HALF_BYTES;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {   // 8 keys = one 16-byte unit of the row
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = ex2(fmaf(__uint_as_float(s[c][u * 8 + 2 * e]), p.scale_log2, -m_used));
+                        const float b = ex2(fmaf(__uint_as_float(s[c][u * 8 + 2 * e + 1]), p.scale_log2, -m_used));
+                        sum += a + b;
+                        w[e] = pack_h16<F16>(a, b);
+                    }
+                    *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + u) ^ rsw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            l += sum;
+            fence_proxy_async_smem();   // P was written through the generic proxy, the MMA reads it through the async one
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->p_full[t]);
+        }
+        // ---- O_t / l -> global
+        if (ok && !mbar_wait(&sh->pv_done[t], (nblocks - 1) & 1, AT_WAIT_CYCLES)) {
+            if (lane == 0) {
+                atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                atomicExch(&p.status[1], 770 + t);
+            }
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const float inv = 1.f / l;
+            const int qrow = q0 + t * AT_BM + row;
+            uint8_t* orow = static_cast<uint8_t*>(p.out) +
+                            2 * (batch * p.o_stride_b + head * p.o_stride_h + static_cast<long long>(qrow) * p.o_stride_t);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tc_ld_32x32b_x32(o_tmem + c * 32, o);
+                tc_wait_ld();
+                if (qrow < p.q_len) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = pack_h16<F16>(__uint_as_float(o[u * 8 + 2 * e]) * inv, __uint_as_float(o[u * 8 + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 64 + u * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == AT_MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// 4-D tiled map (channel, token, head, batch) over a 16-bit tensor whose 128 channels are contiguous.
+static int attn_tmap(CUtensorMap* map, const void* base, int dtype, int batch, int heads, int tokens, const int64_t* stride) {
+    SVDQ_CHECK_ARG(stride[0] >= 0 && stride[1] > 0 && stride[2] >= AT_D && stride[0] % 8 == 0 && stride[1] % 8 == 0 && stride[2] % 8 == 0,
+                   "attention: strides must be multiples of 8 elements (16 bytes), the token stride at least 128");
+    const uint64_t dims[4] = {AT_D, static_cast<uint64_t>(tokens), static_cast<uint64_t>(heads), static_cast<uint64_t>(batch)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(stride[2]) * 2, static_cast<uint64_t>(stride[1]) * 2,
+                                 static_cast<uint64_t>(batch > 1 ? stride[0] : stride[1]) * 2};
+    const uint32_t box[4] = {64, AT_BN, 1, 1};
+    return make_tmap_nd(map, base, dtype == SVDQ_DTYPE_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                        dims, strides, box, true);
+}
+
+template <bool F16>
+static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid,
+                            cudaStream_t stream) {
+    auto kern = attention_fwd_kernel<F16>;
+    static std::atomic<uint64_t> attr_done{0};
+    if (int rc = ensure_dynamic_smem(kern, AT_SMEM, attr_done)) return rc;
+    kern<<<grid, AT_THREADS, AT_SMEM, stream>>>(tq, tk, tv, p);
+    SVDQ_CUDA(cudaGetLastError());
+    return SVDQ_OK;
+}
+
+}  // namespace svdq
+
+extern "C" int svdq_attention(const svdq_attention_args* a, void* stream) {
+    using namespace svdq;
+    SVDQ_CHECK_ARG(a != nullptr, "attention: null args");
+    SVDQ_CHECK_ARG(a->q && a->k && a->v && a->out, "attention: null tensor pointer");
+    SVDQ_CHECK_ARG(a->head_dim == AT_D, "attention: head_dim %d (only 128, as attention.cuh:13)", a->head_dim);
+    SVDQ_CHECK_ARG(a->batch > 0 && a->heads > 0 && a->q_len > 0 && a->kv_len > 0 && a->heads <= 65535 && a->batch <= 65535,
+                   "attention: bad sizes");
+    SVDQ_CHECK_ARG(a->dtype == SVDQ_DTYPE_BF16 || a->dtype == SVDQ_DTYPE_FP16, "attention: bad dtype %d", a->dtype);
+    SVDQ_CHECK_ARG(aligned(a->q, 16) && aligned(a->k, 16) && aligned(a->v, 16) && aligned(a->out, 16),
+                   "attention: tensors must be 16-byte aligned");
+    SVDQ_CHECK_ARG(a->o_stride[0] % 8 == 0 && a->o_stride[1] % 8 == 0 && a->o_stride[2] % 8 == 0,
+                   "attention: output strides must be multiples of 8 elements");
+    if (int rc = check_arch()) return rc;
+    CUtensorMap tq, tk, tv;
+    if (int rc = attn_tmap(&tq, a->q, a->dtype, a->batch, a->heads, a->q_len, a->q_stride)) return rc;
+    if (int rc = attn_tmap(&tk, a->k, a->dtype, a->batch, a->heads, a->kv_len, a->k_stride)) return rc;
+    if (int rc = attn_tmap(&tv, a->v, a->dtype, a->batch, a->heads, a->kv_len, a->v_stride)) return rc;
+    AttnParams p = {};
+    p.out = a->out;
+    p.o_stride_b = a->o_stride[0];
+    p.o_stride_h = a->o_stride[1];
+    p.o_stride_t = a->o_stride[2];
+    p.q_len = a->q_len;
+    p.kv_len = a->kv_len;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    if (int rc = status_words(&p.status)) return rc;
+    const dim3 grid((a->q_len + AT_TILES * AT_BM - 1) / (AT_TILES * AT_BM), a->heads, a->batch);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return a->dtype == SVDQ_DTYPE_FP16 ? launch_attention<true>(tq, tk, tv, p, grid, st) : launch_attention<false>(tq, tk, tv, p, grid, st);
+}

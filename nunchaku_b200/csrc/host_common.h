@@ -80,6 +80,11 @@ int make_tmap_2d(CUtensorMap* map, const void* base, int elem /*CUtensorMapDataT
 int make_tmap_3d(CUtensorMap* map, const void* base, int elem, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                  uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);
 
+// Tiled map of rank 2..4 (dimension 0 innermost and contiguous; `strides_bytes` for dimensions 1..rank-1, in any order of
+// magnitude); out-of-range boxes read zeros.
+int make_tmap_nd(CUtensorMap* map, const void* base, int elem, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                 const uint32_t* box, bool swizzle128);
+
 // Pointer / shape / alignment / architecture checks shared by the GEMM entry points.
 int check_gemm_common(const svdq_gemm_args* a);
 

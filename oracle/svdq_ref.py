@@ -385,3 +385,20 @@ def ref_litela(qkv: torch.Tensor, heads: int, eps: float = 1e-6):
     o = torch.einsum("bshc,bhrc->bshr", q, vk.float().double())                         # [B,S,H,33]
     out = (o[..., :32].float() / (o[..., 32:].float() + eps)).to(torch.bfloat16)
     return out.reshape(B, S, D), vk.float()
+
+
+def ref_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, round_p: bool = True) -> torch.Tensor:
+    """Softmax attention per (batch, head) on 16-bit q [B, H, Tq, D], k, v [B, H, Tkv, D] as the reference's kernel states it
+    (src/kernels/zgemm/attention.cuh:226-330, launcher attention.cu:10-96): S = q k^T in fp32, the scale folded with log2(e)
+    into an exp2 (``cuda_exp2(fmaf(val, scale, -rowmax_scaled))``), the row sum taken from the fp32 exponentials, the
+    exponentials rounded to the 16-bit type for the product with v, fp32 accumulation, one division by the row sum and one
+    rounding at the end.  The order of the block-wise running maximum is an implementation choice (it only moves the
+    rounding point of P by a power of two); here the row maximum is global.  Returns [B, Tq, H*D] in q's dtype."""
+    B, H, Tq, D = q.shape
+    s = (q.double() @ k.double().transpose(-1, -2)).float() * (scale * 1.4426950408889634)
+    p = torch.exp2(s - s.amax(dim=-1, keepdim=True))
+    l = p.double().sum(-1, keepdim=True)
+    if round_p:
+        p = p.to(q.dtype).float()
+    o = (p.double() @ v.double()) / l
+    return o.float().to(q.dtype).transpose(1, 2).reshape(B, Tq, H * D)

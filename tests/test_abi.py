@@ -49,6 +49,7 @@ def test_struct_layout_matches_c(lib, tmp_path):
         "svdq_ln_modulate_args": lib.LnModulateArgs,
         "svdq_gate_residual_args": lib.GateResidualArgs,
         "svdq_litela_args": lib.LiteLAArgs,
+        "svdq_attention_args": lib.AttentionArgs,
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, cls in structs.items():

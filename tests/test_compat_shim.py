@@ -29,6 +29,7 @@ def test_shim_signatures_follow_the_reference_binding():
 
     assert list(inspect.signature(_C.ops.gemm_w4a4).parameters) == GEMM_ARGS            # nunchaku/csrc/ops.h:10-38
     assert list(inspect.signature(_C.ops.quantize_w4a4_act_fuse_lora).parameters) == QUANT_ARGS   # ops.h:82-89
+    assert list(inspect.signature(_C.ops.attention_fp16).parameters) == ["q", "k", "v", "o", "scale"]   # ops.h:112-118
     for name in ("set_log_level", "set_cuda_stack_limit", "disable_memory_auto_release", "trim_memory", "set_faster_i2f_mode"):
         assert callable(getattr(_C.utils, name))                                           # pybind.cpp:118-123
     _C.utils.set_log_level("debug")

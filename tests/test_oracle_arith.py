@@ -119,3 +119,24 @@ def test_group_quantize_flags_rounding_ties():
     v[0, 2] = 2.75
     codes, scales, tie = R.group_quantize(v.to(torch.bfloat16), fp4=True)
     assert bool(tie[0, 1]) and not bool(tie[0, 2])
+
+
+def test_ref_attention_is_softmax_attention():
+    """The attention restatement against plain loops over rows (exact softmax in float64), and its one deliberate deviation:
+    probabilities rounded to the 16-bit type before the product with v (attention.cuh packs P as 16-bit fragments)."""
+    g = torch.Generator().manual_seed(4)
+    B, H, Tq, Tk = 1, 2, 5, 37
+    q = torch.randn(B, H, Tq, 128, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, H, Tk, 128, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H, Tk, 128, generator=g).to(torch.bfloat16)
+    scale = 128 ** -0.5
+    exact = R.ref_attention(q, k, v, scale, round_p=False)
+    rounded = R.ref_attention(q, k, v, scale)
+    for h in range(H):
+        for t in range(Tq):
+            s = (k[0, h].double() @ q[0, h, t].double()) * scale
+            p = torch.exp(s - s.max())
+            o = (p[:, None] * v[0, h].double()).sum(0) / p.sum()
+            assert torch.allclose(exact[0, t, 128 * h: 128 * h + 128].double(), o, rtol=2 ** -8, atol=1e-6)
+    assert R.rel_l2(rounded, exact) < 3e-3
+    assert R.ref_attention(q.half(), k.half(), v.half(), scale).dtype == torch.float16
