@@ -11,14 +11,16 @@
 //
 // How it is laid out on a B200.  One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks
 // the keys in blocks of 128:
-//   warp 8      producer: TMA loads of Q (once) and of the K / V blocks into a 3-slot ring of 32 KB (128B swizzle);
+//   warp 8      producer: TMA loads of Q (once) and of the K / V blocks into a 5-slot ring of 32 KB (128B swizzle);
 //   warp 9      MMA issuer: per tile and block S_t = Q_t K_j^T (8 x tcgen05.mma kind::f16 M128 N128 K16, both operands
-//               K-major) into TMEM, then O_t += P_t V_j (A = P_t from shared memory, B = V_j as it lies in memory, i.e.
+//               K-major) into TMEM, then O_t += P_t V_j (A = P_t from tensor memory, B = V_j as it lies in memory, i.e.
 //               MN-major: no transposed copy of V is ever made);
 //   warps 0-7   (232 registers each, the others give theirs back) two softmax warpgroups, one per tile, one query row per thread: tcgen05.ld of the row of S, running
-//               maximum, exp2, row sum, P_t as 16-bit into a swizzled shared-memory tile, arrive.
+//               maximum, exp2, row sum, P_t as packed 16-bit pairs over the first 64 columns of S_t (tcgen05.st), arrive.
 // The two tiles alternate on the tensor pipe: while one warpgroup is in its exponentials the issuer runs the other
 // tile's P V and the next Q K^T.  TMEM: S_0, S_1, O_0, O_1, 128 columns each (all 512).
+// Shared-memory bandwidth is the budget that shapes this: a 128 x 128 x 16 MMA with both operands in shared memory reads
+// 8 KB in its 64 cycles, all of the 128 bytes per cycle an SM has, so P goes through tensor memory (P V then reads V alone).
 // Running maximum: O lives in TMEM and is only rescaled (tcgen05.ld / multiply / tcgen05.st by the tile's own
 // warpgroup, between two P V products) when some row's maximum has grown by more than 8 in the exponent since the
 // last rescale; until then the stale maximum is used for P and the row sum alike, which is exact algebra (the final
@@ -41,16 +43,16 @@ constexpr int AT_TILES = 2;                // tiles per CTA
 constexpr int AT_BN = 128;                 // keys per block
 constexpr int AT_HALF_BYTES = 128 * 128;   // one [128 rows x 64 x 16-bit] swizzled box
 constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;
-constexpr int AT_SLOTS = 3;                // K / V ring
+constexpr int AT_SLOTS = 5;                // K / V ring
 constexpr int AT_PRODUCER_WARP = 8, AT_MMA_WARP = 9;   // warps 10 and 11 only complete the third warpgroup
 constexpr int AT_THREADS = 12 * 32;
 constexpr int AT_REGS_SOFTMAX = 232, AT_REGS_OTHER = 40;   // 8 x 32 x 232 + 4 x 32 x 40 = 64512 of 65536 registers
-constexpr int AT_SMEM = 1024 + (2 * AT_TILES + AT_SLOTS) * AT_TILE_BYTES + 256;
+constexpr int AT_SMEM = 1024 + (AT_TILES + AT_SLOTS) * AT_TILE_BYTES + 256;
 constexpr long long AT_WAIT_CYCLES = 600000000ll;   // ~0.3 s
 constexpr float AT_RESCALE_STEP = 8.f;
 
 struct AttnShared {
-    uint64_t q_full, kv_full[AT_SLOTS], kv_empty[AT_SLOTS], s_full[AT_TILES], p_full[AT_TILES], pv_done[AT_TILES];
+    uint64_t q_full, kv_full[AT_SLOTS], kv_empty[AT_SLOTS], s_full[AT_TILES], p_half[AT_TILES][2], pv_done[AT_TILES];
     uint32_t tmem_base;
 };
 
@@ -76,6 +78,17 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same with A in tensor memory: lane = row, every 32-bit column holds two consecutive K elements (the lower index in
+// the lower half), so a K-step of 16 is 8 columns.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -113,6 +126,35 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair of values on the FMA pipe instead of the special-function unit: x = n + f with n = rint(x) and f in
+// [-0.5, 0.5]; 2^f by a cubic (relative error 7.6e-5, a sixth of fp16's rounding step and a 25th of bf16's), n added to
+// the exponent field.  Adding 1.5 * 2^23 rounds x to an integer and leaves it in the low mantissa bits.  x is clamped
+// at -125 (the result is then ~2e-38 instead of less).
+__device__ __forceinline__ float2 exp2_fma2(float2 x) {
+    x.x = fmaxf(x.x, -125.f);
+    x.y = fmaxf(x.y, -125.f);
+    const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+    float2 r = __ffma2_rn(f, make_float2(0.05520550534129143f, 0.05520550534129143f), make_float2(0.24261397123336792f, 0.24261397123336792f));
+    r = __ffma2_rn(r, f, make_float2(0.6932547688484192f, 0.6932547688484192f));
+    r = __ffma2_rn(r, f, make_float2(0.9999276995658875f, 0.9999276995658875f));
+    return make_float2(__int_as_float(__float_as_int(r.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23)));
+}
+
+// Of the four pairs in every 8-key unit, this many take the FMA-pipe exponential (the rest ex2.approx): with all 32768
+// exponentials of a key block on the special-function unit it is busy for as long as the tensor pipe.
+#ifndef AT_POLY_PAIRS
+#define AT_POLY_PAIRS 0
+#endif
+
 template <bool F16>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -120,8 +162,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     extern __shared__ __align__(1024) uint8_t at_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_s = smem;                                   // [tile][half]
-    uint8_t* p_s = q_s + AT_TILES * AT_TILE_BYTES;         // [tile][key half]
-    uint8_t* kv_s = p_s + AT_TILES * AT_TILE_BYTES;        // [slot][half]
+    uint8_t* kv_s = q_s + AT_TILES * AT_TILE_BYTES;        // [slot][half]
     AttnShared* sh = reinterpret_cast<AttnShared*>(kv_s + AT_SLOTS * AT_TILE_BYTES);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -137,7 +178,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         for (int t = 0; t < AT_TILES; ++t) {
             mbar_init(&sh->s_full[t], 1);
-            mbar_init(&sh->p_full[t], 4);
+            mbar_init(&sh->p_half[t][0], 4);
+            mbar_init(&sh->p_half[t][1], 4);
             mbar_init(&sh->pv_done[t], 1);
         }
         fence_mbar_init();
@@ -180,7 +222,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // ------------------------------------------------------------------ MMA issuer (the whole warp walks the loop, lane 0 issues)
         constexpr uint32_t IDESC_QK = idesc_h16(AT_BM, AT_BN, F16, false);
         constexpr uint32_t IDESC_PV = idesc_h16(AT_BM, AT_D, F16, true);
-        const uint32_t q_u32 = smem_u32(q_s), p_u32 = smem_u32(p_s), kv_u32 = smem_u32(kv_s);
+        const uint32_t q_u32 = smem_u32(q_s), kv_u32 = smem_u32(kv_s);
         bool ok = true;
         // S_t = Q_t K^T from ring slot `slot`: 8 k-steps of 16 channels, 32 bytes apart inside the swizzled 128-byte rows
         auto issue_qk = [&](int t, int slot) {
@@ -190,15 +232,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                            smem_desc_sw128(kv_u32 + slot * AT_TILE_BYTES + off), IDESC_QK, kk > 0);
             }
         };
-        // O_t (+)= P_t V: 8 k-steps of 16 keys; V rows are keys, so a k-step is 16 rows = 2048 bytes further on
-        auto issue_pv = [&](int t, int slot, bool acc) {
-            for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t aoff = (kk >> 2) * AT_HALF_BYTES + (kk & 3) * 32;
-                tc_mma_f16(tmem + 2 * AT_BN + t * AT_D, smem_desc_sw128(p_u32 + t * AT_TILE_BYTES + aoff),
-                           smem_desc_sw128_mn(kv_u32 + slot * AT_TILE_BYTES + kk * 2048, AT_HALF_BYTES, 1024), IDESC_PV,
-
-                           acc || kk > 0);
-            }
+        // O_t (+)= P_t V: 8 k-steps of 16 keys; P_t sits in the first 64 columns of S_t (two keys per column); V rows are
+        // keys, so a k-step is 16 rows = 2048 bytes further on
+        auto issue_pv = [&](int t, int slot, bool acc, int hf) {
+            for (int kk = hf * 4; kk < hf * 4 + 4; ++kk)
+                tc_mma_f16_ts(tmem + 2 * AT_BN + t * AT_D, tmem + t * AT_BN + kk * 8,
+                              smem_desc_sw128_mn(kv_u32 + slot * AT_TILE_BYTES + kk * 2048, AT_HALF_BYTES, 1024), IDESC_PV, acc || kk > 0);
         };
         auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
             if (!ok) return false;
@@ -229,14 +268,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const bool more = j + 1 < nblocks;
             if (!wait(&sh->kv_full[vslot], (iv / AT_SLOTS) & 1, 720)) break;
             for (int t = 0; t < AT_TILES; ++t) {
-                if (!wait(&sh->p_full[t], j & 1, 730 + t)) break;
+                if (!wait(&sh->p_half[t][0], j & 1, 730 + t)) break;
                 if (more && t == 0 && !wait(&sh->kv_full[kslot], (ik / AT_SLOTS) & 1, 740)) break;
                 tc_fence_after_sync();
+                if (lane == 0) issue_pv(t, vslot, j > 0, 0);
+                __syncwarp();
+                if (!wait(&sh->p_half[t][1], j & 1, 735 + t)) break;
+                tc_fence_after_sync();
                 if (lane == 0) {
-                    issue_pv(t, vslot, j > 0);
+                    issue_pv(t, vslot, j > 0, 1);
                     tc_commit(&sh->pv_done[t]);
                     if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[vslot]);
-                    if (more) {
+                    if (more) {   // overwrites P_t: behind P V in the tensor pipe's order
                         issue_qk(t, kslot);
                         tc_commit(&sh->s_full[t]);
                         if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[kslot]);
@@ -255,10 +298,53 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
         const uint32_t s_tmem = tmem + lane_addr + t * AT_BN;
         const uint32_t o_tmem = tmem + lane_addr + 2 * AT_BN + t * AT_D;
-        uint8_t* p_row = p_s + t * AT_TILE_BYTES + row * 128;
-        const int rsw = row & 7;
         float m_used = 0.f, l = 0.f;
         bool ok = true;
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        // 64 keys (two 32-column chunks of S) -> 32 columns of packed 16-bit pairs, and their sum
+        auto exp_half = [&](const uint32_t (&a)[32], const uint32_t (&b)[32], float m, uint32_t (&w)[32]) {
+            const float2 nm2 = make_float2(-m, -m);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int e = (i & 15) * 2;
+                const float2 v = i < 16 ? make_float2(__uint_as_float(a[e]), __uint_as_float(a[e + 1]))
+                                        : make_float2(__uint_as_float(b[e]), __uint_as_float(b[e + 1]));
+                const float2 x = __ffma2_rn(v, sc2, nm2);
+                float2 r;
+                if ((i & 3) >= 4 - AT_POLY_PAIRS) {
+                    r = exp2_fma2(x);
+                } else {
+                    r.x = ex2(x.x);
+                    r.y = ex2(x.y);
+                }
+                sum2[i & 1] = __fadd2_rn(sum2[i & 1], r);
+                w[i] = pack_h16<F16>(r.x, r.y);
+            }
+            return (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+        };
+        auto max_half = [&](const uint32_t (&a)[32], const uint32_t (&b)[32]) {
+            float m0 = __uint_as_float(a[0]), m1 = __uint_as_float(b[0]);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                m0 = max3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+                m1 = max3(m1, __uint_as_float(b[i]), __uint_as_float(b[i + 1]));
+            }
+            return fmaxf(m0, m1);
+        };
+        auto mask = [&](uint32_t (&a)[32], int first, int valid) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (first + i >= valid) a[i] = 0xff800000u;   // -inf
+        };
+        // P half `hf` is complete in tensor memory: the issuer may run its four k-steps of P V
+        auto publish = [&](int hf, const uint32_t (&w)[32]) {
+            tc_st_32x32b_x32(s_tmem + hf * 32, w);   // over this thread's own S values, which are all in registers by now
+            tc_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->p_half[t][hf]);
+        };
         for (int j = 0; j < nblocks; ++j) {
             if (!mbar_wait(&sh->s_full[t], j & 1, AT_WAIT_CYCLES)) {
                 if (lane == 0) {
@@ -269,41 +355,42 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 break;
             }
             tc_fence_after_sync();
-            uint32_t s[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(s_tmem + c * 32, s[c]);
-            tc_wait_ld();
+            // The row of S arrives in two halves; the exponentials of the first are computed with the maximum in use while
+            // the second is still on its way, and only its (rare) growth by more than the step makes them be redone.
             const int valid = p.kv_len - j * AT_BN;   // keys of this block that exist
+            uint32_t s0[32], s1[32], s2[32], s3[32], w[32];
+            tc_ld_32x32b_x32(s_tmem, s0);
+            tc_ld_32x32b_x32(s_tmem + 32, s1);
+            tc_wait_ld();
+            tc_ld_32x32b_x32(s_tmem + 64, s2);
+            tc_ld_32x32b_x32(s_tmem + 96, s3);
             if (valid < AT_BN) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i >= valid) s[c][i] = 0xff800000u;   // -inf
+                mask(s0, 0, valid);
+                mask(s1, 32, valid);
             }
-            float mx = __uint_as_float(s[0][0]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            float mx = max_half(s0, s1);
+            float sum_a = exp_half(s0, s1, m_used, w);
+            tc_wait_ld();
+            if (valid < AT_BN) {
+                mask(s2, 64, valid);
+                mask(s3, 96, valid);
+            }
+            mx = fmaxf(mx, max_half(s2, s3));
             const float ms = mx * p.scale_log2;
-            if (j == 0) {
-                m_used = ms;
-            } else {
-                // P_t and O_t are read by the previous P V product until it has completed
-                if (!mbar_wait(&sh->pv_done[t], (j - 1) & 1, AT_WAIT_CYCLES)) {
-                    if (lane == 0) {
-                        atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
-                        atomicExch(&p.status[1], 760 + t);
+            const bool grow = j == 0 || ms > m_used + AT_RESCALE_STEP;
+            if (__any_sync(0xffffffffu, grow)) {
+                if (j > 0) {
+                    // O_t is written by the previous P V product until it has completed
+                    if (!mbar_wait(&sh->pv_done[t], (j - 1) & 1, AT_WAIT_CYCLES)) {
+                        if (lane == 0) {
+                            atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
+                            atomicExch(&p.status[1], 760 + t);
+                        }
+                        ok = false;
+                        break;
                     }
-                    ok = false;
-                    break;
-                }
-                const bool grow = ms > m_used + AT_RESCALE_STEP;
-                if (__any_sync(0xffffffffu, grow)) {
                     tc_fence_after_sync();
                     const float alpha = grow ? ex2(m_used - ms) : 1.f;
-                    if (grow) m_used = ms;
                     l *= alpha;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -316,29 +403,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     }
                     tc_wait_st();
                 }
-            }
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint8_t* dst = p_row + (c >> 1) * AT_HALF_BYTES;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {   // 8 keys = one 16-byte unit of the row
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float a = ex2(fmaf(__uint_as_float(s[c][u * 8 + 2 * e]), p.scale_log2, -m_used));
-                        const float b = ex2(fmaf(__uint_as_float(s[c][u * 8 + 2 * e + 1]), p.scale_log2, -m_used));
-                        sum += a + b;
-                        w[e] = pack_h16<F16>(a, b);
-                    }
-                    *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + u) ^ rsw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                if (grow) {
+                    m_used = ms;
+                    sum_a = exp_half(s0, s1, m_used, w);
                 }
             }
-            l += sum;
-            fence_proxy_async_smem();   // P was written through the generic proxy, the MMA reads it through the async one
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->p_full[t]);
+            publish(0, w);
+            const float sum_b = exp_half(s2, s3, m_used, w);
+            publish(1, w);
+            l += sum_a + sum_b;
         }
         // ---- O_t / l -> global
         if (ok && !mbar_wait(&sh->pv_done[t], (nblocks - 1) & 1, AT_WAIT_CYCLES)) {
