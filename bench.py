@@ -326,6 +326,31 @@ def rowwise_kernels(dev, peaks, reps=20):
     return res
 
 
+def attention_kernel(dev, peaks, reps=10, batch=8):
+    """The softmax attention of a FLUX block, [batch, 24, 4608, 128] bf16, token-major as the QKV projection's epilogue leaves it:
+    this library's tcgen05 kernel against the measured bf16 matmul peak (4 * B * H * T^2 * 128 flop), with torch's library
+    attention on the same tensors beside it."""
+    from nunchaku_b200.ops import attention
+
+    H_, T, D_ = 24, 4608, 128
+    g = torch.Generator(device=dev).manual_seed(3)
+    q, k, v = (torch.randn(batch, T, H_, D_, generator=g, device=dev).to(torch.bfloat16).transpose(1, 2) for _ in range(3))
+    out = torch.empty(batch, T, H_ * D_, device=dev, dtype=torch.bfloat16)
+    for _ in range(3):
+        attention(q, k, v, out=out)
+        torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    t_own = event_times([lambda: attention(q, k, v, out=out)], reps)[0]
+    t_lib = event_times([lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v)], reps)[0]
+    flop = 4.0 * batch * H_ * T * T * D_
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, T, H_ * D_).float()
+    rel = ((out.float() - ref).norm() / ref.norm()).item()
+    tf = flop / (t_own * 1e-3) / 1e12
+    return {"workload": f"softmax attention [{batch}, {H_}, {T}, {D_}] bf16, token-major", "kernel": "attention_fwd_kernel (tcgen05, TMEM)",
+            "us": t_own * 1e3, "tflops": tf, "frac_bf16_peak": tf / peaks["bf16_tflops"], "peak_bf16_tflops": peaks["bf16_tflops"],
+            "library_sdpa_us": t_lib * 1e3, "library_sdpa_tflops": flop / (t_lib * 1e-3) / 1e12, "rel_l2_vs_library": rel,
+            "launches_timed": reps}
+
+
 def reference_int4_kernels(dev):
     """The reference's own INT4 kernels (compiled from the reference tree into oracle/_ref, mma.sync, no sm_100 tuning)
     timed on this GPU on the same case as ``int4_config0``: a baseline beside the CPU port, not the product path."""
@@ -365,7 +390,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model-steps", action="store_true", help="skip the FLUX / SANA transformer-step legs and the INT4 case")
-    ap.add_argument("--only", default=None, choices=["mlp", "int4", "rowwise"],
+    ap.add_argument("--only", default=None, choices=["mlp", "int4", "rowwise", "attention"],
                     help="profiler captures: run just this leg (a few launches of it) and print its record")
     ap.add_argument("--shape", default=None, help="M,K,N override: a smaller case of the same path for profiler captures "
                     "(the default is the benchmark workload); implies --no-model-steps")
@@ -398,6 +423,8 @@ def main():
             rec = mlp_chain_config2(dev, peaks, 8500.0, reps=max(2, args.steps))
         elif args.only == "rowwise":
             rec = rowwise_kernels(dev, peaks, reps=max(2, args.steps))
+        elif args.only == "attention":   # one image: a capture-sized case of the same kernel
+            rec = attention_kernel(dev, peaks, reps=max(2, args.steps), batch=1)
         else:
             rec = int4_config0(dev, peaks)
         print(json.dumps(rec), flush=True)
@@ -550,6 +577,7 @@ def main():
             line["int4_config0"] = int4_config0(dev, peaks)
             line["mlp_chain_config2"] = mlp_chain_config2(dev, peaks, fp4_peak)
             line["rowwise_kernels"] = rowwise_kernels(dev, peaks)
+            line["attention"] = attention_kernel(dev, peaks)
         D.barrier()
         from nunchaku_b200.models import flux_bench, sana_bench
         line["flux_step"] = flux_bench.run(global_batch=8, reps=10, warmup=2, graph=True)

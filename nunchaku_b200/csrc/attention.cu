@@ -14,19 +14,29 @@
 //   warp 8      producer: TMA loads of Q (once) and of the K / V blocks into a 5-slot ring of 32 KB (128B swizzle);
 //   warp 9      MMA issuer: per tile and block S_t = Q_t K_j^T (8 x tcgen05.mma kind::f16 M128 N128 K16, both operands
 //               K-major) into TMEM, then O_t += P_t V_j (A = P_t from tensor memory, B = V_j as it lies in memory, i.e.
-//               MN-major: no transposed copy of V is ever made);
-//   warps 0-7   (232 registers each, the others give theirs back) two softmax warpgroups, one per tile, one query row per thread: tcgen05.ld of the row of S, running
-//               maximum, exp2, row sum, P_t as packed 16-bit pairs over the first 64 columns of S_t (tcgen05.st), arrive.
+//               MN-major: no transposed copy of V is ever made), in two halves of 64 keys as they are handed over.
+//               The whole warp walks the loop, one elected lane issues, descriptors are a constant upper half plus a
+//               lower half moved by immediates: with per-thread 64-bit descriptors the issue took 88 cycles per MMA
+//               against the 64 it runs;
+//   warps 0-7   two softmax warpgroups (232 registers each, the others give theirs back), one per tile, one query row
+//               per thread: tcgen05.ld of the row of S in two halves, running maximum, exp2, row sum, P_t as packed
+//               16-bit pairs over the row's own columns of S_t (tcgen05.st), arrive per half.
 // The two tiles alternate on the tensor pipe: while one warpgroup is in its exponentials the issuer runs the other
-// tile's P V and the next Q K^T.  TMEM: S_0, S_1, O_0, O_1, 128 columns each (all 512).
-// Shared-memory bandwidth is the budget that shapes this: a 128 x 128 x 16 MMA with both operands in shared memory reads
-// 8 KB in its 64 cycles, all of the 128 bytes per cycle an SM has, so P goes through tensor memory (P V then reads V alone).
+// tile's P V and next Q K^T.  TMEM: S_0, S_1, O_0, O_1, 128 columns each (all 512).
+// Two budgets shape this.  Shared-memory bandwidth: a 128 x 128 x 16 MMA with both operands in shared memory reads 8 KB
+// in its 64 cycles, all of the 128 bytes per cycle an SM has, so P goes through tensor memory (P V then reads V alone;
+// with P in shared memory the kernel ran at 1.06 against 1.19 PFLOP/s).  Latency: a tile's chain S -> exponentials ->
+// P -> P V -> next Q K^T -> S is serial (P lies over S, so the next Q K^T follows P V), and two tiles only half fill the
+// tensor pipe unless the softmax part is short: the exponentials of the first half are computed with the maximum in
+// use while the second half is still being loaded, a quarter of them on the FMA pipe (exp2_fma2), and the first half of
+// P is released to the issuer while the second is computed.  (Two threads per row, four softmax warpgroups, was slower:
+// the exchange of the half-row maxima through shared memory cost more than the halved chain gained.)
 // Running maximum: O lives in TMEM and is only rescaled (tcgen05.ld / multiply / tcgen05.st by the tile's own
 // warpgroup, between two P V products) when some row's maximum has grown by more than 8 in the exponent since the
 // last rescale; until then the stale maximum is used for P and the row sum alike, which is exact algebra (the final
-// division cancels it) and keeps P <= 2^8.
-// Per key block and CTA: 4 x 8 MMAs = 2048 tensor-pipe cycles against 32768 exponentials on the 16-per-cycle
-// special-function unit = 2048 cycles: the kernel is balanced between the two when everything overlaps.
+// division cancels it) and keeps P <= 2^8.  In that rare case the first half's exponentials are redone.
+// Per key block and CTA: 4 x 8 MMAs = 2048 tensor-pipe cycles against 32768 exponentials, 16 per cycle on the
+// special-function unit.
 //
 // Every wait is bounded; a role whose wait runs out records SVDQ_ERR_TIMEOUT and leaves its loop.
 #include <cuda_bf16.h>
@@ -46,7 +56,10 @@ constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;
 constexpr int AT_SLOTS = 5;                // K / V ring
 constexpr int AT_PRODUCER_WARP = 8, AT_MMA_WARP = 9;   // warps 10 and 11 only complete the third warpgroup
 constexpr int AT_THREADS = 12 * 32;
-constexpr int AT_REGS_SOFTMAX = 232, AT_REGS_OTHER = 40;   // 8 x 32 x 232 + 4 x 32 x 40 = 64512 of 65536 registers
+// setmaxnreg moves registers inside the pool the CTA was launched with (384 threads x 168): 8 x 32 x 232 + 4 x 32 x 40 is
+// all of it.  An increase beyond the pool would wait forever.
+constexpr int AT_REGS_LAUNCH = 168, AT_REGS_SOFTMAX = 232, AT_REGS_OTHER = 40;
+static_assert(8 * AT_REGS_SOFTMAX + 4 * AT_REGS_OTHER <= 12 * AT_REGS_LAUNCH, "register budget");
 constexpr int AT_SMEM = 1024 + (AT_TILES + AT_SLOTS) * AT_TILE_BYTES + 256;
 constexpr long long AT_WAIT_CYCLES = 600000000ll;   // ~0.3 s
 constexpr float AT_RESCALE_STEP = 8.f;
@@ -89,6 +102,30 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The two forms with descriptors given as 32-bit halves: the upper half (strides, swizzle) is a constant of the kernel and
+// the lower half (start address in 16-byte units, leading byte offset) moves by small immediates, so that an unrolled
+// issue loop needs no 64-bit arithmetic.  A and B share the upper half in the first form.
+__device__ __forceinline__ void tc_mma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -149,10 +186,23 @@ __device__ __forceinline__ float2 exp2_fma2(float2 x) {
                        __int_as_float(__float_as_int(r.y) + (__float_as_int(t.y) << 23)));
 }
 
-// Of the four pairs in every 8-key unit, this many take the FMA-pipe exponential (the rest ex2.approx): with all 32768
-// exponentials of a key block on the special-function unit it is busy for as long as the tensor pipe.
+// Of every four pairs, this many take the FMA-pipe exponential (the rest ex2.approx): with all 32768 exponentials of a
+// key block on the special-function unit it is busy for as long as the tensor pipe.  Measured on [8, 24, 4608, 128]:
+// 0 -> 1204, 1 -> 1256, 2 -> 1238 TFLOP/s.
 #ifndef AT_POLY_PAIRS
-#define AT_POLY_PAIRS 0
+#define AT_POLY_PAIRS 1
+#endif
+
+#ifdef AT_PROF
+__device__ long long at_prof[32];
+__device__ long long at_ev[4][12];   // key blocks 8..11 of CTA 0: time stamps of the two tiles' softmax and MMA events
+#define AT_EV(j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (j) >= 8 && (j) < 12) at_ev[(j) - 8][slot] = clock64(); } while (0)
+#define AT_T(v) const long long v = clock64()
+#define AT_ADD(slot, t0) prof_acc[slot] += clock64() - (t0)
+#else
+#define AT_T(v)
+#define AT_ADD(slot, t0)
+#define AT_EV(j, slot)
 #endif
 
 template <bool F16>
@@ -222,22 +272,34 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         // ------------------------------------------------------------------ MMA issuer (the whole warp walks the loop, lane 0 issues)
         constexpr uint32_t IDESC_QK = idesc_h16(AT_BM, AT_BN, F16, false);
         constexpr uint32_t IDESC_PV = idesc_h16(AT_BM, AT_D, F16, true);
-        const uint32_t q_u32 = smem_u32(q_s), kv_u32 = smem_u32(kv_s);
+        // The whole warp walks the loop and one elected lane issues (descriptors, TMEM addresses and barrier addresses then
+        // stay warp-uniform); descriptors are a constant upper half and a lower half that moves by immediates (16-byte
+        // units: a tile or ring slot is 2048, its second 64-channel half 1024, a K-step inside a swizzled row 2, 16 key rows 128).
+        const uint64_t qd = smem_desc_sw128(smem_u32(q_s)), kd = smem_desc_sw128(smem_u32(kv_s));
+        const uint64_t vd = smem_desc_sw128_mn(smem_u32(kv_s), AT_HALF_BYTES, 1024);
+        const uint32_t hi_k = static_cast<uint32_t>(qd >> 32), hi_v = static_cast<uint32_t>(vd >> 32);
+        const uint32_t q_lo = static_cast<uint32_t>(qd), k_lo = static_cast<uint32_t>(kd), v_lo = static_cast<uint32_t>(vd);
+        constexpr uint32_t UNIT_TILE = AT_TILE_BYTES >> 4, UNIT_HALF = AT_HALF_BYTES >> 4;
         bool ok = true;
-        // S_t = Q_t K^T from ring slot `slot`: 8 k-steps of 16 channels, 32 bytes apart inside the swizzled 128-byte rows
-        auto issue_qk = [&](int t, int slot) {
+#ifdef AT_PROF
+        long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long prof_t0 = clock64();
+#endif
+        // S_t = Q_t K^T from the ring slot at `slot_off`: 8 k-steps of 16 channels (elected lane only)
+        auto issue_qk = [&](int t, uint32_t slot_off) {
+#pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t off = (kk >> 2) * AT_HALF_BYTES + (kk & 3) * 32;
-                tc_mma_f16(tmem + t * AT_BN, smem_desc_sw128(q_u32 + t * AT_TILE_BYTES + off),
-                           smem_desc_sw128(kv_u32 + slot * AT_TILE_BYTES + off), IDESC_QK, kk > 0);
+                const uint32_t off = (kk >> 2) * UNIT_HALF + (kk & 3) * 2;
+                tc_mma_f16_lo(tmem + t * AT_BN, q_lo + t * UNIT_TILE + off, k_lo + slot_off + off, hi_k, IDESC_QK, kk > 0);
             }
         };
-        // O_t (+)= P_t V: 8 k-steps of 16 keys; P_t sits in the first 64 columns of S_t (two keys per column); V rows are
-        // keys, so a k-step is 16 rows = 2048 bytes further on
-        auto issue_pv = [&](int t, int slot, bool acc, int hf) {
-            for (int kk = hf * 4; kk < hf * 4 + 4; ++kk)
-                tc_mma_f16_ts(tmem + 2 * AT_BN + t * AT_D, tmem + t * AT_BN + kk * 8,
-                              smem_desc_sw128_mn(kv_u32 + slot * AT_TILE_BYTES + kk * 2048, AT_HALF_BYTES, 1024), IDESC_PV, acc || kk > 0);
+        // O_t (+)= P_t V for the 64 keys of half `hf`: 4 k-steps of 16 keys.  That half of P_t sits in the first 32 columns
+        // of the half's 64 columns of S_t (two keys per column); V rows are keys.
+        auto issue_pv = [&](int t, uint32_t slot_off, uint32_t acc, int hf) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+                tc_mma_f16_ts_lo(tmem + 2 * AT_BN + t * AT_D, tmem + t * AT_BN + hf * 64 + k4 * 8,
+                                 v_lo + slot_off + (hf * 4 + k4) * 128, hi_v, IDESC_PV, (hf | k4) ? 1u : acc);
         };
         auto wait = [&](uint64_t* bar, uint32_t parity, int code) {
             if (!ok) return false;
@@ -250,10 +312,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             return ok;
         };
-        // ring item i (K_j: 2j, V_j: 2j + 1): slot i % 3, parity (i / 3) & 1
+        // ring item i (K_j: 2j, V_j: 2j + 1): slot i % AT_SLOTS, parity (i / AT_SLOTS) & 1
         if (wait(&sh->q_full, 0, 710) && wait(&sh->kv_full[0], 0, 711)) {
             tc_fence_after_sync();
-            if (lane == 0) {
+            if (elect_one()) {
                 issue_qk(0, 0);
                 tc_commit(&sh->s_full[0]);
                 issue_qk(1, 0);
@@ -265,29 +327,52 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int j = 0; j < nblocks && ok; ++j) {
             const int iv = 2 * j + 1, ik = 2 * j + 2;
             const int vslot = iv % AT_SLOTS, kslot = ik % AT_SLOTS;
+            const uint32_t voff = vslot * UNIT_TILE, koff = kslot * UNIT_TILE;
             const bool more = j + 1 < nblocks;
+            AT_T(tv);
             if (!wait(&sh->kv_full[vslot], (iv / AT_SLOTS) & 1, 720)) break;
+            AT_ADD(0, tv);
+#pragma unroll
             for (int t = 0; t < AT_TILES; ++t) {
+                AT_T(tp0);
                 if (!wait(&sh->p_half[t][0], j & 1, 730 + t)) break;
+                AT_ADD(1 + t, tp0);
+                AT_EV(j, 6 + t * 3);
+                AT_T(tk);
                 if (more && t == 0 && !wait(&sh->kv_full[kslot], (ik / AT_SLOTS) & 1, 740)) break;
+                AT_ADD(0, tk);
                 tc_fence_after_sync();
-                if (lane == 0) issue_pv(t, vslot, j > 0, 0);
+                AT_T(ti0);
+                if (elect_one()) issue_pv(t, voff, j > 0, 0);
                 __syncwarp();
+                AT_ADD(5, ti0);
+                AT_T(tp1);
                 if (!wait(&sh->p_half[t][1], j & 1, 735 + t)) break;
+                AT_ADD(3 + t, tp1);
+                AT_EV(j, 7 + t * 3);
                 tc_fence_after_sync();
-                if (lane == 0) {
-                    issue_pv(t, vslot, j > 0, 1);
+                AT_T(ti1);
+                if (elect_one()) {
+                    issue_pv(t, voff, 1u, 1);
                     tc_commit(&sh->pv_done[t]);
                     if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[vslot]);
                     if (more) {   // overwrites P_t: behind P V in the tensor pipe's order
-                        issue_qk(t, kslot);
+                        issue_qk(t, koff);
                         tc_commit(&sh->s_full[t]);
                         if (t == AT_TILES - 1) tc_commit(&sh->kv_empty[kslot]);
                     }
                 }
                 __syncwarp();
+                AT_ADD(5, ti1);
+                AT_EV(j, 8 + t * 3);
             }
         }
+#ifdef AT_PROF
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
+            for (int i = 0; i < 8; ++i) at_prof[i] = prof_acc[i];
+            at_prof[7] = clock64() - prof_t0;
+        }
+#endif
     } else if (warp > AT_MMA_WARP) {
         reg_dealloc<AT_REGS_OTHER>();
     } else {
@@ -300,6 +385,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t o_tmem = tmem + lane_addr + 2 * AT_BN + t * AT_D;
         float m_used = 0.f, l = 0.f;
         bool ok = true;
+#ifdef AT_PROF
+        long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long prof_t0 = clock64();
+#endif
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
         // 64 keys (two 32-column chunks of S) -> 32 columns of packed 16-bit pairs, and their sum
         auto exp_half = [&](const uint32_t (&a)[32], const uint32_t (&b)[32], float m, uint32_t (&w)[32]) {
@@ -339,13 +428,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         };
         // P half `hf` is complete in tensor memory: the issuer may run its four k-steps of P V
         auto publish = [&](int hf, const uint32_t (&w)[32]) {
-            tc_st_32x32b_x32(s_tmem + hf * 32, w);   // over this thread's own S values, which are all in registers by now
+            tc_st_32x32b_x32(s_tmem + hf * 64, w);   // over this thread's own S values, which are all in registers by now
             tc_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->p_half[t][hf]);
         };
         for (int j = 0; j < nblocks; ++j) {
+            AT_T(ts);
             if (!mbar_wait(&sh->s_full[t], j & 1, AT_WAIT_CYCLES)) {
                 if (lane == 0) {
                     atomicExch(&p.status[0], SVDQ_ERR_TIMEOUT);
@@ -354,7 +444,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 ok = false;
                 break;
             }
+            AT_ADD(0, ts);
+            if (quad == 0) AT_EV(j, t * 3 + 0);
             tc_fence_after_sync();
+            AT_T(tl);
             // The row of S arrives in two halves; the exponentials of the first are computed with the maximum in use while
             // the second is still on its way, and only its (rare) growth by more than the step makes them be redone.
             const int valid = p.kv_len - j * AT_BN;   // keys of this block that exist
@@ -362,6 +455,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tc_ld_32x32b_x32(s_tmem, s0);
             tc_ld_32x32b_x32(s_tmem + 32, s1);
             tc_wait_ld();
+            AT_ADD(1, tl);
+            AT_T(te);
             tc_ld_32x32b_x32(s_tmem + 64, s2);
             tc_ld_32x32b_x32(s_tmem + 96, s3);
             if (valid < AT_BN) {
@@ -370,6 +465,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
             float mx = max_half(s0, s1);
             float sum_a = exp_half(s0, s1, m_used, w);
+            AT_ADD(2, te);
+            if (quad == 0) AT_EV(j, t * 3 + 1);
+            AT_T(tg);
             tc_wait_ld();
             if (valid < AT_BN) {
                 mask(s2, 64, valid);
@@ -408,11 +506,25 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     sum_a = exp_half(s0, s1, m_used, w);
                 }
             }
+            AT_ADD(3, tg);
+            AT_T(tp);
             publish(0, w);
+            AT_ADD(4, tp);
+            AT_T(te2);
             const float sum_b = exp_half(s2, s3, m_used, w);
+            AT_ADD(5, te2);
+            AT_T(tp2);
             publish(1, w);
+            AT_ADD(6, tp2);
+            if (quad == 0) AT_EV(j, t * 3 + 2);
             l += sum_a + sum_b;
         }
+#ifdef AT_PROF
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 0 && lane == 0) {
+            for (int i = 0; i < 7; ++i) at_prof[8 + i] = prof_acc[i];
+            at_prof[15] = clock64() - prof_t0;
+        }
+#endif
         // ---- O_t / l -> global
         if (ok && !mbar_wait(&sh->pv_done[t], (nblocks - 1) & 1, AT_WAIT_CYCLES)) {
             if (lane == 0) {
@@ -477,6 +589,15 @@ static int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const 
 }
 
 }  // namespace svdq
+
+#ifdef AT_PROF
+extern "C" int svdq_debug_attn_prof(long long* out) {
+    return cudaMemcpyFromSymbol(out, svdq::at_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+}
+extern "C" int svdq_debug_attn_events(long long* out) {
+    return cudaMemcpyFromSymbol(out, svdq::at_ev, sizeof(long long) * 48) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" int svdq_attention(const svdq_attention_args* a, void* stream) {
     using namespace svdq;

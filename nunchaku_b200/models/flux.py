@@ -23,6 +23,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ..ops.attention import attention
 from ..ops.fused import fused_gelu_mlp, gate_residual, layernorm_modulate, qkv_proj_norm_rope
 from ..weights import quantize_linear
 from .linear import SVDQW4A4Linear
@@ -87,8 +88,13 @@ class QKNorm(nn.Module):
         self.k = nn.RMSNorm(dim, eps=1e-6, device=device, dtype=dtype)
 
 
+# "tcgen05": this library's attention kernel for 128-wide heads (anything else falls through to the library call);
+# "sdpa": torch.nn.functional.scaled_dot_product_attention everywhere, for comparison.
+ATTENTION_BACKEND = {"name": "tcgen05"}
+
+
 def _attention(q, k, v, heads: int, cos, sin, norm: QKNorm | None, norms=None):
-    """q, k, v: [B, S, heads*D] -> [B, S, heads*D] (bf16 SDPA)."""
+    """q, k, v: [B, S, heads*D] (views with any row stride) -> [B, S, heads*D]."""
     B, S, C = q.shape
     D = C // heads
     q = q.view(B, S, heads, D).transpose(1, 2)
@@ -97,6 +103,8 @@ def _attention(q, k, v, heads: int, cos, sin, norm: QKNorm | None, norms=None):
     if cos is not None:
         q = apply_rope(q, cos, sin)
         k = apply_rope(k, cos, sin)
+    if ATTENTION_BACKEND["name"] == "tcgen05" and D == 128 and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
+        return attention(q, k, v)   # token-major in and out: no transposed copies
     o = F.scaled_dot_product_attention(q, k, v)
     return o.transpose(1, 2).reshape(B, S, C)
 

@@ -21,6 +21,7 @@ import torch
 
 from .. import _lib
 from .. import distributed as D
+from . import flux as F_
 from .flux import FluxTransformer
 from .step_timing import device_time_split, timed_steps
 
@@ -82,6 +83,14 @@ def run(global_batch: int = 8, reps: int = 10, warmup: int = 2, precision: str =
         ms, per_run = timed_steps(step, reps, warmup, host)
         wall_ms = (time.perf_counter() - t_host) * 1e3 / (reps + warmup)
         prof = device_time_split(eager) if (split and rank == 0) else None
+        # the same step with the library's attention in place of this library's kernel, both by eager launches
+        compare = {}
+        if split:
+            for name in ("tcgen05", "sdpa"):
+                F_.ATTENTION_BACKEND["name"] = name
+                compare[name + "_ms"] = round(D.max_over_ranks(timed_steps(eager, 3, 1, {})[0], dev), 2)
+            F_.ATTENTION_BACKEND["name"] = "tcgen05"
+            compare["mode"] = "eager launches, 3 runs each, max over ranks"
     ms_max = D.max_over_ranks(ms, dev)
     ms_min = -D.max_over_ranks(-ms, dev)
     status = _lib.device_status()
@@ -96,7 +105,9 @@ def run(global_batch: int = 8, reps: int = 10, warmup: int = 2, precision: str =
         "w4a4_linears": len(model.w4a4_linears()), "weights": "random packed" if random_packed else "random-init bf16, quantised on the GPU (smooth, rank-32 SVD, group quantise)",
         "model_build_s": round(build_s, 1), "host_ms_per_step": round(wall_ms, 2), "host_enqueue_ms_per_step": round(host.get("enqueue_ms_per_step", 0.0), 2), "cuda_graph": bool(graph), "cuda_graph_fallback": graph_note,
         "finite": bool(torch.isfinite(out["y"]).all()), "device_time_split": prof, "per_run_ms": [round(v, 2) for v in per_run],
-        "attention": "torch scaled_dot_product_attention (library kernel)",
+        "attention_compare": compare,
+        "attention": ("svdq_attention (this library's tcgen05 kernel, csrc/attention.cu)" if F_.ATTENTION_BACKEND["name"] == "tcgen05"
+                      else "torch scaled_dot_product_attention (library kernel)"),
     }
 
 
