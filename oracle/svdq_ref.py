@@ -393,7 +393,9 @@ def ref_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
     into an exp2 (``cuda_exp2(fmaf(val, scale, -rowmax_scaled))``), the row sum taken from the fp32 exponentials, the
     exponentials rounded to the 16-bit type for the product with v, fp32 accumulation, one division by the row sum and one
     rounding at the end.  The order of the block-wise running maximum is an implementation choice (it only moves the
-    rounding point of P by a power of two); here the row maximum is global.  Returns [B, Tq, H*D] in q's dtype."""
+    rounding point of P by a power of two); here the row maximum is global.  Parity unpinned: the reference's tests hold no
+    vectors for this kernel; tests/test_oracle_arith.py pins this function to float64 softmax loops.  Returns [B, Tq, H*D] in
+    q's dtype."""
     B, H, Tq, D = q.shape
     s = (q.double() @ k.double().transpose(-1, -2)).float() * (scale * 1.4426950408889634)
     p = torch.exp2(s - s.amax(dim=-1, keepdim=True))
