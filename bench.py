@@ -10,7 +10,8 @@ weights with the rank-32 SVD component removed, N(0,0.02) low-rank factors and b
 One step = one pass of the path over one batch: activation quantiser + GEMM.  At N > 1 every rank
 runs the same step on its own batch (the path shards along M without communication): weak scaling.
 After that leg the same process times, into sub-objects of the same JSON line: the INT4 variant on the M=4096,
-K=N=3072 case (`int4_config0`), a FLUX.1-dev-architecture transformer step at global batch 8 (`flux_step`) and a
+K=N=3072 case (`int4_config0`), the FLUX MLP chain (`mlp_chain_config2`), the row-wise kernels and the softmax attention of a
+FLUX block (`rowwise_kernels`, `attention`), a FLUX.1-dev-architecture transformer step at global batch 8 (`flux_step`) and a
 SANA-1.6B-architecture step at global batch 32 (`sana_step`), both sharded along the batch over the ranks.
 Prints one JSON line on rank 0.
 """
