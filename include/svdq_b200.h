@@ -206,7 +206,7 @@ typedef struct svdq_relayout_args {
 int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream);
 
 /*
- * RMSNorm of q and k per head + rotary embedding, in place on the bf16 output of a fused QKV projection
+ * RMSNorm of q and k per head + rotary embedding, in place on the 16-bit output of a fused QKV projection
  * [rows, 3 * heads * 128] (Q third, K third; V untouched).  What the reference does inside the QKV GEMM's
  * epilogue: EpilogueRMSNormRope, src/kernels/zgemm/epilogues.cuh:269-425, called from
  * nunchaku/ops/fused.py:50-110 (fused_qkv_norm_rottary); same arithmetic (fp32, one rounding), but the rotary table
@@ -214,9 +214,9 @@ int svdq_w4a4_relayout_act(const svdq_relayout_args* args, void* stream);
  * or the reference's fragment-packed [1, M, 128] tensor (rotary_packed below).
  */
 typedef struct svdq_norm_rope_args {
-    void* qkv;                /* bf16 [rows, 3 * heads * 128], modified in place */
-    const void* weight_q;     /* bf16 [128] */
-    const void* weight_k;     /* bf16 [128] */
+    void* qkv;                /* bf16 / fp16 (`dtype`) [rows, 3 * heads * 128], modified in place */
+    const void* weight_q;     /* [128], qkv's type */
+    const void* weight_k;     /* [128], qkv's type */
     const float* cos;         /* fp32 [seq_len, 64] */
     const float* sin;         /* fp32 [seq_len, 64] */
     int64_t rows;
@@ -225,7 +225,7 @@ typedef struct svdq_norm_rope_args {
     /* Optional (all NULL / 0 for the plain in-place form):
      * rotary_packed - the reference's own rotary tensor instead of cos / sin: fp32 [seq_len, 128] in the fragment
      *   order pack_rotemb produces (nunchaku/models/embeddings.py:88-120; seq_len a multiple of 16);
-     * out_q / out_k / out_v - write the three thirds head-major, bf16 [rows / seq_len, heads, tokens_pad, 128], instead
+     * out_q / out_k / out_v - write the three thirds head-major, [rows / seq_len, heads, tokens_pad, 128] of qkv's type, instead
      *   of in place (the job of EpiloguePackQKV, epilogues.cuh:427-550; there the destination is the fragment order of
      *   the reference's own fp16 attention kernel with NaN-masked K padding, here it is plain row-major for a
      *   TMA / library attention, and rows at or beyond attn_tokens, when attn_tokens > 0, are written as zeros).
@@ -236,43 +236,46 @@ typedef struct svdq_norm_rope_args {
     void* out_k;
     void* out_v;
     int32_t tokens_pad, attn_tokens, token_offset, token_major;
+    int32_t dtype;            /* SVDQ_DTYPE_* of qkv, the norm weights and out_q / out_k / out_v */
 } svdq_norm_rope_args;
 int svdq_qk_norm_rope(const svdq_norm_rope_args* args, void* stream);
 
 /*
- * out = LayerNorm(x) * (1 + scale[b]) + shift[b]: no affine, fp32 statistics, bf16 in / out, b = row / rows_per_batch.
+ * out = LayerNorm(x) * (1 + scale[b]) + shift[b]: no affine, fp32 statistics, 16-bit in / out, b = row / rows_per_batch.
  * The AdaLN-Zero step in front of each W4A4 projection of a FLUX block.  No counterpart on the reference's W4A4
  * path (its blocks call separate fused norm kernels, src/kernels/layernorm_kernels.cu); provided for the block harness.
  */
 typedef struct svdq_ln_modulate_args {
-    const void* x;            /* bf16 [rows, cols] */
-    const void* scale;        /* bf16 [batches, mod_stride], first `cols` entries of a row are used */
-    const void* shift;        /* bf16, same geometry */
-    void* out;                /* bf16 [rows, cols] */
+    const void* x;            /* bf16 / fp16 (`dtype`) [rows, cols] */
+    const void* scale;        /* [batches, mod_stride], first `cols` entries of a row are used */
+    const void* shift;        /* same geometry */
+    void* out;                /* [rows, cols] */
     int64_t rows, rows_per_batch, mod_stride;
     int32_t cols;             /* 256, 1024, 2240, 2304 or 3072 */
     float eps;                /* 1e-5 = torch.nn.functional.layer_norm default */
+    int32_t dtype;            /* SVDQ_DTYPE_* of all four tensors */
 } svdq_ln_modulate_args;
 int svdq_layernorm_modulate(const svdq_ln_modulate_args* args, void* stream);
 
 /*
- * Gated residual of a DiT block: out = x + gate[batch] * (y (+ z)), bf16, one pass (x, y, z, out: [rows, cols]; gate
+ * Gated residual of a DiT block: out = x + gate[batch] * (y (+ z)), bf16 or fp16, one pass (x, y, z, out: [rows, cols]; gate
  * [batches, gate_stride] with its first `cols` entries used, or NULL for 1; out may be x).  Like svdq_layernorm_modulate
  * it has no counterpart in the reference's W4A4 path; provided for the block harness.
  */
 typedef struct svdq_gate_residual_args {
     const void* x;
-    const void* gate;         /* bf16 or NULL */
+    const void* gate;         /* or NULL */
     const void* y;
-    const void* z;            /* bf16 or NULL: a second addend inside the gate */
+    const void* z;            /* or NULL: a second addend inside the gate */
     void* out;
     int64_t rows, rows_per_batch, gate_stride;
     int32_t cols;             /* multiple of 8 */
+    int32_t dtype;            /* SVDQ_DTYPE_* of all tensors */
 } svdq_gate_residual_args;
 int svdq_gate_residual(const svdq_gate_residual_args* args, void* stream);
 
 /*
- * ReLU linear attention of SANA on the bf16 output of the fused QKV projection: per (batch, head)
+ * ReLU linear attention of SANA on the 16-bit output of the fused QKV projection: per (batch, head)
  * vk = [V | 1]^T relu(K) over the tokens (fp32), then out = (relu(Q) vk^T)[:32] / ((relu(Q) vk^T)[32] + eps).
  * What the reference does in the QKV GEMM's epilogue plus a second kernel: EpilogueLiteLA and vk_mul_q_kernel,
  * src/kernels/zgemm/epilogues.cuh:552-761, launched from gemm_w4a4_launch_impl.cuh:311-345,426-448 and called by
@@ -280,14 +283,15 @@ int svdq_gate_residual(const svdq_gate_residual_args* args, void* stream);
  * then 64 columns [K_h | V_h] per head, D = heads * 32.  Deterministic (no atomics, nothing to zero).
  */
 typedef struct svdq_litela_args {
-    const void* qkv;          /* bf16 [batches, tokens, 3 * heads * 32] */
-    void* out;                /* bf16 [batches, tokens, heads * 32] */
+    const void* qkv;          /* bf16 / fp16 (`dtype`) [batches, tokens, 3 * heads * 32] */
+    void* out;                /* [batches, tokens, heads * 32], qkv's type */
     float* vk;                /* fp32 [batches, heads, 33, 32] or NULL: the reference's out_vk */
     int32_t batches, tokens, heads;
     float eps;                /* 1e-6 in the reference */
     int32_t mode;             /* 0: all of it.  The reference's two launches on their own: 1 = what EpilogueLiteLA leaves
-                                 (vk, and relu(Q) as bf16 in `out`; vk required); 2 = vk_mul_q_kernel (`out` holds
+                                 (vk, and relu(Q) in `out`; vk required); 2 = vk_mul_q_kernel (`out` holds
                                  relu(Q) and is finished in place from vk; qkv is not read and may be NULL)        */
+    int32_t dtype;            /* SVDQ_DTYPE_* of qkv and out */
 } svdq_litela_args;
 int svdq_litela(const svdq_litela_args* args, void* stream);
 

@@ -154,6 +154,7 @@ class NormRopeArgs(Structure):
         ("attn_tokens", c_int32),
         ("token_offset", c_int32),
         ("token_major", c_int32),
+        ("dtype", c_int32),
     ]
 
 
@@ -168,6 +169,7 @@ class LnModulateArgs(Structure):
         ("mod_stride", ctypes.c_int64),
         ("cols", c_int32),
         ("eps", c_float),
+        ("dtype", c_int32),
     ]
 
 
@@ -182,6 +184,7 @@ class GateResidualArgs(Structure):
         ("rows_per_batch", ctypes.c_int64),
         ("gate_stride", ctypes.c_int64),
         ("cols", c_int32),
+        ("dtype", c_int32),
     ]
 
 
@@ -215,6 +218,7 @@ class LiteLAArgs(Structure):
         ("heads", c_int32),
         ("eps", c_float),
         ("mode", c_int32),
+        ("dtype", c_int32),
     ]
 
 

@@ -13,22 +13,19 @@
 // fp32, the reference's out_vk) when the caller asks for it.
 //
 // Traffic: reads 3*D bf16 per token once (K|V as one 128-byte line per token and head, Q as 64 bytes), writes D bf16.
-#include <cuda_bf16.h>
-
+//
+// Compiled once per 16-bit type (see dtype.cuh): bf16 here, fp16 from litela_f16.cu; the entry point picks by `dtype`.
+#include "dtype.cuh"
 #include "host_common.h"
 
 namespace svdq {
+namespace SVDQ_DT {
 
 constexpr int LA_HD = 32;
 constexpr int LA_WARPS = 8;
 constexpr int LA_SLAB = 16;                      // tokens per warp step = the k (phase 1) / m (phase 2) extent of one mma
 
-__device__ __forceinline__ void la_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
+__device__ __forceinline__ void la_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) { mma_16816(c, a, b0, b1); }
 __device__ __forceinline__ void la_ldsm(uint32_t (&r)[4], uint32_t saddr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
@@ -37,16 +34,18 @@ __device__ __forceinline__ void la_ldsm_t(uint32_t (&r)[4], uint32_t saddr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
 }
-// max(x, 0) on two packed bf16 values
+// max(x, 0) on two packed 16-bit values
 __device__ __forceinline__ uint32_t la_relu2(uint32_t w) {
+#ifdef SVDQ_F16
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&w), __float2half2_rn(0.f));
+#else
     const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&w), __floats2bfloat162_rn(0.f, 0.f));
+#endif
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 __device__ __forceinline__ uint4 la_relu8(uint4 w) { return make_uint4(la_relu2(w.x), la_relu2(w.y), la_relu2(w.z), la_relu2(w.w)); }
-__device__ __forceinline__ uint32_t la_pack(float a, float b) {
-    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
+__device__ __forceinline__ uint32_t la_pack(float a, float b) { return pack2(make_float2(a, b)); }
+constexpr uint32_t kLaOnes2 = kF16 ? 0x3c003c00u : 0x3f803f80u;   // two packed 1.0
 
 // Both contractions run on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 accumulation):
 //   phase 1  vk[r, c] = sum_tok Vx[tok, r] * relu(K)[tok, c]: M = r (Vx = V with a 33rd column of ones, which makes row 32 the
@@ -57,7 +56,7 @@ __device__ __forceinline__ uint32_t la_pack(float a, float b) {
 //   phase 2  o[tok, j] = sum_i relu(Q)[tok, i] * vk[j, i]: M = tokens, N = j (33 -> five 8-column tiles), K = i.  vk is fp32:
 //            it enters as a bf16 high part plus a bf16 low part (two mma per tile; the split is exact to 2^-17).
 __global__ void __launch_bounds__(LA_WARPS * 32)
-litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out, float* __restrict__ vk_out,
+litela_kernel(const h16* __restrict__ qkv, h16* __restrict__ out, float* __restrict__ vk_out,
               int tokens, int heads, float eps, int mode) {
     __shared__ __align__(128) float part[LA_WARPS][LA_HD + 1][LA_HD];   // 33.8 KB; a warp's slice doubles as its staging tile
     __shared__ __align__(16) float vk[LA_HD + 1][LA_HD];
@@ -66,8 +65,8 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
     const int g = lane >> 2, t4 = lane & 3;
     const int D = heads * LA_HD;
     const size_t pitch = static_cast<size_t>(3) * D;
-    const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * tokens * pitch;
-    const __nv_bfloat16* kv = base + D + 64 * h;
+    const h16* base = qkv + static_cast<size_t>(b) * tokens * pitch;
+    const h16* kv = base + D + 64 * h;
     uint8_t* tile = reinterpret_cast<uint8_t*>(&part[warp][0][0]);   // 16 tokens x 128 B ([K | V]) or 16 x 64 B (Q)
     const uint32_t tile_s = static_cast<uint32_t>(__cvta_generic_to_shared(tile));
     // mode 0: everything.  The reference does it in two launches, and the two halves exist on their own for callers
@@ -87,7 +86,7 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
         // A fragment of the ones row: row g = 0 of the third m-tile is 1 for every token of the slab
-        const uint32_t one2 = g == 0 ? 0x3f803f80u : 0u;
+        const uint32_t one2 = g == 0 ? kLaOnes2 : 0u;
         const uint32_t ones[4] = {one2, 0u, one2, 0u};
         // a lane brings 16-byte chunk (lane & 7) of the lines of tokens (lane >> 3) + 4 i
         auto load_slab = [&](int t0, uint4 (&w)[4]) {
@@ -165,8 +164,23 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
     }
 
     // -------------------------------------------------------------------- phase 2
-    // B fragments of vk^T (column j = 8 n + g, rows i = 16 s + 2 t4 .. and + 8), high and low bf16 parts; the fifth n-tile
+    // B fragments of vk^T (column j = 8 n + g, rows i = 16 s + 2 t4 .. and + 8), high and low 16-bit parts; the fifth n-tile
     // holds row 32 (the denominator) in its column 0
+    // fp16 has 5 exponent bits: vk (sums over all tokens) is brought to [2^13, 2^14) at its largest entry by a power of two
+    // first; numerator and denominator of the quotient below carry the same factor, eps takes it too.
+    float vscale = 1.f;
+    if constexpr (kF16) {
+        float m = 0.f;
+        for (int i = lane; i < (LA_HD + 1) * LA_HD; i += 32) m = fmaxf(m, fabsf(vk[i >> 5][i & 31]));
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        if (m > 0.f && m < 3.0e38f) {
+            const int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xff) - 127;   // floor(log2 m) for normal m
+            int k = 13 - e;
+            k = k < -100 ? -100 : (k > 100 ? 100 : k);
+            vscale = __uint_as_float(static_cast<uint32_t>(127 + k) << 23);
+        }
+    }
     uint32_t bh[5][2][2], bl[5][2][2];
 #pragma unroll
     for (int nt = 0; nt < 5; ++nt)
@@ -177,10 +191,10 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
                 const int j = 8 * nt + g, i = 16 * ks + 8 * hh + 2 * t4;
                 float v0 = 0.f, v1 = 0.f;
                 if (j <= LA_HD) {
-                    v0 = vk[j][i];
-                    v1 = vk[j][i + 1];
+                    v0 = vk[j][i] * vscale;
+                    v1 = vk[j][i + 1] * vscale;
                 }
-                const float h0 = __bfloat162float(__float2bfloat16_rn(v0)), h1 = __bfloat162float(__float2bfloat16_rn(v1));
+                const float h0 = h2f(f2h(v0)), h1 = h2f(f2h(v1));
                 bh[nt][ks][hh] = la_pack(h0, h1);
                 bl[nt][ks][hh] = la_pack(v0 - h0, v1 - h1);
             }
@@ -214,8 +228,8 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
             }
         }
         // the denominators of rows g and g + 8 sit in column 0 of the fifth tile: lanes with t4 == 0
-        const float den0 = __shfl_sync(0xffffffffu, o[4][0], lane & ~3) + eps;
-        const float den1 = __shfl_sync(0xffffffffu, o[4][2], lane & ~3) + eps;
+        const float den0 = __shfl_sync(0xffffffffu, o[4][0], lane & ~3) + eps * vscale;
+        const float den1 = __shfl_sync(0xffffffffu, o[4][2], lane & ~3) + eps * vscale;
         const int ta = t0 + g, tb = t0 + g + 8;
         // lane t4 of a quad holds columns 8 n + 2 t4 (+1) of every n-tile n; a 4 x 4 transpose of words inside the quad gives
         // it the eight columns of n-tile t4 instead: one 16-byte store per row, 64 contiguous bytes per quad
@@ -247,10 +261,7 @@ litela_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__
     }
 }
 
-}  // namespace svdq
-
-extern "C" int svdq_litela(const svdq_litela_args* a, void* stream) {
-    using namespace svdq;
+int litela_impl(const svdq_litela_args* a, void* stream) {
     SVDQ_CHECK_ARG(a && a->out && (a->qkv || a->mode == 2) && (a->vk || a->mode == 0), "litela: null pointer");
     SVDQ_CHECK_ARG(a->mode >= 0 && a->mode <= 2, "litela: mode must be 0 (all), 1 (vk and relu(Q) only) or 2 (finish from vk)");
     SVDQ_CHECK_ARG(a->batches > 0 && a->batches <= 65535 && a->tokens > 0 && a->heads > 0,
@@ -258,7 +269,24 @@ extern "C" int svdq_litela(const svdq_litela_args* a, void* stream) {
     SVDQ_CHECK_ARG(aligned(a->qkv, 16) && aligned(a->out, 16) && aligned(a->vk, 16), "litela: tensors must be 16-byte aligned");
     if (int rc = check_arch()) return rc;
     litela_kernel<<<dim3(a->heads, a->batches), LA_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(a->qkv), static_cast<__nv_bfloat16*>(a->out), a->vk, a->tokens, a->heads, a->eps, a->mode);
+        static_cast<const h16*>(a->qkv), static_cast<h16*>(a->out), a->vk, a->tokens, a->heads, a->eps, a->mode);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }
+
+}  // namespace SVDQ_DT
+}  // namespace svdq
+
+#ifndef SVDQ_F16
+namespace svdq {
+namespace hf {
+int litela_impl(const svdq_litela_args* a, void* stream);
+}
+}  // namespace svdq
+
+extern "C" int svdq_litela(const svdq_litela_args* a, void* stream) {
+    if (a && a->dtype == SVDQ_DTYPE_FP16) return svdq::hf::litela_impl(a, stream);
+    if (a && a->dtype != SVDQ_DTYPE_BF16) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, "litela: bad dtype %d", a->dtype);
+    return svdq::bf::litela_impl(a, stream);
+}
+#endif

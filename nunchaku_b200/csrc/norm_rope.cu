@@ -14,19 +14,17 @@
 // (eps 1e-5) followed by x * (1 + scale[b]) + shift[b], bf16 in and out, fp32 statistics; one warp per row with the
 // row held in registers (two passes over registers, one over memory).  Not part of the reference's W4A4 path (the
 // reference has its own fused norm kernels); it is here so that the block harness is not bound by library glue.
-#include <cuda_bf16.h>
-
+//
+// Compiled once per 16-bit type (see dtype.cuh): bf16 here, fp16 from norm_rope_f16.cu; the entry points pick by `dtype`.
+#include "dtype.cuh"
 #include "host_common.h"
 
 namespace svdq {
+namespace SVDQ_DT {
 
-__device__ __forceinline__ float2 bf2(uint32_t w) {
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-__device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
-    const __nv_bfloat162 o = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&o);
-}
+__device__ __forceinline__ float2 bf2(uint32_t w) { return unpack2(w); }
+__device__ __forceinline__ uint32_t pack_bf2(float a, float b) { return pack2(make_float2(a, b)); }
+constexpr uint32_t kOnes2 = kF16 ? 0x3c003c00u : 0x3f803f80u;   // two packed 1.0
 
 // PACKED: the rotary table is the reference's fragment-packed fp32 tensor (pack_rotemb, nunchaku/models/embeddings.py:88-120):
 // for row m = 16 mb + 8 h + g and column pair p = 4 j + t, {sin, cos} sit at ((((mb*16 + j)*8 + g)*4 + t)*2 + h)*2.
@@ -35,10 +33,10 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
 // token_offset on; rows at or beyond attn_tokens (when given) become zeros.
 template <bool PACKED, bool SPLIT>
 __global__ void __launch_bounds__(256)
-qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
+qk_norm_rope_kernel(h16* __restrict__ qkv, const h16* __restrict__ wq, const h16* __restrict__ wk,
                     const float* __restrict__ cosp, const float* __restrict__ sinp, long long rows, int seq_len, int heads,
-                    float eps, __nv_bfloat16* __restrict__ out_q, __nv_bfloat16* __restrict__ out_k,
-                    __nv_bfloat16* __restrict__ out_v, int tokens_pad, int attn_tokens, int token_offset, int token_major) {
+                    float eps, h16* __restrict__ out_q, h16* __restrict__ out_k,
+                    h16* __restrict__ out_v, int tokens_pad, int attn_tokens, int token_offset, int token_major) {
     const int lane = threadIdx.x & 31;
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
@@ -52,7 +50,7 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
         const long long row = it / (heads * PARTS);
         const int rem = static_cast<int>(it - row * heads * PARTS);
         const int which = rem / heads, head = rem - which * heads;
-        __nv_bfloat16* p = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + head * 128 + lane * 4;
+        h16* p = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + head * 128 + lane * 4;
         const long long pos = row % seq_len;
         uint2 o = *reinterpret_cast<const uint2*>(p);
         if (which < 2) {
@@ -84,7 +82,7 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
         }
         if constexpr (SPLIT) {
             if (attn_tokens > 0 && pos >= attn_tokens) o = make_uint2(0u, 0u);
-            __nv_bfloat16* dst = which == 0 ? out_q : which == 1 ? out_k : out_v;
+            h16* dst = which == 0 ? out_q : which == 1 ? out_k : out_v;
             const long long b = row / seq_len, tok = token_offset + pos;
             const long long at = token_major ? (b * tokens_pad + tok) * heads + head : (b * heads + head) * tokens_pad + tok;
             *reinterpret_cast<uint2*>(dst + at * 128 + lane * 4) = o;
@@ -98,8 +96,8 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
 // (j*32 + lane) * 8; only the first TAIL lanes hold a last chunk (TAIL = 32: C = 256 V)
 template <int V, int TAIL = 32>
 __global__ void __launch_bounds__(256)
-layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
-                          const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ out, long long rows,
+layernorm_modulate_kernel(const h16* __restrict__ x, const h16* __restrict__ scale,
+                          const h16* __restrict__ shift, h16* __restrict__ out, long long rows,
                           long long rows_per_batch, long long mod_stride, float eps) {
     constexpr int C = (V - 1) * 256 + TAIL * 8;
     const int lane = threadIdx.x & 31;
@@ -146,9 +144,9 @@ layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 s2 = bf2(scw[i]), h2 = bf2(shw[i]);
-                // the library sequence it replaces rounds the normalised value to bf16 before modulating
-                const float n0 = __bfloat162float(__float2bfloat16_rn((v[j][2 * i] - mean) * rstd));
-                const float n1 = __bfloat162float(__float2bfloat16_rn((v[j][2 * i + 1] - mean) * rstd));
+                // the library sequence it replaces rounds the normalised value to the 16-bit type before modulating
+                const float n0 = h2f(f2h((v[j][2 * i] - mean) * rstd));
+                const float n1 = h2f(f2h((v[j][2 * i + 1] - mean) * rstd));
                 o[i] = pack_bf2(n0 * (1.0f + s2.x) + h2.x, n1 * (1.0f + s2.y) + h2.y);
             }
             op[j * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -168,8 +166,8 @@ static int grid_for(long long warps_needed) {
 // DiT block, one pass with 16-byte accesses (the library's broadcasting multiply and add are two passes, neither vectorised).
 // fp32 arithmetic, one rounding.  `out` may alias x.
 __global__ void __launch_bounds__(256)
-gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ y,
-                     const __nv_bfloat16* __restrict__ z, __nv_bfloat16* out, long long rows, long long rows_per_batch,
+gate_residual_kernel(const h16* __restrict__ x, const h16* __restrict__ gate, const h16* __restrict__ y,
+                     const h16* __restrict__ z, h16* out, long long rows, long long rows_per_batch,
                      long long gate_stride, int cols) {
     const int c8 = cols >> 3;
     const long long total = rows * c8;
@@ -180,7 +178,7 @@ gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         const uint4 xw = reinterpret_cast<const uint4*>(x)[i];
         const uint4 yw = reinterpret_cast<const uint4*>(y)[i];
         const uint4 gw = gate ? *reinterpret_cast<const uint4*>(gate + (row / rows_per_batch) * gate_stride + 8 * c)
-                              : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+                              : make_uint4(kOnes2, kOnes2, kOnes2, kOnes2);
         uint4 zw = make_uint4(0, 0, 0, 0);
         if (z) zw = reinterpret_cast<const uint4*>(z)[i];
         const uint32_t xs[4] = {xw.x, xw.y, xw.z, xw.w}, ys[4] = {yw.x, yw.y, yw.z, yw.w}, gs[4] = {gw.x, gw.y, gw.z, gw.w},
@@ -195,10 +193,7 @@ gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     }
 }
 
-}  // namespace svdq
-
-extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
-    using namespace svdq;
+int qk_norm_rope_impl(const svdq_norm_rope_args* a, void* stream) {
     SVDQ_CHECK_ARG(a && a->qkv && a->weight_q && a->weight_k && ((a->cos && a->sin) || a->rotary_packed), "qk_norm_rope: null pointer");
     SVDQ_CHECK_ARG(a->rows > 0 && a->seq_len > 0 && a->heads > 0 && a->rows % a->seq_len == 0,
                    "qk_norm_rope: rows (%lld) must be a positive multiple of seq_len (%d)", static_cast<long long>(a->rows), a->seq_len);
@@ -216,9 +211,9 @@ extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
     const float* tab = a->rotary_packed ? a->rotary_packed : a->cos;
     auto launch = [&](auto kernel) {
         kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-            static_cast<__nv_bfloat16*>(a->qkv), static_cast<const __nv_bfloat16*>(a->weight_q),
-            static_cast<const __nv_bfloat16*>(a->weight_k), tab, a->sin, a->rows, a->seq_len, a->heads, a->eps,
-            static_cast<__nv_bfloat16*>(a->out_q), static_cast<__nv_bfloat16*>(a->out_k), static_cast<__nv_bfloat16*>(a->out_v),
+            static_cast<h16*>(a->qkv), static_cast<const h16*>(a->weight_q),
+            static_cast<const h16*>(a->weight_k), tab, a->sin, a->rows, a->seq_len, a->heads, a->eps,
+            static_cast<h16*>(a->out_q), static_cast<h16*>(a->out_k), static_cast<h16*>(a->out_v),
             a->tokens_pad, a->attn_tokens, a->token_offset, a->token_major);
     };
     if (a->rotary_packed) {
@@ -230,8 +225,7 @@ extern "C" int svdq_qk_norm_rope(const svdq_norm_rope_args* a, void* stream) {
     return SVDQ_OK;
 }
 
-extern "C" int svdq_layernorm_modulate(const svdq_ln_modulate_args* a, void* stream) {
-    using namespace svdq;
+int layernorm_modulate_impl(const svdq_ln_modulate_args* a, void* stream) {
     SVDQ_CHECK_ARG(a && a->x && a->scale && a->shift && a->out, "layernorm_modulate: null pointer");
     SVDQ_CHECK_ARG(a->rows > 0 && a->rows_per_batch > 0 && a->rows % a->rows_per_batch == 0 && a->mod_stride >= a->cols &&
                        a->mod_stride % 8 == 0,
@@ -241,10 +235,10 @@ extern "C" int svdq_layernorm_modulate(const svdq_ln_modulate_args* a, void* str
     if (int rc = check_arch()) return rc;
     const int grid = grid_for(a->rows);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a->x);
-    const __nv_bfloat16* sc = static_cast<const __nv_bfloat16*>(a->scale);
-    const __nv_bfloat16* sh = static_cast<const __nv_bfloat16*>(a->shift);
-    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a->out);
+    const h16* x = static_cast<const h16*>(a->x);
+    const h16* sc = static_cast<const h16*>(a->scale);
+    const h16* sh = static_cast<const h16*>(a->shift);
+    h16* o = static_cast<h16*>(a->out);
     switch (a->cols) {
         case 256: layernorm_modulate_kernel<1><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
         case 1024: layernorm_modulate_kernel<4><<<grid, 256, 0, st>>>(x, sc, sh, o, a->rows, a->rows_per_batch, a->mod_stride, a->eps); break;
@@ -257,8 +251,7 @@ extern "C" int svdq_layernorm_modulate(const svdq_ln_modulate_args* a, void* str
     return SVDQ_OK;
 }
 
-extern "C" int svdq_gate_residual(const svdq_gate_residual_args* a, void* stream) {
-    using namespace svdq;
+int gate_residual_impl(const svdq_gate_residual_args* a, void* stream) {
     SVDQ_CHECK_ARG(a && a->x && a->y && a->out, "gate_residual: null pointer");
     SVDQ_CHECK_ARG(a->rows > 0 && a->rows_per_batch > 0 && a->rows % a->rows_per_batch == 0 && a->cols > 0 && a->cols % 8 == 0 &&
                        (a->gate == nullptr || (a->gate_stride >= a->cols && a->gate_stride % 8 == 0)),
@@ -272,8 +265,31 @@ extern "C" int svdq_gate_residual(const svdq_gate_residual_args* a, void* stream
     const long long want = (total + 255) / 256;
     const int grid = static_cast<int>(want < 16LL * sms ? want : 16LL * sms);
     gate_residual_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(a->x), static_cast<const __nv_bfloat16*>(a->gate), static_cast<const __nv_bfloat16*>(a->y),
-        static_cast<const __nv_bfloat16*>(a->z), static_cast<__nv_bfloat16*>(a->out), a->rows, a->rows_per_batch, a->gate_stride, a->cols);
+        static_cast<const h16*>(a->x), static_cast<const h16*>(a->gate), static_cast<const h16*>(a->y),
+        static_cast<const h16*>(a->z), static_cast<h16*>(a->out), a->rows, a->rows_per_batch, a->gate_stride, a->cols);
     SVDQ_CUDA(cudaGetLastError());
     return SVDQ_OK;
 }
+
+}  // namespace SVDQ_DT
+}  // namespace svdq
+
+#ifndef SVDQ_F16
+namespace svdq {
+namespace hf {
+int qk_norm_rope_impl(const svdq_norm_rope_args* a, void* stream);
+int layernorm_modulate_impl(const svdq_ln_modulate_args* a, void* stream);
+int gate_residual_impl(const svdq_gate_residual_args* a, void* stream);
+}  // namespace hf
+}  // namespace svdq
+
+#define SVDQ_ROWWISE_ENTRY(name, args_t, impl)                                                                       \
+    extern "C" int name(const args_t* a, void* stream) {                                                             \
+        if (a && a->dtype == SVDQ_DTYPE_FP16) return svdq::hf::impl(a, stream);                                      \
+        if (a && a->dtype != SVDQ_DTYPE_BF16) return svdq::fail(SVDQ_ERR_INVALID_ARGUMENT, #name ": bad dtype %d", a->dtype); \
+        return svdq::bf::impl(a, stream);                                                                            \
+    }
+SVDQ_ROWWISE_ENTRY(svdq_qk_norm_rope, svdq_norm_rope_args, qk_norm_rope_impl)
+SVDQ_ROWWISE_ENTRY(svdq_layernorm_modulate, svdq_ln_modulate_args, layernorm_modulate_impl)
+SVDQ_ROWWISE_ENTRY(svdq_gate_residual, svdq_gate_residual_args, gate_residual_impl)
+#endif

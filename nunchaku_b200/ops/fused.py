@@ -6,7 +6,7 @@ import ctypes
 import torch
 
 from .. import _lib
-from ..utils import ceil_divide, on_device, ptr, require_cuda_contiguous, stream_ptr
+from ..utils import HALF_DTYPES, ceil_divide, dtype_code, on_device, ptr, require_cuda_contiguous, stream_ptr
 from .gemm import svdq_gemm_w4a4_cuda
 
 
@@ -96,8 +96,8 @@ def unpack_rotemb(rotary_emb: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]
 def _norm_rope_packed(qkv, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn_tokens: int) -> None:
     """The RMSNorm + RoPE (+ head-major split) step of the QKV epilogue on the projection's bf16 tile ``qkv`` [rows, 3*dim],
     with the reference's packed rotary tensor [B_r, M_r, 128] (B_r * M_r rows; the table repeats over ``qkv``'s rows)."""
-    require_cuda_contiguous("norm_q", norm_q, (torch.bfloat16,))
-    require_cuda_contiguous("norm_k", norm_k, (torch.bfloat16,))
+    require_cuda_contiguous("norm_q", norm_q, (qkv.dtype,))
+    require_cuda_contiguous("norm_k", norm_k, (qkv.dtype,))
     require_cuda_contiguous("rotary_emb", rotary_emb, (torch.float32,))
     if rotary_emb.dim() != 3 or rotary_emb.shape[2] != 128:
         raise ValueError("rotary_emb must be the packed fp32 tensor [B, M, 128] (gemm_w4a4_launch_impl.cuh:351-354)")
@@ -108,12 +108,12 @@ def _norm_rope_packed(qkv, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn
         raise ValueError("the QKV width must be 3 * heads * 128 and the row count a multiple of the rotary table's rows")
     heads = dim // 128
     args = _lib.NormRopeArgs(qkv=ptr(qkv), weight_q=ptr(norm_q), weight_k=ptr(norm_k), cos=None, sin=None, rows=rows,
-                             seq_len=table_rows, heads=heads, eps=1e-6, rotary_packed=ptr(rotary_emb))
+                             seq_len=table_rows, heads=heads, eps=1e-6, rotary_packed=ptr(rotary_emb), dtype=dtype_code(qkv.dtype))
     if out_q is not None:
         for n, t in (("out_q", out_q), ("out_k", out_k), ("out_v", out_v)):
             if t is None:
                 raise ValueError("out_q, out_k and out_v go together")
-            require_cuda_contiguous(n, t, (torch.bfloat16,))
+            require_cuda_contiguous(n, t, (qkv.dtype,))
             if t.dim() != 4 or t.shape[1] != heads or t.shape[3] != 128 or t.shape[0] * table_rows != rows or t.shape[2] < table_rows:
                 raise ValueError(f"{n} must be [rows / table rows, heads, tokens_pad >= table rows, 128]")
         args.out_q, args.out_k, args.out_v = ptr(out_q), ptr(out_k), ptr(out_v)
@@ -124,9 +124,9 @@ def _norm_rope_packed(qkv, norm_q, norm_k, rotary_emb, out_q, out_k, out_v, attn
 
 def _litela_epilogue(qkv: torch.Tensor, out_vk: torch.Tensor, out_linearattn: torch.Tensor) -> None:
     """What ``EpilogueLiteLA`` leaves behind (gemm_w4a4_launch_impl.cuh:311-345): ``out_vk`` [B, heads, 33, 32] fp32 and
-    relu(Q) as bf16 in ``out_linearattn`` [B, tokens, N/3], from the projection's bf16 tile ``qkv`` [B*tokens, N]."""
+    relu(Q) in ``out_linearattn`` [B, tokens, N/3], from the projection's 16-bit tile ``qkv`` [B*tokens, N] (same dtype)."""
     require_cuda_contiguous("out_vk", out_vk, (torch.float32,))
-    require_cuda_contiguous("out_linearattn", out_linearattn, (torch.bfloat16,))
+    require_cuda_contiguous("out_linearattn", out_linearattn, (qkv.dtype,))
     if out_vk.dim() != 4 or out_vk.shape[2:] != (33, 32) or out_linearattn.dim() != 3:
         raise ValueError("out_vk must be [B, heads, 33, 32] and out_linearattn [B, tokens, N/3]")
     B, heads = out_vk.shape[0], out_vk.shape[1]
@@ -134,19 +134,20 @@ def _litela_epilogue(qkv: torch.Tensor, out_vk: torch.Tensor, out_linearattn: to
     if heads * 96 != qkv.shape[-1] or out_linearattn.shape != (B, tokens, heads * 32) or qkv.numel() != B * tokens * heads * 96:
         raise ValueError("linear attention: N must be 3 * heads * 32 and the rows B * tokens")
     args = _lib.LiteLAArgs(qkv=ptr(qkv), out=ptr(out_linearattn), vk=ptr(out_vk), batches=B, tokens=tokens, heads=heads,
-                           eps=1e-6, mode=1)
+                           eps=1e-6, mode=1, dtype=dtype_code(qkv.dtype))
     _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(qkv.device)))
 
 
 def linearattn_vk_mul_q(q: torch.Tensor, vk: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """In place on ``q`` [B, tokens, heads*32] (relu(Q), bf16): ``o = q @ vk^T`` per head, ``q <- o[:32] / (o[32] + eps)``
+    """In place on ``q`` [B, tokens, heads*32] (relu(Q), bf16 or fp16): ``o = q @ vk^T`` per head, ``q <- o[:32] / (o[32] + eps)``
     (``linearattn_vk_mul_q``, gemm_w4a4_launch_impl.cuh:426-448; ``vk_mul_q_kernel``, epilogues.cuh:704-759)."""
-    require_cuda_contiguous("q", q, (torch.bfloat16,))
+    require_cuda_contiguous("q", q, HALF_DTYPES)
     require_cuda_contiguous("vk", vk, (torch.float32,))
     B, tokens, D = q.shape
     if vk.shape != (B, D // 32, 33, 32):
         raise ValueError("vk must be [B, heads, 33, 32]")
-    args = _lib.LiteLAArgs(qkv=None, out=ptr(q), vk=ptr(vk), batches=B, tokens=tokens, heads=D // 32, eps=eps, mode=2)
+    args = _lib.LiteLAArgs(qkv=None, out=ptr(q), vk=ptr(vk), batches=B, tokens=tokens, heads=D // 32, eps=eps, mode=2,
+                           dtype=dtype_code(q.dtype))
     with on_device(q.device):
         _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(q.device)))
     return q
@@ -158,24 +159,24 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
     """RMSNorm of q and k per 128-wide head and rotary embedding, in place on the output of a fused QKV projection
     (what ``fused_qkv_norm_rottary``, ``nunchaku/ops/fused.py:50-110``, gets from the GEMM epilogue).
 
-    qkv: bf16 [B, S, 3*heads*128] (or [B*S, ...] with ``cos.shape[0]`` dividing the rows); cos, sin: fp32 [S, 64].
-    With ``out = (q, k, v)``, three bf16 [B, S_total, heads*128] buffers, the three thirds are written there instead
+    qkv: bf16 or fp16 [B, S, 3*heads*128] (or [B*S, ...] with ``cos.shape[0]`` dividing the rows); cos, sin: fp32 [S, 64].
+    With ``out = (q, k, v)``, three [B, S_total, heads*128] buffers of qkv's dtype, the three thirds are written there instead
     (token-major, rows ``token_offset .. token_offset + S``): the two streams of a joint block fill one set of buffers
     that attention reads without any concatenation.
     """
-    require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
-    require_cuda_contiguous("weight_q", weight_q, (torch.bfloat16,))
-    require_cuda_contiguous("weight_k", weight_k, (torch.bfloat16,))
+    require_cuda_contiguous("qkv", qkv, HALF_DTYPES)
+    require_cuda_contiguous("weight_q", weight_q, (qkv.dtype,))
+    require_cuda_contiguous("weight_k", weight_k, (qkv.dtype,))
     require_cuda_contiguous("cos", cos, (torch.float32,))
     require_cuda_contiguous("sin", sin, (torch.float32,))
     if qkv.shape[-1] != 3 * heads * 128 or cos.shape != sin.shape or cos.shape[-1] != 64:
         raise ValueError("qk_norm_rope: qkv must be [..., 3*heads*128] and cos/sin [seq_len, 64]")
     rows = qkv.numel() // qkv.shape[-1]
     args = _lib.NormRopeArgs(qkv=ptr(qkv), weight_q=ptr(weight_q), weight_k=ptr(weight_k), cos=ptr(cos), sin=ptr(sin),
-                             rows=rows, seq_len=cos.shape[0], heads=heads, eps=eps)
+                             rows=rows, seq_len=cos.shape[0], heads=heads, eps=eps, dtype=dtype_code(qkv.dtype))
     if out is not None:
         for t in out:
-            require_cuda_contiguous("out", t, (torch.bfloat16,))
+            require_cuda_contiguous("out", t, (qkv.dtype,))
             if t.dim() != 3 or t.shape[2] != heads * 128 or t.shape[0] * cos.shape[0] != rows:
                 raise ValueError("qk_norm_rope: out tensors must be [rows / S, S_total, heads*128]")
         args.out_q, args.out_k, args.out_v = ptr(out[0]), ptr(out[1]), ptr(out[2])
@@ -186,17 +187,18 @@ def qk_norm_rope(qkv: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tens
 
 
 def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
-    """``layer_norm(x) * (1 + scale) + shift`` (no affine) for x bf16 [B, S, C] and per-batch scale / shift bf16 [B, C]
-    (views into a wider modulation tensor are fine as long as rows are contiguous)."""
-    require_cuda_contiguous("x", x, (torch.bfloat16,))
+    """``layer_norm(x) * (1 + scale) + shift`` (no affine) for x bf16 or fp16 [B, S, C] and per-batch scale / shift [B, C] of
+    the same dtype (views into a wider modulation tensor are fine as long as rows are contiguous)."""
+    require_cuda_contiguous("x", x, HALF_DTYPES)
     B, S, C = x.shape
     if scale.shape != (B, C) or shift.shape != (B, C) or scale.stride(1) != 1 or shift.stride(1) != 1:
         raise ValueError("layernorm_modulate: scale / shift must be [B, C] with unit column stride")
-    if scale.stride(0) != shift.stride(0) or scale.dtype != torch.bfloat16 or shift.dtype != torch.bfloat16:
-        raise ValueError("layernorm_modulate: scale and shift must be bf16 views with the same row stride")
+    if scale.stride(0) != shift.stride(0) or scale.dtype != x.dtype or shift.dtype != x.dtype:
+        raise ValueError("layernorm_modulate: scale and shift must be views of x's dtype with the same row stride")
     out = torch.empty_like(x)
     args = _lib.LnModulateArgs(x=ptr(x), scale=scale.data_ptr(), shift=shift.data_ptr(), out=ptr(out), rows=B * S,
-                               rows_per_batch=S, mod_stride=scale.stride(0) if B > 1 else max(scale.stride(0), C), cols=C, eps=eps)
+                               rows_per_batch=S, mod_stride=scale.stride(0) if B > 1 else max(scale.stride(0), C), cols=C, eps=eps,
+                               dtype=dtype_code(x.dtype))
     with on_device(x.device):
         _lib.check(_lib.load().svdq_layernorm_modulate(ctypes.byref(args), stream_ptr(x.device)))
     return out
@@ -204,24 +206,24 @@ def layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor
 
 def gate_residual(x: torch.Tensor, gate: torch.Tensor | None, y: torch.Tensor, z: torch.Tensor | None = None,
                   out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x + gate[:, None, :] * (y (+ z))`` for bf16 x, y, z [B, S, C] and a per-batch gate bf16 [B, C] (a view with unit column
-    stride is fine; None = 1): the gated residual after a projection, in one pass.  ``out`` defaults to a new tensor and may
+    """``x + gate[:, None, :] * (y (+ z))`` for bf16 or fp16 x, y, z [B, S, C] and a per-batch gate [B, C] of the same dtype (a view
+    with unit column stride is fine; None = 1): the gated residual after a projection, in one pass.  ``out`` defaults to a new tensor and may
     be ``x``."""
-    require_cuda_contiguous("x", x, (torch.bfloat16,))
-    require_cuda_contiguous("y", y, (torch.bfloat16,))
-    require_cuda_contiguous("z", z, (torch.bfloat16,))
+    require_cuda_contiguous("x", x, HALF_DTYPES)
+    require_cuda_contiguous("y", y, (x.dtype,))
+    require_cuda_contiguous("z", z, (x.dtype,))
     B, S, C = x.shape
     if y.shape != x.shape or (z is not None and z.shape != x.shape) or C % 8:
         raise ValueError("gate_residual: x, y, z must be [B, S, C] with C a multiple of 8")
     stride = 0
     if gate is not None:
-        if gate.shape != (B, C) or gate.stride(1) != 1 or gate.dtype != torch.bfloat16 or not gate.is_cuda:
-            raise ValueError("gate_residual: gate must be a bf16 [B, C] view with unit column stride")
+        if gate.shape != (B, C) or gate.stride(1) != 1 or gate.dtype != x.dtype or not gate.is_cuda:
+            raise ValueError("gate_residual: gate must be a [B, C] view of x's dtype with unit column stride")
         stride = gate.stride(0) if B > 1 else max(gate.stride(0), C)
     if out is None:
         out = torch.empty_like(x)
     args = _lib.GateResidualArgs(x=ptr(x), gate=None if gate is None else gate.data_ptr(), y=ptr(y), z=ptr(z), out=ptr(out),
-                                 rows=B * S, rows_per_batch=S, gate_stride=stride, cols=C)
+                                 rows=B * S, rows_per_batch=S, gate_stride=stride, cols=C, dtype=dtype_code(x.dtype))
     with on_device(x.device):
         _lib.check(_lib.load().svdq_gate_residual(ctypes.byref(args), stream_ptr(x.device)))
     return out
@@ -231,16 +233,16 @@ def litela_attention(qkv: torch.Tensor, heads: int, eps: float = 1e-6, return_vk
     """ReLU linear attention of SANA on the bf16 output of the fused QKV projection (what ``EpilogueLiteLA`` in the QKV
     GEMM plus ``linearattn_vk_mul_q`` compute for ``SanaLinearAttention::forward``, ``src/SanaModel.cpp:25-106``).
 
-    qkv: bf16 [B, S, 3*heads*32], columns [Q of all heads | (K_h, V_h) 64 per head].  Returns bf16 [B, S, heads*32]
-    (and the fp32 ``vk`` [B, heads, 33, 32] when asked)."""
-    require_cuda_contiguous("qkv", qkv, (torch.bfloat16,))
+    qkv: bf16 or fp16 [B, S, 3*heads*32], columns [Q of all heads | (K_h, V_h) 64 per head].  Returns [B, S, heads*32] of the
+    same dtype (and the fp32 ``vk`` [B, heads, 33, 32] when asked)."""
+    require_cuda_contiguous("qkv", qkv, HALF_DTYPES)
     if qkv.dim() != 3 or qkv.shape[-1] != 3 * heads * 32:
         raise ValueError("litela_attention: qkv must be [B, S, 3*heads*32]")
     B, S, _ = qkv.shape
-    out = torch.empty(B, S, heads * 32, dtype=torch.bfloat16, device=qkv.device)
+    out = torch.empty(B, S, heads * 32, dtype=qkv.dtype, device=qkv.device)
     vk = torch.empty(B, heads, 33, 32, dtype=torch.float32, device=qkv.device) if return_vk else None
     args = _lib.LiteLAArgs(qkv=ptr(qkv), out=ptr(out), vk=ptr(vk) if vk is not None else None, batches=B, tokens=S,
-                           heads=heads, eps=eps)
+                           heads=heads, eps=eps, dtype=dtype_code(qkv.dtype))
     with on_device(qkv.device):
         _lib.check(_lib.load().svdq_litela(ctypes.byref(args), stream_ptr(qkv.device)))
     return (out, vk) if return_vk else out

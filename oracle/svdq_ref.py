@@ -339,7 +339,7 @@ def ref_qk_norm_rope(qkv: torch.Tensor, w_q: torch.Tensor, w_k: torch.Tensor, co
                      heads: int, eps: float = 1e-6) -> torch.Tensor:
     """EpilogueRMSNormRope (src/kernels/zgemm/epilogues.cuh:330-405) on a bf16 [rows, 3*heads*128] QKV output:
     per head of the Q and K thirds ``coef = rsqrt(sum(float(y)^2)/128 + eps)``, ``v = float(y) * (coef * float(w))``,
-    pairs (2p, 2p+1) rotated by (cos, sin)[row % S, p] in fp32, one rounding to bf16.  V is untouched.
+    pairs (2p, 2p+1) rotated by (cos, sin)[row % S, p] in fp32, one rounding to the input's 16-bit type.  V is untouched.
     cos, sin: fp32 [S, 64]."""
     rows, C = qkv.shape
     dim = heads * 128
@@ -354,7 +354,7 @@ def ref_qk_norm_rope(qkv: torch.Tensor, w_q: torch.Tensor, w_k: torch.Tensor, co
         v = y * (coef * w.to(F32)[None, None, :])
         a, b = v[..., 0::2], v[..., 1::2]
         r = torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(rows, dim)
-        out[:, which * dim:(which + 1) * dim] = r.to(BF16)
+        out[:, which * dim:(which + 1) * dim] = r.to(qkv.dtype)
     return out
 
 
@@ -364,8 +364,8 @@ def ref_layernorm_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Te
     xf = x.to(F32)
     mean = xf.mean(-1, keepdim=True)
     var = ((xf - mean) ** 2).mean(-1, keepdim=True)
-    n = ((xf - mean) * torch.rsqrt(var + eps)).to(BF16).to(F32)
-    return (n * (1.0 + scale.to(F32)[:, None, :]) + shift.to(F32)[:, None, :]).to(BF16)
+    n = ((xf - mean) * torch.rsqrt(var + eps)).to(x.dtype).to(F32)
+    return (n * (1.0 + scale.to(F32)[:, None, :]) + shift.to(F32)[:, None, :]).to(x.dtype)
 
 
 def ref_litela(qkv: torch.Tensor, heads: int, eps: float = 1e-6):
@@ -383,7 +383,7 @@ def ref_litela(qkv: torch.Tensor, heads: int, eps: float = 1e-6):
     v1 = torch.cat([v, torch.ones(B, S, heads, 1, dtype=torch.float64)], dim=-1)       # [B,S,H,33]
     vk = torch.einsum("bshr,bshc->bhrc", v1, k)                                         # [B,H,33,32]
     o = torch.einsum("bshc,bhrc->bshr", q, vk.float().double())                         # [B,S,H,33]
-    out = (o[..., :32].float() / (o[..., 32:].float() + eps)).to(torch.bfloat16)
+    out = (o[..., :32].float() / (o[..., 32:].float() + eps)).to(qkv.dtype)
     return out.reshape(B, S, D), vk.float()
 
 

@@ -126,3 +126,71 @@ def test_gate_residual_matches_torch(B, S, C, with_z, with_gate):
     # in place on x
     x2 = x.clone()
     assert gate_residual(x2, gate, y, z if with_z else None, out=x2) is x2 and torch.equal(x2, got)
+
+
+def _f16_close(got, exp, ulps=1.0, frac=0.999):
+    """as _bf16_close with fp16's step (2^-10 relative)"""
+    d = (got.float() - exp.float()).abs()
+    step = exp.float().abs().clamp(min=1e-6) * 2.0 ** -10
+    assert (d <= ulps * step).float().mean().item() >= frac
+    assert (d <= 4 * step + 1e-6).all()
+
+
+def test_rowwise_kernels_in_fp16():
+    """The same kernels compiled for fp16 tensors (`dtype` of their argument structs) against the same restatements."""
+    from nunchaku_b200.ops import gate_residual, layernorm_modulate, linearattn_vk_mul_q, litela_attention, qk_norm_rope
+
+    g = torch.Generator().manual_seed(77)
+    B, S, heads = 2, 100, 3
+    dim = heads * 128
+    qkv = (torch.randn(B * S, 3 * dim, generator=g) * 2).half()
+    wq, wk = (1 + 0.2 * torch.randn(128, generator=g)).half(), (1 + 0.2 * torch.randn(128, generator=g)).half()
+    ang = torch.rand(S, 64, generator=g) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    exp = R.ref_qk_norm_rope(qkv, wq, wk, cos, sin, heads)
+    got = qk_norm_rope(qkv.cuda().view(B, S, 3 * dim), wq.cuda(), wk.cuda(), cos.cuda(), sin.cuda(), heads).cpu().view(B * S, 3 * dim)
+    assert got.dtype == torch.float16 and torch.equal(got[:, 2 * dim:], qkv[:, 2 * dim:])
+    _f16_close(got[:, :2 * dim], exp[:, :2 * dim])
+    # token-major split outputs
+    outs = tuple(torch.zeros(B, S + 28, dim, dtype=torch.float16, device="cuda") for _ in range(3))
+    qk_norm_rope(qkv.cuda().view(B, S, 3 * dim), wq.cuda(), wk.cuda(), cos.cuda(), sin.cuda(), heads, out=outs, token_offset=28)
+    for i in range(3):
+        assert torch.equal(outs[i][:, 28:].cpu().reshape(B * S, dim), got[:, i * dim:(i + 1) * dim])
+        assert (outs[i][:, :28] == 0).all()
+
+    x = torch.randn(B, S, 1024, generator=g).half()
+    sc, sh = (torch.randn(B, 1024, generator=g) * 0.1).half(), (torch.randn(B, 1024, generator=g) * 0.1).half()
+    _f16_close(layernorm_modulate(x.cuda(), sc.cuda(), sh.cuda()).cpu(), R.ref_layernorm_modulate(x, sc, sh))
+    y, z = torch.randn(B, S, 1024, generator=g).half(), torch.randn(B, S, 1024, generator=g).half()
+    exp = (x.double() + sc.double()[:, None, :] * (y.double() + z.double())).half()
+    # one fused multiply-add in fp32, then one rounding to fp16: a double rounding against the float64 value now and then
+    _f16_close(gate_residual(x.cuda(), sc.cuda(), y.cuda(), z.cuda()).cpu(), exp, ulps=1.0, frac=0.9995)
+    assert torch.equal(gate_residual(x.cuda(), None, y.cuda()).cpu(), (x.float() + y.float()).half())
+
+    lh = 5
+    q3 = torch.randn(B, 700, 3 * lh * 32, generator=g).half()
+    q3[..., lh * 32:] *= 6      # vk far outside fp16's precision sweet spot: sums of ~700 products of size ~20
+    exp, exp_vk = R.ref_litela(q3, lh)
+    got, vk = litela_attention(q3.cuda(), lh, return_vk=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == (0, 0)
+    assert got.dtype == torch.float16 and R.rel_l2(vk.cpu(), exp_vk) <= 1e-5
+    g32, e32 = got.float().cpu(), exp.float()
+    assert R.rel_l2(g32, e32) <= 4e-4
+    assert ((g32 - e32).abs() <= 2.0 ** -10 * e32.abs() + 1e-6).all()
+    # the second half on its own (vk_mul_q_kernel): relu(Q) in place
+    rq = q3[..., :lh * 32].clamp_min(0).contiguous().cuda()
+    assert torch.equal(linearattn_vk_mul_q(rq, vk), got)
+
+
+def test_rowwise_kernels_reject_mixed_dtypes():
+    from nunchaku_b200.ops import gate_residual, qk_norm_rope
+
+    x = torch.zeros(1, 8, 256, dtype=torch.float16, device="cuda")
+    with pytest.raises(ValueError):
+        gate_residual(x, None, x.bfloat16())
+    qkv = torch.zeros(1, 8, 384, dtype=torch.float16, device="cuda")
+    w = torch.ones(128, dtype=torch.bfloat16, device="cuda")
+    t = torch.zeros(8, 64, device="cuda")
+    with pytest.raises(ValueError):
+        qk_norm_rope(qkv, w, w, t, t, 1)
