@@ -155,7 +155,7 @@ typedef struct svdq_gemm_args {
     int32_t dtype;            /* SVDQ_DTYPE_* of out, ascales / oscales (INT4), next_smooth, next_lora_down;
                                  the prepared weights do not depend on it beyond what prepare_weights read   */
     /* RMSNorm + rotary embedding of a fused QKV projection inside the epilogue (EpilogueRMSNormRope, epilogues.cuh:269-425):
-       set rope_cos to ask for it (NVFP4, bf16, no activation, N = 3 * rope_heads * 128 with rope_heads even, M a multiple of
+       set rope_cos to ask for it (NVFP4, no activation, N = 3 * rope_heads * 128 with rope_heads even, M a multiple of
        rope_seq_len, rope_seq_len a multiple of 32; otherwise SVDQ_ERR_UNSUPPORTED: run svdq_gemm_w4a4 and svdq_qk_norm_rope).
        q and k heads are normalised and rotated, v passes through.  The result goes to `out` [M, N], or, when rope_out_q is
        set, to three token-major tensors [M / rope_seq_len, rope_tokens_pad, rope_heads * 128] from token rope_token_offset on

@@ -1494,9 +1494,9 @@ int gemm_nvfp4_impl(const svdq_gemm_args* a, cudaStream_t stream) {
         // RMSNorm + rotary embedding of a fused QKV projection inside the epilogue
         const int dim = a->rope_heads * 128;
         const bool split = a->rope_out_q != nullptr;
-        if (kF16 || requant || a->activation != SVDQ_ACT_NONE || a->N != 3 * dim || n_out(a) != a->N || dim % G_BN != 0 ||
+        if (requant || a->activation != SVDQ_ACT_NONE || a->N != 3 * dim || n_out(a) != a->N || dim % G_BN != 0 ||
             a->rope_seq_len <= 0 || a->rope_seq_len % 32 != 0 || a->M % a->rope_seq_len != 0 || (!split && a->out == nullptr))
-            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): this fused RMSNorm + RoPE epilogue is built for bf16, a plain QKV projection "
+            return fail(SVDQ_ERR_UNSUPPORTED, "gemm(nvfp4): this fused RMSNorm + RoPE epilogue is built for a plain QKV projection "
                                               "with N = 3 * heads * 128 (heads even), rows = batch * seq_len and seq_len a multiple of 32");
         SVDQ_CHECK_ARG(a->rope_sin && a->rope_norm_q && a->rope_norm_k && aligned(a->rope_cos, 16) && aligned(a->rope_sin, 16),
                        "gemm(nvfp4): rope_sin, rope_norm_q, rope_norm_k are required; the tables must be 16-byte aligned");

@@ -17,6 +17,14 @@ def _bf16_close(got, exp, ulps=1.0, frac=0.999):
     assert (d <= 4 * step + 1e-6).all()
 
 
+def _f16_close(got, exp, ulps=1.0, frac=0.999):
+    """as _bf16_close with fp16's step (2^-10 relative)"""
+    d = (got.float() - exp.float()).abs()
+    step = exp.float().abs().clamp(min=1e-6) * 2.0 ** -10
+    assert (d <= ulps * step).float().mean().item() >= frac
+    assert (d <= 4 * step + 1e-6).all()
+
+
 @pytest.mark.parametrize("B,S,heads", [(1, 48, 2), (3, 100, 24)])
 def test_qk_norm_rope_matches_oracle(B, S, heads):
     from nunchaku_b200.ops import qk_norm_rope
@@ -68,9 +76,11 @@ def test_litela_matches_oracle(B, S, heads):
     assert ((g32 - e32).abs() <= 2.0 ** -7 * e32.abs() + 1e-6).all()
 
 
-@pytest.mark.parametrize("B,S,heads,split", [(2, 64, 2, False), (1, 320, 4, True), (3, 96, 2, True),
-                                                 (2, 50, 2, True)])   # the last: not a shape of the fused epilogue (second kernel)
-def test_qkv_projection_with_norm_rope_in_the_gemm_epilogue(B, S, heads, split):
+@pytest.mark.parametrize("B,S,heads,split,dtype", [(2, 64, 2, False, torch.bfloat16), (1, 320, 4, True, torch.bfloat16),
+                                                       (3, 96, 2, True, torch.bfloat16),
+                                                       (2, 50, 2, True, torch.bfloat16),   # not a shape of the fused epilogue (second kernel)
+                                                       (2, 96, 2, True, torch.float16), (1, 64, 2, False, torch.float16)])
+def test_qkv_projection_with_norm_rope_in_the_gemm_epilogue(B, S, heads, split, dtype):
     """RMSNorm + rotary embedding inside the QKV GEMM's epilogue (svdq_gemm_args.rope_*) against (a) the same projection
     followed by the row-wise kernel and (b) the oracle on the GEMM's own bf16 tile.  The two GPU paths differ only in the
     order of the 128 additions of the sum of squares, which can move a result by one bf16 ulp now and then."""
@@ -79,35 +89,36 @@ def test_qkv_projection_with_norm_rope_in_the_gemm_epilogue(B, S, heads, split):
 
     C = heads * 128
     torch.manual_seed(S + heads)
-    x = R.make_activations(B * S, C, seed=S)
-    lin = R.make_linear(C, 3 * C, 32, fp4=True, x_absmax=x.float().abs().amax(0), seed=S + 1, mode="svd", wcscales=True)
+    close = _bf16_close if dtype == torch.bfloat16 else _f16_close
+    x = R.make_activations(B * S, C, seed=S, dtype=dtype)
+    lin = R.make_linear(C, 3 * C, 32, fp4=True, x_absmax=x.float().abs().amax(0), seed=S + 1, mode="svd", wcscales=True, dtype=dtype)
     m = H.to_module(lin)
-    wq = (1.0 + 0.1 * torch.randn(128)).to(torch.bfloat16).cuda()
-    wk = (1.0 + 0.1 * torch.randn(128)).to(torch.bfloat16).cuda()
+    wq = (1.0 + 0.1 * torch.randn(128)).to(dtype).cuda()
+    wk = (1.0 + 0.1 * torch.randn(128)).to(dtype).cuda()
     ang = torch.rand(S, 64) * 6.28
     cos, sin = ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous()
     xg = x.cuda().view(B, S, C)
     tile = m(xg)                                                   # plain projection: the bf16 tile
     off, S_total = 32, S + 64
     if split:
-        outs = tuple(torch.full((B, S_total, C), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3))
-        ref = tuple(torch.full((B, S_total, C), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+        outs = tuple(torch.full((B, S_total, C), float("nan"), dtype=dtype, device="cuda") for _ in range(3))
+        ref = tuple(torch.full((B, S_total, C), float("nan"), dtype=dtype, device="cuda") for _ in range(3))
         assert qkv_proj_norm_rope(xg, m, wq, wk, cos, sin, heads, out=outs, token_offset=off) is None
         qk_norm_rope(tile.clone(), wq, wk, cos, sin, heads, out=ref, token_offset=off)
         torch.cuda.synchronize()
         assert _lib.device_status() == (0, 0)
         for g, e in zip(outs, ref):
             assert torch.isnan(g[:, :off].float()).all() and torch.isnan(g[:, off + S:].float()).all()   # nothing else written
-            _bf16_close(g[:, off:off + S].float().cpu(), e[:, off:off + S].float().cpu(), ulps=1.0, frac=0.9995)
+            close(g[:, off:off + S].float().cpu(), e[:, off:off + S].float().cpu(), ulps=1.0, frac=0.9995)
         got = torch.cat([t[:, off:off + S] for t in outs], dim=-1)
     else:
         got = qkv_proj_norm_rope(xg, m, wq, wk, cos, sin, heads)
         ref = qk_norm_rope(tile.clone(), wq, wk, cos, sin, heads)
         torch.cuda.synchronize()
         assert _lib.device_status() == (0, 0)
-        _bf16_close(got.float().cpu(), ref.float().cpu(), ulps=1.0, frac=0.9995)
+        close(got.float().cpu(), ref.float().cpu(), ulps=1.0, frac=0.9995)
     exp = R.ref_qk_norm_rope(tile.cpu().view(B * S, 3 * C), wq.cpu(), wk.cpu(), cos.cpu(), sin.cpu(), heads)
-    _bf16_close(got.float().cpu().view(B * S, 3 * C), exp.float(), ulps=1.0, frac=0.999)
+    close(got.float().cpu().view(B * S, 3 * C), exp.float(), ulps=1.0, frac=0.999)
 
 
 @pytest.mark.parametrize("B,S,C,with_z,with_gate", [(2, 70, 256, False, True), (3, 50, 2240, True, True), (1, 333, 3072, False, False)])
@@ -126,14 +137,6 @@ def test_gate_residual_matches_torch(B, S, C, with_z, with_gate):
     # in place on x
     x2 = x.clone()
     assert gate_residual(x2, gate, y, z if with_z else None, out=x2) is x2 and torch.equal(x2, got)
-
-
-def _f16_close(got, exp, ulps=1.0, frac=0.999):
-    """as _bf16_close with fp16's step (2^-10 relative)"""
-    d = (got.float() - exp.float()).abs()
-    step = exp.float().abs().clamp(min=1e-6) * 2.0 ** -10
-    assert (d <= ulps * step).float().mean().item() >= frac
-    assert (d <= 4 * step + 1e-6).all()
 
 
 def test_rowwise_kernels_in_fp16():
