@@ -313,7 +313,7 @@ def svdq_gemm_w4a4_cuda(
             raise ValueError("out_linearattn needs out_vk (gemm_w4a4_launch_impl.cuh:313)")
         activation = _lib.ACT_NONE
         M = M_pad
-        tmp_out = out = torch.empty(M_pad, N, dtype=half, device=dev)
+        tmp_out = out = torch.empty(M_pad, N, dtype=prepared.half_dtype, device=dev)
     else:
         if out is None and rope_out is None:
             raise ValueError("either `out` or (`qout`, `oscales`) must be given")
