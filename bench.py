@@ -346,7 +346,12 @@ def attention_kernel(dev, peaks, reps=10, batch=8):
     ref = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, T, H_ * D_).float()
     rel = ((out.float() - ref).norm() / ref.norm()).item()
     tf = flop / (t_own * 1e-3) / 1e12
-    return {"workload": f"softmax attention [{batch}, {H_}, {T}, {D_}] bf16, token-major", "kernel": "attention_fwd_kernel (tcgen05, TMEM)",
+    one = {}
+    if batch > 1:   # one image: what a rank runs when the step's batch is sharded over eight GPUs (2.9 waves of CTAs)
+        q1, k1, v1, o1 = q[:1], k[:1], v[:1], out[:1]
+        one = {"one_image_us": event_times([lambda: attention(q1, k1, v1, out=o1)], reps)[0] * 1e3,
+               "one_image_library_sdpa_us": event_times([lambda: torch.nn.functional.scaled_dot_product_attention(q1, k1, v1)], reps)[0] * 1e3}
+    return {**one, "workload": f"softmax attention [{batch}, {H_}, {T}, {D_}] bf16, token-major", "kernel": "attention_fwd_kernel (tcgen05, TMEM)",
             "us": t_own * 1e3, "tflops": tf, "frac_bf16_peak": tf / peaks["bf16_tflops"], "peak_bf16_tflops": peaks["bf16_tflops"],
             "library_sdpa_us": t_lib * 1e3, "library_sdpa_tflops": flop / (t_lib * 1e-3) / 1e12, "rel_l2_vs_library": rel,
             "launches_timed": reps}
