@@ -39,3 +39,28 @@ def test_linear_and_mlp_chain_in_a_cuda_graph(fp4):
             torch.cuda.synchronize()
             assert torch.equal(y, y_eager) and torch.equal(z, z_eager)
     assert _lib.device_status() == (0, 0)
+
+
+def test_attention_in_a_cuda_graph():
+    """Captured after one warm-up call (which caches the per-device state), the attention kernel replays to the eager result
+    bit for bit: it is deterministic (no atomics) and neither allocates outside torch's pool nor synchronises."""
+    from nunchaku_b200 import _lib
+    from nunchaku_b200.ops import attention
+
+    g = torch.Generator(device="cuda").manual_seed(9)
+    q, k, v = (torch.randn(2, 333, 3, 128, device="cuda", generator=g).bfloat16().transpose(1, 2) for _ in range(3))
+    o_eager = attention(q, k, v).clone()
+    assert torch.equal(attention(q, k, v), o_eager)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg, stream=side):
+            o = attention(q, k, v)
+    for _ in range(2):
+        o.zero_()
+        cg.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(o, o_eager)
+    assert _lib.device_status() == (0, 0)
