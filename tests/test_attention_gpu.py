@@ -113,3 +113,32 @@ def test_attention_rejects_what_it_cannot_run():
     q = torch.zeros(1, 2, 64, 128, dtype=torch.float32, device="cuda")
     with pytest.raises(ValueError):
         attention(q, q, q)
+
+
+def test_attention_degenerate_inputs():
+    """one query; all-equal scores (uniform weights: the mean of V); a scale so large that the softmax is one-hot; magnitudes
+    near the top of bf16's range of useful scores (products of ~1e4 before scaling)"""
+    from nunchaku_b200.ops import attention
+
+    g = torch.Generator().manual_seed(17)
+    q, k, v = _inputs(1, 2, 1, 300, torch.bfloat16, seed=1)
+    o1 = attention(q.cuda(), k.cuda(), v.cuda()).float().cpu()
+    e1 = R.ref_attention(q, k, v, 128 ** -0.5, round_p=False).float()
+    assert R.rel_l2(o1, e1) <= 5e-3 and (o1 - e1).abs().max() <= 2.0 ** -8    # 256 values only: a looser norm, plus an absolute bound
+    q, k, v = _inputs(1, 2, 130, 260, torch.bfloat16, seed=2)
+    o = attention(torch.zeros_like(q).cuda(), k.cuda(), v.cuda()).float().cpu()
+    mean_v = v.float().mean(dim=2).reshape(1, 1, 2 * 128).expand(1, 130, 256)
+    assert R.rel_l2(o, mean_v) <= 3e-3
+    # one-hot: out = V[argmax]
+    o = attention(q.cuda(), k.cuda(), v.cuda(), scale=50.0).cpu()
+    s = q.float() @ k.float().transpose(-1, -2)
+    top2 = s.topk(2, dim=-1).values
+    clear = (top2[..., 0] - top2[..., 1]) * 50.0 * 1.4427 > 30      # rows whose runner-up weighs less than 2^-30
+    idx = s.argmax(-1)                                               # [1, 2, 130]
+    exp = torch.gather(v, 2, idx[..., None].expand(1, 2, 130, 128)).transpose(1, 2).reshape(1, 130, 256)
+    m = clear.transpose(1, 2).reshape(1, 130, 2, 1).expand(1, 130, 2, 128).reshape(1, 130, 256)
+    assert clear.float().mean() > 0.5 and torch.equal(o[m], exp[m])
+    assert torch.isfinite(o.float()).all()
+    q2 = (torch.randn(1, 2, 64, 128, generator=g) * 30).to(torch.bfloat16)
+    k2 = (torch.randn(1, 2, 200, 128, generator=g) * 30).to(torch.bfloat16)
+    _check(q2, k2, v[:, :, :200])
