@@ -296,6 +296,22 @@ typedef struct svdq_litela_args {
 int svdq_litela(const svdq_litela_args* args, void* stream);
 
 /*
+ * INT4 weight quantiser: a 16-bit weight [N, K] -> signed 4-bit codes with one 16-bit scale per row and group of 64, in the
+ * packed layouts svdq_w4a4_prepare_weights reads (qweight as NunchakuWeightPacker.pack_weight lays it out, wscales as
+ * pack_scale).  Replaces quantize_w4a4_wgt (src/kernels/zgemm/zgemm.h:48, gemm_w4a4.cu:132-136, kernel
+ * gemm_w4a4.cuh:661-689), bit for bit: scale = max|w| / 7 and rscale = 7 / max|w| in the 16-bit type,
+ * code = sat_s4(rint(rscale * w)) with the product rounded to 16 bits first.
+ */
+typedef struct svdq_quantize_wgt_args {
+    const void* input;        /* bf16 / fp16 (`dtype`) [N, K] row-major */
+    void* qweight;            /* int8 [N, K/2], reference-packed */
+    void* wscales;            /* [K/64, N] of the input's type, reference-packed */
+    int32_t N, K;             /* multiples of 128 and 64 */
+    int32_t dtype;
+} svdq_quantize_wgt_args;
+int svdq_quantize_w4a4_wgt(const svdq_quantize_wgt_args* args, void* stream);
+
+/*
  * Softmax attention forward, 128-wide heads: out = softmax(scale * Q K^T) V per (batch, head), fp32 accumulation, the
  * probabilities rounded to the 16-bit type before the second product.  Replaces attention_fp16
  * (src/kernels/zgemm/attention.cu:10-96, bound at nunchaku/csrc/pybind.cpp:111, called from

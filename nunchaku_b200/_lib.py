@@ -188,6 +188,17 @@ class GateResidualArgs(Structure):
     ]
 
 
+class QuantizeWgtArgs(Structure):
+    _fields_ = [
+        ("input", c_void_p),
+        ("qweight", c_void_p),
+        ("wscales", c_void_p),
+        ("N", c_int32),
+        ("K", c_int32),
+        ("dtype", c_int32),
+    ]
+
+
 class AttentionArgs(Structure):
     _fields_ = [
         ("q", c_void_p),
@@ -236,6 +247,7 @@ EXPORTS = {
     "svdq_gate_residual": (c_int32, [POINTER(GateResidualArgs), c_void_p]),
     "svdq_litela": (c_int32, [POINTER(LiteLAArgs), c_void_p]),
     "svdq_attention": (c_int32, [POINTER(AttentionArgs), c_void_p]),
+    "svdq_quantize_w4a4_wgt": (c_int32, [POINTER(QuantizeWgtArgs), c_void_p]),
     "svdq_device_status": (c_int32, [POINTER(c_int32), POINTER(c_int32)]),
     "svdq_last_error_string": (c_char_p, []),
     "svdq_version": (c_int32, []),

@@ -11,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["api.cu", "quantize.cu", "quantize_f16.cu", "prepare.cu", "gemm_w4a4.cu", "gemm_w4a4_f16.cu", "norm_rope.cu", "norm_rope_f16.cu", "litela.cu", "litela_f16.cu", "attention.cu",
+SOURCES = ["api.cu", "quantize.cu", "quantize_f16.cu", "quantize_wgt.cu", "prepare.cu", "gemm_w4a4.cu", "gemm_w4a4_f16.cu", "norm_rope.cu", "norm_rope_f16.cu", "litela.cu", "litela_f16.cu", "attention.cu",
            "peak_probe.cu"]
 # the fp16 builds are the bf16 sources compiled again with the 16-bit type switched
 INCLUDES = {"quantize_f16.cu": "quantize.cu", "gemm_w4a4_f16.cu": "gemm_w4a4.cu", "norm_rope_f16.cu": "norm_rope.cu", "litela_f16.cu": "litela.cu"}

@@ -81,3 +81,27 @@ def svdq_quantize_w4a4_act_fuse_lora_cuda(
     with on_device(dev):
         _lib.check(_lib.load().svdq_quantize_w4a4_act_fuse_lora(ctypes.byref(args), stream_ptr(dev)))
     return output, oscales, lora_act_out
+
+
+def svdq_quantize_w4a4_wgt(input: torch.Tensor, output: torch.Tensor | None = None,
+                           oscales: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """INT4 weight quantiser: bf16 / fp16 ``input`` [N, K] -> (``qweight`` int8 [N, K/2], ``wscales`` [K/64, N] of the input's
+    dtype), both in the packed layouts of ``SVDQW4A4Linear``'s parameters (``nunchaku::kernels::quantize_w4a4_wgt``,
+    src/kernels/zgemm/zgemm.h:48: input, output, oscales in that order, written in place when given).  Arithmetic as the
+    reference's kernel does it, in the 16-bit type: scale = max|w| / 7, code = sat_s4(rint(w * (7 / max|w|)))."""
+    require_cuda_contiguous("input", input, HALF_DTYPES)
+    if input.dim() != 2 or input.shape[0] % 128 or input.shape[1] % 64:
+        raise ValueError("input must be [N, K] with N a multiple of 128 and K of 64")
+    N, K = input.shape
+    if output is None:
+        output = torch.empty(N, K // 2, dtype=torch.int8, device=input.device)
+    if oscales is None:
+        oscales = torch.empty(K // 64, N, dtype=input.dtype, device=input.device)
+    require_cuda_contiguous("output", output, (torch.int8, torch.uint8))
+    require_cuda_contiguous("oscales", oscales, (input.dtype,))
+    if output.numel() != N * K // 2 or oscales.numel() != N * K // 64:
+        raise ValueError("output must hold N * K / 2 bytes and oscales N * K / 64 values")
+    args = _lib.QuantizeWgtArgs(input=ptr(input), qweight=ptr(output), wscales=ptr(oscales), N=N, K=K, dtype=dtype_code(input.dtype))
+    with on_device(input.device):
+        _lib.check(_lib.load().svdq_quantize_w4a4_wgt(ctypes.byref(args), stream_ptr(input.device)))
+    return output, oscales

@@ -156,4 +156,21 @@ int ref_int4_vk_mul_q(void *q, float *vk, int batch, int tokens, int heads, int 
 
 const char *ref_int4_last_error(void) { return g_error.c_str(); }
 
+// quantize_w4a4_wgt (src/kernels/zgemm/zgemm.h:48; gemm_w4a4_launch_impl.cuh:547-570): 16-bit weight [N, K] -> packed INT4
+// codes [N, K/2] and packed group scales [K/64, N]
+int ref_int4_quantize_wgt(const void *input, void *output, void *oscales, int N, int K, int fp16, int device, void *stream) {
+    try {
+        CUDAStreamContext ctx(static_cast<cudaStream_t>(stream));
+        const Tensor::ScalarType H = fp16 ? Tensor::FP16 : Tensor::BF16;
+        Tensor in = wrap(input, {N, K}, H, device), out = wrap(output, {N, K / 2}, Tensor::INT8, device),
+               sc = wrap(oscales, {K / 64, N}, H, device);
+        if (fp16) LaunchFP16::quantize_w4a4_wgt(in, out, sc);
+        else LaunchBF16::quantize_w4a4_wgt(in, out, sc);
+        return 0;
+    } catch (const std::exception &e) {
+        g_error = e.what();
+        return -1;
+    }
+}
+
 }  // extern "C"

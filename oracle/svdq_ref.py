@@ -404,3 +404,22 @@ def ref_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
         p = p.to(q.dtype).float()
     o = (p.double() @ v.double()) / l
     return o.float().to(q.dtype).transpose(1, 2).reshape(B, Tq, H * D)
+
+
+def ref_quantize_wgt_int4(w: torch.Tensor):
+    """The reference's INT4 weight quantiser (quantize_w4a4_wgt_kernel + quantize_w4a4_warp,
+    src/kernels/zgemm/gemm_w4a4.cuh:661-689,527-620) on a bf16 weight [N, K]: per row and group of 64, all in bf16,
+    ``scale = max|w| / 7``, ``rscale = 7 / max|w|``, ``code = sat_s4(rint(bf16(rscale * w)))`` (round to nearest even; a zero
+    group gives inf * 0 = NaN -> 0).  Returns logical (codes uint8 nibbles [N, K], scales bf16 [K/64, N]).  bf16 only: the
+    reference's fp16 division is the approximate-reciprocal ``__hdiv``, which only the kernel itself reproduces."""
+    assert w.dtype == BF16
+    N, K = w.shape
+    g = w.reshape(N, K // 64, 64)
+    m = g.float().abs().amax(dim=2).to(BF16)
+    seven = torch.tensor(7.0, dtype=BF16)
+    scale = m / seven                      # bf16 division: the fp32 quotient rounded once
+    rscale = seven / m                     # inf for a zero group
+    h = (rscale.unsqueeze(2) * g)          # bf16 product, rounded once; inf * 0 = NaN
+    q = torch.nan_to_num(h.float(), nan=0.0, posinf=7.0, neginf=-8.0).round().clamp(-8, 7).to(torch.int32)
+    codes = (q & 0xF).to(torch.uint8).reshape(N, K)
+    return codes, scale.t().contiguous()

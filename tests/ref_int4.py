@@ -42,6 +42,8 @@ def load():
         lib.ref_int4_quantize.argtypes = [POINTER(QuantArgs), c_void_p]
         lib.ref_int4_gemm.argtypes = [POINTER(GemmArgs), c_void_p]
         lib.ref_int4_vk_mul_q.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        if hasattr(lib, "ref_int4_quantize_wgt"):
+            lib.ref_int4_quantize_wgt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.ref_int4_last_error.restype = ctypes.c_char_p
         _lib = lib
     return _lib
@@ -113,3 +115,17 @@ def gemm(act, wgt, ascales, wscales, *, out=None, qout=None, oscales=None, lora_
 def vk_mul_q(q: torch.Tensor, vk: torch.Tensor):
     B, tokens, D = q.shape
     _check(load().ref_int4_vk_mul_q(_p(q), _p(vk), B, tokens, D // 32, q.device.index or 0, _stream(q.device)))
+
+
+def has_quantize_wgt() -> bool:
+    return available() and hasattr(load(), "ref_int4_quantize_wgt")
+
+
+def quantize_wgt(w: torch.Tensor):
+    """The reference's quantize_w4a4_wgt on a bf16 / fp16 CUDA weight [N, K] -> (packed int8 [N, K/2], packed scales [K/64, N])."""
+    N, K = w.shape
+    out = torch.empty(N, K // 2, dtype=torch.int8, device=w.device)
+    sc = torch.empty(K // 64, N, dtype=w.dtype, device=w.device)
+    _check(load().ref_int4_quantize_wgt(_p(w), _p(out), _p(sc), N, K, int(w.dtype == torch.float16), w.device.index or 0,
+                                        _stream(w.device)))
+    return out, sc

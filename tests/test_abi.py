@@ -50,6 +50,7 @@ def test_struct_layout_matches_c(lib, tmp_path):
         "svdq_gate_residual_args": lib.GateResidualArgs,
         "svdq_litela_args": lib.LiteLAArgs,
         "svdq_attention_args": lib.AttentionArgs,
+        "svdq_quantize_wgt_args": lib.QuantizeWgtArgs,
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, cls in structs.items():
