@@ -140,3 +140,17 @@ def test_ref_attention_is_softmax_attention():
             assert torch.allclose(exact[0, t, 128 * h: 128 * h + 128].double(), o, rtol=2 ** -8, atol=1e-6)
     assert R.rel_l2(rounded, exact) < 3e-3
     assert R.ref_attention(q.half(), k.half(), v.half(), scale).dtype == torch.float16
+
+
+def test_ref_quantize_wgt_int4_by_hand():
+    """The weight-quantiser restatement on hand-computed groups: every step in bf16 (gemm_w4a4.cuh:527-620)."""
+    w = torch.zeros(1, 128, dtype=torch.bfloat16)
+    w[0, 0], w[0, 1], w[0, 2], w[0, 3] = 7.0, -7.0, 3.5, 0.49       # max 7: scale 1, rscale 1
+    w[0, 64], w[0, 65] = 1.0, -1.0                                   # max 1: scale bf16(1/7), rscale 7
+    codes, scales = R.ref_quantize_wgt_int4(w)
+    assert codes[0, :4].tolist() == [7, 9, 4, 0]                     # 7, -7 (two's complement nibble), rint(3.5) = 4 (even), 0
+    assert codes[0, 64:66].tolist() == [7, 9]
+    assert scales[0, 0].item() == 1.0 and scales[1, 0] == torch.tensor(1.0 / 7.0).to(torch.bfloat16)
+    assert (codes[0, 4:64] == 0).all()
+    z, zs = R.ref_quantize_wgt_int4(torch.zeros(1, 64, dtype=torch.bfloat16))
+    assert (z == 0).all() and zs[0, 0].item() == 0.0                 # inf * 0 = NaN -> 0
