@@ -42,28 +42,20 @@ qk_norm_rope_kernel(h16* __restrict__ qkv, const h16* __restrict__ wq, const h16
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
     const int dim = heads * 128;
     constexpr int PARTS = SPLIT ? 3 : 2;
-    const long long items = rows * heads * PARTS;    // (row, q|k|v, head)
+    // A warp's unit of work is one third (q, k or, when splitting, v) of one row: every head of it in turn, four heads'
+    // lines asked for before the first is worked on.  Row, position and the lane's rotary entries are found once per unit
+    // (with one item = one head per loop turn, the 64-bit divisions that located it cost more than the arithmetic).
+    const long long units = rows * PARTS;
     // norm weights of this lane's 4 columns, for q and k
     const uint2 wq2 = *reinterpret_cast<const uint2*>(wq + lane * 4);
     const uint2 wk2 = *reinterpret_cast<const uint2*>(wk + lane * 4);
-    for (long long it = warp; it < items; it += nwarps) {
-        const long long row = it / (heads * PARTS);
-        const int rem = static_cast<int>(it - row * heads * PARTS);
-        const int which = rem / heads, head = rem - which * heads;
-        h16* p = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + head * 128 + lane * 4;
-        const long long pos = row % seq_len;
-        uint2 o = *reinterpret_cast<const uint2*>(p);
+    for (long long unit = warp; unit < units; unit += nwarps) {
+        const long long row = unit / PARTS;
+        const int which = static_cast<int>(unit - row * PARTS);
+        const long long b = row / seq_len;
+        const int pos = static_cast<int>(row - b * seq_len);
+        float2 c = make_float2(1.f, 1.f), s = make_float2(0.f, 0.f);
         if (which < 2) {
-            const float2 y0 = bf2(o.x), y1 = bf2(o.y);
-            float ss = y0.x * y0.x + y0.y * y0.y + y1.x * y1.x + y1.y * y1.y;
-#pragma unroll
-            for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
-            const float coef = rsqrtf(ss * (1.0f / 128.0f) + eps);
-            const uint2 w = which ? wk2 : wq2;
-            const float2 w0 = bf2(w.x), w1 = bf2(w.y);
-            const float a0 = y0.x * (coef * w0.x), b0 = y0.y * (coef * w0.y);
-            const float a1 = y1.x * (coef * w1.x), b1 = y1.y * (coef * w1.y);
-            float2 c, s;
             if constexpr (PACKED) {
                 // pairs 2*lane and 2*lane + 1: j = lane / 2, t = 2 * (lane & 1) + {0, 1}
                 const long long mb = pos >> 4;
@@ -74,20 +66,45 @@ qk_norm_rope_kernel(h16* __restrict__ qkv, const h16* __restrict__ wq, const h16
                 s = make_float2(sc0.x, sc1.x);
                 c = make_float2(sc0.y, sc1.y);
             } else {
-                c = *reinterpret_cast<const float2*>(cosp + pos * 64 + lane * 2);
-                s = *reinterpret_cast<const float2*>(sinp + pos * 64 + lane * 2);
+                c = *reinterpret_cast<const float2*>(cosp + static_cast<long long>(pos) * 64 + lane * 2);
+                s = *reinterpret_cast<const float2*>(sinp + static_cast<long long>(pos) * 64 + lane * 2);
             }
-            o.x = pack_bf2(a0 * c.x - b0 * s.x, a0 * s.x + b0 * c.x);
-            o.y = pack_bf2(a1 * c.y - b1 * s.y, a1 * s.y + b1 * c.y);
         }
+        const uint2 w = which ? wk2 : wq2;
+        const float2 w0 = bf2(w.x), w1 = bf2(w.y);
+        h16* src = qkv + row * (3LL * dim) + static_cast<long long>(which) * dim + lane * 4;
+        const bool zero = SPLIT && attn_tokens > 0 && pos >= attn_tokens;
+        h16* dst = src;
+        long long dstride = 128;   // elements between heads at the destination
         if constexpr (SPLIT) {
-            if (attn_tokens > 0 && pos >= attn_tokens) o = make_uint2(0u, 0u);
-            h16* dst = which == 0 ? out_q : which == 1 ? out_k : out_v;
-            const long long b = row / seq_len, tok = token_offset + pos;
-            const long long at = token_major ? (b * tokens_pad + tok) * heads + head : (b * heads + head) * tokens_pad + tok;
-            *reinterpret_cast<uint2*>(dst + at * 128 + lane * 4) = o;
-        } else {
-            *reinterpret_cast<uint2*>(p) = o;
+            h16* base = which == 0 ? out_q : which == 1 ? out_k : out_v;
+            const long long tok = token_offset + pos;
+            dst = base + (token_major ? (b * tokens_pad + tok) * heads * 128 : (b * heads * tokens_pad + tok) * 128) + lane * 4;
+            dstride = token_major ? 128 : static_cast<long long>(tokens_pad) * 128;
+        }
+        for (int h0 = 0; h0 < heads; h0 += 4) {
+            uint2 ov[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (h0 + u < heads) ov[u] = *reinterpret_cast<const uint2*>(src + (h0 + u) * 128);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (h0 + u >= heads) break;
+                uint2 o = ov[u];
+                if (which < 2) {
+                    const float2 y0 = bf2(o.x), y1 = bf2(o.y);
+                    float ss = y0.x * y0.x + y0.y * y0.y + y1.x * y1.x + y1.y * y1.y;
+#pragma unroll
+                    for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+                    const float coef = rsqrtf(ss * (1.0f / 128.0f) + eps);
+                    const float a0 = y0.x * (coef * w0.x), b0 = y0.y * (coef * w0.y);
+                    const float a1 = y1.x * (coef * w1.x), b1 = y1.y * (coef * w1.y);
+                    o.x = pack_bf2(a0 * c.x - b0 * s.x, a0 * s.x + b0 * c.x);
+                    o.y = pack_bf2(a1 * c.y - b1 * s.y, a1 * s.y + b1 * c.y);
+                }
+                if (zero) o = make_uint2(0u, 0u);
+                *reinterpret_cast<uint2*>(dst + (h0 + u) * dstride) = o;
+            }
         }
     }
 }
@@ -207,7 +224,7 @@ int qk_norm_rope_impl(const svdq_norm_rope_args* a, void* stream) {
                    "qk_norm_rope: out_q, out_k and out_v go together, with tokens_pad >= token_offset + seq_len and "
                    "0 <= attn_tokens <= seq_len");
     if (int rc = check_arch()) return rc;
-    const long long items = static_cast<long long>(a->rows) * a->heads * (split ? 3 : 2);
+    const long long items = static_cast<long long>(a->rows) * (split ? 3 : 2);   // one warp per third of a row
     const float* tab = a->rotary_packed ? a->rotary_packed : a->cos;
     auto launch = [&](auto kernel) {
         kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(
