@@ -112,7 +112,7 @@ qk_norm_rope_kernel(h16* __restrict__ qkv, const h16* __restrict__ wq, const h16
 // C = 8 * (32 * (V - 1) + TAIL) columns: each lane holds V chunks of 8 columns (16 bytes), chunk j at column
 // (j*32 + lane) * 8; only the first TAIL lanes hold a last chunk (TAIL = 32: C = 256 V)
 template <int V, int TAIL = 32>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 layernorm_modulate_kernel(const h16* __restrict__ x, const h16* __restrict__ scale,
                           const h16* __restrict__ shift, h16* __restrict__ out, long long rows,
                           long long rows_per_batch, long long mod_stride, float eps) {
@@ -122,29 +122,33 @@ layernorm_modulate_kernel(const h16* __restrict__ x, const h16* __restrict__ sca
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
     for (long long row = warp; row < rows; row += nwarps) {
+        // The row stays in registers as it was loaded (16-bit pairs, V x 4 words) and is unpacked again in each of the three
+        // passes: as fp32 it took 206 registers per thread, i.e. one block of eight warps per SM and too few loads in flight.
         const uint4* xp = reinterpret_cast<const uint4*>(x + row * C);
-        float v[V][8];
+        uint4 raw[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) raw[j] = (j < V - 1 || last) ? xp[j * 32 + lane] : make_uint4(0, 0, 0, 0);
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            const uint4 w = (j < V - 1 || last) ? xp[j * 32 + lane] : make_uint4(0, 0, 0, 0);
-            const float2 f0 = bf2(w.x), f1 = bf2(w.y), f2 = bf2(w.z), f3 = bf2(w.w);
-            v[j][0] = f0.x; v[j][1] = f0.y; v[j][2] = f1.x; v[j][3] = f1.y;
-            v[j][4] = f2.x; v[j][5] = f2.y; v[j][6] = f3.x; v[j][7] = f3.y;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum += v[j][i];
+            const float2 f0 = bf2(raw[j].x), f1 = bf2(raw[j].y), f2 = bf2(raw[j].z), f3 = bf2(raw[j].w);
+            sum += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
         }
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
         const float mean = sum * (1.0f / C);
         float var = 0.f;
 #pragma unroll
-        for (int j = 0; j < V; ++j)
+        for (int j = 0; j < V; ++j) {
+            if (j == V - 1 && !last) break;
+            const uint32_t w4[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float d = v[j][i] - mean;
-                var += (j < V - 1 || last) ? d * d : 0.f;
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = bf2(w4[i]);
+                const float d0 = f.x - mean, d1 = f.y - mean;
+                var += d0 * d0 + d1 * d1;
             }
+        }
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) var += __shfl_xor_sync(0xffffffffu, var, m);
         const float rstd = rsqrtf(var * (1.0f / C) + eps);
@@ -157,13 +161,14 @@ layernorm_modulate_kernel(const h16* __restrict__ x, const h16* __restrict__ sca
             if (j == V - 1 && !last) break;
             const uint4 sc = scp[j * 32 + lane], sh = shp[j * 32 + lane];
             const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+            const uint32_t w4[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float2 s2 = bf2(scw[i]), h2 = bf2(shw[i]);
+                const float2 s2 = bf2(scw[i]), h2 = bf2(shw[i]), f = bf2(w4[i]);
                 // the library sequence it replaces rounds the normalised value to the 16-bit type before modulating
-                const float n0 = h2f(f2h((v[j][2 * i] - mean) * rstd));
-                const float n1 = h2f(f2h((v[j][2 * i + 1] - mean) * rstd));
+                const float n0 = h2f(f2h((f.x - mean) * rstd));
+                const float n1 = h2f(f2h((f.y - mean) * rstd));
                 o[i] = pack_bf2(n0 * (1.0f + s2.x) + h2.x, n1 * (1.0f + s2.y) + h2.y);
             }
             op[j * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
